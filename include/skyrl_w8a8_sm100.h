@@ -1,0 +1,231 @@
+/*
+ * C ABI of the B200 (sm_100a) W8A8 multi-LoRA MLP kernels.
+ *
+ * Every entry point enqueues work on the caller's CUDA stream and returns
+ * without synchronising; buffers are owned by the caller (for XLA: by XLA, as
+ * results of the custom call) and must stay alive until the stream reaches the
+ * end of the enqueued work.  Entry points return 0 on success or a negative
+ * SKYRL_ERR_* code; the message of the last error of the calling thread is
+ * available from skyrl_w8a8_last_error().  They never throw and never allocate
+ * device memory: scratch comes from the caller-supplied workspace.
+ *
+ * Naming and versioning follow the reference's native-ABI convention
+ * (rocm/compile_probes/down_lora_residual_gfx1100_abi.h:12-85: versioned
+ * symbols, explicit device addresses + dimensions, layout asserted at compile
+ * time).  Citations below are file:line inside the reference project.
+ *
+ * Device data layouts
+ *   activations ........ bf16 [M, K] row-major
+ *   packed weight ...... int8 [N, K] (K contiguous; the reference stores
+ *                        [K, N]: skyrl/tx/kernels/quantized_lora.py:20-41; the
+ *                        reference's own design asks for a load-time permute to
+ *                        a canonical device weight: rocm/QUANTIZED_FFI.md:69-74)
+ *   weight scales ...... fp32 [N] (the exact value of the reference's bf16
+ *                        per-output scale, group_size == K)
+ *   gate_up ............ N = 2*I physical columns, interleaved
+ *                        (gate0, up0, gate1, up1, ...): skyrl/tx/layers/lora.py:338-351
+ *   packed LoRA A ...... bf16 [A, 64, K]  (rank padded to 64 rows with zeros; the
+ *                        reference stores [A, K, r]: skyrl/tx/layers/lora.py:259-268)
+ *   packed LoRA B ...... bf16 [A, N, 64]  (rank padded to 64 columns with zeros;
+ *                        reference [A, r, N])
+ *   LoRA scaling ....... fp32 [A]
+ *   adapter ids ........ int32 [M], one per token row (NULL = every row uses adapter 0)
+ */
+#ifndef SKYRL_W8A8_SM100_H_
+#define SKYRL_W8A8_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define SKYRL_API __attribute__((visibility("default")))
+#else
+#define SKYRL_API
+#endif
+
+#define SKYRL_W8A8_ABI_VERSION 1
+#define SKYRL_LORA_RANK_PAD 64 /* packed LoRA tables hold 64 rank slots            */
+#define SKYRL_TILE_ROWS 128    /* rows of one M tile (one adapter per tile)         */
+
+#define SKYRL_OK 0
+#define SKYRL_ERR_INVALID_ARGUMENT (-1) /* shape / alignment / null / alias violation    */
+#define SKYRL_ERR_LAUNCH (-2)           /* CUDA reported an error at enqueue time        */
+#define SKYRL_ERR_UNSUPPORTED (-3)      /* valid request outside the built kernel set    */
+#define SKYRL_ERR_WORKSPACE (-4)        /* workspace missing, misaligned or too small    */
+#define SKYRL_ERR_DRIVER (-5)           /* CUDA driver entry point unavailable           */
+
+typedef void* skyrl_stream_t; /* cudaStream_t */
+
+/* epilogue selector of the GEMM kernel */
+#define SKYRL_EPI_LINEAR 0   /* y[M, N] bf16                                          */
+#define SKYRL_EPI_SWIGLU 1   /* h[M, N/2] bf16 = silu(gate) * up on interleaved pairs */
+#define SKYRL_EPI_RESIDUAL 2 /* out[M, N] bf16 = bf16(y) + residual                   */
+#define SKYRL_EPI_ACC_I32 3  /* raw int32 accumulator [M, N] (parity / debug)         */
+#define SKYRL_EPI_PARTIAL_F32 4 /* fp32 [M, N] before the cast (tensor-parallel partial sums) */
+
+SKYRL_API int skyrl_w8a8_abi_version(void);
+SKYRL_API const char* skyrl_w8a8_last_error(void);
+
+/* ------------------------------------------------------------------------- *
+ * Stage kernels
+ * ------------------------------------------------------------------------- */
+
+/* Stable sort of token rows by adapter id and the M-tile list over the sorted
+ * row space.  Replaces prepare_routing (skyrl/tx/layers/util.py:66-87: argsort,
+ * bincount, unsort) and the ragged grouping of skyrl/tx/layers/lora.py:142-157.
+ *   perm[i]      original row of sorted position i                 int32 [m]
+ *   tiles[4*t..] (first sorted row, row count <= 128, adapter, 0)  int32 [4*max_tiles]
+ *   num_tiles    device scalar, number of tiles written
+ * adapter_ids == NULL: identity permutation, uniform tiles of adapter 0.
+ * status: device int32, set non-zero on a bad id or tile overflow.            */
+SKYRL_API int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, int32_t num_adapters, int32_t* perm,
+                              int32_t* tiles, int32_t* num_tiles, int32_t max_tiles, int32_t* status,
+                              skyrl_stream_t stream);
+
+/* RMSNorm (optional) + per-token absmax int8 quantisation in one pass.
+ * Replaces Qwen3_5RMSNorm.__call__ (skyrl/tx/models/qwen3_5.py:269-278) and
+ * _dynamic_group_quantize with group_size == K
+ * (skyrl/tx/kernels/quantized_lora.py:199-212).
+ *   x          bf16 [*, k], row pitch x_row_stride elements
+ *   rms_delta  bf16 [k] or NULL (no normalisation)
+ *   row_map    int32 [m] source row of each output row, or NULL (identity)
+ *   xq         int8 [m, k] codes;  sx fp32 [m] scales (1.0 for an all-zero row)
+ *   xn         bf16 [m, k] normalised (and gathered) activations, or NULL     */
+SKYRL_API int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, const void* rms_delta, float eps,
+                             const int32_t* row_map, int32_t m, int32_t k, void* xq, float* sx, void* xn,
+                             skyrl_stream_t stream);
+
+/* LoRA-A projection on the tensor cores: z[i, :] = s[a] * (x[i, :] @ A[a]) for
+ * the adapter a of row i's tile, written as a bf16 (hi, lo) pair with
+ * hi + lo == fp32(z) to 16 bits.  Replaces the first ragged_dot of
+ * skyrl/tx/layers/lora.py:150 and `x.f32 @ lora_a.f32` of
+ * skyrl/tx/kernels/quantized_lora.py:301.
+ *   x bf16 [m, k] in sorted row order; lora_a_packed bf16 [A, 64, k];
+ *   z_hi, z_lo bf16 [m, 64]                                                   */
+SKYRL_API int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
+                               const float* lora_scaling, int32_t num_adapters, int32_t rank, const int32_t* tiles,
+                               const int32_t* num_tiles, int32_t max_tiles, void* z_hi, void* z_lo, int32_t* status,
+                               skyrl_stream_t stream);
+
+/* Arguments of the int8 tensor-core GEMM with fused epilogue.  Computes
+ *   acc = xq @ wq^T (int32, exact);  v = (f32(acc) * sx[m]) * sw[n] + z[m,:] @ B[a]^T
+ * (skyrl/tx/kernels/quantized_lora.py:242-254, 298-304) and applies `epilogue`. */
+typedef struct SkyrlW8A8GemmArgs {
+  uint32_t struct_size;     /* sizeof(SkyrlW8A8GemmArgs)                              */
+  int32_t epilogue;         /* SKYRL_EPI_*                                             */
+  int32_t m, n, k;          /* rows (sorted space), physical out features, in features */
+  int32_t rank;             /* LoRA rank (0 = frozen base only), <= 64                 */
+  int32_t num_adapters;
+  int32_t max_tiles;        /* capacity of `tiles`                                     */
+  const void* xq;           /* int8 [m, k]                                             */
+  const float* sx;          /* fp32 [m]                                                */
+  const void* wq;           /* int8 [n, k] packed                                      */
+  const float* sw;          /* fp32 [n]                                                */
+  const void* z_hi;         /* bf16 [m, 64] or NULL when rank == 0                     */
+  const void* z_lo;         /* bf16 [m, 64]                                            */
+  const void* lora_b_packed;/* bf16 [A, n, 64]                                         */
+  const int32_t* tiles;     /* int32 [4 * max_tiles] from skyrl_lora_route_sm100_v1    */
+  const int32_t* num_tiles; /* device scalar                                           */
+  const int32_t* out_row_map; /* int32 [m]: output (and residual) row of sorted row i; NULL = identity */
+  const void* residual;     /* bf16 [m, n] for SKYRL_EPI_RESIDUAL                      */
+  void* out;                /* see SKYRL_EPI_*                                         */
+  int64_t out_row_stride;   /* elements                                                */
+  int64_t residual_row_stride;
+  int32_t* status;          /* device int32, non-zero after a bounded wait ran out     */
+} SkyrlW8A8GemmArgs;
+
+SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Operator entry points (what the reference's custom-call layer binds)
+ * ------------------------------------------------------------------------- */
+
+/* One W8A8 LoRA linear, y = bf16(dequant(xq wq^T) + s (x A) B).
+ * Typed-FFI handler it stands in for: rocm/QUANTIZED_FFI.md:587-599
+ * (x, w8, sw, a, b, scaling -> y on the caller's stream); Python operator:
+ * w8a8_lora_linear / w8a8_frozen_linear, skyrl/tx/kernels/rocm/w8a8_lora.py:827-920.
+ * Fused front half: bf16_rms_gate_up_lora_swiglu_contiguous,
+ * skyrl/tx/kernels/rocm/bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757.
+ * Fused back half: bf16_lora_residual, skyrl/tx/kernels/rocm/bf16_lora_residual.py:507-566. */
+typedef struct SkyrlW8A8LinearArgs {
+  uint32_t struct_size;
+  int32_t epilogue;          /* SKYRL_EPI_LINEAR / _SWIGLU / _RESIDUAL / _ACC_I32 / _PARTIAL_F32 */
+  int32_t m, n, k;
+  int32_t rank;              /* 0 = frozen base only */
+  int32_t num_adapters;
+  int32_t reserved0;
+  const void* x;             /* bf16 [m, k] */
+  int64_t x_row_stride;
+  const void* rms_delta;     /* bf16 [k] or NULL: RMSNorm(1 + delta) in front of the quantiser */
+  float rms_eps;
+  int32_t reserved1;
+  const void* wq;            /* int8 [n, k] packed */
+  const float* sw;           /* fp32 [n] */
+  const void* lora_a_packed; /* bf16 [A, 64, k] */
+  const void* lora_b_packed; /* bf16 [A, n, 64] */
+  const float* lora_scaling; /* fp32 [A] */
+  const int32_t* adapter_ids;/* int32 [m] or NULL */
+  const void* residual;      /* bf16 [m, n] (SKYRL_EPI_RESIDUAL) */
+  int64_t residual_row_stride;
+  void* out;
+  int64_t out_row_stride;
+  void* workspace;           /* >= skyrl_w8a8_linear_workspace_bytes(m, k), 1024-byte aligned */
+  size_t workspace_bytes;
+  int32_t* status;           /* device int32, zeroed by the caller */
+} SkyrlW8A8LinearArgs;
+
+SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters);
+SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
+
+/* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
+ * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
+ * skyrl/tx/models/qwen3_5.py:786-826; Qwen3MLP, skyrl/tx/models/qwen3.py:100-131). */
+typedef struct SkyrlW8A8MlpArgs {
+  uint32_t struct_size;
+  int32_t m, hidden, inter;  /* rows, hidden size H, intermediate size I (gate_up has 2*I columns) */
+  int32_t rank, num_adapters;
+  int32_t down_epilogue;     /* SKYRL_EPI_RESIDUAL, or SKYRL_EPI_PARTIAL_F32 for a row-parallel shard */
+  float rms_eps;
+  const void* x;             /* bf16 [m, H] */
+  const void* rms_delta;     /* bf16 [H] or NULL */
+  const void* residual;      /* bf16 [m, H]; NULL = x */
+  const void* gu_wq;         /* int8 [2I, H] */
+  const float* gu_sw;        /* fp32 [2I] */
+  const void* gu_a_packed;   /* bf16 [A, 64, H] */
+  const void* gu_b_packed;   /* bf16 [A, 2I, 64] */
+  const float* gu_scaling;
+  const void* dn_wq;         /* int8 [H, I] */
+  const float* dn_sw;        /* fp32 [H] */
+  const void* dn_a_packed;   /* bf16 [A, 64, I] */
+  const void* dn_b_packed;   /* bf16 [A, H, 64] */
+  const float* dn_scaling;
+  const int32_t* adapter_ids;/* int32 [m] or NULL */
+  void* out;                 /* bf16 [m, H] (or fp32 [m, H] partial sums in sorted... see down_epilogue) */
+  void* workspace;           /* >= skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, num_adapters) */
+  size_t workspace_bytes;
+  int32_t* status;
+} SkyrlW8A8MlpArgs;
+
+SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
+SKYRL_API int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* args, skyrl_stream_t stream);
+
+/* ------------------------------------------------------------------------- *
+ * Pack helpers (load-time, device to device)
+ * ------------------------------------------------------------------------- */
+/* int8 [K, N] reference codes -> int8 [N, K] packed (quantized_lora.py:20-41).           */
+SKYRL_API int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_nk, skyrl_stream_t stream);
+/* bf16 [A, K, r] -> bf16 [A, 64, K] (skyrl/tx/layers/lora.py:259-268).                   */
+SKYRL_API int skyrl_pack_lora_a_sm100_v1(const void* a_akr, int32_t num_adapters, int32_t k, int32_t rank, void* a_packed,
+                               skyrl_stream_t stream);
+/* bf16 [A, r, N] -> bf16 [A, N, 64].                                                     */
+SKYRL_API int skyrl_pack_lora_b_sm100_v1(const void* b_arn, int32_t num_adapters, int32_t rank, int32_t n, void* b_packed,
+                               skyrl_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SKYRL_W8A8_SM100_H_ */

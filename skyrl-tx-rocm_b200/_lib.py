@@ -1,0 +1,125 @@
+"""ctypes binding of the C-ABI library (include/skyrl_w8a8_sm100.h).
+
+The library is loaded once and kept alive for the life of the process, like the
+reference keeps its typed-FFI library handle
+(skyrl/tx/kernels/rocm/gdn_ffi_smoke.py:323,349-353).  There is no fallback: if
+the library is missing, every operator raises.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "lib" / "libskyrl_w8a8_sm100.so"
+
+EPI_LINEAR, EPI_SWIGLU, EPI_RESIDUAL, EPI_ACC_I32, EPI_PARTIAL_F32 = 0, 1, 2, 3, 4
+LORA_RANK_PAD = 64
+TILE_ROWS = 128
+
+ERROR_NAMES = {
+    -1: "invalid argument", -2: "launch failure", -3: "unsupported", -4: "workspace", -5: "driver entry point",
+}
+STATUS_NAMES = {
+    101: "bounded wait ran out in the TMA producer", 102: "bounded wait ran out in the MMA issuer",
+    103: "bounded wait ran out in the epilogue", 104: "bounded wait ran out in the LoRA step",
+    201: "adapter id outside [0, num_adapters)", 202: "tile list overflow",
+}
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("epilogue", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("rank", C.c_int32), ("num_adapters", C.c_int32), ("max_tiles", C.c_int32),
+        ("xq", C.c_void_p), ("sx", C.c_void_p), ("wq", C.c_void_p), ("sw", C.c_void_p),
+        ("z_hi", C.c_void_p), ("z_lo", C.c_void_p), ("lora_b_packed", C.c_void_p),
+        ("tiles", C.c_void_p), ("num_tiles", C.c_void_p), ("out_row_map", C.c_void_p),
+        ("residual", C.c_void_p), ("out", C.c_void_p),
+        ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
+    ]
+
+
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("epilogue", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("rank", C.c_int32), ("num_adapters", C.c_int32), ("reserved0", C.c_int32),
+        ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("rms_delta", C.c_void_p),
+        ("rms_eps", C.c_float), ("reserved1", C.c_int32),
+        ("wq", C.c_void_p), ("sw", C.c_void_p), ("lora_a_packed", C.c_void_p), ("lora_b_packed", C.c_void_p),
+        ("lora_scaling", C.c_void_p), ("adapter_ids", C.c_void_p), ("residual", C.c_void_p),
+        ("residual_row_stride", C.c_int64), ("out", C.c_void_p), ("out_row_stride", C.c_int64),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
+class MlpArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("m", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32),
+        ("rank", C.c_int32), ("num_adapters", C.c_int32), ("down_epilogue", C.c_int32), ("rms_eps", C.c_float),
+        ("x", C.c_void_p), ("rms_delta", C.c_void_p), ("residual", C.c_void_p),
+        ("gu_wq", C.c_void_p), ("gu_sw", C.c_void_p), ("gu_a_packed", C.c_void_p), ("gu_b_packed", C.c_void_p),
+        ("gu_scaling", C.c_void_p),
+        ("dn_wq", C.c_void_p), ("dn_sw", C.c_void_p), ("dn_a_packed", C.c_void_p), ("dn_b_packed", C.c_void_p),
+        ("dn_scaling", C.c_void_p),
+        ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
+# name -> (restype, argtypes); every symbol the header declares
+SYMBOLS = {
+    "skyrl_w8a8_abi_version": (C.c_int, []),
+    "skyrl_w8a8_last_error": (C.c_char_p, []),
+    "skyrl_lora_route_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_int32, C.c_void_p, C.c_void_p]),
+    "skyrl_rms_quant_sm100_v1": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_int32,
+                                           C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "skyrl_lora_a_proj_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
+                                             C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+                                             C.c_void_p, C.c_void_p]),
+    "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "skyrl_w8a8_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "skyrl_w8a8_mlp_block_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p]),
+    "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "skyrl_pack_lora_a_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "skyrl_pack_lora_b_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class SkyrlKernelError(RuntimeError):
+    """The C-ABI library rejected a call or failed to enqueue it."""
+
+
+def load():
+    """Return the loaded library; raises if it was not built (no fallback path)."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not LIB_PATH.exists():
+                raise SkyrlKernelError(
+                    f"{LIB_PATH} is missing: build it with `python skyrl-tx-rocm_b200/build.py` "
+                    "(the W8A8 operators have no CPU or eager fallback)"
+                )
+            lib = C.CDLL(str(LIB_PATH))
+            for name, (restype, argtypes) in SYMBOLS.items():
+                fn = getattr(lib, name)
+                fn.restype = restype
+                fn.argtypes = argtypes
+            if lib.skyrl_w8a8_abi_version() != 1:
+                raise SkyrlKernelError("C-ABI version mismatch")
+            _lib = lib
+        return _lib
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load().skyrl_w8a8_last_error().decode("utf-8", "replace")
+        exc = ValueError if rc == -1 else SkyrlKernelError
+        raise exc(f"{what}: {ERROR_NAMES.get(rc, rc)}: {msg}")

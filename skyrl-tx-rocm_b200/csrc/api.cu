@@ -1,0 +1,339 @@
+// Host side of the C ABI: error reporting, TMA descriptor encoding and the
+// operator entry points that chain the stage kernels on the caller's stream.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace skyrl {
+
+static thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+static int encode(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank, const void* base, const cuuint64_t* dims,
+                  const cuuint64_t* strides, const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(SKYRL_ERR_DRIVER, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dtype, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SKYRL_ERR_INVALID_ARGUMENT, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SKYRL_OK;
+}
+
+int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  (void)elem_bytes;
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_pitch_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  return encode(map, dtype, 2, base, dims, strides, box);
+}
+
+int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t d0,
+                   uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
+                   uint32_t box1) {
+  (void)elem_bytes;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  return encode(map, dtype, 3, base, dims, strides, box);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// ---- workspace carving -------------------------------------------------------
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static inline int max_tiles_for(int m, int num_adapters) {
+  return (m + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS + (num_adapters > 0 ? num_adapters : 1);
+}
+
+struct Carver {
+  unsigned char* base;
+  size_t off = 0;
+  explicit Carver(void* b) : base(static_cast<unsigned char*>(b)) {}
+  template <typename T>
+  T* take(size_t count) {
+    off = align_up(off, 1024);
+    T* p = base != nullptr ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+  size_t total() const { return align_up(off, 1024); }
+};
+
+struct LinearWs {
+  int32_t* perm;
+  int32_t* tiles;
+  int32_t* num_tiles;
+  int8_t* xq;
+  float* sx;
+  uint16_t* xn;
+  uint16_t* z_hi;
+  uint16_t* z_lo;
+  size_t bytes;
+};
+
+static LinearWs carve_linear(void* ws, int m, int k, int num_adapters) {
+  Carver c(ws);
+  LinearWs w;
+  const int mt = max_tiles_for(m, num_adapters);
+  w.perm = c.take<int32_t>(m);
+  w.tiles = c.take<int32_t>(4 * static_cast<size_t>(mt));
+  w.num_tiles = c.take<int32_t>(4);
+  w.xq = c.take<int8_t>(static_cast<size_t>(m) * k);
+  w.sx = c.take<float>(m);
+  w.xn = c.take<uint16_t>(static_cast<size_t>(m) * k);
+  w.z_hi = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_lo = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.bytes = c.total();
+  return w;
+}
+
+struct MlpWs {
+  int32_t* perm;
+  int32_t* tiles;
+  int32_t* num_tiles;
+  int8_t* xq;
+  float* sx;
+  uint16_t* xn;
+  uint16_t* z_hi;
+  uint16_t* z_lo;
+  uint16_t* h;
+  int8_t* hq;
+  float* sh;
+  size_t bytes;
+};
+
+static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters) {
+  Carver c(ws);
+  MlpWs w;
+  const int mt = max_tiles_for(m, num_adapters);
+  w.perm = c.take<int32_t>(m);
+  w.tiles = c.take<int32_t>(4 * static_cast<size_t>(mt));
+  w.num_tiles = c.take<int32_t>(4);
+  w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
+  w.sx = c.take<float>(m);
+  w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
+  w.z_hi = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_lo = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.h = c.take<uint16_t>(static_cast<size_t>(m) * inter);
+  w.hq = c.take<int8_t>(static_cast<size_t>(m) * inter);
+  w.sh = c.take<float>(m);
+  w.bytes = c.total();
+  return w;
+}
+
+static int check_ws(const void* ws, size_t have, size_t need, const char* who) {
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 1023u) != 0)
+    return fail(SKYRL_ERR_WORKSPACE, "%s: workspace must be non-null and 1024-byte aligned", who);
+  if (have < need) return fail(SKYRL_ERR_WORKSPACE, "%s: workspace has %zu bytes, needs %zu", who, have, need);
+  return SKYRL_OK;
+}
+
+}  // namespace skyrl
+
+using namespace skyrl;
+
+extern "C" int skyrl_w8a8_abi_version(void) { return SKYRL_W8A8_ABI_VERSION; }
+extern "C" const char* skyrl_w8a8_last_error(void) { return g_last_error; }
+
+extern "C" size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters) {
+  if (m <= 0 || k <= 0) return 0;
+  return carve_linear(nullptr, m, k, num_adapters).bytes;
+}
+
+extern "C" size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters) {
+  if (m <= 0 || hidden <= 0 || inter <= 0) return 0;
+  return carve_mlp(nullptr, m, hidden, inter, num_adapters).bytes;
+}
+
+extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: args is null");
+  if (a->struct_size != sizeof(SkyrlW8A8LinearArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: struct_size %u does not match ABI v%d (%zu)", a->struct_size,
+                SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8LinearArgs));
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: non-positive shape");
+  if (a->x == nullptr || a->wq == nullptr || a->sw == nullptr || a->out == nullptr || a->status == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: null buffer");
+  if (a->rank < 0 || a->rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "linear: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a->rank);
+  const bool lora = a->rank > 0;
+  if (lora && (a->lora_a_packed == nullptr || a->lora_b_packed == nullptr || a->lora_scaling == nullptr ||
+               a->num_adapters <= 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: LoRA tables missing");
+  if (a->adapter_ids != nullptr && a->num_adapters <= 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: adapter ids given without adapters");
+  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
+  const LinearWs w = carve_linear(a->workspace, a->m, a->k, na);
+  int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "linear");
+  if (rc) return rc;
+  const int mt = max_tiles_for(a->m, na);
+  const bool routed = a->adapter_ids != nullptr;
+
+  if ((rc = launch_route(a->adapter_ids, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status, stream))) return rc;
+  const bool need_xn = lora && (routed || a->rms_delta != nullptr || a->x_row_stride != a->k);
+  if ((rc = launch_rms_quant(a->x, a->x_row_stride, a->rms_delta, a->rms_eps, routed ? w.perm : nullptr, a->m, a->k,
+                             w.xq, w.sx, need_xn ? w.xn : nullptr, stream)))
+    return rc;
+  if (lora) {
+    const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
+    if ((rc = launch_lora_a_proj(xa, a->m, a->k, a->lora_a_packed, a->lora_scaling, na, a->rank, w.tiles, w.num_tiles,
+                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+      return rc;
+  }
+  SkyrlW8A8GemmArgs g;
+  g.struct_size = sizeof(g);
+  g.epilogue = a->epilogue;
+  g.m = a->m;
+  g.n = a->n;
+  g.k = a->k;
+  g.rank = a->rank;
+  g.num_adapters = na;
+  g.max_tiles = mt;
+  g.xq = w.xq;
+  g.sx = w.sx;
+  g.wq = a->wq;
+  g.sw = a->sw;
+  g.z_hi = lora ? w.z_hi : nullptr;
+  g.z_lo = lora ? w.z_lo : nullptr;
+  g.lora_b_packed = a->lora_b_packed;
+  g.tiles = w.tiles;
+  g.num_tiles = w.num_tiles;
+  g.out_row_map = routed ? w.perm : nullptr;
+  g.residual = a->residual;
+  g.out = a->out;
+  g.out_row_stride = a->out_row_stride;
+  g.residual_row_stride = a->residual_row_stride;
+  g.status = a->status;
+  return launch_gemm(g, stream);
+}
+
+extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: args is null");
+  if (a->struct_size != sizeof(SkyrlW8A8MlpArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: struct_size %u does not match ABI v%d (%zu)", a->struct_size,
+                SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8MlpArgs));
+  if (a->m <= 0 || a->hidden <= 0 || a->inter <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: non-positive shape");
+  if (a->x == nullptr || a->gu_wq == nullptr || a->gu_sw == nullptr || a->dn_wq == nullptr || a->dn_sw == nullptr ||
+      a->out == nullptr || a->status == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: null buffer");
+  if (a->down_epilogue != SKYRL_EPI_RESIDUAL && a->down_epilogue != SKYRL_EPI_PARTIAL_F32 &&
+      a->down_epilogue != SKYRL_EPI_LINEAR)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: down_epilogue must be RESIDUAL, LINEAR or PARTIAL_F32");
+  if (a->rank < 0 || a->rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "mlp: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a->rank);
+  const bool lora = a->rank > 0;
+  if (lora && (a->gu_a_packed == nullptr || a->gu_b_packed == nullptr || a->gu_scaling == nullptr ||
+               a->dn_a_packed == nullptr || a->dn_b_packed == nullptr || a->dn_scaling == nullptr ||
+               a->num_adapters <= 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: LoRA tables missing");
+  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
+  const MlpWs w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, na);
+  int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "mlp");
+  if (rc) return rc;
+  const int mt = max_tiles_for(a->m, na);
+  const bool routed = a->adapter_ids != nullptr;
+  const int32_t* perm = routed ? w.perm : nullptr;
+
+  if ((rc = launch_route(a->adapter_ids, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status, stream))) return rc;
+
+  // front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU, h stays in sorted row order
+  const bool need_xn = lora && (routed || a->rms_delta != nullptr);
+  if ((rc = launch_rms_quant(a->x, a->hidden, a->rms_delta, a->rms_eps, perm, a->m, a->hidden, w.xq, w.sx,
+                             need_xn ? w.xn : nullptr, stream)))
+    return rc;
+  if (lora) {
+    const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
+    if ((rc = launch_lora_a_proj(xa, a->m, a->hidden, a->gu_a_packed, a->gu_scaling, na, a->rank, w.tiles, w.num_tiles,
+                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+      return rc;
+  }
+  SkyrlW8A8GemmArgs g;
+  g.struct_size = sizeof(g);
+  g.epilogue = SKYRL_EPI_SWIGLU;
+  g.m = a->m;
+  g.n = 2 * a->inter;
+  g.k = a->hidden;
+  g.rank = a->rank;
+  g.num_adapters = na;
+  g.max_tiles = mt;
+  g.xq = w.xq;
+  g.sx = w.sx;
+  g.wq = a->gu_wq;
+  g.sw = a->gu_sw;
+  g.z_hi = lora ? w.z_hi : nullptr;
+  g.z_lo = lora ? w.z_lo : nullptr;
+  g.lora_b_packed = a->gu_b_packed;
+  g.tiles = w.tiles;
+  g.num_tiles = w.num_tiles;
+  g.out_row_map = nullptr;
+  g.residual = nullptr;
+  g.out = w.h;
+  g.out_row_stride = a->inter;
+  g.residual_row_stride = 0;
+  g.status = a->status;
+  if ((rc = launch_gemm(g, stream))) return rc;
+
+  // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
+  if ((rc = launch_rms_quant(w.h, a->inter, nullptr, 0.f, nullptr, a->m, a->inter, w.hq, w.sh, nullptr, stream)))
+    return rc;
+  if (lora) {
+    if ((rc = launch_lora_a_proj(w.h, a->m, a->inter, a->dn_a_packed, a->dn_scaling, na, a->rank, w.tiles, w.num_tiles,
+                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+      return rc;
+  }
+  g.epilogue = a->down_epilogue;
+  g.n = a->hidden;
+  g.k = a->inter;
+  g.xq = w.hq;
+  g.sx = w.sh;
+  g.wq = a->dn_wq;
+  g.sw = a->dn_sw;
+  g.lora_b_packed = a->dn_b_packed;
+  g.out_row_map = perm;
+  g.residual = a->residual != nullptr ? a->residual : a->x;
+  g.out = a->out;
+  g.out_row_stride = a->hidden;
+  g.residual_row_stride = a->hidden;
+  return launch_gemm(g, stream);
+}

@@ -1,0 +1,38 @@
+// Host-side helpers shared by the translation units of the C-ABI library.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/skyrl_w8a8_sm100.h"
+
+namespace skyrl {
+
+// Records the message returned by skyrl_w8a8_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+
+// cuTensorMapEncodeTiled resolved through the runtime (no link-time libcuda
+// dependency, so the library loads on a machine without a driver).
+// 2-D / 3-D row-major tensors, 128-byte swizzle, zero fill out of bounds.
+int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t inner,
+                   uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t d0,
+                   uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
+                   uint32_t box1);
+
+int sm_count();
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// kernel launchers implemented in the .cu files
+int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
+                 int max_tiles, int32_t* status, cudaStream_t stream);
+int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
+                     int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
+int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
+                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_hi, void* z_lo,
+                       int32_t* status, cudaStream_t stream);
+int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream);
+
+}  // namespace skyrl

@@ -1,0 +1,217 @@
+// LoRA-A projection on the tensor cores: for every 128-row tile of the
+// adapter-sorted row space, z = s[a] * (x_tile @ A[a]) with a bf16 tcgen05 MMA
+// (fp32 accumulator in TMEM, products of bf16 inputs are exact), written out as
+// a bf16 (hi, lo) pair so that the rank-r contraction of the GEMM epilogue sees
+// z to 16 significant bits.  HBM-bound: x is streamed once through a 6-stage
+// TMA pipeline, one CTA per tile.
+//
+// Reference arithmetic: `x.astype(f32) @ lora_a.astype(f32)`
+// (skyrl/tx/kernels/quantized_lora.py:301) and the first ragged_dot of
+// skyrl/tx/layers/lora.py:150; the per-adapter scaling of lora.py:155-156 is
+// folded in here.
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace skyrl {
+
+constexpr int PROJ_BM = 128;
+constexpr int PROJ_BK = 64;  // bf16 elements per stage row (128 bytes)
+constexpr int PROJ_N = SKYRL_LORA_RANK_PAD;
+constexpr int PROJ_STAGES = 6;
+constexpr int PROJ_A_BYTES = PROJ_BM * 128;
+constexpr int PROJ_B_BYTES = PROJ_N * 128;
+constexpr int PROJ_STAGE_BYTES = PROJ_A_BYTES + PROJ_B_BYTES;
+constexpr int PROJ_BAR_OFF = PROJ_STAGES * PROJ_STAGE_BYTES;
+constexpr int PROJ_SMEM_BYTES = PROJ_BAR_OFF + (2 * PROJ_STAGES + 1) * 8 + 16 + 1024;
+constexpr int PROJ_THREADS = 192;
+constexpr int PROJ_TMEM_COLS = 64;
+
+struct ProjParams {
+  CUtensorMap tm_x;  // bf16 [M, K], box 64 x 128
+  CUtensorMap tm_a;  // bf16 [A, 64, K], box 64 x 64 x 1
+  const float* scaling;
+  const int4* tiles;
+  const int32_t* num_tiles;
+  __nv_bfloat16* z_hi;
+  __nv_bfloat16* z_lo;
+  int32_t* status;
+  int k;
+};
+
+__global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __grid_constant__ ProjParams p) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PROJ_BAR_OFF);
+  uint64_t* empty_bar = full_bar + PROJ_STAGES;
+  uint64_t* acc_full = empty_bar + PROJ_STAGES;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  if (static_cast<int>(blockIdx.x) >= *p.num_tiles) return;  // uniform for the CTA
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PROJ_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_ptr_smem, PROJ_TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int4 tile = __ldg(p.tiles + blockIdx.x);
+  const int kblocks = (p.k + PROJ_BK - 1) / PROJ_BK;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      tma_prefetch_desc(&p.tm_x);
+      tma_prefetch_desc(&p.tm_a);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) break;
+        unsigned char* sa = smem + stage * PROJ_STAGE_BYTES;
+        mbar_expect_tx(&full_bar[stage], PROJ_STAGE_BYTES);
+        tma_load_2d(sa, &p.tm_x, kb * PROJ_BK, tile.x, &full_bar[stage]);
+        tma_load_3d(sa + PROJ_A_BYTES, &p.tm_a, kb * PROJ_BK, 0, tile.z, &full_bar[stage]);
+        if (++stage == PROJ_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, PROJ_BM, PROJ_N);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + stage * PROJ_STAGE_BYTES);
+        const uint64_t adesc = make_desc_sw128(sa);
+        const uint64_t bdesc = make_desc_sw128(sa + PROJ_A_BYTES);
+#pragma unroll
+        for (int j = 0; j < PROJ_BK / 16; ++j) mma_bf16(tmem_base, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+        mma_commit(&empty_bar[stage]);
+        if (++stage == PROJ_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) mma_commit(acc_full);
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0u, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
+    if (ok) {
+      tc_fence_after_sync();
+      const float s = __ldg(p.scaling + tile.z);
+      const bool row_valid = r < tile.y;
+      const int64_t row = tile.x + r;
+#pragma unroll
+      for (int cc = 0; cc < PROJ_N / 32; ++cc) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + cc * 32, v);
+        tmem_wait_ld();
+        if (row_valid) {
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float z0 = __fmul_rn(__uint_as_float(v[2 * i]), s);
+            const float z1 = __fmul_rn(__uint_as_float(v[2 * i + 1]), s);
+            const float h0 = round_bf16(z0), h1 = round_bf16(z1);
+            hi[i] = pack_bf16x2(h0, h1);
+            lo[i] = pack_bf16x2(__fsub_rn(z0, h0), __fsub_rn(z1, h1));
+          }
+          uint4* dh = reinterpret_cast<uint4*>(p.z_hi + row * PROJ_N + cc * 32);
+          uint4* dl = reinterpret_cast<uint4*>(p.z_lo + row * PROJ_N + cc * 32);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+            dl[g] = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, PROJ_TMEM_COLS);
+  }
+}
+
+int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
+                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_hi, void* z_lo,
+                       int32_t* status, cudaStream_t stream) {
+  if (x == nullptr || a_packed == nullptr || scaling == nullptr || tiles == nullptr || num_tiles == nullptr ||
+      z_hi == nullptr || z_lo == nullptr || status == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: null buffer");
+  if (m <= 0 || k <= 0 || num_adapters <= 0 || max_tiles <= 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: non-positive shape");
+  if (k % 8 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: K must be a multiple of 8, got %d", k);
+  if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "lora_a_proj: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
+  if (!aligned16(x) || !aligned16(a_packed) || !aligned16(z_hi) || !aligned16(z_lo) || !aligned16(tiles))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: buffers must be 16-byte aligned");
+  if (z_hi == z_lo || x == z_hi || x == z_lo) return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: aliased buffers");
+  ProjParams p;
+  int rc;
+  if ((rc = encode_tmap_2d(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, k, m, static_cast<uint64_t>(k) * 2,
+                           PROJ_BK, PROJ_BM)))
+    return rc;
+  if ((rc = encode_tmap_3d(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_packed, k, SKYRL_LORA_RANK_PAD,
+                           num_adapters, static_cast<uint64_t>(k) * 2,
+                           static_cast<uint64_t>(k) * 2 * SKYRL_LORA_RANK_PAD, PROJ_BK, PROJ_N)))
+    return rc;
+  p.scaling = scaling;
+  p.tiles = reinterpret_cast<const int4*>(tiles);
+  p.num_tiles = num_tiles;
+  p.z_hi = static_cast<__nv_bfloat16*>(z_hi);
+  p.z_lo = static_cast<__nv_bfloat16*>(z_lo);
+  p.status = status;
+  p.k = k;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e =
+        cudaFuncSetAttribute(lora_a_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  lora_a_proj_kernel<<<max_tiles, PROJ_THREADS, PROJ_SMEM_BYTES, stream>>>(p);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+}  // namespace skyrl
+
+extern "C" int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
+                                          const float* lora_scaling, int32_t num_adapters, int32_t rank,
+                                          const int32_t* tiles, const int32_t* num_tiles, int32_t max_tiles, void* z_hi,
+                                          void* z_lo, int32_t* status, skyrl_stream_t stream) {
+  return skyrl::launch_lora_a_proj(x, m, k, lora_a_packed, lora_scaling, num_adapters, rank, tiles, num_tiles,
+                                   max_tiles, z_hi, z_lo, status, static_cast<cudaStream_t>(stream));
+}

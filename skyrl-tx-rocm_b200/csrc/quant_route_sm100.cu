@@ -1,0 +1,329 @@
+// HBM-bound front-end kernels of the W8A8 multi-LoRA path:
+//   * route_kernel ....... stable counting sort of token rows by adapter id and
+//                          the list of 128-row M tiles (one adapter per tile)
+//   * rms_quant_kernel ... optional RMSNorm(1 + delta), per-token absmax, int8 codes
+//   * pack kernels ....... one-time layout changes of weights and LoRA tables
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace skyrl {
+
+// ----------------------------------------------------------------------------
+// Routing.  One CTA; the histogram is parallel, the stable scatter is done by a
+// single warp with match_any so that rows of an adapter keep their order
+// (the reference's argsort is used the same way: skyrl/tx/layers/util.py:82-87).
+// ----------------------------------------------------------------------------
+constexpr int ROUTE_THREADS = 1024;
+constexpr int ROUTE_MAX_ADAPTERS = 4096;
+
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* __restrict__ perm,
+             int32_t* __restrict__ tiles, int32_t* __restrict__ num_tiles, int max_tiles, int32_t* status) {
+  __shared__ int counts[ROUTE_MAX_ADAPTERS];
+  __shared__ int cursor[ROUTE_MAX_ADAPTERS];
+  const int tid = threadIdx.x;
+
+  if (ids == nullptr) {
+    for (int i = tid; i < m; i += ROUTE_THREADS) perm[i] = i;
+    const int nt = (m + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS;
+    if (nt > max_tiles) {
+      if (tid == 0) {
+        atomicCAS(status, 0, STATUS_TILE_OVERFLOW);
+        *num_tiles = 0;
+      }
+      return;
+    }
+    for (int t = tid; t < nt; t += ROUTE_THREADS) {
+      const int r0 = t * SKYRL_TILE_ROWS;
+      reinterpret_cast<int4*>(tiles)[t] = make_int4(r0, min(SKYRL_TILE_ROWS, m - r0), 0, 0);
+    }
+    if (tid == 0) *num_tiles = nt;
+    return;
+  }
+
+  for (int a = tid; a < num_adapters; a += ROUTE_THREADS) counts[a] = 0;
+  __syncthreads();
+  for (int i = tid; i < m; i += ROUTE_THREADS) {
+    int a = ids[i];
+    if (a < 0 || a >= num_adapters) {
+      atomicCAS(status, 0, STATUS_BAD_ADAPTER_ID);
+      a = min(max(a, 0), num_adapters - 1);
+    }
+    atomicAdd(&counts[a], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int start = 0, t = 0;
+    bool overflow = false;
+    for (int a = 0; a < num_adapters; ++a) {
+      const int cnt = counts[a];
+      cursor[a] = start;
+      for (int off = 0; off < cnt; off += SKYRL_TILE_ROWS) {
+        if (t < max_tiles) {
+          reinterpret_cast<int4*>(tiles)[t] = make_int4(start + off, min(SKYRL_TILE_ROWS, cnt - off), a, 0);
+        } else {
+          overflow = true;
+        }
+        ++t;
+      }
+      start += cnt;
+    }
+    if (overflow) {
+      atomicCAS(status, 0, STATUS_TILE_OVERFLOW);
+      t = 0;
+    }
+    *num_tiles = t;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    const unsigned lt_mask = (1u << tid) - 1u;
+    for (int base = 0; base < m; base += 32) {
+      const int i = base + tid;
+      const bool active = i < m;
+      int a = active ? ids[i] : -1;
+      if (active) a = min(max(a, 0), num_adapters - 1);
+      const unsigned peers = __match_any_sync(0xffffffffu, a);
+      const int rank = __popc(peers & lt_mask);
+      if (active) perm[cursor[a] + rank] = i;
+      __syncwarp();
+      if (active && rank == 0) cursor[a] += __popc(peers);
+      __syncwarp();
+    }
+  }
+}
+
+int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
+                 int max_tiles, int32_t* status, cudaStream_t stream) {
+  if (m <= 0 || perm == nullptr || tiles == nullptr || num_tiles == nullptr || status == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: m must be positive and perm/tiles/num_tiles/status non-null");
+  if (ids != nullptr && (num_adapters <= 0 || num_adapters > ROUTE_MAX_ADAPTERS))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: num_adapters must be in [1, %d], got %d", ROUTE_MAX_ADAPTERS,
+                num_adapters);
+  if (max_tiles <= 0 || !aligned16(tiles))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: tiles must be 16-byte aligned with max_tiles > 0");
+  route_kernel<<<1, ROUTE_THREADS, 0, stream>>>(ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, status);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "route launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+// ----------------------------------------------------------------------------
+// RMSNorm + per-token int8 quantisation.  One CTA per output row; the row is
+// staged in shared memory so HBM is read once.  Arithmetic follows the
+// reference exactly: fp32 mean of squares, (x * rinv) * (1 + delta) rounded to
+// bf16 (skyrl/tx/models/qwen3_5.py:274-278), then amax / 127 and
+// rint(x / scale) with IEEE division (skyrl/tx/kernels/quantized_lora.py:207-211).
+// ----------------------------------------------------------------------------
+constexpr int QUANT_THREADS = 256;
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  __syncthreads();  // protects `red` against the previous use
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < QUANT_THREADS / 32; ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+  return r;
+}
+
+__global__ void __launch_bounds__(QUANT_THREADS)
+rms_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const __nv_bfloat16* __restrict__ delta,
+                 float eps, const int32_t* __restrict__ row_map, int k, int8_t* __restrict__ xq,
+                 float* __restrict__ sx, __nv_bfloat16* __restrict__ xn) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint4* row = reinterpret_cast<uint4*>(smem_raw);  // k / 8 vectors of 8 bf16
+  __shared__ float red[QUANT_THREADS / 32];
+
+  const int out_row = blockIdx.x;
+  const int64_t src_row = row_map != nullptr ? row_map[out_row] : out_row;
+  const uint4* src = reinterpret_cast<const uint4*>(x + src_row * x_row_stride);
+  const int nvec = k >> 3;
+  const bool norm = delta != nullptr;
+
+  float ss = 0.f, amax = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+    const uint4 u = __ldg(src + v);
+    row[v] = u;
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = bf16_lo(w[j]), b = bf16_hi(w[j]);
+      if (norm) {
+        ss = fmaf(a, a, ss);
+        ss = fmaf(b, b, ss);
+      } else {
+        amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+      }
+    }
+  }
+  if (norm) {
+    ss = block_reduce(ss, false, red);
+    const float var = __fdiv_rn(ss, static_cast<float>(k));
+    const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
+    const uint4* dvec = reinterpret_cast<const uint4*>(delta);
+    uint4* xn_row = xn != nullptr ? reinterpret_cast<uint4*>(xn + static_cast<int64_t>(out_row) * k) : nullptr;
+    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+      const uint4 u = row[v];
+      const uint4 d = __ldg(dvec + v);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = __fmul_rn(__fmul_rn(bf16_lo(w[j]), rinv), __fadd_rn(1.0f, bf16_lo(dw[j])));
+        const float b = __fmul_rn(__fmul_rn(bf16_hi(w[j]), rinv), __fadd_rn(1.0f, bf16_hi(dw[j])));
+        o[j] = pack_bf16x2(a, b);
+        amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+      }
+      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+      row[v] = ov;
+      if (xn_row != nullptr) xn_row[v] = ov;
+    }
+  } else if (xn != nullptr) {
+    uint4* xn_row = reinterpret_cast<uint4*>(xn + static_cast<int64_t>(out_row) * k);
+    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) xn_row[v] = row[v];
+  }
+  amax = block_reduce(amax, true, red);
+  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  if (threadIdx.x == 0) sx[out_row] = scale;
+
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(out_row) * k);
+  for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+    const uint4 u = row[v];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int qa = __float2int_rn(__fdiv_rn(bf16_lo(w[j]), scale));
+      int qb = __float2int_rn(__fdiv_rn(bf16_hi(w[j]), scale));
+      qa = max(-127, min(127, qa));
+      qb = max(-127, min(127, qb));
+      const uint32_t two = (static_cast<uint32_t>(qa) & 0xffu) | ((static_cast<uint32_t>(qb) & 0xffu) << 8);
+      packed[j >> 1] |= two << ((j & 1) * 16);
+    }
+    dst[v] = make_uint2(packed[0], packed[1]);
+  }
+}
+
+int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
+                     int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream) {
+  if (x == nullptr || xq == nullptr || sx == nullptr || m <= 0 || k <= 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: null buffer or non-positive shape");
+  if (k % 16 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: K must be a multiple of 16, got %d", k);
+  if (x_row_stride < k || x_row_stride % 8 != 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: row stride must be >= K and a multiple of 8 elements");
+  if (!aligned16(x) || !aligned16(xq) || (xn != nullptr && !aligned16(xn)) ||
+      (rms_delta != nullptr && !aligned16(rms_delta)))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: buffers must be 16-byte aligned");
+  if (x == xq || x == xn) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: inputs and outputs must not alias");
+  const size_t smem = static_cast<size_t>(k) * 2;
+  if (smem > 200 * 1024) return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant: K=%d exceeds the staged-row limit", k);
+  static bool attr_set = false;  // idempotent; a benign race only repeats the call
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(rms_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  rms_quant_kernel<<<m, QUANT_THREADS, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), x_row_stride, static_cast<const __nv_bfloat16*>(rms_delta), eps, row_map,
+      k, static_cast<int8_t*>(xq), sx, static_cast<__nv_bfloat16*>(xn));
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+// ----------------------------------------------------------------------------
+// Pack kernels (load time).  Tiled transposes through shared memory.
+// ----------------------------------------------------------------------------
+template <typename T>
+__global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int cols,
+                                 int64_t in_batch, int64_t out_batch, int out_pitch) {
+  // in [B, rows, cols] -> out [B, cols, out_pitch] with out[b, c, r] = in[b, r, c]; out is pre-zeroed.
+  __shared__ T tile[32][33];
+  const T* ib = in + blockIdx.z * in_batch;
+  T* ob = out + blockIdx.z * out_batch;
+  const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < cols) tile[j][threadIdx.x] = ib[static_cast<int64_t>(r) * cols + c];
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < rows && c < cols) ob[static_cast<int64_t>(c) * out_pitch + r] = tile[threadIdx.x][j];
+  }
+}
+
+template <typename T>
+static int run_transpose(const T* in, T* out, int batch, int rows, int cols, int64_t out_batch, int out_pitch,
+                         size_t out_bytes, cudaStream_t stream) {
+  cudaError_t e = cudaMemsetAsync(out, 0, out_bytes, stream);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "pack memset: %s", cudaGetErrorString(e));
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
+  if (grid.y > 65535 || grid.z > 65535) return fail(SKYRL_ERR_UNSUPPORTED, "pack: shape exceeds the launch grid");
+  transpose_kernel<T><<<grid, block, 0, stream>>>(in, out, rows, cols, static_cast<int64_t>(rows) * cols, out_batch,
+                                                   out_pitch);
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "pack launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+}  // namespace skyrl
+
+using namespace skyrl;
+
+extern "C" int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_nk,
+                                             skyrl_stream_t stream) {
+  if (codes_kn == nullptr || wq_nk == nullptr || k <= 0 || n <= 0 || codes_kn == wq_nk)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_weight: null/aliased buffer or non-positive shape");
+  // rows = K, cols = N  ->  out [N, K]
+  return run_transpose<int8_t>(static_cast<const int8_t*>(codes_kn), static_cast<int8_t*>(wq_nk), 1, k, n,
+                               static_cast<int64_t>(n) * k, k, static_cast<size_t>(n) * k,
+                               static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_pack_lora_a_sm100_v1(const void* a_akr, int32_t num_adapters, int32_t k, int32_t rank,
+                                          void* a_packed, skyrl_stream_t stream) {
+  if (a_akr == nullptr || a_packed == nullptr || num_adapters <= 0 || k <= 0 || rank <= 0 || a_akr == a_packed)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_lora_a: null/aliased buffer or non-positive shape");
+  if (rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "pack_lora_a: rank %d exceeds %d", rank, SKYRL_LORA_RANK_PAD);
+  // per adapter: in [K, r] -> out [64, K] (rows >= r stay zero)
+  return run_transpose<uint16_t>(static_cast<const uint16_t*>(a_akr), static_cast<uint16_t*>(a_packed), num_adapters,
+                                 k, rank, static_cast<int64_t>(SKYRL_LORA_RANK_PAD) * k, k,
+                                 static_cast<size_t>(num_adapters) * SKYRL_LORA_RANK_PAD * k * 2,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_pack_lora_b_sm100_v1(const void* b_arn, int32_t num_adapters, int32_t rank, int32_t n,
+                                          void* b_packed, skyrl_stream_t stream) {
+  if (b_arn == nullptr || b_packed == nullptr || num_adapters <= 0 || n <= 0 || rank <= 0 || b_arn == b_packed)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_lora_b: null/aliased buffer or non-positive shape");
+  if (rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "pack_lora_b: rank %d exceeds %d", rank, SKYRL_LORA_RANK_PAD);
+  // per adapter: in [r, N] -> out [N, 64] (columns >= r stay zero)
+  return run_transpose<uint16_t>(static_cast<const uint16_t*>(b_arn), static_cast<uint16_t*>(b_packed), num_adapters,
+                                 rank, n, static_cast<int64_t>(n) * SKYRL_LORA_RANK_PAD, SKYRL_LORA_RANK_PAD,
+                                 static_cast<size_t>(num_adapters) * n * SKYRL_LORA_RANK_PAD * 2,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, int32_t num_adapters, int32_t* perm,
+                                         int32_t* tiles, int32_t* num_tiles, int32_t max_tiles, int32_t* status,
+                                         skyrl_stream_t stream) {
+  return launch_route(adapter_ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, status,
+                      static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, const void* rms_delta, float eps,
+                                        const int32_t* row_map, int32_t m, int32_t k, void* xq, float* sx, void* xn,
+                                        skyrl_stream_t stream) {
+  return launch_rms_quant(x, x_row_stride, rms_delta, eps, row_map, m, k, xq, sx, xn,
+                          static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,512 @@
+// Persistent, warp-specialised W8A8 GEMM with fused dequant / LoRA-B / SwiGLU /
+// residual epilogue for sm_100a.
+//
+//   acc[m, n]  = sum_k xq[m, k] * wq[n, k]                (tcgen05.mma kind::i8, int32 in TMEM)
+//   v[m, n]    = (f32(acc) * sx[m]) * sw[n]               (skyrl/tx/kernels/quantized_lora.py:248-252)
+//   v[m, n]   += sum_j z[m, j] * B[a(m)][n, j]            (tcgen05.mma kind::f16 onto the SAME TMEM
+//                                                          columns, z = bf16 hi + bf16 lo, quantized_lora.py:301-304)
+//   out        = epilogue(v)                              (one bf16 cast, then SwiGLU / residual)
+//
+// Roles (192 threads): warps 0-3 drain TMEM (warp w owns TMEM lanes 32w..32w+31),
+// warp 4 is the TMA producer, warp 5 issues the int8 MMAs and owns the TMEM
+// allocation.  Two accumulator stages of BN columns let the epilogue of tile t
+// overlap the main loop of tile t+1.  The LoRA term does not get accumulator
+// columns of its own (2 x 256 int32 columns already fill the 512-column TMEM):
+// the epilogue rewrites the int32 accumulator in place as dequantised fp32,
+// then one elected epilogue thread issues the rank-r bf16 MMAs that accumulate
+// z @ B^T onto it, and the tile is read back a second time for the final cast.
+//
+// Rows live in the adapter-sorted space: every 128-row M tile comes from the
+// tile list and holds rows of one adapter; rows past the tile's count are
+// computed but never stored.  Every wait is bounded (see ptx_sm100.cuh).
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace skyrl {
+
+constexpr int BM = 128;       // rows per tile == TMEM lanes
+constexpr int BK = 128;       // int8 elements (bytes) of K per pipeline stage: one 128-byte swizzled row
+constexpr int UMMA_K_I8 = 32; // K of one kind::i8 instruction
+constexpr int GEMM_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int LORA_ROW_BYTES = SKYRL_LORA_RANK_PAD * 2;  // 128-byte rows of z and packed B
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int STAGES = (BN == 256) ? 3 : 5;
+  static constexpr int A_BYTES = BM * BK;
+  static constexpr int B_BYTES = BN * BK;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int ZHI_OFF = STAGES * STAGE_BYTES;
+  static constexpr int ZLO_OFF = ZHI_OFF + BM * LORA_ROW_BYTES;
+  static constexpr int BT_OFF = ZLO_OFF + BM * LORA_ROW_BYTES;
+  static constexpr int LORA_BYTES = 2 * BM * LORA_ROW_BYTES + BN * LORA_ROW_BYTES;
+  static constexpr int BAR_OFF = BT_OFF + BN * LORA_ROW_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;
+  static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr/abort + alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;
+};
+
+struct GemmParams {
+  CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
+  CUtensorMap tm_w;    // int8 [N, K], box 128 x BN
+  CUtensorMap tm_zhi;  // bf16 [M, 64], box 64 x 128
+  CUtensorMap tm_zlo;
+  CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
+  const float* sx;
+  const float* sw;
+  const int4* tiles;
+  const int32_t* num_tiles;
+  const int32_t* out_row_map;
+  const __nv_bfloat16* residual;
+  void* out;
+  int64_t out_stride;
+  int64_t res_stride;
+  int32_t* status;
+  int m, n, k;
+  int rank_blocks;  // ceil(rank / 16) MMAs per z half
+  int band;         // M tiles per raster band
+};
+
+struct TileCoord {
+  int m_idx, n_idx;
+};
+// Raster order: bands of `band` M tiles; inside a band the M index runs fastest,
+// so CTAs running at the same time share few distinct weight tiles and the
+// activation band stays L2-resident while the weights stream past once.
+__device__ __forceinline__ TileCoord tile_coord(int t, int tm, int tn, int band) {
+  const int per_band = band * tn;
+  const int b = t / per_band;
+  const int rem = t - b * per_band;
+  const int rows = min(band, tm - b * band);
+  TileCoord c;
+  c.n_idx = rem / rows;
+  c.m_idx = b * band + (rem - c.n_idx * rows);
+  return c;
+}
+
+__device__ __forceinline__ float silu_f32(float t) { return __fdiv_rn(t, 1.0f + expf(-t)); }
+
+template <int BN, int EPI, bool HAS_LORA>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::STAGES;
+  uint64_t* tmem_full = bars + 2 * Cfg::STAGES;       // [2]
+  uint64_t* tmem_empty = tmem_full + 2;               // [2]
+  uint64_t* lora_full = tmem_empty + 2;               // TMA -> LoRA operands landed
+  uint64_t* lora_empty = lora_full + 1;               // LoRA MMAs done reading smem
+  uint64_t* conv_done = lora_empty + 1;               // 128 epilogue threads rewrote the accumulator
+  uint64_t* lora_done = conv_done + 1;                // LoRA MMAs accumulated into TMEM
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full[s], 1);
+      mbar_init(&tmem_empty[s], EPI_THREADS);
+    }
+    mbar_init(lora_full, 1);
+    mbar_init(lora_empty, 1);
+    mbar_init(conv_done, EPI_THREADS);
+    mbar_init(lora_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_ptr_smem, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&p.tm_xq);
+    tma_prefetch_desc(&p.tm_w);
+    if (HAS_LORA) {
+      tma_prefetch_desc(&p.tm_zhi);
+      tma_prefetch_desc(&p.tm_zlo);
+      tma_prefetch_desc(&p.tm_b);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int tm = *p.num_tiles;
+  const int tn = (p.n + BN - 1) / BN;
+  const int total = tm * tn;
+  const int kblocks = (p.k + BK - 1) / BK;
+  const int band = min(p.band, max(tm, 1));
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, lora_it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const TileCoord c = tile_coord(t, tm, tn, band);
+        const int4 tile = __ldg(p.tiles + c.m_idx);
+        const int n0 = c.n_idx * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          unsigned char* sa = smem + stage * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          tma_load_2d(sa, &p.tm_xq, kb * BK, tile.x, &full_bar[stage]);
+          tma_load_2d(sa + Cfg::A_BYTES, &p.tm_w, kb * BK, n0, &full_bar[stage]);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (HAS_LORA && ok) {
+          // Issued after the tile's main-loop loads so that waiting for the
+          // previous tile's LoRA MMAs never delays the weight stream.
+          ok = mbar_wait(lora_empty, (lora_it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          mbar_expect_tx(lora_full, Cfg::LORA_BYTES);
+          tma_load_2d(smem + Cfg::ZHI_OFF, &p.tm_zhi, 0, tile.x, lora_full);
+          tma_load_2d(smem + Cfg::ZLO_OFF, &p.tm_zlo, 0, tile.x, lora_full);
+          tma_load_3d(smem + Cfg::BT_OFF, &p.tm_b, 0, n0, tile.z, lora_full);
+          ++lora_it;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ int8 MMA issuer ---------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, BM, BN);
+      int stage = 0;
+      uint32_t phase = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
+        ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + s * BN;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint64_t adesc = make_desc_sw128(sa);
+          const uint64_t bdesc = make_desc_sw128(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K_I8; ++j) {
+            mma_i8(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[stage]);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) mma_commit(&tmem_full[s]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps 0-3 -------------------------
+    constexpr uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, BN);
+    const int r = warp * 32 + lane;  // row of the tile == TMEM lane
+    uint32_t it = 0, lora_it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const TileCoord c = tile_coord(t, tm, tn, band);
+      const int4 tile = __ldg(p.tiles + c.m_idx);
+      const int n0 = c.n_idx * BN;
+      const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
+      const bool row_valid = r < tile.y;
+      const int srow = tile.x + r;
+      const float sxr = row_valid ? __ldg(p.sx + srow) : 0.f;
+      const int64_t orow = row_valid ? (p.out_row_map != nullptr ? __ldg(p.out_row_map + srow) : srow) : 0;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[s], aphase, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tbase = tmem_base + s * BN + (static_cast<uint32_t>(warp * 32) << 16);
+
+      if (HAS_LORA) {
+        // pass 1: int32 accumulator -> dequantised fp32, in place
+#pragma unroll 1
+        for (int cc = 0; cc < BN / 32; ++cc) {
+          uint32_t v[32];
+          __syncwarp();
+          tmem_ld32(tbase + cc * 32, v);
+          tmem_wait_ld();
+          const int nc = n0 + cc * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (nc + g * 4 < p.n) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
+            v[4 * g + 0] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x));
+            v[4 * g + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y));
+            v[4 * g + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z));
+            v[4 * g + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w));
+          }
+          tmem_st32(tbase + cc * 32, v);
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(conv_done);
+        if (threadIdx.x == 0) {
+          bool lok = mbar_wait(conv_done, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA);
+          lok = lok && mbar_wait(lora_full, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA);
+          if (lok) {
+            tc_fence_after_sync();
+            const uint64_t zh = make_desc_sw128(smem_u32(smem + Cfg::ZHI_OFF));
+            const uint64_t zl = make_desc_sw128(smem_u32(smem + Cfg::ZLO_OFF));
+            const uint64_t bd = make_desc_sw128(smem_u32(smem + Cfg::BT_OFF));
+            const uint32_t d = tmem_base + s * BN;
+            for (int kk = 0; kk < p.rank_blocks; ++kk) {
+              mma_bf16(d, zh + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+              mma_bf16(d, zl + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+            }
+            mma_commit(lora_empty);
+            mma_commit(lora_done);
+          }
+        }
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(lora_done, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA));
+        if (!ok) break;
+        tc_fence_after_sync();
+        ++lora_it;
+      }
+
+      // pass 2: final values -> global memory
+#pragma unroll 1
+      for (int cc = 0; cc < BN / 32; ++cc) {
+        uint32_t v[32];
+        __syncwarp();
+        tmem_ld32(tbase + cc * 32, v);
+        tmem_wait_ld();
+        const int nc = n0 + cc * 32;
+        if (EPI == SKYRL_EPI_ACC_I32) {
+          if (row_valid) {
+            int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + orow * p.out_stride + nc);
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              if (nc + g * 4 < p.n) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          }
+          continue;
+        }
+        float f[32];
+        if (HAS_LORA) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (nc + g * 4 < p.n) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
+            f[4 * g + 0] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x);
+            f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
+            f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
+            f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
+          }
+        }
+        if (!row_valid) continue;
+        if (EPI == SKYRL_EPI_PARTIAL_F32) {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            if (nc + g * 4 < p.n) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+        } else if (EPI == SKYRL_EPI_LINEAR) {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            if (nc + g * 8 < p.n)
+              dst[g] = make_uint4(pack_bf16x2(f[8 * g], f[8 * g + 1]), pack_bf16x2(f[8 * g + 2], f[8 * g + 3]),
+                                  pack_bf16x2(f[8 * g + 4], f[8 * g + 5]), pack_bf16x2(f[8 * g + 6], f[8 * g + 7]));
+        } else if (EPI == SKYRL_EPI_RESIDUAL) {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
+          const uint4* res = reinterpret_cast<const uint4*>(p.residual + orow * p.res_stride + nc);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (nc + g * 8 < p.n) {
+              const uint4 rv = __ldg(res + g);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float a = __fadd_rn(round_bf16(f[8 * g + 2 * j]), bf16_lo(rw[j]));
+                const float b = __fadd_rn(round_bf16(f[8 * g + 2 * j + 1]), bf16_hi(rw[j]));
+                o[j] = pack_bf16x2(a, b);
+              }
+              dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        } else if (EPI == SKYRL_EPI_SWIGLU) {
+          // columns (2i, 2i+1) = (gate_i, up_i); 32 physical columns -> 16 outputs
+          uint4* dst =
+              reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + (nc >> 1));
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            if (nc + g * 16 < p.n) {
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int i0 = 16 * g + 4 * j;
+                const float h0 = __fmul_rn(silu_f32(round_bf16(f[i0])), round_bf16(f[i0 + 1]));
+                const float h1 = __fmul_rn(silu_f32(round_bf16(f[i0 + 2])), round_bf16(f[i0 + 3]));
+                o[j] = pack_bf16x2(h0, h1);
+              }
+              dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty[s]);
+    }
+  }
+
+  // ------------------------------ teardown -------------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    // give copies still in flight time to land before shared memory is released
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN, int EPI, bool HAS_LORA>
+static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kernel = w8a8_gemm_kernel<BN, EPI, HAS_LORA>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+template <int BN>
+static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStream_t stream) {
+  switch (epi) {
+    case SKYRL_EPI_LINEAR:
+      return lora ? launch_variant<BN, SKYRL_EPI_LINEAR, true>(p, grid, stream)
+                  : launch_variant<BN, SKYRL_EPI_LINEAR, false>(p, grid, stream);
+    case SKYRL_EPI_SWIGLU:
+      return lora ? launch_variant<BN, SKYRL_EPI_SWIGLU, true>(p, grid, stream)
+                  : launch_variant<BN, SKYRL_EPI_SWIGLU, false>(p, grid, stream);
+    case SKYRL_EPI_RESIDUAL:
+      return lora ? launch_variant<BN, SKYRL_EPI_RESIDUAL, true>(p, grid, stream)
+                  : launch_variant<BN, SKYRL_EPI_RESIDUAL, false>(p, grid, stream);
+    case SKYRL_EPI_PARTIAL_F32:
+      return lora ? launch_variant<BN, SKYRL_EPI_PARTIAL_F32, true>(p, grid, stream)
+                  : launch_variant<BN, SKYRL_EPI_PARTIAL_F32, false>(p, grid, stream);
+    case SKYRL_EPI_ACC_I32:
+      return launch_variant<BN, SKYRL_EPI_ACC_I32, false>(p, grid, stream);
+    default:
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
+  }
+}
+
+int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
+  if (a.struct_size != sizeof(SkyrlW8A8GemmArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: struct_size %u does not match ABI v%d (%zu)", a.struct_size,
+                SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8GemmArgs));
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: non-positive shape");
+  if (a.k % 16 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: K must be a multiple of 16, got %d", a.k);
+  if (a.n % 16 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: N must be a multiple of 16, got %d", a.n);
+  if (a.xq == nullptr || a.sx == nullptr || a.wq == nullptr || a.sw == nullptr || a.out == nullptr ||
+      a.tiles == nullptr || a.num_tiles == nullptr || a.status == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: null buffer");
+  if (!aligned16(a.xq) || !aligned16(a.wq) || !aligned16(a.sw) || !aligned16(a.out) || !aligned16(a.tiles))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: buffers must be 16-byte aligned");
+  if (a.rank < 0 || a.rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "gemm: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a.rank);
+  const bool lora = a.rank > 0;
+  if (lora && (a.z_hi == nullptr || a.z_lo == nullptr || a.lora_b_packed == nullptr || a.num_adapters <= 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: LoRA buffers missing");
+  if (lora && a.epilogue == SKYRL_EPI_ACC_I32)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the int32 accumulator output excludes the LoRA term");
+  if (a.epilogue == SKYRL_EPI_RESIDUAL && (a.residual == nullptr || !aligned16(a.residual) ||
+                                           a.residual_row_stride < a.n || a.residual_row_stride % 8 != 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: residual missing, misaligned or with a bad stride");
+  const int64_t out_cols = a.epilogue == SKYRL_EPI_SWIGLU ? a.n / 2 : a.n;
+  if (a.epilogue == SKYRL_EPI_SWIGLU && a.n % 32 != 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: SwiGLU needs N (2*I) to be a multiple of 32, got %d", a.n);
+  if (a.out_row_stride < out_cols || a.out_row_stride % 8 != 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output stride must be >= the row length and a multiple of 8");
+  if (a.out == a.xq || a.out == a.wq || a.out == a.z_hi || a.out == a.z_lo)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output aliases an input");
+  if (a.max_tiles <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: max_tiles must be positive");
+
+  // Narrow tiles when wide ones would leave SMs idle.
+  const int sms = sm_count();
+  if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
+  const int64_t tiles256 = static_cast<int64_t>(a.max_tiles) * ((a.n + 255) / 256);
+  const int bn = (tiles256 >= sms) ? 256 : 128;
+
+  GemmParams p;
+  int rc;
+  if ((rc = encode_tmap_2d(&p.tm_xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.k, a.m, a.k, BK, BM))) return rc;
+  if ((rc = encode_tmap_2d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, a.k, a.n, a.k, BK, bn))) return rc;
+  if (lora) {
+    if ((rc = encode_tmap_2d(&p.tm_zhi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_hi, SKYRL_LORA_RANK_PAD, a.m,
+                             LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM)))
+      return rc;
+    if ((rc = encode_tmap_2d(&p.tm_zlo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_lo, SKYRL_LORA_RANK_PAD, a.m,
+                             LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM)))
+      return rc;
+    if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
+                             a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
+                             SKYRL_LORA_RANK_PAD, bn)))
+      return rc;
+  } else {
+    p.tm_zhi = p.tm_xq;
+    p.tm_zlo = p.tm_xq;
+    p.tm_b = p.tm_xq;
+  }
+  p.sx = a.sx;
+  p.sw = a.sw;
+  p.tiles = reinterpret_cast<const int4*>(a.tiles);
+  p.num_tiles = a.num_tiles;
+  p.out_row_map = a.out_row_map;
+  p.residual = static_cast<const __nv_bfloat16*>(a.residual);
+  p.out = a.out;
+  p.out_stride = a.out_row_stride;
+  p.res_stride = a.residual_row_stride;
+  p.status = a.status;
+  p.m = a.m;
+  p.n = a.n;
+  p.k = a.k;
+  p.rank_blocks = (a.rank + 15) / 16;
+  p.band = 16;
+  const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn - 1) / bn);
+  const int grid = static_cast<int>(max_total < sms ? max_total : sms);
+  return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
+                   : launch_bn<128>(p, a.epilogue, lora, grid, stream);
+}
+
+}  // namespace skyrl
+
+extern "C" int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream) {
+  if (args == nullptr) return skyrl::fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: args is null");
+  return skyrl::launch_gemm(*args, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,553 @@
+"""Python operator surface of the B200 W8A8 multi-LoRA MLP kernels.
+
+Mirrors the operators the reference's model layers call (names, positional
+order, `enabled=` discipline and error types), generalised to W8A8 with
+per-token adapters:
+
+* `w8a8_lora_linear`, `w8a8_frozen_linear` ... skyrl/tx/kernels/rocm/w8a8_lora.py:827-920
+* `w8a8_rms_gate_up_lora_swiglu` ............ skyrl/tx/kernels/rocm/bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757
+* `w8a8_down_lora_residual` ................. skyrl/tx/kernels/rocm/bf16_lora_residual.py:507-566
+* `w8a8_mlp_block` .......................... Qwen3_5MLP.forward_with_post_attention_rms, skyrl/tx/models/qwen3_5.py:786-826
+* `GroupQuantizedWeight`, `quantize_frozen_weight` ... skyrl/tx/kernels/quantized_lora.py:20-41,128-171
+
+torch is used for device memory and streams only; all arithmetic of the path
+runs in the hand-written CUDA library behind the C ABI
+(include/skyrl_w8a8_sm100.h).  There is no CPU or eager fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS,
+                   SkyrlKernelError)
+
+__all__ = (
+    "GroupQuantizedWeight", "PackedW8Weight", "PackedLoRA", "SkyrlKernelError",
+    "quantize_frozen_weight", "pack_weight", "pack_lora", "prepare_routing", "rms_quant",
+    "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
+    "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block",
+    "check_status", "RMS_EPS",
+)
+
+RMS_EPS = 1e-6
+MAX_LORA_RANK = LORA_RANK_PAD
+
+
+# --------------------------------------------------------------------------- #
+# storage
+# --------------------------------------------------------------------------- #
+@dataclass(frozen=True)
+class GroupQuantizedWeight:
+    """The reference's storage contract (quantized_lora.py:20-41): int8 codes
+    [Kpad, N], scales [Kpad / group_size, N]."""
+
+    codes: torch.Tensor
+    scales: torch.Tensor
+    original_in_features: int
+    padded_in_features: int
+    bits: int
+    group_size: int
+
+
+@dataclass(frozen=True)
+class PackedW8Weight:
+    """Device format of a per-output-channel W8 weight: int8 [Npad, K] with K
+    contiguous, fp32 scales [Npad]; `out_features` <= Npad (Npad % 32 == 0)."""
+
+    wq: torch.Tensor
+    sw: torch.Tensor
+    in_features: int
+    out_features: int
+
+    @property
+    def padded_out_features(self) -> int:
+        return self.wq.shape[0]
+
+
+@dataclass(frozen=True)
+class PackedLoRA:
+    """Device format of the LoRA tables of one projection: A as bf16
+    [A, 64, K], B as bf16 [A, Npad, 64], scaling fp32 [A]."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+    scaling: torch.Tensor
+    rank: int
+    num_adapters: int
+
+
+def _validate_exact_bool(name: str, value) -> None:
+    if type(value) is not bool:
+        raise TypeError(f"{name} must be an exact bool")
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise SkyrlKernelError(f"{name} must live on a CUDA device: the W8A8 operators have no CPU path")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def quantize_frozen_weight(weight: torch.Tensor, *, bits: int = 8, group_size: int | None = None,
+                           scale_dtype: torch.dtype = torch.bfloat16) -> GroupQuantizedWeight:
+    """Offline symmetric quantiser of a [K, N] weight (quantized_lora.py:128-171).
+
+    `group_size=None` means one group over all of K (per-output-channel), the
+    scheme every benchmark configuration uses.  Codes are computed with the
+    fp32 scale; the stored scale is cast to `scale_dtype` afterwards.
+    """
+    if bits != 8:
+        raise ValueError(f"the B200 path stores W8 codes only, got bits={bits}")
+    if weight.ndim != 2:
+        raise ValueError(f"weight must have shape [K, N], got {tuple(weight.shape)}")
+    if not weight.is_floating_point():
+        raise TypeError(f"weight must be floating point, got {weight.dtype}")
+    k, n = weight.shape
+    if group_size is None:
+        group_size = k + (k % 2)
+    if group_size <= 0 or group_size % 2:
+        raise ValueError(f"group_size must be a positive even integer, got {group_size}")
+    kpad = (k + group_size - 1) // group_size * group_size
+    w32 = torch.zeros((kpad, n), dtype=torch.float32, device=weight.device)
+    w32[:k] = weight.to(torch.float32)
+    grouped = w32.view(-1, group_size, n)
+    amax = grouped.abs().amax(dim=1)
+    scales = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    codes = torch.clamp(torch.round(grouped / scales[:, None, :]), -127, 127).to(torch.int8)
+    return GroupQuantizedWeight(codes.view(kpad, n).contiguous(), scales.to(scale_dtype), k, kpad, 8, group_size)
+
+
+def pack_weight(weight: GroupQuantizedWeight) -> PackedW8Weight:
+    """[K, N] codes + [1, N] scales -> K-major int8 [Npad, K] + fp32 [Npad] on the device."""
+    if weight.bits != 8:
+        raise ValueError(f"the B200 path requires W8 codes, got W{weight.bits}")
+    if weight.codes.ndim != 2 or weight.codes.dtype != torch.int8:
+        raise TypeError("W8 codes must be a rank-two INT8 array")
+    if weight.scales.ndim != 2 or not weight.scales.is_floating_point():
+        raise TypeError("W8 scales must be a rank-two floating-point array")
+    if weight.group_size != weight.padded_in_features or weight.scales.shape[0] != 1:
+        raise ValueError(
+            "pack_weight takes one scale per output channel (group_size == K); "
+            f"got group_size={weight.group_size} for K={weight.padded_in_features}"
+        )
+    _require_cuda(weight.codes, "weight.codes")
+    kpad, n = weight.codes.shape
+    k = kpad
+    if k % 16:
+        k = (kpad + 15) // 16 * 16
+    npad = (n + 31) // 32 * 32
+    codes = weight.codes
+    if k != kpad or npad != n:
+        padded = torch.zeros((k, npad), dtype=torch.int8, device=codes.device)
+        padded[:kpad, :n] = codes
+        codes = padded
+    codes = codes.contiguous()
+    wq = torch.empty((npad, k), dtype=torch.int8, device=codes.device)
+    lib = _lib.load()
+    _lib.check(lib.skyrl_pack_weight_kn_sm100_v1(_ptr(codes), k, npad, _ptr(wq), _stream()), "pack_weight")
+    sw = torch.zeros((npad,), dtype=torch.float32, device=codes.device)
+    sw[:n] = weight.scales[0].to(torch.float32)
+    return PackedW8Weight(wq, sw, k, n)
+
+
+def pack_lora(lora_a: torch.Tensor, lora_b: torch.Tensor, lora_scaling, *, in_features: int | None = None,
+              padded_out_features: int | None = None) -> PackedLoRA:
+    """LoRA tables in the reference layout (A [A, K, r], B [A, r, N], scaling [A];
+    2-D A/B + scalar = one adapter: lora.py:259-268) -> device format."""
+    if isinstance(lora_a, PackedLoRA):
+        return lora_a
+    _require_cuda(lora_a, "lora_a")
+    _require_cuda(lora_b, "lora_b")
+    if lora_a.dtype != torch.bfloat16 or lora_b.dtype != torch.bfloat16:
+        raise TypeError("LoRA A and B must both be BF16")
+    if lora_a.ndim == 2 and lora_b.ndim == 2:
+        lora_a, lora_b = lora_a[None], lora_b[None]
+    if lora_a.ndim != 3 or lora_b.ndim != 3:
+        raise ValueError("lora_a and lora_b must both be rank-two or both rank-three")
+    na, k, r = lora_a.shape
+    if lora_b.shape[0] != na or lora_b.shape[1] != r:
+        raise ValueError(f"incompatible LoRA shapes: A={tuple(lora_a.shape)}, B={tuple(lora_b.shape)}")
+    n = lora_b.shape[2]
+    if r > MAX_LORA_RANK:
+        raise ValueError(f"LoRA rank must not exceed {MAX_LORA_RANK}, got {r}")
+    scaling = torch.as_tensor(lora_scaling, dtype=torch.float32, device=lora_a.device).reshape(-1)
+    if scaling.numel() != na:
+        raise ValueError(f"lora_scaling must have {na} entries, got {scaling.numel()}")
+    kp = in_features if in_features is not None else (k + 15) // 16 * 16
+    npad = padded_out_features if padded_out_features is not None else (n + 31) // 32 * 32
+    if kp < k or npad < n:
+        raise ValueError("packed LoRA dimensions must not be smaller than the logical ones")
+    a_src, b_src = lora_a.contiguous(), lora_b.contiguous()
+    if kp != k:
+        a_src = torch.zeros((na, kp, r), dtype=torch.bfloat16, device=lora_a.device)
+        a_src[:, :k] = lora_a
+    if npad != n:
+        b_src = torch.zeros((na, r, npad), dtype=torch.bfloat16, device=lora_a.device)
+        b_src[:, :, :n] = lora_b
+    a_packed = torch.empty((na, LORA_RANK_PAD, kp), dtype=torch.bfloat16, device=lora_a.device)
+    b_packed = torch.empty((na, npad, LORA_RANK_PAD), dtype=torch.bfloat16, device=lora_a.device)
+    lib = _lib.load()
+    _lib.check(lib.skyrl_pack_lora_a_sm100_v1(_ptr(a_src), na, kp, r, _ptr(a_packed), _stream()), "pack_lora_a")
+    _lib.check(lib.skyrl_pack_lora_b_sm100_v1(_ptr(b_src), na, r, npad, _ptr(b_packed), _stream()), "pack_lora_b")
+    return PackedLoRA(a_packed, b_packed, scaling.contiguous(), r, na)
+
+
+# --------------------------------------------------------------------------- #
+# per-device scratch (torch owns the memory; the C ABI never allocates)
+# --------------------------------------------------------------------------- #
+_workspaces: dict[int, torch.Tensor] = {}
+_status: dict[int, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None or ws.numel() < nbytes + 1024:
+        ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        _workspaces[idx] = ws
+    off = (-ws.data_ptr()) % 1024
+    return ws[off: off + nbytes]
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _status.get(idx)
+    if st is None:
+        st = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[idx] = st
+    return st
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel recorded a failure (bounded wait ran
+    out, adapter id out of range).  The operators themselves never synchronise."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _status_word(device)
+    code = int(st[0].item())
+    if code != 0:
+        st.zero_()
+        raise SkyrlKernelError(f"device status {code}: {_lib.STATUS_NAMES.get(code, 'unknown')}")
+
+
+# --------------------------------------------------------------------------- #
+# validation shared by the operators
+# --------------------------------------------------------------------------- #
+def _check_x(x: torch.Tensor, k_logical: int) -> torch.Tensor:
+    _require_cuda(x, "x")
+    if x.ndim < 2 or x.numel() == 0:
+        raise ValueError(f"x must have a nonempty row domain and final K axis, got {tuple(x.shape)}")
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"x must be BF16, got {x.dtype}")
+    if x.shape[-1] != k_logical:
+        raise ValueError(f"x K={x.shape[-1]} does not match W8 K={k_logical}")
+    return x.reshape(-1, x.shape[-1])
+
+
+def _pad_cols(x2: torch.Tensor, k: int) -> torch.Tensor:
+    if x2.shape[1] == k and x2.stride(1) == 1 and x2.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0:
+        return x2
+    out = torch.zeros((x2.shape[0], k), dtype=x2.dtype, device=x2.device)
+    out[:, : x2.shape[1]] = x2
+    return out
+
+
+def _check_ids(adapter_ids, m: int, lora: PackedLoRA | None):
+    if adapter_ids is None:
+        if lora is not None and lora.num_adapters != 1:
+            raise ValueError("adapter_ids is required when the LoRA tables hold more than one adapter")
+        return None
+    _require_cuda(adapter_ids, "adapter_ids")
+    if adapter_ids.dtype != torch.int32:
+        raise TypeError(f"adapter_ids must be INT32, got {adapter_ids.dtype}")
+    if adapter_ids.shape != (m,):
+        raise ValueError(f"adapter_ids must have shape ({m},), got {tuple(adapter_ids.shape)}")
+    return adapter_ids.contiguous()
+
+
+def _weight_of(weight) -> PackedW8Weight:
+    if isinstance(weight, PackedW8Weight):
+        return weight
+    if isinstance(weight, GroupQuantizedWeight):
+        return pack_weight(weight)
+    raise TypeError("weight must be a GroupQuantizedWeight or a PackedW8Weight")
+
+
+def _lora_of(weight: PackedW8Weight, lora_a, lora_b, lora_scaling) -> PackedLoRA:
+    if isinstance(lora_a, PackedLoRA):
+        lora = lora_a
+    else:
+        a_k = lora_a.shape[-2]
+        if a_k not in (weight.in_features,) and not (a_k <= weight.in_features < a_k + 16):
+            raise ValueError(f"lora_a K={a_k} does not match W8 K={weight.in_features}")
+        if lora_b.shape[-1] != weight.out_features:
+            raise ValueError(f"LoRA output N={lora_b.shape[-1]} does not match weight N={weight.out_features}")
+        lora = pack_lora(lora_a, lora_b, lora_scaling, in_features=weight.in_features,
+                         padded_out_features=weight.padded_out_features)
+    if lora.a.shape[2] != weight.in_features or lora.b.shape[1] != weight.padded_out_features:
+        raise ValueError("packed LoRA tables do not match the packed weight")
+    return lora
+
+
+def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilogue, *, rms_delta=None, eps=RMS_EPS,
+                residual=None, out=None):
+    lib = _lib.load()
+    m = x2.shape[0]
+    k, npad = weight.in_features, weight.padded_out_features
+    x2 = _pad_cols(x2, k)
+    dev = x2.device
+    if epilogue == EPI_SWIGLU:
+        out_cols, out_dtype = npad // 2, torch.bfloat16
+    elif epilogue == EPI_ACC_I32:
+        out_cols, out_dtype = npad, torch.int32
+    elif epilogue == EPI_PARTIAL_F32:
+        out_cols, out_dtype = npad, torch.float32
+    else:
+        out_cols, out_dtype = npad, torch.bfloat16
+    if out is None:
+        out = torch.empty((m, out_cols), dtype=out_dtype, device=dev)
+    na = lora.num_adapters if lora is not None else 1
+    nbytes = lib.skyrl_w8a8_linear_workspace_bytes(m, k, na)
+    ws = _workspace(dev, nbytes)
+    st = _status_word(dev)
+    a = _lib.LinearArgs()
+    a.struct_size = C.sizeof(_lib.LinearArgs)
+    a.epilogue = epilogue
+    a.m, a.n, a.k = m, npad, k
+    a.rank = lora.rank if lora is not None else 0
+    a.num_adapters = na
+    a.x = x2.data_ptr()
+    a.x_row_stride = x2.stride(0)
+    a.rms_delta = rms_delta.data_ptr() if rms_delta is not None else None
+    a.rms_eps = float(eps)
+    a.wq = weight.wq.data_ptr()
+    a.sw = weight.sw.data_ptr()
+    if lora is not None:
+        a.lora_a_packed = lora.a.data_ptr()
+        a.lora_b_packed = lora.b.data_ptr()
+        a.lora_scaling = lora.scaling.data_ptr()
+    a.adapter_ids = ids.data_ptr() if ids is not None else None
+    if residual is not None:
+        a.residual = residual.data_ptr()
+        a.residual_row_stride = residual.stride(0)
+    a.out = out.data_ptr()
+    a.out_row_stride = out.stride(0)
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = nbytes
+    a.status = st.data_ptr()
+    _lib.check(lib.skyrl_w8a8_lora_forward_sm100_v1(C.byref(a), _stream()), "w8a8_lora_forward")
+    return out
+
+
+def _pad_delta(rms_delta, k_logical: int, k: int):
+    _require_cuda(rms_delta, "rms_delta")
+    if rms_delta.dtype != torch.bfloat16 or rms_delta.shape != (k_logical,):
+        raise TypeError(f"rms_delta must be BF16 with shape ({k_logical},)")
+    if k == k_logical:
+        return rms_delta.contiguous()
+    raise ValueError("RMSNorm fusion needs K to be a multiple of 16")
+
+
+# --------------------------------------------------------------------------- #
+# operators
+# --------------------------------------------------------------------------- #
+def w8a8_frozen_linear(x, weight, *, enabled: bool = False, interpret: bool = False, block_m: int = 128,
+                       block_n: int = 256, row_superblock: int = 0):
+    """Frozen W8A8 base only (w8a8_lora.py:827-867).  Tile-size keywords are
+    accepted for signature compatibility and ignored."""
+    _validate_exact_bool("enabled", enabled)
+    _validate_exact_bool("interpret", interpret)
+    if not enabled:
+        raise RuntimeError("the W8A8 frozen-linear kernel is disabled by default")
+    w = _weight_of(weight)
+    k_logical = weight.original_in_features if isinstance(weight, GroupQuantizedWeight) else w.in_features
+    x2 = _check_x(x, k_logical)
+    y = _run_linear(x2, w, None, None, EPI_LINEAR)
+    return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
+
+
+def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_ids=None, *, enabled: bool = False,
+                     interpret: bool = False, block_m: int = 128, block_n: int = 256, row_superblock: int = 0):
+    """y = bf16(dequant(xq wq^T) + s (x A) B) (w8a8_lora.py:870-920).
+
+    `lora_a` [K, r] / `lora_b` [r, N] / scalar scaling select one adapter as in
+    the reference; [A, K, r] / [A, r, N] / [A] with `adapter_ids` int32 [M]
+    select an adapter per token row.  A `PackedLoRA` may be passed as `lora_a`.
+    """
+    _validate_exact_bool("enabled", enabled)
+    _validate_exact_bool("interpret", interpret)
+    if not enabled:
+        raise RuntimeError("the W8A8 LoRA kernel is disabled by default")
+    w = _weight_of(weight)
+    k_logical = weight.original_in_features if isinstance(weight, GroupQuantizedWeight) else w.in_features
+    x2 = _check_x(x, k_logical)
+    lora = _lora_of(w, lora_a, lora_b, lora_scaling)
+    ids = _check_ids(adapter_ids, x2.shape[0], lora)
+    y = _run_linear(x2, w, lora, ids, EPI_LINEAR)
+    return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
+
+
+def w8a8_int32_accumulator(x, weight, *, enabled: bool = False):
+    """Raw int32 accumulator xq @ wq^T and the activation codes' scales, for
+    bit-exact parity checks (quantized_lora.py:242-247)."""
+    _validate_exact_bool("enabled", enabled)
+    if not enabled:
+        raise RuntimeError("the W8A8 accumulator probe is disabled by default")
+    w = _weight_of(weight)
+    x2 = _check_x(x, w.in_features if not isinstance(weight, GroupQuantizedWeight) else weight.original_in_features)
+    acc = _run_linear(x2, w, None, None, EPI_ACC_I32)
+    return acc[:, : w.out_features]
+
+
+def w8a8_rms_gate_up_lora_swiglu(x, rms_delta, frozen_weight, lora_a, lora_b=None, lora_scaling=None,
+                                 adapter_ids=None, *, enabled: bool = False, eps: float = RMS_EPS):
+    """h = swiglu(W8A8-LoRA gate_up(rmsnorm(x))) with interleaved (gate, up)
+    columns; never materialises the [M, 2I] projection
+    (bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757).  `rms_delta=None`
+    skips the normalisation."""
+    _validate_exact_bool("enabled", enabled)
+    if not enabled:
+        raise RuntimeError("the W8A8 RMS+gate/up+SwiGLU kernel is disabled by default")
+    w = _weight_of(frozen_weight)
+    if w.out_features % 2:
+        raise ValueError("gate_up needs an even number of physical output columns")
+    k_logical = frozen_weight.original_in_features if isinstance(frozen_weight, GroupQuantizedWeight) else w.in_features
+    x2 = _check_x(x, k_logical)
+    lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
+    ids = _check_ids(adapter_ids, x2.shape[0], lora)
+    delta = _pad_delta(rms_delta, k_logical, w.in_features) if rms_delta is not None else None
+    h = _run_linear(x2, w, lora, ids, EPI_SWIGLU, rms_delta=delta, eps=eps)
+    inter = w.out_features // 2
+    return h[:, :inter].reshape(*x.shape[:-1], inter)
+
+
+def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=None, residual=None,
+                            adapter_ids=None, *, enabled: bool = False):
+    """out = residual + W8A8-LoRA down(x) (bf16_lora_residual.py:507-566)."""
+    _validate_exact_bool("enabled", enabled)
+    if not enabled:
+        raise RuntimeError("the W8A8 down+residual kernel is disabled by default")
+    w = _weight_of(frozen_weight)
+    k_logical = frozen_weight.original_in_features if isinstance(frozen_weight, GroupQuantizedWeight) else w.in_features
+    x2 = _check_x(x, k_logical)
+    lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
+    ids = _check_ids(adapter_ids, x2.shape[0], lora)
+    if residual is None:
+        y = _run_linear(x2, w, lora, ids, EPI_LINEAR)
+    else:
+        _require_cuda(residual, "residual")
+        if residual.dtype != torch.bfloat16:
+            raise TypeError(f"residual must be BF16, got {residual.dtype}")
+        r2 = residual.reshape(-1, residual.shape[-1])
+        if r2.shape != (x2.shape[0], w.out_features):
+            raise ValueError(f"residual must have shape ({x2.shape[0]}, {w.out_features}), got {tuple(r2.shape)}")
+        r2 = _pad_cols(r2, w.padded_out_features)
+        y = _run_linear(x2, w, lora, ids, EPI_RESIDUAL, residual=r2)
+    return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
+
+
+def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: PackedLoRA | None,
+                   down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
+                   enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL):
+    """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
+    the adapter routing computed once and h kept on the device in sorted row
+    order (qwen3_5.py:786-826).  Takes packed weights and tables only."""
+    _validate_exact_bool("enabled", enabled)
+    if not enabled:
+        raise RuntimeError("the W8A8 MLP block is disabled by default")
+    if not isinstance(gate_up_weight, PackedW8Weight) or not isinstance(down_weight, PackedW8Weight):
+        raise TypeError("w8a8_mlp_block takes PackedW8Weight weights")
+    hidden, two_i = gate_up_weight.in_features, gate_up_weight.padded_out_features
+    inter = two_i // 2
+    if gate_up_weight.out_features != two_i or down_weight.out_features != down_weight.padded_out_features:
+        raise ValueError("w8a8_mlp_block needs feature sizes that are multiples of 32")
+    if down_weight.in_features != inter or down_weight.out_features != hidden:
+        raise ValueError("down weight does not match gate_up weight")
+    x2 = _check_x(x, hidden)
+    x2 = _pad_cols(x2, hidden)
+    m = x2.shape[0]
+    if (gate_up_lora is None) != (down_lora is None):
+        raise ValueError("give LoRA tables for both projections or for neither")
+    ids = _check_ids(adapter_ids, m, gate_up_lora)
+    delta = _pad_delta(rms_delta, hidden, hidden) if rms_delta is not None else None
+    lib = _lib.load()
+    dev = x2.device
+    na = gate_up_lora.num_adapters if gate_up_lora is not None else 1
+    nbytes = lib.skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na)
+    ws = _workspace(dev, nbytes)
+    st = _status_word(dev)
+    if out is None:
+        out = torch.empty((m, hidden), dtype=torch.float32 if down_epilogue == EPI_PARTIAL_F32 else torch.bfloat16,
+                          device=dev)
+    a = _lib.MlpArgs()
+    a.struct_size = C.sizeof(_lib.MlpArgs)
+    a.m, a.hidden, a.inter = m, hidden, inter
+    a.rank = gate_up_lora.rank if gate_up_lora is not None else 0
+    a.num_adapters = na
+    a.down_epilogue = down_epilogue
+    a.rms_eps = float(eps)
+    a.x = x2.data_ptr()
+    a.rms_delta = delta.data_ptr() if delta is not None else None
+    if residual is not None:
+        r2 = _pad_cols(residual.reshape(-1, residual.shape[-1]), hidden)
+        a.residual = r2.data_ptr()
+    a.gu_wq, a.gu_sw = gate_up_weight.wq.data_ptr(), gate_up_weight.sw.data_ptr()
+    a.dn_wq, a.dn_sw = down_weight.wq.data_ptr(), down_weight.sw.data_ptr()
+    if gate_up_lora is not None:
+        if gate_up_lora.rank != down_lora.rank or gate_up_lora.num_adapters != down_lora.num_adapters:
+            raise ValueError("gate_up and down LoRA tables must share rank and adapter count")
+        a.gu_a_packed, a.gu_b_packed = gate_up_lora.a.data_ptr(), gate_up_lora.b.data_ptr()
+        a.gu_scaling = gate_up_lora.scaling.data_ptr()
+        a.dn_a_packed, a.dn_b_packed = down_lora.a.data_ptr(), down_lora.b.data_ptr()
+        a.dn_scaling = down_lora.scaling.data_ptr()
+    a.adapter_ids = ids.data_ptr() if ids is not None else None
+    a.out = out.data_ptr()
+    a.workspace = ws.data_ptr()
+    a.workspace_bytes = nbytes
+    a.status = st.data_ptr()
+    _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
+    return out.reshape(*x.shape[:-1], hidden) if out.shape[0] == m else out
+
+
+# --------------------------------------------------------------------------- #
+# stage-level entry points (used by the parity tests)
+# --------------------------------------------------------------------------- #
+def prepare_routing(adapter_ids, m: int, num_adapters: int):
+    """Device statement of prepare_routing (layers/util.py:66-87): returns
+    (perm int32 [m], tiles int32 [T, 4], num_tiles int32 [1])."""
+    lib = _lib.load()
+    dev = adapter_ids.device if adapter_ids is not None else torch.device("cuda", torch.cuda.current_device())
+    max_tiles = (m + TILE_ROWS - 1) // TILE_ROWS + max(num_adapters, 1)
+    perm = torch.empty(m, dtype=torch.int32, device=dev)
+    tiles = torch.zeros((max_tiles, 4), dtype=torch.int32, device=dev)
+    num = torch.zeros(4, dtype=torch.int32, device=dev)
+    st = _status_word(dev)
+    _lib.check(lib.skyrl_lora_route_sm100_v1(_ptr(adapter_ids), m, num_adapters, _ptr(perm), _ptr(tiles), _ptr(num),
+                                             max_tiles, _ptr(st), _stream()), "lora_route")
+    return perm, tiles, num
+
+
+def rms_quant(x, rms_delta=None, *, eps: float = RMS_EPS, row_map=None, want_normalized: bool = False):
+    """RMSNorm (optional) + per-token int8 quantisation: returns (codes int8
+    [M, K], scales fp32 [M], normalised bf16 [M, K] or None)."""
+    lib = _lib.load()
+    _require_cuda(x, "x")
+    m, k = x.shape
+    xq = torch.empty((m, k), dtype=torch.int8, device=x.device)
+    sx = torch.empty((m,), dtype=torch.float32, device=x.device)
+    xn = torch.empty((m, k), dtype=torch.bfloat16, device=x.device) if want_normalized else None
+    _lib.check(lib.skyrl_rms_quant_sm100_v1(_ptr(x), x.stride(0), _ptr(rms_delta), float(eps), _ptr(row_map), m, k,
+                                            _ptr(xq), _ptr(sx), _ptr(xn), _stream()), "rms_quant")
+    return xq, sx, xn

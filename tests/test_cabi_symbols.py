@@ -1,0 +1,79 @@
+"""The C-ABI library builds, loads and exports every symbol the header declares (no GPU needed)."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "skyrl_w8a8_sm100.h"
+
+
+def _declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(skyrl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = _declared_symbols()
+    for required in (
+        "skyrl_w8a8_lora_forward_sm100_v1", "skyrl_w8a8_mlp_block_sm100_v1", "skyrl_w8a8_gemm_sm100_v1",
+        "skyrl_rms_quant_sm100_v1", "skyrl_lora_a_proj_sm100_v1", "skyrl_lora_route_sm100_v1",
+    ):
+        assert required in names
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    from skyrl_tx_rocm_b200 import _lib
+
+    if not _lib.LIB_PATH.exists():
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("skyrl_build", ROOT / "skyrl-tx-rocm_b200" / "build.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build_library()
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    declared = _declared_symbols()
+    assert declared, "no symbols parsed from the header"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert set(declared) == set(_lib.SYMBOLS), "ctypes binding and header disagree"
+    loaded = _lib.load()
+    assert loaded.skyrl_w8a8_abi_version() == 1
+
+
+def test_struct_sizes_are_stable():
+    from skyrl_tx_rocm_b200 import _lib
+
+    # Natural alignment, no packing: these sizes are part of ABI v1 and are
+    # checked against struct_size by every entry point.
+    assert ctypes.sizeof(_lib.GemmArgs) == 32 + 12 * 8 + 2 * 8 + 8
+    assert ctypes.sizeof(_lib.LinearArgs) == 32 + 3 * 8 + 8 + 7 * 8 + 8 + 8 + 8 + 8 + 8 + 8
+    assert ctypes.sizeof(_lib.MlpArgs) == 32 + 18 * 8
+
+
+def test_disabled_by_default_and_exact_bool():
+    import torch
+
+    import skyrl_tx_rocm_b200 as S
+
+    x = torch.zeros((2, 16), dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="disabled by default"):
+        S.w8a8_lora_linear(x, None, None)
+    with pytest.raises(TypeError, match="exact bool"):
+        S.w8a8_lora_linear(x, None, None, enabled=1)
+    with pytest.raises(RuntimeError, match="disabled by default"):
+        S.w8a8_mlp_block(x, None, None, None, None, None)
+
+
+def test_no_cpu_fallback():
+    import torch
+
+    import skyrl_tx_rocm_b200 as S
+
+    w = S.quantize_frozen_weight(torch.randn(16, 32))
+    assert w.codes.dtype == torch.int8 and w.scales.shape == (1, 32) and w.group_size == 16
+    with pytest.raises(S.SkyrlKernelError, match="CUDA"):
+        S.pack_weight(w)

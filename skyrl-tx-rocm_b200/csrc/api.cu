@@ -58,11 +58,11 @@ int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, 
 
 int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t d0,
                    uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
-                   uint32_t box1) {
+                   uint32_t box1, uint32_t box2) {
   (void)elem_bytes;
   const cuuint64_t dims[3] = {d0, d1, d2};
   const cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
-  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t box[3] = {box0, box1, box2};
   return encode(map, dtype, 3, base, dims, strides, box);
 }
 
@@ -106,8 +106,7 @@ struct LinearWs {
   int8_t* xq;
   float* sx;
   uint16_t* xn;
-  uint16_t* z_hi;
-  uint16_t* z_lo;
+  uint16_t* z_parts;
   size_t bytes;
 };
 
@@ -121,8 +120,7 @@ static LinearWs carve_linear(void* ws, int m, int k, int num_adapters) {
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * k);
   w.sx = c.take<float>(m);
   w.xn = c.take<uint16_t>(static_cast<size_t>(m) * k);
-  w.z_hi = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
-  w.z_lo = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   w.bytes = c.total();
   return w;
 }
@@ -134,8 +132,7 @@ struct MlpWs {
   int8_t* xq;
   float* sx;
   uint16_t* xn;
-  uint16_t* z_hi;
-  uint16_t* z_lo;
+  uint16_t* z_parts;
   uint16_t* h;
   int8_t* hq;
   float* sh;
@@ -152,8 +149,7 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
   w.sx = c.take<float>(m);
   w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
-  w.z_hi = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
-  w.z_lo = c.take<uint16_t>(static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   w.h = c.take<uint16_t>(static_cast<size_t>(m) * inter);
   w.hq = c.take<int8_t>(static_cast<size_t>(m) * inter);
   w.sh = c.take<float>(m);
@@ -217,7 +213,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   if (lora) {
     const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
     if ((rc = launch_lora_a_proj(xa, a->m, a->k, a->lora_a_packed, a->lora_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+                                 mt, w.z_parts, a->status, stream)))
       return rc;
   }
   SkyrlW8A8GemmArgs g;
@@ -233,8 +229,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   g.sx = w.sx;
   g.wq = a->wq;
   g.sw = a->sw;
-  g.z_hi = lora ? w.z_hi : nullptr;
-  g.z_lo = lora ? w.z_lo : nullptr;
+  g.z_parts = lora ? w.z_parts : nullptr;
   g.lora_b_packed = a->lora_b_packed;
   g.tiles = w.tiles;
   g.num_tiles = w.num_tiles;
@@ -244,7 +239,10 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   g.out_row_stride = a->out_row_stride;
   g.residual_row_stride = a->residual_row_stride;
   g.status = a->status;
-  return launch_gemm(g, stream);
+  if (a->timing_events[0] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[0]), stream);
+  rc = launch_gemm(g, stream);
+  if (a->timing_events[1] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[1]), stream);
+  return rc;
 }
 
 extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_stream_t stream_) {
@@ -285,7 +283,7 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   if (lora) {
     const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
     if ((rc = launch_lora_a_proj(xa, a->m, a->hidden, a->gu_a_packed, a->gu_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+                                 mt, w.z_parts, a->status, stream)))
       return rc;
   }
   SkyrlW8A8GemmArgs g;
@@ -301,8 +299,7 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   g.sx = w.sx;
   g.wq = a->gu_wq;
   g.sw = a->gu_sw;
-  g.z_hi = lora ? w.z_hi : nullptr;
-  g.z_lo = lora ? w.z_lo : nullptr;
+  g.z_parts = lora ? w.z_parts : nullptr;
   g.lora_b_packed = a->gu_b_packed;
   g.tiles = w.tiles;
   g.num_tiles = w.num_tiles;
@@ -312,14 +309,16 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   g.out_row_stride = a->inter;
   g.residual_row_stride = 0;
   g.status = a->status;
+  if (a->timing_events[0] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[0]), stream);
   if ((rc = launch_gemm(g, stream))) return rc;
+  if (a->timing_events[1] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[1]), stream);
 
   // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
   if ((rc = launch_rms_quant(w.h, a->inter, nullptr, 0.f, nullptr, a->m, a->inter, w.hq, w.sh, nullptr, stream)))
     return rc;
   if (lora) {
     if ((rc = launch_lora_a_proj(w.h, a->m, a->inter, a->dn_a_packed, a->dn_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_hi, w.z_lo, a->status, stream)))
+                                 mt, w.z_parts, a->status, stream)))
       return rc;
   }
   g.epilogue = a->down_epilogue;
@@ -330,10 +329,32 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   g.wq = a->dn_wq;
   g.sw = a->dn_sw;
   g.lora_b_packed = a->dn_b_packed;
-  g.out_row_map = perm;
+  g.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : perm;
   g.residual = a->residual != nullptr ? a->residual : a->x;
   g.out = a->out;
   g.out_row_stride = a->hidden;
   g.residual_row_stride = a->hidden;
-  return launch_gemm(g, stream);
+  if (a->timing_events[2] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[2]), stream);
+  rc = launch_gemm(g, stream);
+  if (a->timing_events[3] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[3]), stream);
+  return rc;
+}
+
+extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, const float* reduced, void* out,
+                                                    int32_t row_begin, int32_t row_count, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || reduced == nullptr || out == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize: null argument");
+  if (a->struct_size != sizeof(SkyrlW8A8MlpArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize: struct_size does not match ABI v%d", SKYRL_W8A8_ABI_VERSION);
+  if (a->m <= 0 || a->hidden <= 0 || a->hidden % 8 != 0 || row_begin < 0 || row_count <= 0 ||
+      row_begin + row_count > a->m)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize: bad shape or row range");
+  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
+  const MlpWs w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, na);
+  int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "tp_finalize");
+  if (rc) return rc;
+  const void* residual = a->residual != nullptr ? a->residual : a->x;
+  return launch_tp_finalize(reduced, a->adapter_ids != nullptr ? w.perm : nullptr, residual, out, a->hidden, row_begin,
+                            row_count, stream);
 }

@@ -19,7 +19,7 @@ int encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, 
                    uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
 int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base, uint64_t d0,
                    uint64_t d1, uint64_t d2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
-                   uint32_t box1);
+                   uint32_t box1, uint32_t box2 = 1);
 
 int sm_count();
 
@@ -31,8 +31,10 @@ int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
-                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_hi, void* z_lo,
+                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream);
 int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream);
+int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
+                       int row_begin, int row_count, cudaStream_t stream);
 
 }  // namespace skyrl

@@ -1,8 +1,8 @@
 // LoRA-A projection on the tensor cores: for every 128-row tile of the
 // adapter-sorted row space, z = s[a] * (x_tile @ A[a]) with a bf16 tcgen05 MMA
 // (fp32 accumulator in TMEM, products of bf16 inputs are exact), written out as
-// a bf16 (hi, lo) pair so that the rank-r contraction of the GEMM epilogue sees
-// z to 16 significant bits.  HBM-bound: x is streamed once through a 6-stage
+// three bf16 planes (hi, mid, lo) that sum to the fp32 value exactly, so that the
+// rank-r contraction of the GEMM epilogue sees z at full fp32 precision.  HBM-bound: x is streamed once through a 6-stage
 // TMA pipeline, one CTA per tile.
 //
 // Reference arithmetic: `x.astype(f32) @ lora_a.astype(f32)`
@@ -32,8 +32,8 @@ struct ProjParams {
   const float* scaling;
   const int4* tiles;
   const int32_t* num_tiles;
-  __nv_bfloat16* z_hi;
-  __nv_bfloat16* z_lo;
+  __nv_bfloat16* z_parts;  // [3, m, 64]
+  int64_t plane;           // m * 64
   int32_t* status;
   int k;
 };
@@ -129,20 +129,25 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
         tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + cc * 32, v);
         tmem_wait_ld();
         if (row_valid) {
-          uint32_t hi[16], lo[16];
+          uint32_t hi[16], mid[16], lo[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float z0 = __fmul_rn(__uint_as_float(v[2 * i]), s);
             const float z1 = __fmul_rn(__uint_as_float(v[2 * i + 1]), s);
             const float h0 = round_bf16(z0), h1 = round_bf16(z1);
+            const float r0 = __fsub_rn(z0, h0), r1 = __fsub_rn(z1, h1);  // exact
+            const float m0 = round_bf16(r0), m1 = round_bf16(r1);
             hi[i] = pack_bf16x2(h0, h1);
-            lo[i] = pack_bf16x2(__fsub_rn(z0, h0), __fsub_rn(z1, h1));
+            mid[i] = pack_bf16x2(m0, m1);
+            lo[i] = pack_bf16x2(__fsub_rn(r0, m0), __fsub_rn(r1, m1));  // <= 8 bits left: exact in bf16
           }
-          uint4* dh = reinterpret_cast<uint4*>(p.z_hi + row * PROJ_N + cc * 32);
-          uint4* dl = reinterpret_cast<uint4*>(p.z_lo + row * PROJ_N + cc * 32);
+          uint4* dh = reinterpret_cast<uint4*>(p.z_parts + row * PROJ_N + cc * 32);
+          uint4* dm = reinterpret_cast<uint4*>(p.z_parts + p.plane + row * PROJ_N + cc * 32);
+          uint4* dl = reinterpret_cast<uint4*>(p.z_parts + 2 * p.plane + row * PROJ_N + cc * 32);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+            dm[g] = make_uint4(mid[4 * g], mid[4 * g + 1], mid[4 * g + 2], mid[4 * g + 3]);
             dl[g] = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
           }
         }
@@ -164,19 +169,19 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
 }
 
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
-                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_hi, void* z_lo,
+                       int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream) {
   if (x == nullptr || a_packed == nullptr || scaling == nullptr || tiles == nullptr || num_tiles == nullptr ||
-      z_hi == nullptr || z_lo == nullptr || status == nullptr)
+      z_parts == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: null buffer");
   if (m <= 0 || k <= 0 || num_adapters <= 0 || max_tiles <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: non-positive shape");
   if (k % 8 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: K must be a multiple of 8, got %d", k);
   if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "lora_a_proj: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
-  if (!aligned16(x) || !aligned16(a_packed) || !aligned16(z_hi) || !aligned16(z_lo) || !aligned16(tiles))
+  if (!aligned16(x) || !aligned16(a_packed) || !aligned16(z_parts) || !aligned16(tiles))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: buffers must be 16-byte aligned");
-  if (z_hi == z_lo || x == z_hi || x == z_lo) return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: aliased buffers");
+  if (x == z_parts) return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: aliased buffers");
   ProjParams p;
   int rc;
   if ((rc = encode_tmap_2d(&p.tm_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, k, m, static_cast<uint64_t>(k) * 2,
@@ -189,8 +194,8 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
   p.scaling = scaling;
   p.tiles = reinterpret_cast<const int4*>(tiles);
   p.num_tiles = num_tiles;
-  p.z_hi = static_cast<__nv_bfloat16*>(z_hi);
-  p.z_lo = static_cast<__nv_bfloat16*>(z_lo);
+  p.z_parts = static_cast<__nv_bfloat16*>(z_parts);
+  p.plane = static_cast<int64_t>(m) * PROJ_N;
   p.status = status;
   p.k = k;
   static bool attr_set = false;
@@ -210,8 +215,8 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
 
 extern "C" int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
                                           const float* lora_scaling, int32_t num_adapters, int32_t rank,
-                                          const int32_t* tiles, const int32_t* num_tiles, int32_t max_tiles, void* z_hi,
-                                          void* z_lo, int32_t* status, skyrl_stream_t stream) {
+                                          const int32_t* tiles, const int32_t* num_tiles, int32_t max_tiles,
+                                          void* z_parts, int32_t* status, skyrl_stream_t stream) {
   return skyrl::launch_lora_a_proj(x, m, k, lora_a_packed, lora_scaling, num_adapters, rank, tiles, num_tiles,
-                                   max_tiles, z_hi, z_lo, status, static_cast<cudaStream_t>(stream));
+                                   max_tiles, z_parts, status, static_cast<cudaStream_t>(stream));
 }

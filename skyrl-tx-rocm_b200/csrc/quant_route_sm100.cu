@@ -239,6 +239,45 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
 }
 
 // ----------------------------------------------------------------------------
+// Row-parallel finalize: out[perm[i]] = bf16(bf16(sum[i]) + residual[perm[i]]).
+// The two roundings are the reference's: the projection is cast to bf16 once
+// (quantized_lora.py:304) and the residual add is a bf16 add (qwen3_5.py:784).
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+tp_finalize_kernel(const float* __restrict__ reduced, const int32_t* __restrict__ perm,
+                   const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int hidden,
+                   int row_begin) {
+  const int64_t srow = row_begin + blockIdx.x;
+  const int64_t orow = perm != nullptr ? perm[srow] : srow;
+  const float4* src = reinterpret_cast<const float4*>(reduced + srow * hidden);
+  const uint4* res = reinterpret_cast<const uint4*>(residual + orow * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + orow * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    const float4 a = __ldg(src + 2 * v), b = __ldg(src + 2 * v + 1);
+    const uint4 r = __ldg(res + v);
+    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])),
+                         __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
+    dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
+                       int row_begin, int row_count, cudaStream_t stream) {
+  if (residual == nullptr || !aligned16(reduced) || !aligned16(residual) || !aligned16(out))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize: residual missing or buffers not 16-byte aligned");
+  tp_finalize_kernel<<<row_count, 256, 0, stream>>>(reduced, perm, static_cast<const __nv_bfloat16*>(residual),
+                                                    static_cast<__nv_bfloat16*>(out), hidden, row_begin);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_finalize launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+// ----------------------------------------------------------------------------
 // Pack kernels (load time).  Tiled transposes through shared memory.
 // ----------------------------------------------------------------------------
 template <typename T>

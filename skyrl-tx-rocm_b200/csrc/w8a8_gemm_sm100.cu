@@ -4,7 +4,7 @@
 //   acc[m, n]  = sum_k xq[m, k] * wq[n, k]                (tcgen05.mma kind::i8, int32 in TMEM)
 //   v[m, n]    = (f32(acc) * sx[m]) * sw[n]               (skyrl/tx/kernels/quantized_lora.py:248-252)
 //   v[m, n]   += sum_j z[m, j] * B[a(m)][n, j]            (tcgen05.mma kind::f16 onto the SAME TMEM
-//                                                          columns, z = bf16 hi + bf16 lo, quantized_lora.py:301-304)
+//                                                          columns, z = three bf16 planes, quantized_lora.py:301-304)
 //   out        = epilogue(v)                              (one bf16 cast, then SwiGLU / residual)
 //
 // Roles (192 threads): warps 0-3 drain TMEM (warp w owns TMEM lanes 32w..32w+31),
@@ -37,10 +37,10 @@ struct GemmCfg {
   static constexpr int A_BYTES = BM * BK;
   static constexpr int B_BYTES = BN * BK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int ZHI_OFF = STAGES * STAGE_BYTES;
-  static constexpr int ZLO_OFF = ZHI_OFF + BM * LORA_ROW_BYTES;
-  static constexpr int BT_OFF = ZLO_OFF + BM * LORA_ROW_BYTES;
-  static constexpr int LORA_BYTES = 2 * BM * LORA_ROW_BYTES + BN * LORA_ROW_BYTES;
+  static constexpr int Z_OFF = STAGES * STAGE_BYTES;        // three planes (hi, mid, lo) of BM x 128 bytes
+  static constexpr int Z_PLANE_BYTES = BM * LORA_ROW_BYTES;
+  static constexpr int BT_OFF = Z_OFF + 3 * Z_PLANE_BYTES;
+  static constexpr int LORA_BYTES = 3 * Z_PLANE_BYTES + BN * LORA_ROW_BYTES;
   static constexpr int BAR_OFF = BT_OFF + BN * LORA_ROW_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr/abort + alignment slack
@@ -50,8 +50,7 @@ struct GemmCfg {
 struct GemmParams {
   CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
   CUtensorMap tm_w;    // int8 [N, K], box 128 x BN
-  CUtensorMap tm_zhi;  // bf16 [M, 64], box 64 x 128
-  CUtensorMap tm_zlo;
+  CUtensorMap tm_z;    // bf16 [3, M, 64], box 64 x 128 x 3
   CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
   const float* sx;
   const float* sw;
@@ -133,8 +132,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     tma_prefetch_desc(&p.tm_xq);
     tma_prefetch_desc(&p.tm_w);
     if (HAS_LORA) {
-      tma_prefetch_desc(&p.tm_zhi);
-      tma_prefetch_desc(&p.tm_zlo);
+      tma_prefetch_desc(&p.tm_z);
       tma_prefetch_desc(&p.tm_b);
     }
   }
@@ -177,8 +175,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           ok = mbar_wait(lora_empty, (lora_it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
           if (!ok) break;
           mbar_expect_tx(lora_full, Cfg::LORA_BYTES);
-          tma_load_2d(smem + Cfg::ZHI_OFF, &p.tm_zhi, 0, tile.x, lora_full);
-          tma_load_2d(smem + Cfg::ZLO_OFF, &p.tm_zlo, 0, tile.x, lora_full);
+          tma_load_3d(smem + Cfg::Z_OFF, &p.tm_z, 0, tile.x, 0, lora_full);
           tma_load_3d(smem + Cfg::BT_OFF, &p.tm_b, 0, n0, tile.z, lora_full);
           ++lora_it;
         }
@@ -266,13 +263,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           lok = lok && mbar_wait(lora_full, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA);
           if (lok) {
             tc_fence_after_sync();
-            const uint64_t zh = make_desc_sw128(smem_u32(smem + Cfg::ZHI_OFF));
-            const uint64_t zl = make_desc_sw128(smem_u32(smem + Cfg::ZLO_OFF));
             const uint64_t bd = make_desc_sw128(smem_u32(smem + Cfg::BT_OFF));
             const uint32_t d = tmem_base + s * BN;
-            for (int kk = 0; kk < p.rank_blocks; ++kk) {
-              mma_bf16(d, zh + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
-              mma_bf16(d, zl + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+            // smallest plane first, so the low-order terms are not absorbed early
+            for (int plane = 2; plane >= 0; --plane) {
+              const uint64_t zd = make_desc_sw128(smem_u32(smem + Cfg::Z_OFF + plane * Cfg::Z_PLANE_BYTES));
+              for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16(d, zd + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
             }
             mma_commit(lora_empty);
             mma_commit(lora_done);
@@ -441,7 +437,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   if (a.rank < 0 || a.rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "gemm: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a.rank);
   const bool lora = a.rank > 0;
-  if (lora && (a.z_hi == nullptr || a.z_lo == nullptr || a.lora_b_packed == nullptr || a.num_adapters <= 0))
+  if (lora && (a.z_parts == nullptr || !aligned16(a.z_parts) || a.lora_b_packed == nullptr || a.num_adapters <= 0))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: LoRA buffers missing");
   if (lora && a.epilogue == SKYRL_EPI_ACC_I32)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the int32 accumulator output excludes the LoRA term");
@@ -453,7 +449,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: SwiGLU needs N (2*I) to be a multiple of 32, got %d", a.n);
   if (a.out_row_stride < out_cols || a.out_row_stride % 8 != 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output stride must be >= the row length and a multiple of 8");
-  if (a.out == a.xq || a.out == a.wq || a.out == a.z_hi || a.out == a.z_lo)
+  if (a.out == a.xq || a.out == a.wq || a.out == a.z_parts)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output aliases an input");
   if (a.max_tiles <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: max_tiles must be positive");
 
@@ -468,19 +464,15 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   if ((rc = encode_tmap_2d(&p.tm_xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.k, a.m, a.k, BK, BM))) return rc;
   if ((rc = encode_tmap_2d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, a.k, a.n, a.k, BK, bn))) return rc;
   if (lora) {
-    if ((rc = encode_tmap_2d(&p.tm_zhi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_hi, SKYRL_LORA_RANK_PAD, a.m,
-                             LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM)))
-      return rc;
-    if ((rc = encode_tmap_2d(&p.tm_zlo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_lo, SKYRL_LORA_RANK_PAD, a.m,
-                             LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM)))
+    if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, a.m, 3,
+                             LORA_ROW_BYTES, static_cast<uint64_t>(a.m) * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM, 3)))
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
                              SKYRL_LORA_RANK_PAD, bn)))
       return rc;
   } else {
-    p.tm_zhi = p.tm_xq;
-    p.tm_zlo = p.tm_xq;
+    p.tm_z = p.tm_xq;
     p.tm_b = p.tm_xq;
   }
   p.sx = a.sx;

@@ -30,7 +30,8 @@ __all__ = (
     "GroupQuantizedWeight", "PackedW8Weight", "PackedLoRA", "SkyrlKernelError",
     "quantize_frozen_weight", "pack_weight", "pack_lora", "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
-    "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block",
+    "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
+    "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
     "check_status", "RMS_EPS",
 )
 
@@ -302,7 +303,7 @@ def _lora_of(weight: PackedW8Weight, lora_a, lora_b, lora_scaling) -> PackedLoRA
 
 
 def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilogue, *, rms_delta=None, eps=RMS_EPS,
-                residual=None, out=None):
+                residual=None, out=None, timing_events=None):
     lib = _lib.load()
     m = x2.shape[0]
     k, npad = weight.in_features, weight.padded_out_features
@@ -347,6 +348,8 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
     a.workspace = ws.data_ptr()
     a.workspace_bytes = nbytes
     a.status = st.data_ptr()
+    if timing_events is not None:
+        a.timing_events[0], a.timing_events[1] = timing_events[0].cuda_event, timing_events[1].cuda_event
     _lib.check(lib.skyrl_w8a8_lora_forward_sm100_v1(C.byref(a), _stream()), "w8a8_lora_forward")
     return out
 
@@ -379,7 +382,8 @@ def w8a8_frozen_linear(x, weight, *, enabled: bool = False, interpret: bool = Fa
 
 
 def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_ids=None, *, enabled: bool = False,
-                     interpret: bool = False, block_m: int = 128, block_n: int = 256, row_superblock: int = 0):
+                     interpret: bool = False, block_m: int = 128, block_n: int = 256, row_superblock: int = 0,
+                     timing_events=None):
     """y = bf16(dequant(xq wq^T) + s (x A) B) (w8a8_lora.py:870-920).
 
     `lora_a` [K, r] / `lora_b` [r, N] / scalar scaling select one adapter as in
@@ -395,7 +399,7 @@ def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_
     x2 = _check_x(x, k_logical)
     lora = _lora_of(w, lora_a, lora_b, lora_scaling)
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
-    y = _run_linear(x2, w, lora, ids, EPI_LINEAR)
+    y = _run_linear(x2, w, lora, ids, EPI_LINEAR, timing_events=timing_events)
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
@@ -412,7 +416,7 @@ def w8a8_int32_accumulator(x, weight, *, enabled: bool = False):
 
 
 def w8a8_rms_gate_up_lora_swiglu(x, rms_delta, frozen_weight, lora_a, lora_b=None, lora_scaling=None,
-                                 adapter_ids=None, *, enabled: bool = False, eps: float = RMS_EPS):
+                                 adapter_ids=None, *, enabled: bool = False, eps: float = RMS_EPS, timing_events=None):
     """h = swiglu(W8A8-LoRA gate_up(rmsnorm(x))) with interleaved (gate, up)
     columns; never materialises the [M, 2I] projection
     (bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757).  `rms_delta=None`
@@ -428,13 +432,13 @@ def w8a8_rms_gate_up_lora_swiglu(x, rms_delta, frozen_weight, lora_a, lora_b=Non
     lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
     delta = _pad_delta(rms_delta, k_logical, w.in_features) if rms_delta is not None else None
-    h = _run_linear(x2, w, lora, ids, EPI_SWIGLU, rms_delta=delta, eps=eps)
+    h = _run_linear(x2, w, lora, ids, EPI_SWIGLU, rms_delta=delta, eps=eps, timing_events=timing_events)
     inter = w.out_features // 2
     return h[:, :inter].reshape(*x.shape[:-1], inter)
 
 
 def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=None, residual=None,
-                            adapter_ids=None, *, enabled: bool = False):
+                            adapter_ids=None, *, enabled: bool = False, timing_events=None):
     """out = residual + W8A8-LoRA down(x) (bf16_lora_residual.py:507-566)."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
@@ -454,13 +458,14 @@ def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=
         if r2.shape != (x2.shape[0], w.out_features):
             raise ValueError(f"residual must have shape ({x2.shape[0]}, {w.out_features}), got {tuple(r2.shape)}")
         r2 = _pad_cols(r2, w.padded_out_features)
-        y = _run_linear(x2, w, lora, ids, EPI_RESIDUAL, residual=r2)
+        y = _run_linear(x2, w, lora, ids, EPI_RESIDUAL, residual=r2, timing_events=timing_events)
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
 def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: PackedLoRA | None,
                    down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
-                   enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL):
+                   enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
+                   timing_events=None, return_call: bool = False):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only."""
@@ -517,8 +522,28 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     a.workspace = ws.data_ptr()
     a.workspace_bytes = nbytes
     a.status = st.data_ptr()
+    if timing_events is not None:
+        for i, ev in enumerate(timing_events):
+            a.timing_events[i] = ev.cuda_event
     _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
+    if return_call:
+        # keeps the argument block (and through it the workspace layout) for the tensor-parallel finalize
+        return out, (a, x2, delta, ids)
     return out.reshape(*x.shape[:-1], hidden) if out.shape[0] == m else out
+
+
+def w8a8_mlp_tp_finalize(call, reduced: torch.Tensor, out: torch.Tensor, row_begin: int = 0, row_count: int | None = None):
+    """Second half of a row-parallel block: out[perm[i]] = bf16(bf16(reduced[i]) + residual[perm[i]]).
+
+    `call` is the handle returned by `w8a8_mlp_block(..., down_epilogue=EPI_PARTIAL_F32, return_call=True)`;
+    `reduced` is the all-reduced fp32 [M, H] partial-sum buffer in adapter-sorted row order."""
+    a = call[0]
+    lib = _lib.load()
+    if row_count is None:
+        row_count = a.m - row_begin
+    _lib.check(lib.skyrl_w8a8_mlp_tp_finalize_sm100_v1(C.byref(a), _ptr(reduced), _ptr(out), row_begin, row_count,
+                                                     _stream()), "w8a8_mlp_tp_finalize")
+    return out
 
 
 # --------------------------------------------------------------------------- #

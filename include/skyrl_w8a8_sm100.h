@@ -181,6 +181,37 @@ typedef struct SkyrlW8A8LinearArgs {
 SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters);
 SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
 
+/* The same W8A8 LoRA linear for callers that cannot hand over a workspace.
+ * This entry point has no counterpart in the reference.
+ *
+ * Some hosts of this library may not allocate device memory at all at the point
+ * where they call it: an XLA custom-call handler that was not given a scratch
+ * result runs while XLA's allocator owns every byte it planned for the program,
+ * and a serving loop that has handed the whole device to another pool has
+ * nothing left to ask cudaMalloc for.  For them the scratch of the call
+ * (row permutation, tile list, int8 codes, scales, gathered activations and the
+ * LoRA intermediate) lives in a fixed SKYRL_NOALLOC_SCRATCH_BYTES array inside
+ * the library's own device image.  Every GPU on which the library is loaded
+ * holds that array until the process exits.
+ *
+ *  - `args` is the argument block of skyrl_w8a8_lora_forward_sm100_v1; its
+ *    `workspace` and `workspace_bytes` fields are ignored.  Inputs, outputs and
+ *    the status word are still the caller's.
+ *  - A request whose scratch need, skyrl_w8a8_linear_workspace_bytes(m, k,
+ *    num_adapters) (about 3 * m * k bytes), exceeds the array is refused with
+ *    SKYRL_ERR_WORKSPACE and a message naming both sizes; nothing is enqueued.
+ *  - The first call on each device looks the array's device address up (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - The call itself allocates nothing and frees nothing.
+ *  - All calls on a device share the one array, and it keeps what the previous
+ *    call left in it.  Nothing in it has to start at zero (each region is fully
+ *    rewritten before it is read); the tile-count word is cleared on every call
+ *    all the same.  Two calls that overlap on the GPU (different streams, or
+ *    different host threads without ordering between their streams) race on the
+ *    array: order them. */
+#define SKYRL_NOALLOC_SCRATCH_BYTES (32u << 20)
+SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
+
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
  * skyrl/tx/models/qwen3_5.py:786-826; Qwen3MLP, skyrl/tx/models/qwen3.py:100-131). */

@@ -16,6 +16,7 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = PKG / "lib" / "libskyrl_w8a8_sm100.so"
 
 EPI_LINEAR, EPI_SWIGLU, EPI_RESIDUAL, EPI_ACC_I32, EPI_PARTIAL_F32 = 0, 1, 2, 3, 4
+NOALLOC_SCRATCH_BYTES = 32 << 20
 LORA_RANK_PAD = 64
 TILE_ROWS = 128
 
@@ -83,6 +84,7 @@ SYMBOLS = {
     "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "skyrl_w8a8_lora_forward_noalloc_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_mlp_block_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_tp_finalize_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_int32,

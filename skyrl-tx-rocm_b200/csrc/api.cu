@@ -358,3 +358,67 @@ extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, co
   return launch_tp_finalize(reduced, a->adapter_ids != nullptr ? w.perm : nullptr, residual, out, a->hidden, row_begin,
                             row_count, stream);
 }
+
+
+// ---------------------------------------------------------------------------
+// W8A8 LoRA linear without a caller workspace: the scratch is a fixed array in
+// this library's device image.  `g_noalloc_scratch` below is, in host code, only
+// a handle for the symbol; the address kernels can use is looked up once per
+// device with cudaGetSymbolAddress and cached.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SKYRL_NOALLOC_SCRATCH_BYTES];
+
+namespace skyrl {
+
+static int noalloc_scratch(unsigned char** base, size_t* bytes) {
+  static std::mutex mu;
+  static unsigned char* cached[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(SKYRL_ERR_LAUNCH, "noalloc: no current CUDA device (%s)", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // address of the array on the CURRENT device
+    if (e != cudaSuccess || p == nullptr)
+      return fail(SKYRL_ERR_LAUNCH, "noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    cached[dev] = static_cast<unsigned char*>(p);
+  }
+  // the operator carves its scratch on 1024-byte boundaries; the array is only 256-byte aligned
+  const uintptr_t raw = reinterpret_cast<uintptr_t>(cached[dev]);
+  const uintptr_t aligned = (raw + 1023u) & ~static_cast<uintptr_t>(1023u);
+  *base = reinterpret_cast<unsigned char*>(aligned);
+  *bytes = SKYRL_NOALLOC_SCRATCH_BYTES - static_cast<size_t>(aligned - raw);
+  return SKYRL_OK;
+}
+
+}  // namespace skyrl
+
+extern "C" int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs* a, skyrl_stream_t stream_) {
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "noalloc linear: args is null");
+  if (a->struct_size != sizeof(SkyrlW8A8LinearArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "noalloc linear: struct_size %u does not match ABI v%d (%zu)",
+                a->struct_size, SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8LinearArgs));
+  if (a->m <= 0 || a->n <= 0 || a->k <= 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "noalloc linear: non-positive shape");
+  unsigned char* base = nullptr;
+  size_t avail = 0;
+  int rc = noalloc_scratch(&base, &avail);
+  if (rc) return rc;
+  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
+  const LinearWs w = carve_linear(base, a->m, a->k, na);
+  if (w.bytes > avail)
+    return fail(SKYRL_ERR_WORKSPACE,
+                "noalloc linear: m=%d, k=%d needs %zu bytes of scratch, the built-in array holds %zu "
+                "(SKYRL_NOALLOC_SCRATCH_BYTES = %u); use skyrl_w8a8_lora_forward_sm100_v1 with a workspace",
+                a->m, a->k, w.bytes, avail, SKYRL_NOALLOC_SCRATCH_BYTES);
+  // The array keeps the previous call's contents.  Nothing in it is accumulated into, but the
+  // tile count is cleared so that a failed routing pass can never expose a stale count.
+  cudaError_t e = cudaMemsetAsync(w.num_tiles, 0, 4 * sizeof(int32_t), static_cast<cudaStream_t>(stream_));
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "noalloc linear: memset: %s", cudaGetErrorString(e));
+  SkyrlW8A8LinearArgs b = *a;
+  b.workspace = base;
+  b.workspace_bytes = avail;
+  return skyrl_w8a8_lora_forward_sm100_v1(&b, stream_);
+}

@@ -205,9 +205,13 @@ def run_device(args):
             gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * ish, alpha, seed * 131 + rank * 7 + 3, device)
             dn_l = synth_lora(S, torch, wl["adapters"], ish, wl["rank"], hidden, alpha, seed * 131 + rank * 7 + 4, device)
             blocks.append((delta, gu_w, gu_l, dn_w, dn_l))
+        tp_blocks = None
+        if tp > 1:
+            from skyrl_tx_rocm_b200.tp import TensorParallelMLP
+
+            tp_blocks = [TensorParallelMLP(*b) for b in blocks]
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
-        partial = torch.empty((m, hidden), dtype=torch.float32, device=device) if tp > 1 else None
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
         gu_ops_launch = 2.0 * m * hidden * 2 * ish
         dn_ops_launch = 2.0 * m * ish * hidden
@@ -228,10 +232,7 @@ def run_device(args):
                 if tp == 1:
                     S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev)
                 else:
-                    _, call = S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=partial,
-                                               down_epilogue=S.EPI_PARTIAL_F32, timing_events=ev, return_call=True)
-                    dist.all_reduce(partial)
-                    S.w8a8_mlp_tp_finalize(call, partial, dst)
+                    tp_blocks[l].forward(cur, ids_in, out=dst, timing_events=ev)
                 cur = dst
             return cur
     else:

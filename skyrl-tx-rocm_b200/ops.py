@@ -505,6 +505,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     a.rms_eps = float(eps)
     a.x = x2.data_ptr()
     a.rms_delta = delta.data_ptr() if delta is not None else None
+    r2 = None
     if residual is not None:
         r2 = _pad_cols(residual.reshape(-1, residual.shape[-1]), hidden)
         a.residual = r2.data_ptr()
@@ -528,7 +529,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
     if return_call:
         # keeps the argument block (and through it the workspace layout) for the tensor-parallel finalize
-        return out, (a, x2, delta, ids)
+        return out, (a, x2, delta, ids, r2)
     return out.reshape(*x.shape[:-1], hidden) if out.shape[0] == m else out
 
 

@@ -305,6 +305,42 @@ def test_mlp_block(S, m, hidden, inter, rank, na):
     assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
 
 
+@pytest.mark.parametrize("tp", [2, 4])
+def test_tensor_parallel_block_emulated_on_one_gpu(S, tp):
+    # every rank's shard runs in turn on this GPU; the all-reduce is a sum of the fp32 partial buffers
+    from skyrl_tx_rocm_b200 import tp as T
+
+    rng = np.random.default_rng(51)
+    m, hidden, inter, rank, na = 200, 256, 512, 16, 4
+    x, wgu, ga, gb, s, ids = make_case(53, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(59, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    qgu = O.quantize_frozen_weight(wgu, group_size=hidden)
+    total = torch.zeros((m, hidden), dtype=torch.float32, device="cuda")
+    call = None
+    for r in range(tp):
+        codes, scales, gb_r = T.shard_gate_up(qgu.codes, qgu.scales, gb, tp, r)
+        pgu = S.pack_weight(S.GroupQuantizedWeight(to_dev(codes), to_dev(scales), hidden, hidden, 8, hidden))
+        lo, hi = T.shard_bounds(inter, tp, r)
+        qd = O.quantize_frozen_weight(wd[lo:hi], group_size=hi - lo)
+        pd = S.pack_weight(S.GroupQuantizedWeight(to_dev(qd.codes), to_dev(qd.scales), hi - lo, hi - lo, 8, hi - lo))
+        _, da_r = T.shard_down(wd, da, tp, r)
+        lgu = S.pack_lora(to_dev(ga), to_dev(gb_r), to_dev(s), in_features=hidden, padded_out_features=2 * (hi - lo))
+        ld = S.pack_lora(to_dev(da_r), to_dev(db), to_dev(s), in_features=hi - lo, padded_out_features=hidden)
+        block = T.TensorParallelMLP(to_dev(delta), pgu, lgu, pd, ld)
+        xd, idd = to_dev(x), to_dev(ids)
+        part, call = S.w8a8_mlp_block(xd, block.rms_delta, pgu, lgu, pd, ld, idd, enabled=True,
+                                      down_epilogue=S.EPI_PARTIAL_F32, return_call=True)
+        total += part
+    out = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+    S.w8a8_mlp_tp_finalize(call, total, out)
+    S.check_status()
+    want = O.tp_shard_mlp_reference(x, delta, qgu, ga, gb, s, wd, da, db, s, ids, tp)
+    got = to_np(out)
+    assert O.relative_l2(got, want) < 2e-3
+    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
+
+
 # ----------------------------------------------------------------------------- full benchmark sizes, sampled
 def test_config3_accumulator_sampled_tiles(S):
     # Config 3 shape (M=8192, K=4096, 2I=24576): 64 sampled 128x128 tiles of the int32 accumulator

@@ -131,7 +131,7 @@ def synth_weight(S, torch, n, k, seed, device):
         scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
         wq[r0:r1] = torch.clamp(torch.round(w / scale[:, None]), -127, 127).to(torch.int8)
         sw[r0:r1] = scale.to(torch.bfloat16).float()
-    return S.PackedW8Weight(wq, sw, k, n)
+    return S.pack_weight_nk(wq, sw)
 
 
 def synth_lora(S, torch, adapters, k, rank, n, alpha, seed, device):
@@ -222,17 +222,20 @@ def run_device(args):
         h2d = x_host.numel() * 2 + (ids_host.numel() * 4 if ids_host is not None else 0)
         d2h = m * hidden * 2
         out_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
-        launches_per_step = layers * (7 + (2 if tp > 1 else 0))  # route, 2 quant, 2 proj, 2 gemm (+ all-reduce, finalize)
+        # per layer: 2 quantiser, 2 LoRA-A / LoRA-B-rows, 2 GEMM launches (+ finalize under TP); one routing launch per step
+        launches_per_step = layers * (6 + (1 if tp > 1 else 0)) + 1
 
         def step(x_in, ids_in, events=None):
             cur = x_in
             for l, (delta, gu_w, gu_l, dn_w, dn_l) in enumerate(blocks):
                 ev = events[l] if events is not None else None
                 dst = act[l & 1]
+                # adapter ids are the same for every layer of a step: route once, then reuse
                 if tp == 1:
-                    S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev)
+                    S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev,
+                                     reuse_routing=l > 0)
                 else:
-                    tp_blocks[l].forward(cur, ids_in, out=dst, timing_events=ev)
+                    tp_blocks[l].forward(cur, ids_in, out=dst, timing_events=ev, reuse_routing=l > 0)
                 cur = dst
             return cur
     else:
@@ -288,6 +291,25 @@ def run_device(args):
     barrier()
     S.check_status(device)
 
+    # Launch-bound small-batch steps are replayed from a CUDA graph (one capture of the whole step);
+    # the C ABI only enqueues on the current stream, so it is capturable as it stands.
+    use_graph = (m <= 128 and tp == 1) if args.graph == "auto" else (args.graph == "on")
+    graph = None
+    if use_graph:
+        graph_out = [None]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(x_dev, ids)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out[0] = step(x_dev, ids)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
     # ---------------- timed region: inputs resident in HBM ----------------
     step_events = [make_events() for _ in range(args.steps)]
     torch.cuda.synchronize()
@@ -299,12 +321,20 @@ def run_device(args):
     t_end = torch.cuda.Event(enable_timing=True)
     t_begin.record()
     for i in range(args.steps):
-        step(x_dev, ids, step_events[i])
+        if graph is not None:
+            graph.replay()
+        else:
+            step(x_dev, ids, step_events[i])
     t_end.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t_begin.elapsed_time(t_end)
     S.check_status(device)
+    if graph is not None:
+        # per-kernel durations cannot be read from events inside a graph: take them from an eager pass
+        for i in range(args.steps):
+            step(x_dev, ids, step_events[i])
+        torch.cuda.synchronize()
     if dist is not None:
         t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -316,19 +346,28 @@ def run_device(args):
 
     # ---------------- end to end: host buffers, copies inside the timed region ----------------
     e2e_steps = max(2, min(args.steps, 5))
-    for _ in range(2):
-        xd = x_host.to(device, non_blocking=True)
-        idd = ids_host.to(device, non_blocking=True) if ids_host is not None else None
-        out_host.copy_(step(xd, idd), non_blocking=True)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
+
+    def e2e_once():
+        if graph is not None:
+            x_dev.copy_(x_host, non_blocking=True)      # the graph reads these fixed device buffers
+            if ids is not None:
+                ids.copy_(ids_host, non_blocking=True)
+            graph.replay()
+            out_host.copy_(graph_out[0], non_blocking=True)
+            return
         xd = x_host.to(device, non_blocking=True)
         idd = ids_host.to(device, non_blocking=True) if ids_host is not None else None
         if kind == "down":
             res_holder[0] = res_host.to(device, non_blocking=True)
         out_host.copy_(step(xd, idd), non_blocking=True)
+
+    for _ in range(2):
+        e2e_once()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_once()
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
@@ -372,7 +411,7 @@ def run_device(args):
         "data": "synthetic, seeded; random-init weights of the named shapes",
         "config": {"workload": args.workload, "kind": kind, "tokens": m, "layers": layers,
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
-                   "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
+                   "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None, "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -486,6 +525,8 @@ def main():
     ap.add_argument("--m", type=int, default=0, help="override the token count (debugging)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging / small ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
+                    help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -16,10 +16,13 @@
  *
  * Device data layouts
  *   activations ........ bf16 [M, K] row-major
- *   packed weight ...... int8 [N, K] (K contiguous; the reference stores
- *                        [K, N]: skyrl/tx/kernels/quantized_lora.py:20-41; the
- *                        reference's own design asks for a load-time permute to
- *                        a canonical device weight: rocm/QUANTIZED_FFI.md:69-74)
+ *   packed weight ...... int8 [ceil(K / 128), N, 128]: K-block-major, each row 128
+ *                        consecutive K values of one output channel, K zero-padded
+ *                        to the block (the reference stores [K, N]:
+ *                        skyrl/tx/kernels/quantized_lora.py:20-41; its own design asks
+ *                        for a load-time permute to a canonical device weight:
+ *                        rocm/QUANTIZED_FFI.md:69-74).  Any run of output channels of
+ *                        one K block is then one contiguous piece of HBM.
  *   weight scales ...... fp32 [N] (the exact value of the reference's bf16
  *                        per-output scale, group_size == K)
  *   gate_up ............ N = 2*I physical columns, interleaved
@@ -50,6 +53,7 @@ extern "C" {
 #define SKYRL_W8A8_ABI_VERSION 1
 #define SKYRL_LORA_RANK_PAD 64 /* packed LoRA tables hold 64 rank slots            */
 #define SKYRL_TILE_ROWS 128    /* rows of one M tile (one adapter per tile)         */
+#define SKYRL_WEIGHT_KBLOCK 128 /* K values per block of the packed weight layout   */
 
 #define SKYRL_OK 0
 #define SKYRL_ERR_INVALID_ARGUMENT (-1) /* shape / alignment / null / alias violation    */
@@ -73,6 +77,11 @@ SKYRL_API const char* skyrl_w8a8_last_error(void);
 /* ------------------------------------------------------------------------- *
  * Stage kernels
  * ------------------------------------------------------------------------- */
+
+/* Batches of at most SKYRL_TILE_ROWS rows (decode shapes) skip the adapter sort:
+ * the operators keep token order, use one M tile and evaluate the LoRA term row
+ * by row on the CUDA cores (every row carries its own adapter id), so that the
+ * weights are streamed from HBM exactly once however many adapters are in use. */
 
 /* Stable sort of token rows by adapter id and the M-tile list over the sorted
  * row space.  Replaces prepare_routing (skyrl/tx/layers/util.py:66-87: argsort,
@@ -123,7 +132,7 @@ typedef struct SkyrlW8A8GemmArgs {
   int32_t max_tiles;        /* capacity of `tiles`                                     */
   const void* xq;           /* int8 [m, k]                                             */
   const float* sx;          /* fp32 [m]                                                */
-  const void* wq;           /* int8 [n, k] packed                                      */
+  const void* wq;           /* int8 [ceil(k / 128), n, 128] packed                     */
   const float* sw;          /* fp32 [n]                                                */
   const void* z_parts;      /* bf16 [3, m, 64] (hi, mid, lo planes) or NULL when rank == 0 */
   const void* lora_b_packed;/* bf16 [A, n, 64]                                         */
@@ -135,6 +144,10 @@ typedef struct SkyrlW8A8GemmArgs {
   int64_t out_row_stride;   /* elements                                                */
   int64_t residual_row_stride;
   int32_t* status;          /* device int32, non-zero after a bounded wait ran out     */
+  const float* addend;      /* optional fp32 [m, n] (sorted rows) added to the dequantised accumulator
+                               before the epilogue: the row-wise LoRA term of the small-batch path;
+                               requires rank == 0                                       */
+  int64_t addend_row_stride;
 } SkyrlW8A8GemmArgs;
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
@@ -162,7 +175,7 @@ typedef struct SkyrlW8A8LinearArgs {
   const void* rms_delta;     /* bf16 [k] or NULL: RMSNorm(1 + delta) in front of the quantiser */
   float rms_eps;
   int32_t reserved1;
-  const void* wq;            /* int8 [n, k] packed */
+  const void* wq;            /* int8 [ceil(k / 128), n, 128] packed */
   const float* sw;           /* fp32 [n] */
   const void* lora_a_packed; /* bf16 [A, 64, k] */
   const void* lora_b_packed; /* bf16 [A, n, 64] */
@@ -172,13 +185,13 @@ typedef struct SkyrlW8A8LinearArgs {
   int64_t residual_row_stride;
   void* out;
   int64_t out_row_stride;
-  void* workspace;           /* >= skyrl_w8a8_linear_workspace_bytes(m, k), 1024-byte aligned */
+  void* workspace;           /* >= skyrl_w8a8_linear_workspace_bytes(m, n, k, num_adapters), 1024-byte aligned */
   size_t workspace_bytes;
   int32_t* status;           /* device int32, zeroed by the caller */
   void* timing_events[2];    /* optional cudaEvent_t recorded before / after the GEMM kernel */
 } SkyrlW8A8LinearArgs;
 
-SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters);
+SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t num_adapters);
 SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
 
 /* The same W8A8 LoRA linear for callers that cannot hand over a workspace.
@@ -197,8 +210,8 @@ SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, 
  *  - `args` is the argument block of skyrl_w8a8_lora_forward_sm100_v1; its
  *    `workspace` and `workspace_bytes` fields are ignored.  Inputs, outputs and
  *    the status word are still the caller's.
- *  - A request whose scratch need, skyrl_w8a8_linear_workspace_bytes(m, k,
- *    num_adapters) (about 3 * m * k bytes), exceeds the array is refused with
+ *  - A request whose scratch need, skyrl_w8a8_linear_workspace_bytes(m, n, k,
+ *    num_adapters) (about 3 * m * k bytes; m * k + 4 * m * n for m <= 128), exceeds the array is refused with
  *    SKYRL_ERR_WORKSPACE and a message naming both sizes; nothing is enqueued.
  *  - The first call on each device looks the array's device address up (with
  *    that device current).  Make that first call outside any stream capture.
@@ -212,6 +225,11 @@ SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, 
 #define SKYRL_NOALLOC_SCRATCH_BYTES (32u << 20)
 SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
 
+/* flags of SkyrlW8A8MlpArgs */
+#define SKYRL_MLP_REUSE_ROUTING 1u /* the workspace still holds the routing (row permutation, tile list) of an
+                                      earlier call with the same m and adapter_ids: skip the routing kernel.
+                                      Adapter ids do not change between the layers of one forward pass. */
+
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
  * skyrl/tx/models/qwen3_5.py:786-826; Qwen3MLP, skyrl/tx/models/qwen3.py:100-131). */
@@ -224,12 +242,12 @@ typedef struct SkyrlW8A8MlpArgs {
   const void* x;             /* bf16 [m, H] */
   const void* rms_delta;     /* bf16 [H] or NULL */
   const void* residual;      /* bf16 [m, H]; NULL = x */
-  const void* gu_wq;         /* int8 [2I, H] */
+  const void* gu_wq;         /* int8 [ceil(H / 128), 2I, 128] packed */
   const float* gu_sw;        /* fp32 [2I] */
   const void* gu_a_packed;   /* bf16 [A, 64, H] */
   const void* gu_b_packed;   /* bf16 [A, 2I, 64] */
   const float* gu_scaling;
-  const void* dn_wq;         /* int8 [H, I] */
+  const void* dn_wq;         /* int8 [ceil(I / 128), H, 128] packed */
   const float* dn_sw;        /* fp32 [H] */
   const void* dn_a_packed;   /* bf16 [A, 64, I] */
   const void* dn_b_packed;   /* bf16 [A, H, 64] */
@@ -243,6 +261,8 @@ typedef struct SkyrlW8A8MlpArgs {
   int32_t* status;
   void* timing_events[4];    /* optional cudaEvent_t recorded on the stream: before / after the gate_up
                                 GEMM, before / after the down GEMM (NULL = not recorded)             */
+  uint32_t flags;            /* SKYRL_MLP_* */
+  uint32_t reserved;
 } SkyrlW8A8MlpArgs;
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
@@ -261,8 +281,10 @@ SKYRL_API int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* args, 
 /* ------------------------------------------------------------------------- *
  * Pack helpers (load-time, device to device)
  * ------------------------------------------------------------------------- */
-/* int8 [K, N] reference codes -> int8 [N, K] packed (quantized_lora.py:20-41).           */
-SKYRL_API int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_nk, skyrl_stream_t stream);
+/* int8 [K, N] reference codes (quantized_lora.py:20-41) -> packed [ceil(K / 128), N, 128]. */
+SKYRL_API int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_blocked, skyrl_stream_t stream);
+/* int8 [N, K] codes (K contiguous, as checkpoints store [out, in]) -> the same packed layout. */
+SKYRL_API int skyrl_pack_weight_nk_sm100_v1(const void* codes_nk, int32_t n, int32_t k, void* wq_blocked, skyrl_stream_t stream);
 /* bf16 [A, K, r] -> bf16 [A, 64, K] (skyrl/tx/layers/lora.py:259-268).                   */
 SKYRL_API int skyrl_pack_lora_a_sm100_v1(const void* a_akr, int32_t num_adapters, int32_t k, int32_t rank, void* a_packed,
                                skyrl_stream_t stream);

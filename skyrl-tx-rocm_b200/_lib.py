@@ -17,8 +17,10 @@ LIB_PATH = PKG / "lib" / "libskyrl_w8a8_sm100.so"
 
 EPI_LINEAR, EPI_SWIGLU, EPI_RESIDUAL, EPI_ACC_I32, EPI_PARTIAL_F32 = 0, 1, 2, 3, 4
 NOALLOC_SCRATCH_BYTES = 32 << 20
+MLP_REUSE_ROUTING = 1
 LORA_RANK_PAD = 64
 TILE_ROWS = 128
+WEIGHT_KBLOCK = 128
 
 ERROR_NAMES = {
     -1: "invalid argument", -2: "launch failure", -3: "unsupported", -4: "workspace", -5: "driver entry point",
@@ -39,6 +41,7 @@ class GemmArgs(C.Structure):
         ("tiles", C.c_void_p), ("num_tiles", C.c_void_p), ("out_row_map", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
+        ("addend", C.c_void_p), ("addend_row_stride", C.c_int64),
     ]
 
 
@@ -67,6 +70,7 @@ class MlpArgs(C.Structure):
         ("dn_scaling", C.c_void_p),
         ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("timing_events", C.c_void_p * 4),
+        ("flags", C.c_uint32), ("reserved", C.c_uint32),
     ]
 
 
@@ -82,7 +86,7 @@ SYMBOLS = {
                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p]),
     "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
-    "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
+    "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_lora_forward_noalloc_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
@@ -90,6 +94,7 @@ SYMBOLS = {
     "skyrl_w8a8_mlp_tp_finalize_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_int32,
                                                       C.c_int32, C.c_void_p]),
     "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "skyrl_pack_weight_nk_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_a_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_b_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
 }

@@ -99,6 +99,9 @@ struct Carver {
   size_t total() const { return align_up(off, 1024); }
 };
 
+// Batches of at most this many rows take the row-wise LoRA path (no adapter sort, one M tile).
+constexpr int ROWS_PATH_MAX_M = SKYRL_TILE_ROWS;
+
 struct LinearWs {
   int32_t* perm;
   int32_t* tiles;
@@ -106,11 +109,12 @@ struct LinearWs {
   int8_t* xq;
   float* sx;
   uint16_t* xn;
-  uint16_t* z_parts;
+  uint16_t* z_parts;  // bf16 [3, m, 64]; the row-wise path keeps fp32 [m, 64] here instead
+  float* addend;      // fp32 [m, n], row-wise path only
   size_t bytes;
 };
 
-static LinearWs carve_linear(void* ws, int m, int k, int num_adapters) {
+static LinearWs carve_linear(void* ws, int m, int n, int k, int num_adapters) {
   Carver c(ws);
   LinearWs w;
   const int mt = max_tiles_for(m, num_adapters);
@@ -119,8 +123,14 @@ static LinearWs carve_linear(void* ws, int m, int k, int num_adapters) {
   w.num_tiles = c.take<int32_t>(4);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * k);
   w.sx = c.take<float>(m);
-  w.xn = c.take<uint16_t>(static_cast<size_t>(m) * k);
   w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  if (m <= ROWS_PATH_MAX_M) {
+    w.xn = nullptr;
+    w.addend = c.take<float>(static_cast<size_t>(m) * n);
+  } else {
+    w.xn = c.take<uint16_t>(static_cast<size_t>(m) * k);
+    w.addend = nullptr;
+  }
   w.bytes = c.total();
   return w;
 }
@@ -136,6 +146,7 @@ struct MlpWs {
   uint16_t* h;
   int8_t* hq;
   float* sh;
+  float* addend;  // fp32 [m, max(2I, H)], row-wise path only
   size_t bytes;
 };
 
@@ -148,11 +159,18 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   w.num_tiles = c.take<int32_t>(4);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
   w.sx = c.take<float>(m);
-  w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
   w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   w.h = c.take<uint16_t>(static_cast<size_t>(m) * inter);
   w.hq = c.take<int8_t>(static_cast<size_t>(m) * inter);
   w.sh = c.take<float>(m);
+  if (m <= ROWS_PATH_MAX_M) {
+    w.xn = nullptr;
+    const int widest = 2 * inter > hidden ? 2 * inter : hidden;
+    w.addend = c.take<float>(static_cast<size_t>(m) * widest);
+  } else {
+    w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
+    w.addend = nullptr;
+  }
   w.bytes = c.total();
   return w;
 }
@@ -164,6 +182,95 @@ static int check_ws(const void* ws, size_t have, size_t need, const char* who) {
   return SKYRL_OK;
 }
 
+// One W8A8 LoRA projection on rows that are already laid out as the GEMM wants them.
+//   tensor-core route (m > 128): rows adapter-sorted, z planes from lora_a_proj, LoRA inside the GEMM epilogue
+//   row-wise route (m <= 128): rows in token order, z and the LoRA addend from the row kernels
+struct Projection {
+  const void* x;          // bf16 [m, k] source rows
+  int64_t x_stride;
+  const void* rms_delta;  // nullable
+  float eps;
+  const int32_t* gather;  // row gather for the quantiser (sorted route) or NULL
+  bool keep_xn;           // sorted route: x must be re-laid out (gathered / normalised) for the projection MMA
+  int m, n, k, rank, na, mt;
+  const void* wq;
+  const float* sw;
+  const void* a_packed;
+  const void* b_packed;
+  const float* scaling;
+  const int32_t* ids;     // token-order adapter ids (row-wise route)
+  int8_t* xq;
+  float* sx;
+  uint16_t* xn;
+  uint16_t* z_parts;
+  float* addend;
+  const int32_t* tiles;
+  const int32_t* num_tiles;
+  int epilogue;
+  const int32_t* out_row_map;
+  const void* residual;
+  int64_t residual_stride;
+  void* out;
+  int64_t out_stride;
+  int32_t* status;
+  void* ev_begin;
+  void* ev_end;
+};
+
+static int run_projection(const Projection& q, cudaStream_t stream) {
+  const bool lora = q.rank > 0;
+  const bool rows_path = q.m <= ROWS_PATH_MAX_M;
+  int rc;
+  SkyrlW8A8GemmArgs g = {};
+  if (rows_path && lora) {
+    float* z_rows = reinterpret_cast<float*>(q.z_parts);
+    if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.a_packed, q.scaling, q.rank, q.m, q.k,
+                                    q.xq, q.sx, z_rows, stream)))
+      return rc;
+    if ((rc = launch_lora_b_rows(z_rows, q.ids, q.b_packed, q.rank, q.m, q.n, q.addend, q.n, stream))) return rc;
+    g.rank = 0;
+    g.addend = q.addend;
+    g.addend_row_stride = q.n;
+  } else {
+    const bool need_xn = lora && q.keep_xn;
+    if ((rc = launch_rms_quant(q.x, q.x_stride, q.rms_delta, q.eps, q.gather, q.m, q.k, q.xq, q.sx,
+                               need_xn ? q.xn : nullptr, stream)))
+      return rc;
+    if (lora) {
+      const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
+      if ((rc = launch_lora_a_proj(xa, q.m, q.k, q.a_packed, q.scaling, q.na, q.rank, q.tiles, q.num_tiles, q.mt,
+                                   q.z_parts, q.status, stream)))
+        return rc;
+    }
+    g.rank = q.rank;
+    g.z_parts = lora ? q.z_parts : nullptr;
+  }
+  g.struct_size = sizeof(g);
+  g.epilogue = q.epilogue;
+  g.m = q.m;
+  g.n = q.n;
+  g.k = q.k;
+  g.num_adapters = q.na;
+  g.max_tiles = q.mt;
+  g.xq = q.xq;
+  g.sx = q.sx;
+  g.wq = q.wq;
+  g.sw = q.sw;
+  g.lora_b_packed = q.b_packed;
+  g.tiles = q.tiles;
+  g.num_tiles = q.num_tiles;
+  g.out_row_map = q.out_row_map;
+  g.residual = q.residual;
+  g.out = q.out;
+  g.out_row_stride = q.out_stride;
+  g.residual_row_stride = q.residual_stride;
+  g.status = q.status;
+  if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
+  rc = launch_gemm(g, stream);
+  if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
+  return rc;
+}
+
 }  // namespace skyrl
 
 using namespace skyrl;
@@ -171,9 +278,9 @@ using namespace skyrl;
 extern "C" int skyrl_w8a8_abi_version(void) { return SKYRL_W8A8_ABI_VERSION; }
 extern "C" const char* skyrl_w8a8_last_error(void) { return g_last_error; }
 
-extern "C" size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t k, int32_t num_adapters) {
-  if (m <= 0 || k <= 0) return 0;
-  return carve_linear(nullptr, m, k, num_adapters).bytes;
+extern "C" size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t num_adapters) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return carve_linear(nullptr, m, n, k, num_adapters).bytes;
 }
 
 extern "C" size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters) {
@@ -199,50 +306,52 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   if (a->adapter_ids != nullptr && a->num_adapters <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "linear: adapter ids given without adapters");
   const int na = a->num_adapters > 0 ? a->num_adapters : 1;
-  const LinearWs w = carve_linear(a->workspace, a->m, a->k, na);
+  const LinearWs w = carve_linear(a->workspace, a->m, a->n, a->k, na);
   int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "linear");
   if (rc) return rc;
   const int mt = max_tiles_for(a->m, na);
-  const bool routed = a->adapter_ids != nullptr;
+  const bool rows_path = a->m <= ROWS_PATH_MAX_M;
+  const bool routed = a->adapter_ids != nullptr && !rows_path;
 
-  if ((rc = launch_route(a->adapter_ids, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status, stream))) return rc;
-  const bool need_xn = lora && (routed || a->rms_delta != nullptr || a->x_row_stride != a->k);
-  if ((rc = launch_rms_quant(a->x, a->x_row_stride, a->rms_delta, a->rms_eps, routed ? w.perm : nullptr, a->m, a->k,
-                             w.xq, w.sx, need_xn ? w.xn : nullptr, stream)))
+  if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status,
+                         stream)))
     return rc;
-  if (lora) {
-    const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
-    if ((rc = launch_lora_a_proj(xa, a->m, a->k, a->lora_a_packed, a->lora_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_parts, a->status, stream)))
-      return rc;
-  }
-  SkyrlW8A8GemmArgs g;
-  g.struct_size = sizeof(g);
-  g.epilogue = a->epilogue;
-  g.m = a->m;
-  g.n = a->n;
-  g.k = a->k;
-  g.rank = a->rank;
-  g.num_adapters = na;
-  g.max_tiles = mt;
-  g.xq = w.xq;
-  g.sx = w.sx;
-  g.wq = a->wq;
-  g.sw = a->sw;
-  g.z_parts = lora ? w.z_parts : nullptr;
-  g.lora_b_packed = a->lora_b_packed;
-  g.tiles = w.tiles;
-  g.num_tiles = w.num_tiles;
-  g.out_row_map = routed ? w.perm : nullptr;
-  g.residual = a->residual;
-  g.out = a->out;
-  g.out_row_stride = a->out_row_stride;
-  g.residual_row_stride = a->residual_row_stride;
-  g.status = a->status;
-  if (a->timing_events[0] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[0]), stream);
-  rc = launch_gemm(g, stream);
-  if (a->timing_events[1] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[1]), stream);
-  return rc;
+  Projection q = {};
+  q.x = a->x;
+  q.x_stride = a->x_row_stride;
+  q.rms_delta = a->rms_delta;
+  q.eps = a->rms_eps;
+  q.gather = routed ? w.perm : nullptr;
+  q.keep_xn = routed || a->rms_delta != nullptr || a->x_row_stride != a->k;
+  q.m = a->m;
+  q.n = a->n;
+  q.k = a->k;
+  q.rank = a->rank;
+  q.na = na;
+  q.mt = mt;
+  q.wq = a->wq;
+  q.sw = a->sw;
+  q.a_packed = a->lora_a_packed;
+  q.b_packed = a->lora_b_packed;
+  q.scaling = a->lora_scaling;
+  q.ids = a->adapter_ids;
+  q.xq = w.xq;
+  q.sx = w.sx;
+  q.xn = w.xn;
+  q.z_parts = w.z_parts;
+  q.addend = w.addend;
+  q.tiles = w.tiles;
+  q.num_tiles = w.num_tiles;
+  q.epilogue = a->epilogue;
+  q.out_row_map = routed ? w.perm : nullptr;
+  q.residual = a->residual;
+  q.residual_stride = a->residual_row_stride;
+  q.out = a->out;
+  q.out_stride = a->out_row_stride;
+  q.status = a->status;
+  q.ev_begin = a->timing_events[0];
+  q.ev_end = a->timing_events[1];
+  return run_projection(q, stream);
 }
 
 extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_stream_t stream_) {
@@ -270,74 +379,76 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "mlp");
   if (rc) return rc;
   const int mt = max_tiles_for(a->m, na);
-  const bool routed = a->adapter_ids != nullptr;
+  const bool rows_path = a->m <= ROWS_PATH_MAX_M;
+  const bool routed = a->adapter_ids != nullptr && !rows_path;
   const int32_t* perm = routed ? w.perm : nullptr;
 
-  if ((rc = launch_route(a->adapter_ids, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status, stream))) return rc;
-
-  // front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU, h stays in sorted row order
-  const bool need_xn = lora && (routed || a->rms_delta != nullptr);
-  if ((rc = launch_rms_quant(a->x, a->hidden, a->rms_delta, a->rms_eps, perm, a->m, a->hidden, w.xq, w.sx,
-                             need_xn ? w.xn : nullptr, stream)))
-    return rc;
-  if (lora) {
-    const void* xa = need_xn ? static_cast<const void*>(w.xn) : a->x;
-    if ((rc = launch_lora_a_proj(xa, a->m, a->hidden, a->gu_a_packed, a->gu_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_parts, a->status, stream)))
+  if ((a->flags & SKYRL_MLP_REUSE_ROUTING) == 0) {
+    if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status,
+                           stream)))
       return rc;
   }
-  SkyrlW8A8GemmArgs g;
-  g.struct_size = sizeof(g);
-  g.epilogue = SKYRL_EPI_SWIGLU;
-  g.m = a->m;
-  g.n = 2 * a->inter;
-  g.k = a->hidden;
-  g.rank = a->rank;
-  g.num_adapters = na;
-  g.max_tiles = mt;
-  g.xq = w.xq;
-  g.sx = w.sx;
-  g.wq = a->gu_wq;
-  g.sw = a->gu_sw;
-  g.z_parts = lora ? w.z_parts : nullptr;
-  g.lora_b_packed = a->gu_b_packed;
-  g.tiles = w.tiles;
-  g.num_tiles = w.num_tiles;
-  g.out_row_map = nullptr;
-  g.residual = nullptr;
-  g.out = w.h;
-  g.out_row_stride = a->inter;
-  g.residual_row_stride = 0;
-  g.status = a->status;
-  if (a->timing_events[0] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[0]), stream);
-  if ((rc = launch_gemm(g, stream))) return rc;
-  if (a->timing_events[1] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[1]), stream);
+
+  // front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU; h keeps the row order of the GEMM
+  Projection q = {};
+  q.x = a->x;
+  q.x_stride = a->hidden;
+  q.rms_delta = a->rms_delta;
+  q.eps = a->rms_eps;
+  q.gather = perm;
+  q.keep_xn = routed || a->rms_delta != nullptr;
+  q.m = a->m;
+  q.n = 2 * a->inter;
+  q.k = a->hidden;
+  q.rank = a->rank;
+  q.na = na;
+  q.mt = mt;
+  q.wq = a->gu_wq;
+  q.sw = a->gu_sw;
+  q.a_packed = a->gu_a_packed;
+  q.b_packed = a->gu_b_packed;
+  q.scaling = a->gu_scaling;
+  q.ids = a->adapter_ids;
+  q.xq = w.xq;
+  q.sx = w.sx;
+  q.xn = w.xn;
+  q.z_parts = w.z_parts;
+  q.addend = w.addend;
+  q.tiles = w.tiles;
+  q.num_tiles = w.num_tiles;
+  q.epilogue = SKYRL_EPI_SWIGLU;
+  q.out_row_map = nullptr;
+  q.out = w.h;
+  q.out_stride = a->inter;
+  q.status = a->status;
+  q.ev_begin = a->timing_events[0];
+  q.ev_end = a->timing_events[1];
+  if ((rc = run_projection(q, stream))) return rc;
 
   // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
-  if ((rc = launch_rms_quant(w.h, a->inter, nullptr, 0.f, nullptr, a->m, a->inter, w.hq, w.sh, nullptr, stream)))
-    return rc;
-  if (lora) {
-    if ((rc = launch_lora_a_proj(w.h, a->m, a->inter, a->dn_a_packed, a->dn_scaling, na, a->rank, w.tiles, w.num_tiles,
-                                 mt, w.z_parts, a->status, stream)))
-      return rc;
-  }
-  g.epilogue = a->down_epilogue;
-  g.n = a->hidden;
-  g.k = a->inter;
-  g.xq = w.hq;
-  g.sx = w.sh;
-  g.wq = a->dn_wq;
-  g.sw = a->dn_sw;
-  g.lora_b_packed = a->dn_b_packed;
-  g.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : perm;
-  g.residual = a->residual != nullptr ? a->residual : a->x;
-  g.out = a->out;
-  g.out_row_stride = a->hidden;
-  g.residual_row_stride = a->hidden;
-  if (a->timing_events[2] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[2]), stream);
-  rc = launch_gemm(g, stream);
-  if (a->timing_events[3] != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(a->timing_events[3]), stream);
-  return rc;
+  q.x = w.h;
+  q.x_stride = a->inter;
+  q.rms_delta = nullptr;
+  q.gather = nullptr;
+  q.keep_xn = false;
+  q.n = a->hidden;
+  q.k = a->inter;
+  q.wq = a->dn_wq;
+  q.sw = a->dn_sw;
+  q.a_packed = a->dn_a_packed;
+  q.b_packed = a->dn_b_packed;
+  q.scaling = a->dn_scaling;
+  q.xq = w.hq;
+  q.sx = w.sh;
+  q.epilogue = a->down_epilogue;
+  q.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : perm;
+  q.residual = a->residual != nullptr ? a->residual : a->x;
+  q.residual_stride = a->hidden;
+  q.out = a->out;
+  q.out_stride = a->hidden;
+  q.ev_begin = a->timing_events[2];
+  q.ev_end = a->timing_events[3];
+  return run_projection(q, stream);
 }
 
 extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, const float* reduced, void* out,
@@ -355,10 +466,9 @@ extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, co
   int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "tp_finalize");
   if (rc) return rc;
   const void* residual = a->residual != nullptr ? a->residual : a->x;
-  return launch_tp_finalize(reduced, a->adapter_ids != nullptr ? w.perm : nullptr, residual, out, a->hidden, row_begin,
-                            row_count, stream);
+  const bool routed = a->adapter_ids != nullptr && a->m > ROWS_PATH_MAX_M;
+  return launch_tp_finalize(reduced, routed ? w.perm : nullptr, residual, out, a->hidden, row_begin, row_count, stream);
 }
-
 
 // ---------------------------------------------------------------------------
 // W8A8 LoRA linear without a caller workspace: the scratch is a fixed array in
@@ -407,12 +517,12 @@ extern "C" int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArg
   int rc = noalloc_scratch(&base, &avail);
   if (rc) return rc;
   const int na = a->num_adapters > 0 ? a->num_adapters : 1;
-  const LinearWs w = carve_linear(base, a->m, a->k, na);
+  const LinearWs w = carve_linear(base, a->m, a->n, a->k, na);
   if (w.bytes > avail)
     return fail(SKYRL_ERR_WORKSPACE,
-                "noalloc linear: m=%d, k=%d needs %zu bytes of scratch, the built-in array holds %zu "
+                "noalloc linear: m=%d, n=%d, k=%d needs %zu bytes of scratch, the built-in array holds %zu "
                 "(SKYRL_NOALLOC_SCRATCH_BYTES = %u); use skyrl_w8a8_lora_forward_sm100_v1 with a workspace",
-                a->m, a->k, w.bytes, avail, SKYRL_NOALLOC_SCRATCH_BYTES);
+                a->m, a->n, a->k, w.bytes, avail, SKYRL_NOALLOC_SCRATCH_BYTES);
   // The array keeps the previous call's contents.  Nothing in it is accumulated into, but the
   // tile count is cleared so that a failed routing pass can never expose a stale count.
   cudaError_t e = cudaMemsetAsync(w.num_tiles, 0, 4 * sizeof(int32_t), static_cast<cudaStream_t>(stream_));

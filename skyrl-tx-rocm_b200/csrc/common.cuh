@@ -34,6 +34,11 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream);
 int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream);
+int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
+                          const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
+                          float* z_rows, cudaStream_t stream);
+int launch_lora_b_rows(const float* z_rows, const int32_t* ids, const void* b_packed, int rank, int m, int n,
+                       float* addend, int64_t addend_stride, cudaStream_t stream);
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
                        int row_begin, int row_count, cudaStream_t stream);
 

@@ -299,6 +299,42 @@ __global__ void transpose_kernel(const T* __restrict__ in, T* __restrict__ out, 
   }
 }
 
+// Weight codes in the K-block-major device layout [ceil(K / 128), N, 128]: for one 128-byte block of K
+// the rows of all output channels lie back to back, so the TMA box of ANY run of output channels is
+// one contiguous piece of HBM (K zero-padded to the block).
+__global__ void pack_weight_kn_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int k, int n) {
+  // in [K, N] (reference layout) -> out[kb][n][kk] = in[kb * 128 + kk][n]
+  __shared__ int8_t tile[32][33];
+  const int kb = blockIdx.z;
+  const int n0 = blockIdx.x * 32, kk0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int kg = kb * SKYRL_WEIGHT_KBLOCK + kk0 + j, nn = n0 + threadIdx.x;
+    tile[j][threadIdx.x] = (kg < k && nn < n) ? in[static_cast<int64_t>(kg) * n + nn] : int8_t(0);
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int nn = n0 + j, kk = kk0 + threadIdx.x;
+    if (nn < n) out[(static_cast<int64_t>(kb) * n + nn) * SKYRL_WEIGHT_KBLOCK + kk] = tile[threadIdx.x][j];
+  }
+}
+
+__global__ void pack_weight_nk_kernel(const int8_t* __restrict__ in, int8_t* __restrict__ out, int n, int k,
+                                      int64_t vecs) {
+  // in [N, K] (K contiguous) -> out[kb][n][kk]; 16-byte vectors
+  const int vpb = SKYRL_WEIGHT_KBLOCK / 16;
+  for (int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; v < vecs;
+       v += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int q = static_cast<int>(v % vpb);
+    const int64_t row = v / vpb;  // kb * n + nn
+    const int nn = static_cast<int>(row % n);
+    const int kb = static_cast<int>(row / n);
+    const int kg = kb * SKYRL_WEIGHT_KBLOCK + q * 16;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (kg < k) val = __ldg(reinterpret_cast<const uint4*>(in + static_cast<int64_t>(nn) * k + kg));
+    reinterpret_cast<uint4*>(out)[v] = val;
+  }
+}
+
 template <typename T>
 static int run_transpose(const T* in, T* out, int batch, int rows, int cols, int64_t out_batch, int out_pitch,
                          size_t out_bytes, cudaStream_t stream) {
@@ -317,14 +353,38 @@ static int run_transpose(const T* in, T* out, int batch, int rows, int cols, int
 
 using namespace skyrl;
 
-extern "C" int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_nk,
-                                             skyrl_stream_t stream) {
-  if (codes_kn == nullptr || wq_nk == nullptr || k <= 0 || n <= 0 || codes_kn == wq_nk)
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_weight: null/aliased buffer or non-positive shape");
-  // rows = K, cols = N  ->  out [N, K]
-  return run_transpose<int8_t>(static_cast<const int8_t*>(codes_kn), static_cast<int8_t*>(wq_nk), 1, k, n,
-                               static_cast<int64_t>(n) * k, k, static_cast<size_t>(n) * k,
-                               static_cast<cudaStream_t>(stream));
+extern "C" int skyrl_pack_weight_kn_sm100_v1(const void* codes_kn, int32_t k, int32_t n, void* wq_blocked,
+                                             skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (codes_kn == nullptr || wq_blocked == nullptr || k <= 0 || n <= 0 || codes_kn == wq_blocked)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_weight_kn: null/aliased buffer or non-positive shape");
+  const int kb = (k + SKYRL_WEIGHT_KBLOCK - 1) / SKYRL_WEIGHT_KBLOCK;
+  cudaError_t e = cudaMemsetAsync(wq_blocked, 0, static_cast<size_t>(kb) * n * SKYRL_WEIGHT_KBLOCK, stream);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "pack memset: %s", cudaGetErrorString(e));
+  dim3 grid((n + 31) / 32, SKYRL_WEIGHT_KBLOCK / 32, kb), block(32, 8);
+  if (grid.z > 65535) return fail(SKYRL_ERR_UNSUPPORTED, "pack_weight_kn: K exceeds the launch grid");
+  pack_weight_kn_kernel<<<grid, block, 0, stream>>>(static_cast<const int8_t*>(codes_kn), static_cast<int8_t*>(wq_blocked),
+                                                     k, n);
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "pack_weight_kn launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+extern "C" int skyrl_pack_weight_nk_sm100_v1(const void* codes_nk, int32_t n, int32_t k, void* wq_blocked,
+                                             skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (codes_nk == nullptr || wq_blocked == nullptr || k <= 0 || n <= 0 || codes_nk == wq_blocked)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_weight_nk: null/aliased buffer or non-positive shape");
+  if (k % 16 != 0 || !aligned16(codes_nk) || !aligned16(wq_blocked))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_weight_nk: K must be a multiple of 16 and buffers 16-byte aligned");
+  const int kb = (k + SKYRL_WEIGHT_KBLOCK - 1) / SKYRL_WEIGHT_KBLOCK;
+  const int64_t vecs = static_cast<int64_t>(kb) * n * (SKYRL_WEIGHT_KBLOCK / 16);
+  const int blocks = static_cast<int>((vecs + 255) / 256 < 148 * 32 ? (vecs + 255) / 256 : 148 * 32);
+  pack_weight_nk_kernel<<<blocks, 256, 0, stream>>>(static_cast<const int8_t*>(codes_nk),
+                                                    static_cast<int8_t*>(wq_blocked), n, k, vecs);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "pack_weight_nk launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
 }
 
 extern "C" int skyrl_pack_lora_a_sm100_v1(const void* a_akr, int32_t num_adapters, int32_t k, int32_t rank,

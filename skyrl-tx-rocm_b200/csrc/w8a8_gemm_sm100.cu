@@ -42,14 +42,15 @@ struct GemmCfg {
   static constexpr int BT_OFF = Z_OFF + 3 * Z_PLANE_BYTES;
   static constexpr int LORA_BYTES = 3 * Z_PLANE_BYTES + BN * LORA_ROW_BYTES;
   static constexpr int BAR_OFF = BT_OFF + BN * LORA_ROW_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4 + 4;
+  static constexpr int MAX_STAGES = 12;  // the LoRA-free variants reuse the LoRA operand space for extra stages
+  static constexpr int NUM_BARS = 2 * MAX_STAGES + 4 + 4;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr/abort + alignment slack
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
 struct GemmParams {
   CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
-  CUtensorMap tm_w;    // int8 [N, K], box 128 x BN
+  CUtensorMap tm_w;    // int8 [K / 128, N, 128], box 128 x bn_eff x 1
   CUtensorMap tm_z;    // bf16 [3, M, 64], box 64 x 128 x 3
   CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
   const float* sx;
@@ -63,8 +64,13 @@ struct GemmParams {
   int64_t res_stride;
   int32_t* status;
   int m, n, k;
-  int rank_blocks;  // ceil(rank / 16) MMAs per z half
+  int rank_blocks;  // ceil(rank / 16) MMAs per z plane
   int band;         // M tiles per raster band
+  int bn_eff;       // columns per N tile actually used (multiple of 16, <= BN): MMA N, TMA box rows
+  int num_stages;   // pipeline depth and byte pitch of one stage (A tile + bn_eff weight rows)
+  int stage_bytes;
+  const float* addend;     // optional fp32 [M, N] added to the dequantised accumulator (row-wise LoRA term)
+  int64_t addend_stride;
 };
 
 struct TileCoord {
@@ -95,8 +101,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + Cfg::STAGES;
-  uint64_t* tmem_full = bars + 2 * Cfg::STAGES;       // [2]
+  uint64_t* empty_bar = bars + Cfg::MAX_STAGES;
+  uint64_t* tmem_full = bars + 2 * Cfg::MAX_STAGES;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;               // [2]
   uint64_t* lora_full = tmem_empty + 2;               // TMA -> LoRA operands landed
   uint64_t* lora_empty = lora_full + 1;               // LoRA MMAs done reading smem
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) {
+    for (int s = 0; s < Cfg::MAX_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -142,8 +148,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   const int tm = *p.num_tiles;
-  const int tn = (p.n + BN - 1) / BN;
+  const int bn_eff = p.bn_eff;
+  const int tn = (p.n + bn_eff - 1) / bn_eff;
   const int total = tm * tn;
+  const uint32_t stage_tx = Cfg::A_BYTES + bn_eff * BK;
+  const int nstages = p.num_stages;
+  const int stage_bytes = p.stage_bytes;
+  const uint32_t lora_tx = 3 * Cfg::Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES;
   const int kblocks = (p.k + BK - 1) / BK;
   const int band = min(p.band, max(tm, 1));
 
@@ -156,15 +167,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         const TileCoord c = tile_coord(t, tm, tn, band);
         const int4 tile = __ldg(p.tiles + c.m_idx);
-        const int n0 = c.n_idx * BN;
+        const int n0 = c.n_idx * bn_eff;
         for (int kb = 0; kb < kblocks; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
           if (!ok) break;
-          unsigned char* sa = smem + stage * Cfg::STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          unsigned char* sa = smem + stage * stage_bytes;
+          mbar_expect_tx(&full_bar[stage], stage_tx);
           tma_load_2d(sa, &p.tm_xq, kb * BK, tile.x, &full_bar[stage]);
-          tma_load_2d(sa + Cfg::A_BYTES, &p.tm_w, kb * BK, n0, &full_bar[stage]);
-          if (++stage == Cfg::STAGES) {
+          tma_load_3d(sa + Cfg::A_BYTES, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+          if (++stage == nstages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           // previous tile's LoRA MMAs never delays the weight stream.
           ok = mbar_wait(lora_empty, (lora_it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
           if (!ok) break;
-          mbar_expect_tx(lora_full, Cfg::LORA_BYTES);
+          mbar_expect_tx(lora_full, lora_tx);
           tma_load_3d(smem + Cfg::Z_OFF, &p.tm_z, 0, tile.x, 0, lora_full);
           tma_load_3d(smem + Cfg::BT_OFF, &p.tm_b, 0, n0, tile.z, lora_full);
           ++lora_it;
@@ -184,7 +195,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   } else if (warp == 5) {
     // ------------------------------ int8 MMA issuer ---------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, BM, BN);
+      const uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, BM, bn_eff);
       int stage = 0;
       uint32_t phase = 0, it = 0;
       bool ok = true;
@@ -198,7 +209,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           const uint64_t adesc = make_desc_sw128(sa);
           const uint64_t bdesc = make_desc_sw128(sa + Cfg::A_BYTES);
 #pragma unroll
@@ -206,7 +217,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             mma_i8(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
           }
           mma_commit(&empty_bar[stage]);
-          if (++stage == Cfg::STAGES) {
+          if (++stage == nstages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -216,14 +227,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     }
   } else {
     // ------------------------------ epilogue warps 0-3 -------------------------
-    constexpr uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, BN);
+    const uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, bn_eff);
+    const int nchunks = (bn_eff + 31) / 32;
     const int r = warp * 32 + lane;  // row of the tile == TMEM lane
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
       const TileCoord c = tile_coord(t, tm, tn, band);
       const int4 tile = __ldg(p.tiles + c.m_idx);
-      const int n0 = c.n_idx * BN;
+      const int n0 = c.n_idx * bn_eff;
+      const int n_end = min(p.n, n0 + bn_eff);  // first column this tile does not own
       const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
       const bool row_valid = r < tile.y;
       const int srow = tile.x + r;
@@ -238,7 +251,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       if (HAS_LORA) {
         // pass 1: int32 accumulator -> dequantised fp32, in place
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 32; ++cc) {
+        for (int cc = 0; cc < nchunks; ++cc) {
           uint32_t v[32];
           __syncwarp();
           tmem_ld32(tbase + cc * 32, v);
@@ -247,7 +260,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (nc + g * 4 < p.n) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
+            if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
             v[4 * g + 0] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x));
             v[4 * g + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y));
             v[4 * g + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z));
@@ -283,7 +296,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 
       // pass 2: final values -> global memory
 #pragma unroll 1
-      for (int cc = 0; cc < BN / 32; ++cc) {
+      for (int cc = 0; cc < nchunks; ++cc) {
         uint32_t v[32];
         __syncwarp();
         tmem_ld32(tbase + cc * 32, v);
@@ -294,7 +307,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + orow * p.out_stride + nc);
 #pragma unroll
             for (int g = 0; g < 8; ++g)
-              if (nc + g * 4 < p.n) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+              if (nc + g * 4 < n_end) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
           }
           continue;
         }
@@ -306,11 +319,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (nc + g * 4 < p.n) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
+            if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
             f[4 * g + 0] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x);
             f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
             f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
             f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
+          }
+          if (p.addend != nullptr && row_valid) {
+            const float4* ad = reinterpret_cast<const float4*>(p.addend + static_cast<int64_t>(srow) * p.addend_stride + nc);
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (nc + g * 4 < n_end) {
+                const float4 t4 = __ldg(ad + g);
+                f[4 * g + 0] = __fadd_rn(f[4 * g + 0], t4.x);
+                f[4 * g + 1] = __fadd_rn(f[4 * g + 1], t4.y);
+                f[4 * g + 2] = __fadd_rn(f[4 * g + 2], t4.z);
+                f[4 * g + 3] = __fadd_rn(f[4 * g + 3], t4.w);
+              }
+            }
           }
         }
         if (!row_valid) continue;
@@ -318,12 +344,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
 #pragma unroll
           for (int g = 0; g < 8; ++g)
-            if (nc + g * 4 < p.n) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+            if (nc + g * 4 < n_end) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
         } else if (EPI == SKYRL_EPI_LINEAR) {
           uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
 #pragma unroll
           for (int g = 0; g < 4; ++g)
-            if (nc + g * 8 < p.n)
+            if (nc + g * 8 < n_end)
               dst[g] = make_uint4(pack_bf16x2(f[8 * g], f[8 * g + 1]), pack_bf16x2(f[8 * g + 2], f[8 * g + 3]),
                                   pack_bf16x2(f[8 * g + 4], f[8 * g + 5]), pack_bf16x2(f[8 * g + 6], f[8 * g + 7]));
         } else if (EPI == SKYRL_EPI_RESIDUAL) {
@@ -331,7 +357,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           const uint4* res = reinterpret_cast<const uint4*>(p.residual + orow * p.res_stride + nc);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            if (nc + g * 8 < p.n) {
+            if (nc + g * 8 < n_end) {
               const uint4 rv = __ldg(res + g);
               const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
               uint32_t o[4];
@@ -350,7 +376,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
               reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + (nc >> 1));
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
-            if (nc + g * 16 < p.n) {
+            if (nc + g * 16 < n_end) {
               uint32_t o[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -453,23 +479,36 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output aliases an input");
   if (a.max_tiles <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: max_tiles must be positive");
 
-  // Narrow tiles when wide ones would leave SMs idle.
+  // 256-wide N tiles when they fill the GPU; otherwise one wave of narrower tiles sized so that
+  // every SM streams an equal share of the weight (the decode shapes are HBM-bound).
   const int sms = sm_count();
   if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
-  const int64_t tiles256 = static_cast<int64_t>(a.max_tiles) * ((a.n + 255) / 256);
-  const int bn = (tiles256 >= sms) ? 256 : 128;
+  const int mt_est = (a.m + BM - 1) / BM;
+  const int64_t tiles256 = static_cast<int64_t>(mt_est) * ((a.n + 255) / 256);
+  int bn_eff = 256;
+  if (tiles256 < sms) {
+    const int per_mtile = sms / mt_est > 0 ? sms / mt_est : 1;
+    bn_eff = ((a.n + per_mtile - 1) / per_mtile + 15) / 16 * 16;
+    if (bn_eff < 16) bn_eff = 16;
+    if (bn_eff > 256) bn_eff = 256;
+  }
+  const int bn = bn_eff > 128 ? 256 : 128;
+  if (a.addend != nullptr && (lora || !aligned16(a.addend) || a.addend_row_stride < a.n || a.addend_row_stride % 4 != 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: addend excludes the tensor-core LoRA term and needs an aligned [M, N] fp32 buffer");
 
   GemmParams p;
   int rc;
   if ((rc = encode_tmap_2d(&p.tm_xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.k, a.m, a.k, BK, BM))) return rc;
-  if ((rc = encode_tmap_2d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, a.k, a.n, a.k, BK, bn))) return rc;
+  if ((rc = encode_tmap_3d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, BK, a.n, (a.k + BK - 1) / BK, BK,
+                           static_cast<uint64_t>(a.n) * BK, BK, bn_eff)))
+    return rc;
   if (lora) {
     if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, a.m, 3,
                              LORA_ROW_BYTES, static_cast<uint64_t>(a.m) * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM, 3)))
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
-                             SKYRL_LORA_RANK_PAD, bn)))
+                             SKYRL_LORA_RANK_PAD, bn_eff)))
       return rc;
   } else {
     p.tm_z = p.tm_xq;
@@ -490,7 +529,21 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   p.k = a.k;
   p.rank_blocks = (a.rank + 15) / 16;
   p.band = 16;
-  const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn - 1) / bn);
+  p.bn_eff = bn_eff;
+  if (lora) {
+    p.num_stages = bn == 256 ? GemmCfg<256>::STAGES : GemmCfg<128>::STAGES;
+    p.stage_bytes = bn == 256 ? GemmCfg<256>::STAGE_BYTES : GemmCfg<128>::STAGE_BYTES;
+  } else {
+    // no LoRA operands in shared memory: the whole buffer becomes pipeline stages (deep prefetch for the
+    // weight-streaming decode shapes, where bytes in flight per SM decide the achieved HBM bandwidth)
+    const int budget = bn == 256 ? GemmCfg<256>::BAR_OFF : GemmCfg<128>::BAR_OFF;
+    p.stage_bytes = BM * BK + (bn_eff * BK + 1023) / 1024 * 1024;
+    p.num_stages = budget / p.stage_bytes;
+    if (p.num_stages > GemmCfg<256>::MAX_STAGES) p.num_stages = GemmCfg<256>::MAX_STAGES;
+  }
+  p.addend = a.addend;
+  p.addend_stride = a.addend_row_stride;
+  const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff);
   const int grid = static_cast<int>(max_total < sms ? max_total : sms);
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
                    : launch_bn<128>(p, a.epilogue, lora, grid, stream);

@@ -24,11 +24,11 @@ import torch
 
 from . import _lib
 from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS,
-                   SkyrlKernelError)
+                   WEIGHT_KBLOCK, SkyrlKernelError)
 
 __all__ = (
     "GroupQuantizedWeight", "PackedW8Weight", "PackedLoRA", "SkyrlKernelError",
-    "quantize_frozen_weight", "pack_weight", "pack_lora", "prepare_routing", "rms_quant",
+    "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
@@ -57,8 +57,9 @@ class GroupQuantizedWeight:
 
 @dataclass(frozen=True)
 class PackedW8Weight:
-    """Device format of a per-output-channel W8 weight: int8 [Npad, K] with K
-    contiguous, fp32 scales [Npad]; `out_features` <= Npad (Npad % 32 == 0)."""
+    """Device format of a per-output-channel W8 weight: int8 [ceil(K / 128), Npad, 128]
+    (K-block-major: for one block of 128 K values the rows of all output channels are
+    contiguous), fp32 scales [Npad]; `out_features` <= Npad (Npad % 32 == 0)."""
 
     wq: torch.Tensor
     sw: torch.Tensor
@@ -67,7 +68,7 @@ class PackedW8Weight:
 
     @property
     def padded_out_features(self) -> int:
-        return self.wq.shape[0]
+        return self.wq.shape[1]
 
 
 @dataclass(frozen=True)
@@ -156,12 +157,32 @@ def pack_weight(weight: GroupQuantizedWeight) -> PackedW8Weight:
         padded[:kpad, :n] = codes
         codes = padded
     codes = codes.contiguous()
-    wq = torch.empty((npad, k), dtype=torch.int8, device=codes.device)
+    wq = torch.empty(((k + WEIGHT_KBLOCK - 1) // WEIGHT_KBLOCK, npad, WEIGHT_KBLOCK), dtype=torch.int8,
+                     device=codes.device)
     lib = _lib.load()
     _lib.check(lib.skyrl_pack_weight_kn_sm100_v1(_ptr(codes), k, npad, _ptr(wq), _stream()), "pack_weight")
     sw = torch.zeros((npad,), dtype=torch.float32, device=codes.device)
     sw[:n] = weight.scales[0].to(torch.float32)
     return PackedW8Weight(wq, sw, k, n)
+
+
+def pack_weight_nk(codes_nk: torch.Tensor, scales: torch.Tensor) -> PackedW8Weight:
+    """int8 [N, K] codes (K contiguous, the [out, in] order checkpoints use) + per-output-channel
+    scales [N] -> the packed device format.  N must be a multiple of 32 and K of 16."""
+    _require_cuda(codes_nk, "codes_nk")
+    if codes_nk.ndim != 2 or codes_nk.dtype != torch.int8:
+        raise TypeError("W8 codes must be a rank-two INT8 array")
+    n, k = codes_nk.shape
+    if n % 32 or k % 16:
+        raise ValueError(f"pack_weight_nk needs N % 32 == 0 and K % 16 == 0, got N={n}, K={k}")
+    if scales.shape != (n,):
+        raise ValueError(f"scales must have shape ({n},), got {tuple(scales.shape)}")
+    codes_nk = codes_nk.contiguous()
+    wq = torch.empty(((k + WEIGHT_KBLOCK - 1) // WEIGHT_KBLOCK, n, WEIGHT_KBLOCK), dtype=torch.int8,
+                     device=codes_nk.device)
+    lib = _lib.load()
+    _lib.check(lib.skyrl_pack_weight_nk_sm100_v1(_ptr(codes_nk), n, k, _ptr(wq), _stream()), "pack_weight_nk")
+    return PackedW8Weight(wq, scales.to(torch.float32).contiguous(), k, n)
 
 
 def pack_lora(lora_a: torch.Tensor, lora_b: torch.Tensor, lora_scaling, *, in_features: int | None = None,
@@ -320,7 +341,7 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
     if out is None:
         out = torch.empty((m, out_cols), dtype=out_dtype, device=dev)
     na = lora.num_adapters if lora is not None else 1
-    nbytes = lib.skyrl_w8a8_linear_workspace_bytes(m, k, na)
+    nbytes = lib.skyrl_w8a8_linear_workspace_bytes(m, npad, k, na)
     ws = _workspace(dev, nbytes)
     st = _status_word(dev)
     a = _lib.LinearArgs()
@@ -465,7 +486,7 @@ def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=
 def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: PackedLoRA | None,
                    down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
-                   timing_events=None, return_call: bool = False):
+                   timing_events=None, return_call: bool = False, reuse_routing: bool = False):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only."""
@@ -526,6 +547,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     if timing_events is not None:
         for i, ev in enumerate(timing_events):
             a.timing_events[i] = ev.cuda_event
+    if reuse_routing:
+        a.flags = _lib.MLP_REUSE_ROUTING
     _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
     if return_call:
         # keeps the argument block (and through it the workspace layout) for the tensor-parallel finalize

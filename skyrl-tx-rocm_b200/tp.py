@@ -64,7 +64,8 @@ class TensorParallelMLP:
         self.eps = eps
         self._partial = None
 
-    def forward(self, x, adapter_ids=None, *, out=None, residual=None, timing_events=None, all_reduce=None):
+    def forward(self, x, adapter_ids=None, *, out=None, residual=None, timing_events=None, all_reduce=None,
+                reuse_routing=False):
         import torch
 
         from . import ops
@@ -77,7 +78,7 @@ class TensorParallelMLP:
         _, call = ops.w8a8_mlp_block(
             x, self.rms_delta, self.gate_up_weight, self.gate_up_lora, self.down_weight, self.down_lora, adapter_ids,
             residual=residual, enabled=True, eps=self.eps, out=self._partial, down_epilogue=ops.EPI_PARTIAL_F32,
-            timing_events=timing_events, return_call=True)
+            timing_events=timing_events, return_call=True, reuse_routing=reuse_routing)
         if all_reduce is not None:
             all_reduce(self._partial)
         else:

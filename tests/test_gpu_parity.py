@@ -349,7 +349,7 @@ def test_config3_accumulator_sampled_tiles(S):
     x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
     wq = torch.randint(-127, 128, (n, k), generator=gen, device="cuda", dtype=torch.int8)
     sw = torch.full((n,), 1e-3, device="cuda", dtype=torch.float32)
-    packed = S.PackedW8Weight(wq, sw, k, n)
+    packed = S.pack_weight_nk(wq, sw)
     acc = S.w8a8_int32_accumulator(x, packed, enabled=True)
     S.check_status()
     xq, sx, _ = S.rms_quant(x)

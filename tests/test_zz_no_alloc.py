@@ -47,7 +47,7 @@ def _case(S, seed, m, k, n, rank, adapters):
     b = (torch.randn((adapters, rank, n), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
     s = torch.full((adapters,), 2.0, device="cuda")
     ids = torch.randint(0, adapters, (m,), generator=gen, device="cuda", dtype=torch.int32)
-    return x, S.PackedW8Weight(wq, sw, k, n), S.pack_lora(a, b, s, in_features=k, padded_out_features=n), ids
+    return x, S.pack_weight_nk(wq, sw), S.pack_lora(a, b, s, in_features=k, padded_out_features=n), ids
 
 
 def test_noalloc_entry_point_matches_workspace_entry_point_twice():
@@ -62,7 +62,7 @@ def test_noalloc_entry_point_matches_workspace_entry_point_twice():
         x, w, lora, ids = _case(S, seed, m, k, n, rank, adapters)
         want = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
         got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
-        nbytes = lib.skyrl_w8a8_linear_workspace_bytes(m, k, adapters)
+        nbytes = lib.skyrl_w8a8_linear_workspace_bytes(m, n, k, adapters)
         assert 0 < nbytes < _lib.NOALLOC_SCRATCH_BYTES
         ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device="cuda")
         ws = ws[(-ws.data_ptr()) % 1024:][:nbytes]
@@ -83,7 +83,7 @@ def test_noalloc_entry_point_rejects_oversized_requests():
     lib = _lib.load()
     m, k, n = 8192, 4096, 64          # needs about 3 * m * k = 100 MB of scratch
     x = torch.zeros((m, k), dtype=torch.bfloat16, device="cuda")
-    w = S.PackedW8Weight(torch.zeros((n, k), dtype=torch.int8, device="cuda"), torch.ones(n, device="cuda"), k, n)
+    w = S.pack_weight_nk(torch.zeros((n, k), dtype=torch.int8, device="cuda"), torch.ones(n, device="cuda"))
     a8 = torch.zeros((1, k, 8), dtype=torch.bfloat16, device="cuda")
     b8 = torch.zeros((1, 8, n), dtype=torch.bfloat16, device="cuda")
     lora = S.pack_lora(a8, b8, torch.ones(1, device="cuda"), in_features=k, padded_out_features=n)

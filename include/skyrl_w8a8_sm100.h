@@ -144,13 +144,16 @@ typedef struct SkyrlW8A8GemmArgs {
   int64_t out_row_stride;   /* elements                                                */
   int64_t residual_row_stride;
   int32_t* status;          /* device int32, non-zero after a bounded wait ran out     */
-  const float* addend;      /* optional fp32 [m, n] (sorted rows) added to the dequantised accumulator
-                               before the epilogue: the row-wise LoRA term of the small-batch path;
-                               requires rank == 0                                       */
-  int64_t addend_row_stride;
+  int32_t split_k_slabs;    /* SKYRL_EPI_ACC_I32 only: `out` holds this many [m, out_row_stride] int32 slabs
+                               (<= 1: no split).  The kernel may split K over up to that many CTAs per
+                               tile; split s writes its partial sums to slab s and the caller adds the
+                               skyrl_w8a8_gemm_k_splits(...) slabs (int32 addition is exact)      */
+  int32_t reserved;
 } SkyrlW8A8GemmArgs;
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
+/* Number of K splits (slabs written) the GEMM uses for this shape when given `split_k_slabs` slabs. */
+SKYRL_API int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t split_k_slabs);
 
 /* ------------------------------------------------------------------------- *
  * Operator entry points (what the reference's custom-call layer binds)
@@ -189,6 +192,10 @@ typedef struct SkyrlW8A8LinearArgs {
   size_t workspace_bytes;
   int32_t* status;           /* device int32, zeroed by the caller */
   void* timing_events[2];    /* optional cudaEvent_t recorded before / after the GEMM kernel */
+  const void* lora_b_rows;   /* optional dense LoRA-B table bf16 [A, n, lora_b_rows_rank] (rank rounded up to 8)
+                                read by the small-batch path instead of the 64-slot table */
+  int32_t lora_b_rows_rank;
+  int32_t reserved2;
 } SkyrlW8A8LinearArgs;
 
 SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t num_adapters);
@@ -262,7 +269,9 @@ typedef struct SkyrlW8A8MlpArgs {
   void* timing_events[4];    /* optional cudaEvent_t recorded on the stream: before / after the gate_up
                                 GEMM, before / after the down GEMM (NULL = not recorded)             */
   uint32_t flags;            /* SKYRL_MLP_* */
-  uint32_t reserved;
+  int32_t b_rows_rank;       /* row length of the dense LoRA-B tables below */
+  const void* gu_b_rows;     /* optional dense tables bf16 [A, 2I, b_rows_rank] / [A, H, b_rows_rank] for the */
+  const void* dn_b_rows;     /* small-batch path (see SkyrlW8A8LinearArgs.lora_b_rows)                        */
 } SkyrlW8A8MlpArgs;
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
@@ -288,6 +297,9 @@ SKYRL_API int skyrl_pack_weight_nk_sm100_v1(const void* codes_nk, int32_t n, int
 /* bf16 [A, K, r] -> bf16 [A, 64, K] (skyrl/tx/layers/lora.py:259-268).                   */
 SKYRL_API int skyrl_pack_lora_a_sm100_v1(const void* a_akr, int32_t num_adapters, int32_t k, int32_t rank, void* a_packed,
                                skyrl_stream_t stream);
+/* bf16 [A, r, N] -> dense bf16 [A, N, rr], rr = rank rounded up to a multiple of 8 (small-batch path). */
+SKYRL_API int skyrl_pack_lora_b_rows_sm100_v1(const void* b_arn, int32_t num_adapters, int32_t rank, int32_t n, void* b_rows,
+                                    skyrl_stream_t stream);
 /* bf16 [A, r, N] -> bf16 [A, N, 64].                                                     */
 SKYRL_API int skyrl_pack_lora_b_sm100_v1(const void* b_arn, int32_t num_adapters, int32_t rank, int32_t n, void* b_packed,
                                skyrl_stream_t stream);

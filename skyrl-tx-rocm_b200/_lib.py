@@ -41,7 +41,7 @@ class GemmArgs(C.Structure):
         ("tiles", C.c_void_p), ("num_tiles", C.c_void_p), ("out_row_map", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
-        ("addend", C.c_void_p), ("addend_row_stride", C.c_int64),
+        ("split_k_slabs", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -56,6 +56,7 @@ class LinearArgs(C.Structure):
         ("residual_row_stride", C.c_int64), ("out", C.c_void_p), ("out_row_stride", C.c_int64),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
         ("timing_events", C.c_void_p * 2),
+        ("lora_b_rows", C.c_void_p), ("lora_b_rows_rank", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 
@@ -70,7 +71,7 @@ class MlpArgs(C.Structure):
         ("dn_scaling", C.c_void_p),
         ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("timing_events", C.c_void_p * 4),
-        ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("flags", C.c_uint32), ("b_rows_rank", C.c_int32), ("gu_b_rows", C.c_void_p), ("dn_b_rows", C.c_void_p),
     ]
 
 
@@ -86,6 +87,7 @@ SYMBOLS = {
                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p]),
     "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
+    "skyrl_w8a8_gemm_k_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_lora_forward_noalloc_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
@@ -96,6 +98,7 @@ SYMBOLS = {
     "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_weight_nk_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_a_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
+    "skyrl_pack_lora_b_rows_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_b_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
 }
 

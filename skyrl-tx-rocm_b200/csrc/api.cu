@@ -110,7 +110,7 @@ struct LinearWs {
   float* sx;
   uint16_t* xn;
   uint16_t* z_parts;  // bf16 [3, m, 64]; the row-wise path keeps fp32 [m, 64] here instead
-  float* addend;      // fp32 [m, n], row-wise path only
+  int32_t* acc;       // int32 [m, n] accumulator, row-wise path only
   size_t bytes;
 };
 
@@ -126,10 +126,10 @@ static LinearWs carve_linear(void* ws, int m, int n, int k, int num_adapters) {
   w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   if (m <= ROWS_PATH_MAX_M) {
     w.xn = nullptr;
-    w.addend = c.take<float>(static_cast<size_t>(m) * n);
+    w.acc = c.take<int32_t>(static_cast<size_t>(m) * n * plan_gemm(m, n, k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits);
   } else {
     w.xn = c.take<uint16_t>(static_cast<size_t>(m) * k);
-    w.addend = nullptr;
+    w.acc = nullptr;
   }
   w.bytes = c.total();
   return w;
@@ -146,7 +146,7 @@ struct MlpWs {
   uint16_t* h;
   int8_t* hq;
   float* sh;
-  float* addend;  // fp32 [m, max(2I, H)], row-wise path only
+  int32_t* acc;  // int32 [m, max(2I, H)] accumulator, row-wise path only
   size_t bytes;
 };
 
@@ -165,11 +165,14 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   w.sh = c.take<float>(m);
   if (m <= ROWS_PATH_MAX_M) {
     w.xn = nullptr;
-    const int widest = 2 * inter > hidden ? 2 * inter : hidden;
-    w.addend = c.take<float>(static_cast<size_t>(m) * widest);
+    const size_t gu = static_cast<size_t>(m) * 2 * inter *
+                      plan_gemm(m, 2 * inter, hidden, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
+    const size_t dn = static_cast<size_t>(m) * hidden *
+                      plan_gemm(m, hidden, inter, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
+    w.acc = c.take<int32_t>(gu > dn ? gu : dn);
   } else {
     w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
-    w.addend = nullptr;
+    w.acc = nullptr;
   }
   w.bytes = c.total();
   return w;
@@ -184,7 +187,9 @@ static int check_ws(const void* ws, size_t have, size_t need, const char* who) {
 
 // One W8A8 LoRA projection on rows that are already laid out as the GEMM wants them.
 //   tensor-core route (m > 128): rows adapter-sorted, z planes from lora_a_proj, LoRA inside the GEMM epilogue
-//   row-wise route (m <= 128): rows in token order, z and the LoRA addend from the row kernels
+//   row-wise route (m <= 128): rows in token order; the GEMM leaves the int32 accumulator in global
+//   memory (split over K when that fills the GPU better) and a row-wise kernel applies scales, LoRA,
+//   the cast and the SwiGLU / residual step
 struct Projection {
   const void* x;          // bf16 [m, k] source rows
   int64_t x_stride;
@@ -197,13 +202,15 @@ struct Projection {
   const float* sw;
   const void* a_packed;
   const void* b_packed;
+  const void* b_rows;     // dense [A, n, b_rows_rank] LoRA-B table for the row-wise route, or NULL
+  int b_rows_rank;
   const float* scaling;
   const int32_t* ids;     // token-order adapter ids (row-wise route)
   int8_t* xq;
   float* sx;
   uint16_t* xn;
   uint16_t* z_parts;
-  float* addend;
+  int32_t* acc;
   const int32_t* tiles;
   const int32_t* num_tiles;
   int epilogue;
@@ -222,16 +229,41 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   const bool rows_path = q.m <= ROWS_PATH_MAX_M;
   int rc;
   SkyrlW8A8GemmArgs g = {};
-  if (rows_path && lora) {
+  if (rows_path && lora && q.epilogue != SKYRL_EPI_ACC_I32) {
     float* z_rows = reinterpret_cast<float*>(q.z_parts);
     if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.a_packed, q.scaling, q.rank, q.m, q.k,
                                     q.xq, q.sx, z_rows, stream)))
       return rc;
-    if ((rc = launch_lora_b_rows(z_rows, q.ids, q.b_packed, q.rank, q.m, q.n, q.addend, q.n, stream))) return rc;
+    const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
+    g.struct_size = sizeof(g);
+    g.epilogue = SKYRL_EPI_ACC_I32;
+    g.split_k_slabs = MAX_SPLIT_K_SLABS;
+    g.m = q.m;
+    g.n = q.n;
+    g.k = q.k;
     g.rank = 0;
-    g.addend = q.addend;
-    g.addend_row_stride = q.n;
-  } else {
+    g.num_adapters = q.na;
+    g.max_tiles = q.mt;
+    g.xq = q.xq;
+    g.sx = q.sx;
+    g.wq = q.wq;
+    g.sw = q.sw;
+    g.tiles = q.tiles;
+    g.num_tiles = q.num_tiles;
+    g.out = q.acc;
+    g.out_row_stride = q.n;
+    g.status = q.status;
+    if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
+    rc = launch_gemm(g, stream);
+    if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
+    if (rc) return rc;
+    const bool dense = q.b_rows != nullptr;
+    const int brow = dense ? q.b_rows_rank : SKYRL_LORA_RANK_PAD;
+    return launch_finalize_rows(q.epilogue, q.acc, slabs, q.sx, q.sw, z_rows, q.ids, dense ? q.b_rows : q.b_packed,
+                                static_cast<int64_t>(q.n) * brow, brow, q.rank, q.m, q.n, q.residual,
+                                q.residual_stride, q.out, q.out_stride, stream);
+  }
+  {
     const bool need_xn = lora && q.keep_xn;
     if ((rc = launch_rms_quant(q.x, q.x_stride, q.rms_delta, q.eps, q.gather, q.m, q.k, q.xq, q.sx,
                                need_xn ? q.xn : nullptr, stream)))
@@ -339,7 +371,9 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.sx = w.sx;
   q.xn = w.xn;
   q.z_parts = w.z_parts;
-  q.addend = w.addend;
+  q.acc = w.acc;
+  q.b_rows = a->lora_b_rows;
+  q.b_rows_rank = a->lora_b_rows_rank;
   q.tiles = w.tiles;
   q.num_tiles = w.num_tiles;
   q.epilogue = a->epilogue;
@@ -413,7 +447,9 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.sx = w.sx;
   q.xn = w.xn;
   q.z_parts = w.z_parts;
-  q.addend = w.addend;
+  q.acc = w.acc;
+  q.b_rows = a->gu_b_rows;
+  q.b_rows_rank = a->b_rows_rank;
   q.tiles = w.tiles;
   q.num_tiles = w.num_tiles;
   q.epilogue = SKYRL_EPI_SWIGLU;
@@ -437,6 +473,7 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.sw = a->dn_sw;
   q.a_packed = a->dn_a_packed;
   q.b_packed = a->dn_b_packed;
+  q.b_rows = a->dn_b_rows;
   q.scaling = a->dn_scaling;
   q.xq = w.hq;
   q.sx = w.sh;

@@ -33,12 +33,22 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream);
+// Tile width and K split the GEMM launcher chooses for a shape (deterministic per device).
+struct GemmPlan {
+  int bn_eff;
+  int k_splits;
+  int kb_per_split;
+};
+GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs);
+constexpr int MAX_SPLIT_K_SLABS = 16;
 int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream);
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                           const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
                           float* z_rows, cudaStream_t stream);
-int launch_lora_b_rows(const float* z_rows, const int32_t* ids, const void* b_packed, int rank, int m, int n,
-                       float* addend, int64_t addend_stride, cudaStream_t stream);
+int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw, const float* z_rows,
+                         const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
+                         int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
+                         cudaStream_t stream);
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
                        int row_begin, int row_count, cudaStream_t stream);
 

@@ -1,25 +1,32 @@
-// Row-wise LoRA kernels for small batches (decode shapes: a few dozen token
-// rows, almost every row with its own adapter).  Sorting rows by adapter and
-// spending one 128-row tensor-core tile per adapter would multiply the weight
-// traffic by the number of adapters, so here every row carries its adapter id:
+// Row-wise kernels for small batches (decode shapes: a few dozen token rows,
+// almost every row with its own adapter).  Sorting rows by adapter and spending
+// one 128-row tensor-core tile per adapter would multiply the weight traffic by
+// the number of adapters, so here every row carries its adapter id:
 //
-//   rms_quant_rows_kernel<R> ... K1 of the main path (RMSNorm, absmax, int8 codes)
-//                                plus z[m, :] = s[a] * (n[m, :] @ A[a]) while the
-//                                normalised row is still in shared memory
-//   lora_b_rows_kernel ......... addend[m, n] = sum_j z[m, j] * B[a(m)][n, j] (fp32),
-//                                consumed by the GEMM epilogue before the single cast
+//   rms_quant_rows_kernel<R> ... a cluster of 8 CTAs per token row: RMSNorm, absmax, int8 codes and
+//                                z[m, :] = s[a] * (n[m, :] @ A[a]); every CTA owns one eighth of K and
+//                                the three row-wide reductions go through distributed shared memory
+//   finalize_rows_kernel<EPI> .. v = (f32(acc) * sx[m]) * sw[n] + sum_j z[m, j] * B[a(m)][n, j], then the
+//                                single bf16 cast and SwiGLU / residual, from the int32 accumulator the
+//                                GEMM left in global memory
 //
 // Both are HBM/L2-bound CUDA-core kernels; the arithmetic is the reference's
-// fp32 LoRA term (skyrl/tx/kernels/quantized_lora.py:301-304) evaluated per
+// (skyrl/tx/kernels/quantized_lora.py:199-212, 248-252, 301-304) evaluated per
 // token as in skyrl/tx/layers/lora.py:142-157.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace skyrl {
 
-constexpr int ROWS_THREADS = 256;
+constexpr int ROWQ_THREADS = 128;
+constexpr int ROWQ_CLUSTER = 8;
+constexpr int ROWQ_MAX_SLICE_VECS = 512;  // 8 * 512 * 8 = 32768 in-features at most
 
-__device__ __forceinline__ float rows_block_reduce(float v, bool is_max, float* red) {
+__device__ __forceinline__ float rowq_block_reduce(float v, bool is_max, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -31,30 +38,36 @@ __device__ __forceinline__ float rows_block_reduce(float v, bool is_max, float* 
   __syncthreads();
   float r = red[0];
 #pragma unroll
-  for (int w = 1; w < ROWS_THREADS / 32; ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
+  for (int w = 1; w < ROWQ_THREADS / 32; ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
   return r;
 }
 
 template <int R>
-__global__ void __launch_bounds__(ROWS_THREADS)
+__global__ void __cluster_dims__(ROWQ_CLUSTER, 1, 1) __launch_bounds__(ROWQ_THREADS)
 rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
                       const __nv_bfloat16* __restrict__ delta, float eps, const int32_t* __restrict__ ids,
                       const __nv_bfloat16* __restrict__ a_packed, const float* __restrict__ scaling, int k,
                       int8_t* __restrict__ xq, float* __restrict__ sx, float* __restrict__ z_rows) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint4* row = reinterpret_cast<uint4*>(smem_raw);
-  __shared__ float red[ROWS_THREADS / 32];
-  __shared__ float zred[ROWS_THREADS / 32][R];
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ __align__(16) uint4 slice[ROWQ_MAX_SLICE_VECS];
+  __shared__ float red[ROWQ_THREADS / 32];
+  __shared__ float zwarp[ROWQ_THREADS / 32][R];
+  __shared__ float part_ss, part_amax;   // this CTA's partial results, read by the whole cluster
+  __shared__ float part_z[R];
 
-  const int m = blockIdx.x;
-  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * x_row_stride);
+  const int m = blockIdx.x / ROWQ_CLUSTER;
+  const int crank = static_cast<int>(cluster.block_rank());
   const int nvec = k >> 3;
+  const int per = (nvec + ROWQ_CLUSTER - 1) / ROWQ_CLUSTER;
+  const int v0 = crank * per;
+  const int cnt = max(0, min(per, nvec - v0));
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * x_row_stride) + v0;
   const bool norm = delta != nullptr;
 
   float ss = 0.f, amax = 0.f;
-  for (int v = threadIdx.x; v < nvec; v += ROWS_THREADS) {
+  for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
     const uint4 u = __ldg(src + v);
-    row[v] = u;
+    slice[v] = u;
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -68,12 +81,17 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     }
   }
   if (norm) {
-    ss = rows_block_reduce(ss, false, red);
-    const float var = __fdiv_rn(ss, static_cast<float>(k));
+    ss = rowq_block_reduce(ss, false, red);
+    if (threadIdx.x == 0) part_ss = ss;
+    cluster.sync();
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < ROWQ_CLUSTER; ++r) total += *cluster.map_shared_rank(&part_ss, r);  // fixed order
+    const float var = __fdiv_rn(total, static_cast<float>(k));
     const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
-    const uint4* dvec = reinterpret_cast<const uint4*>(delta);
-    for (int v = threadIdx.x; v < nvec; v += ROWS_THREADS) {
-      const uint4 u = row[v];
+    const uint4* dvec = reinterpret_cast<const uint4*>(delta) + v0;
+    for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
+      const uint4 u = slice[v];
       const uint4 d = __ldg(dvec + v);
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
       const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
@@ -85,22 +103,27 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
         o[j] = pack_bf16x2(a, b);
         amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
       }
-      row[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      slice[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
-  amax = rows_block_reduce(amax, true, red);  // also orders the writes to `row` before the reads below
-  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-  if (threadIdx.x == 0) sx[m] = scale;
+  amax = rowq_block_reduce(amax, true, red);
+  if (threadIdx.x == 0) part_amax = amax;
+  cluster.sync();
+  float row_amax = 0.f;
+#pragma unroll
+  for (int r = 0; r < ROWQ_CLUSTER; ++r) row_amax = fmaxf(row_amax, *cluster.map_shared_rank(&part_amax, r));
+  const float scale = row_amax > 0.f ? __fdiv_rn(row_amax, 127.0f) : 1.0f;
+  if (crank == 0 && threadIdx.x == 0) sx[m] = scale;
 
   const int adapter = ids != nullptr ? ids[m] : 0;
-  const uint4* a_base = reinterpret_cast<const uint4*>(a_packed + static_cast<int64_t>(adapter) * SKYRL_LORA_RANK_PAD * k);
+  const uint4* a_base =
+      reinterpret_cast<const uint4*>(a_packed + static_cast<int64_t>(adapter) * SKYRL_LORA_RANK_PAD * k) + v0;
   float acc[R];
 #pragma unroll
   for (int j = 0; j < R; ++j) acc[j] = 0.f;
-
-  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k);
-  for (int v = threadIdx.x; v < nvec; v += ROWS_THREADS) {
-    const uint4 u = row[v];
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k) + v0;
+  for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
+    const uint4 u = slice[v];
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
     float xv[8];
     uint32_t packed[2] = {0u, 0u};
@@ -133,57 +156,97 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     float v = acc[j];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0) zred[warp][j] = v;
+    if (lane == 0) zwarp[warp][j] = v;
   }
   __syncthreads();
-  if (threadIdx.x < SKYRL_LORA_RANK_PAD) {
+  if (threadIdx.x < R) {
+    float z = 0.f;
+#pragma unroll
+    for (int w = 0; w < ROWQ_THREADS / 32; ++w) z += zwarp[w][threadIdx.x];
+    part_z[threadIdx.x] = z;
+  }
+  cluster.sync();
+  if (crank == 0 && threadIdx.x < SKYRL_LORA_RANK_PAD) {
     float z = 0.f;
     if (threadIdx.x < R) {
 #pragma unroll
-      for (int w = 0; w < ROWS_THREADS / 32; ++w) z += zred[w][threadIdx.x];
+      for (int r = 0; r < ROWQ_CLUSTER; ++r) z += cluster.map_shared_rank(part_z, r)[threadIdx.x];  // fixed order
       z = __fmul_rn(z, __ldg(scaling + adapter));
     }
     z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x] = z;
   }
+  cluster.sync();  // no CTA may leave while another still reads its shared memory
 }
 
-__global__ void __launch_bounds__(ROWS_THREADS)
-lora_b_rows_kernel(const float* __restrict__ z_rows, const int32_t* __restrict__ ids,
-                   const __nv_bfloat16* __restrict__ b_packed, int n, int rank_vecs, float* __restrict__ addend,
-                   int64_t addend_stride) {
+template <int EPI>
+__global__ void __launch_bounds__(256)
+finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_stride, const float* __restrict__ sx,
+                     const float* __restrict__ sw,
+                     const float* __restrict__ z_rows, const int32_t* __restrict__ ids,
+                     const __nv_bfloat16* __restrict__ b_table, int64_t b_adapter_stride, int b_row_stride,
+                     int rank_vecs, int n, const __nv_bfloat16* __restrict__ residual, int64_t res_stride,
+                     void* __restrict__ out, int64_t out_stride) {
   __shared__ float zs[SKYRL_LORA_RANK_PAD];
   const int m = blockIdx.y;
-  if (threadIdx.x < SKYRL_LORA_RANK_PAD) zs[threadIdx.x] = z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x];
+  if (rank_vecs > 0 && threadIdx.x < SKYRL_LORA_RANK_PAD)
+    zs[threadIdx.x] = z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x];
   __syncthreads();
-  const int nn = blockIdx.x * ROWS_THREADS + threadIdx.x;
-  if (nn >= n) return;
-  const int adapter = ids != nullptr ? ids[m] : 0;
-  const uint4* brow = reinterpret_cast<const uint4*>(b_packed + (static_cast<int64_t>(adapter) * n + nn) * SKYRL_LORA_RANK_PAD);
-  float acc = 0.f;
-  for (int q = 0; q < rank_vecs; ++q) {
-    const uint4 w = __ldg(brow + q);
-    const uint32_t bv[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      acc = fmaf(zs[8 * q + 2 * j], bf16_lo(bv[j]), acc);
-      acc = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(bv[j]), acc);
-    }
+  const int n0 = 2 * (blockIdx.x * 256 + threadIdx.x);  // this thread owns columns n0 and n0 + 1
+  if (n0 >= n) return;
+  const float sxm = __ldg(sx + m);
+  int2 a2 = __ldg(reinterpret_cast<const int2*>(acc + static_cast<int64_t>(m) * n + n0));
+  for (int sl = 1; sl < slabs; ++sl) {  // split-K partial sums: int32 addition is exact
+    const int2 t2 = __ldg(reinterpret_cast<const int2*>(acc + sl * slab_stride + static_cast<int64_t>(m) * n + n0));
+    a2.x += t2.x;
+    a2.y += t2.y;
   }
-  addend[static_cast<int64_t>(m) * addend_stride + nn] = acc;
+  const float2 w2 = __ldg(reinterpret_cast<const float2*>(sw + n0));
+  float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a2.x), sxm), w2.x);
+  float f1 = __fmul_rn(__fmul_rn(__int2float_rn(a2.y), sxm), w2.y);
+  if (rank_vecs > 0) {
+    const int adapter = ids != nullptr ? ids[m] : 0;
+    const __nv_bfloat16* b0 = b_table + static_cast<int64_t>(adapter) * b_adapter_stride +
+                              static_cast<int64_t>(n0) * b_row_stride;
+    const uint4* r0 = reinterpret_cast<const uint4*>(b0);
+    const uint4* r1 = reinterpret_cast<const uint4*>(b0 + b_row_stride);
+    float l0 = 0.f, l1 = 0.f;
+    for (int q = 0; q < rank_vecs; ++q) {
+      const uint4 u0 = __ldg(r0 + q), u1 = __ldg(r1 + q);
+      const uint32_t c0[4] = {u0.x, u0.y, u0.z, u0.w};
+      const uint32_t c1[4] = {u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        l0 = fmaf(zs[8 * q + 2 * j], bf16_lo(c0[j]), l0);
+        l0 = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(c0[j]), l0);
+        l1 = fmaf(zs[8 * q + 2 * j], bf16_lo(c1[j]), l1);
+        l1 = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(c1[j]), l1);
+      }
+    }
+    f0 = __fadd_rn(f0, l0);
+    f1 = __fadd_rn(f1, l1);
+  }
+  if (EPI == SKYRL_EPI_PARTIAL_F32) {
+    *reinterpret_cast<float2*>(static_cast<float*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+        make_float2(f0, f1);
+  } else if (EPI == SKYRL_EPI_SWIGLU) {
+    const float g = round_bf16(f0), u = round_bf16(f1);
+    const float h = __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u);
+    static_cast<__nv_bfloat16*>(out)[static_cast<int64_t>(m) * out_stride + (n0 >> 1)] = __float2bfloat16_rn(h);
+  } else if (EPI == SKYRL_EPI_RESIDUAL) {
+    const uint32_t rv = __ldg(reinterpret_cast<const uint32_t*>(residual + static_cast<int64_t>(m) * res_stride + n0));
+    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+        pack_bf16x2(__fadd_rn(round_bf16(f0), bf16_lo(rv)), __fadd_rn(round_bf16(f1), bf16_hi(rv)));
+  } else {
+    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+        pack_bf16x2(f0, f1);
+  }
 }
 
 template <int R>
 static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                                const void* a_packed, const float* scaling, int m, int k, void* xq, float* sx,
                                float* z_rows, cudaStream_t stream) {
-  auto kernel = rms_quant_rows_kernel<R>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant_rows attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
-  kernel<<<m, ROWS_THREADS, static_cast<size_t>(k) * 2, stream>>>(
+  rms_quant_rows_kernel<R><<<m * ROWQ_CLUSTER, ROWQ_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), x_row_stride, static_cast<const __nv_bfloat16*>(rms_delta), eps, ids,
       static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx, z_rows);
   cudaError_t e = cudaPeekAtLastError();
@@ -202,8 +265,8 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: row stride must be >= K and a multiple of 8 elements");
   if (!aligned16(x) || !aligned16(xq) || !aligned16(a_packed) || (rms_delta != nullptr && !aligned16(rms_delta)))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: buffers must be 16-byte aligned");
-  if (static_cast<size_t>(k) * 2 > 200 * 1024)
-    return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: K=%d exceeds the staged-row limit", k);
+  if ((k >> 3) > ROWQ_CLUSTER * ROWQ_MAX_SLICE_VECS)
+    return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: K=%d exceeds %d", k, ROWQ_CLUSTER * ROWQ_MAX_SLICE_VECS * 8);
   if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
   if (rank <= 16)
@@ -213,17 +276,36 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
   return launch_rows_variant<64>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream);
 }
 
-int launch_lora_b_rows(const float* z_rows, const int32_t* ids, const void* b_packed, int rank, int m, int n,
-                       float* addend, int64_t addend_stride, cudaStream_t stream) {
-  if (z_rows == nullptr || b_packed == nullptr || addend == nullptr || m <= 0 || n <= 0 || m > 65535)
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_b_rows: null buffer or bad shape");
-  if (!aligned16(b_packed) || addend_stride < n)
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_b_rows: misaligned table or short addend stride");
-  dim3 grid((n + ROWS_THREADS - 1) / ROWS_THREADS, m);
-  lora_b_rows_kernel<<<grid, ROWS_THREADS, 0, stream>>>(z_rows, ids, static_cast<const __nv_bfloat16*>(b_packed), n,
-                                                        (rank + 7) / 8, addend, addend_stride);
+int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw,
+                         const float* z_rows,
+                         const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
+                         int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
+                         cudaStream_t stream) {
+  if (acc == nullptr || sx == nullptr || sw == nullptr || out == nullptr || m <= 0 || n <= 0 || n % 2 != 0 ||
+      m > 65535)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: null buffer or bad shape");
+  if (rank > 0 && (z_rows == nullptr || b_table == nullptr || !aligned16(b_table) || b_row_stride % 8 != 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: LoRA operands missing or misaligned");
+  if (epilogue == SKYRL_EPI_RESIDUAL && residual == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: residual missing");
+  dim3 grid((n / 2 + 255) / 256, m);
+  const int rank_vecs = (rank + 7) / 8;
+  const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(b_table);
+  const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(residual);
+#define SKYRL_FINALIZE(E)                                                                                        \
+  finalize_rows_kernel<E><<<grid, 256, 0, stream>>>(acc, slabs, static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, bt, \
+                                                    b_adapter_stride, b_row_stride, rank_vecs, n, res, res_stride,   \
+                                                    out, out_stride)
+  switch (epilogue) {
+    case SKYRL_EPI_LINEAR: SKYRL_FINALIZE(SKYRL_EPI_LINEAR); break;
+    case SKYRL_EPI_SWIGLU: SKYRL_FINALIZE(SKYRL_EPI_SWIGLU); break;
+    case SKYRL_EPI_RESIDUAL: SKYRL_FINALIZE(SKYRL_EPI_RESIDUAL); break;
+    case SKYRL_EPI_PARTIAL_F32: SKYRL_FINALIZE(SKYRL_EPI_PARTIAL_F32); break;
+    default: return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: unsupported epilogue %d", epilogue);
+  }
+#undef SKYRL_FINALIZE
   cudaError_t e = cudaPeekAtLastError();
-  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_b_rows launch: %s", cudaGetErrorString(e));
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "finalize_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
 

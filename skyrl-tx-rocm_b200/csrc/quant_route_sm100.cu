@@ -413,6 +413,18 @@ extern "C" int skyrl_pack_lora_b_sm100_v1(const void* b_arn, int32_t num_adapter
                                  static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int skyrl_pack_lora_b_rows_sm100_v1(const void* b_arn, int32_t num_adapters, int32_t rank, int32_t n,
+                                               void* b_rows, skyrl_stream_t stream) {
+  if (b_arn == nullptr || b_rows == nullptr || num_adapters <= 0 || n <= 0 || rank <= 0 || b_arn == b_rows)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "pack_lora_b_rows: null/aliased buffer or non-positive shape");
+  if (rank > SKYRL_LORA_RANK_PAD)
+    return fail(SKYRL_ERR_UNSUPPORTED, "pack_lora_b_rows: rank %d exceeds %d", rank, SKYRL_LORA_RANK_PAD);
+  const int rr = (rank + 7) / 8 * 8;
+  return run_transpose<uint16_t>(static_cast<const uint16_t*>(b_arn), static_cast<uint16_t*>(b_rows), num_adapters,
+                                 rank, n, static_cast<int64_t>(n) * rr, rr,
+                                 static_cast<size_t>(num_adapters) * n * rr * 2, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, int32_t num_adapters, int32_t* perm,
                                          int32_t* tiles, int32_t* num_tiles, int32_t max_tiles, int32_t* status,
                                          skyrl_stream_t stream) {

@@ -19,6 +19,8 @@
 // Rows live in the adapter-sorted space: every 128-row M tile comes from the
 // tile list and holds rows of one adapter; rows past the tile's count are
 // computed but never stored.  Every wait is bounded (see ptx_sm100.cuh).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -69,8 +71,10 @@ struct GemmParams {
   int bn_eff;       // columns per N tile actually used (multiple of 16, <= BN): MMA N, TMA box rows
   int num_stages;   // pipeline depth and byte pitch of one stage (A tile + bn_eff weight rows)
   int stage_bytes;
-  const float* addend;     // optional fp32 [M, N] added to the dequantised accumulator (row-wise LoRA term)
-  int64_t addend_stride;
+  int k_splits;     // > 1: each tile covers kb_per_split K blocks and writes its int32 partial sums to slab (t % k_splits)
+  int kb_per_split;
+  int64_t slab_stride;  // elements between slabs of the int32 output
+  int a_rows;       // rows of the activation TMA box (64 when the batch has at most 64 rows, else 128)
 };
 
 struct TileCoord {
@@ -150,8 +154,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   const int tm = *p.num_tiles;
   const int bn_eff = p.bn_eff;
   const int tn = (p.n + bn_eff - 1) / bn_eff;
-  const int total = tm * tn;
-  const uint32_t stage_tx = Cfg::A_BYTES + bn_eff * BK;
+  const int ksplits = p.k_splits;
+  const int total = tm * tn * ksplits;
+  const int a_bytes = p.a_rows * BK;  // the MMA still reads 128 rows; rows past a_rows hold stale finite int8
+  const uint32_t stage_tx = a_bytes + bn_eff * BK;
   const int nstages = p.num_stages;
   const int stage_bytes = p.stage_bytes;
   const uint32_t lora_tx = 3 * Cfg::Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES;
@@ -165,16 +171,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       uint32_t phase = 0, lora_it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const TileCoord c = tile_coord(t, tm, tn, band);
+        const TileCoord c = tile_coord(t / ksplits, tm, tn, band);
         const int4 tile = __ldg(p.tiles + c.m_idx);
         const int n0 = c.n_idx * bn_eff;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kb0 = (t % ksplits) * p.kb_per_split;
+        const int kb1 = min(kblocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
           if (!ok) break;
           unsigned char* sa = smem + stage * stage_bytes;
           mbar_expect_tx(&full_bar[stage], stage_tx);
           tma_load_2d(sa, &p.tm_xq, kb * BK, tile.x, &full_bar[stage]);
-          tma_load_3d(sa + Cfg::A_BYTES, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+          tma_load_3d(sa + a_bytes, &p.tm_w, 0, n0, kb, &full_bar[stage]);
           if (++stage == nstages) {
             stage = 0;
             phase ^= 1u;
@@ -205,16 +213,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d = tmem_base + s * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kb0 = (t % ksplits) * p.kb_per_split;
+        const int kb1 = min(kblocks, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
           const uint64_t adesc = make_desc_sw128(sa);
-          const uint64_t bdesc = make_desc_sw128(sa + Cfg::A_BYTES);
+          const uint64_t bdesc = make_desc_sw128(sa + a_bytes);
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K_I8; ++j) {
-            mma_i8(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0 ? 1u : 0u);
+            mma_i8(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb != kb0 || j != 0) ? 1u : 0u);
           }
           mma_commit(&empty_bar[stage]);
           if (++stage == nstages) {
@@ -233,7 +243,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-      const TileCoord c = tile_coord(t, tm, tn, band);
+      const TileCoord c = tile_coord(t / ksplits, tm, tn, band);
       const int4 tile = __ldg(p.tiles + c.m_idx);
       const int n0 = c.n_idx * bn_eff;
       const int n_end = min(p.n, n0 + bn_eff);  // first column this tile does not own
@@ -304,7 +314,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         const int nc = n0 + cc * 32;
         if (EPI == SKYRL_EPI_ACC_I32) {
           if (row_valid) {
-            int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + orow * p.out_stride + nc);
+            // split K: every split owns one [M, N] slab; the consumer adds the slabs (exact in int32)
+            int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + (t % ksplits) * p.slab_stride +
+                                                orow * p.out_stride + nc);
 #pragma unroll
             for (int g = 0; g < 8; ++g)
               if (nc + g * 4 < n_end) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
@@ -324,19 +336,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
             f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
             f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
-          }
-          if (p.addend != nullptr && row_valid) {
-            const float4* ad = reinterpret_cast<const float4*>(p.addend + static_cast<int64_t>(srow) * p.addend_stride + nc);
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (nc + g * 4 < n_end) {
-                const float4 t4 = __ldg(ad + g);
-                f[4 * g + 0] = __fadd_rn(f[4 * g + 0], t4.x);
-                f[4 * g + 1] = __fadd_rn(f[4 * g + 1], t4.y);
-                f[4 * g + 2] = __fadd_rn(f[4 * g + 2], t4.z);
-                f[4 * g + 3] = __fadd_rn(f[4 * g + 3], t4.w);
-              }
-            }
           }
         }
         if (!row_valid) continue;
@@ -448,6 +447,40 @@ static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStre
   }
 }
 
+GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs) {
+  GemmPlan pl;
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;  // planning without a device (workspace queries): the B200 count
+  const int mt_est = (m + BM - 1) / BM;
+  const int kblocks = (k + BK - 1) / BK;
+  const int64_t tiles256 = static_cast<int64_t>(mt_est) * ((n + 255) / 256);
+  pl.bn_eff = 256;
+  pl.k_splits = 1;
+  pl.kb_per_split = kblocks;
+  // 256-wide N tiles when they fill the GPU; otherwise one wave of narrower tiles sized so that every SM
+  // streams an equal share of the weight (the decode shapes are HBM-bound) ...
+  if (tiles256 < sms) {
+    const int per_mtile = sms / mt_est > 0 ? sms / mt_est : 1;
+    int bn = ((n + per_mtile - 1) / per_mtile + 15) / 16 * 16;
+    if (bn < 16) bn = 16;
+    if (bn > 256) bn = 256;
+    pl.bn_eff = bn;
+    if (bn < 96 && epilogue == SKYRL_EPI_ACC_I32 && max_slabs > 1) {
+      // ... unless that makes the tiles so narrow that every CTA re-reads the same activation codes for
+      // little weight data: then keep wide tiles and split K over slabs of the int32 output instead.
+      pl.bn_eff = n >= 256 ? 256 : (n + 15) / 16 * 16;
+      const int tn = (n + pl.bn_eff - 1) / pl.bn_eff;
+      int want = sms / (mt_est * tn);
+      if (want > max_slabs) want = max_slabs;
+      if (want < 1) want = 1;
+      if (want > kblocks) want = kblocks;
+      pl.kb_per_split = (kblocks + want - 1) / want;
+      pl.k_splits = (kblocks + pl.kb_per_split - 1) / pl.kb_per_split;
+    }
+  }
+  return pl;
+}
+
 int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   if (a.struct_size != sizeof(SkyrlW8A8GemmArgs))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: struct_size %u does not match ABI v%d (%zu)", a.struct_size,
@@ -479,26 +512,22 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: output aliases an input");
   if (a.max_tiles <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: max_tiles must be positive");
 
-  // 256-wide N tiles when they fill the GPU; otherwise one wave of narrower tiles sized so that
-  // every SM streams an equal share of the weight (the decode shapes are HBM-bound).
   const int sms = sm_count();
   if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
-  const int mt_est = (a.m + BM - 1) / BM;
-  const int64_t tiles256 = static_cast<int64_t>(mt_est) * ((a.n + 255) / 256);
-  int bn_eff = 256;
-  if (tiles256 < sms) {
-    const int per_mtile = sms / mt_est > 0 ? sms / mt_est : 1;
-    bn_eff = ((a.n + per_mtile - 1) / per_mtile + 15) / 16 * 16;
-    if (bn_eff < 16) bn_eff = 16;
-    if (bn_eff > 256) bn_eff = 256;
+  const GemmPlan pl = plan_gemm(a.m, a.n, a.k, a.epilogue, a.split_k_slabs);
+  int bn_eff = pl.bn_eff;
+  const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
+  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_BN")) {  // tuning aid: force the N tile width
+    const int v = atoi(dbg);
+    if (v >= 16 && v <= 256 && v % 16 == 0) bn_eff = v;
   }
   const int bn = bn_eff > 128 ? 256 : 128;
-  if (a.addend != nullptr && (lora || !aligned16(a.addend) || a.addend_row_stride < a.n || a.addend_row_stride % 4 != 0))
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: addend excludes the tensor-core LoRA term and needs an aligned [M, N] fp32 buffer");
 
   GemmParams p;
   int rc;
-  if ((rc = encode_tmap_2d(&p.tm_xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.k, a.m, a.k, BK, BM))) return rc;
+  if ((rc = encode_tmap_2d(&p.tm_xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.k, a.m, a.k, BK,
+                           (!lora && a.m <= 64) ? 64 : BM)))
+    return rc;
   if ((rc = encode_tmap_3d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, BK, a.n, (a.k + BK - 1) / BK, BK,
                            static_cast<uint64_t>(a.n) * BK, BK, bn_eff)))
     return rc;
@@ -537,13 +566,19 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     // no LoRA operands in shared memory: the whole buffer becomes pipeline stages (deep prefetch for the
     // weight-streaming decode shapes, where bytes in flight per SM decide the achieved HBM bandwidth)
     const int budget = bn == 256 ? GemmCfg<256>::BAR_OFF : GemmCfg<128>::BAR_OFF;
-    p.stage_bytes = BM * BK + (bn_eff * BK + 1023) / 1024 * 1024;
+    p.stage_bytes = (a.m <= 64 ? 64 : BM) * BK + (bn_eff * BK + 1023) / 1024 * 1024;
     p.num_stages = budget / p.stage_bytes;
     if (p.num_stages > GemmCfg<256>::MAX_STAGES) p.num_stages = GemmCfg<256>::MAX_STAGES;
+    if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_STAGES")) {  // tuning aid: cap the pipeline depth
+      const int v = atoi(dbg);
+      if (v >= 1 && v < p.num_stages) p.num_stages = v;
+    }
   }
-  p.addend = a.addend;
-  p.addend_stride = a.addend_row_stride;
-  const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff);
+  p.k_splits = k_splits;
+  p.kb_per_split = kb_per_split;
+  p.slab_stride = static_cast<int64_t>(a.m) * a.out_row_stride;
+  p.a_rows = (!lora && a.m <= 64) ? 64 : BM;
+  const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff) * k_splits;
   const int grid = static_cast<int>(max_total < sms ? max_total : sms);
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
                    : launch_bn<128>(p, a.epilogue, lora, grid, stream);
@@ -554,4 +589,9 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
 extern "C" int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream) {
   if (args == nullptr) return skyrl::fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: args is null");
   return skyrl::launch_gemm(*args, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t split_k_slabs) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return skyrl::plan_gemm(m, n, k, SKYRL_EPI_ACC_I32, split_k_slabs).k_splits;
 }

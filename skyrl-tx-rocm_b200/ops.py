@@ -74,13 +74,15 @@ class PackedW8Weight:
 @dataclass(frozen=True)
 class PackedLoRA:
     """Device format of the LoRA tables of one projection: A as bf16
-    [A, 64, K], B as bf16 [A, Npad, 64], scaling fp32 [A]."""
+    [A, 64, K], B as bf16 [A, Npad, 64] (tensor-core path) and as dense bf16
+    [A, Npad, rr] with rr = rank rounded up to 8 (small-batch path), scaling fp32 [A]."""
 
     a: torch.Tensor
     b: torch.Tensor
     scaling: torch.Tensor
     rank: int
     num_adapters: int
+    b_rows: torch.Tensor | None = None
 
 
 def _validate_exact_bool(name: str, value) -> None:
@@ -224,7 +226,10 @@ def pack_lora(lora_a: torch.Tensor, lora_b: torch.Tensor, lora_scaling, *, in_fe
     lib = _lib.load()
     _lib.check(lib.skyrl_pack_lora_a_sm100_v1(_ptr(a_src), na, kp, r, _ptr(a_packed), _stream()), "pack_lora_a")
     _lib.check(lib.skyrl_pack_lora_b_sm100_v1(_ptr(b_src), na, r, npad, _ptr(b_packed), _stream()), "pack_lora_b")
-    return PackedLoRA(a_packed, b_packed, scaling.contiguous(), r, na)
+    rr = (r + 7) // 8 * 8
+    b_rows = torch.empty((na, npad, rr), dtype=torch.bfloat16, device=lora_a.device)
+    _lib.check(lib.skyrl_pack_lora_b_rows_sm100_v1(_ptr(b_src), na, r, npad, _ptr(b_rows), _stream()), "pack_lora_b_rows")
+    return PackedLoRA(a_packed, b_packed, scaling.contiguous(), r, na, b_rows)
 
 
 # --------------------------------------------------------------------------- #
@@ -360,6 +365,8 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
         a.lora_a_packed = lora.a.data_ptr()
         a.lora_b_packed = lora.b.data_ptr()
         a.lora_scaling = lora.scaling.data_ptr()
+        if lora.b_rows is not None:
+            a.lora_b_rows, a.lora_b_rows_rank = lora.b_rows.data_ptr(), lora.b_rows.shape[2]
     a.adapter_ids = ids.data_ptr() if ids is not None else None
     if residual is not None:
         a.residual = residual.data_ptr()
@@ -539,6 +546,9 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         a.gu_scaling = gate_up_lora.scaling.data_ptr()
         a.dn_a_packed, a.dn_b_packed = down_lora.a.data_ptr(), down_lora.b.data_ptr()
         a.dn_scaling = down_lora.scaling.data_ptr()
+        if gate_up_lora.b_rows is not None and down_lora.b_rows is not None:
+            a.gu_b_rows, a.dn_b_rows = gate_up_lora.b_rows.data_ptr(), down_lora.b_rows.data_ptr()
+            a.b_rows_rank = gate_up_lora.b_rows.shape[2]
     a.adapter_ids = ids.data_ptr() if ids is not None else None
     a.out = out.data_ptr()
     a.workspace = ws.data_ptr()

@@ -30,6 +30,7 @@ def _args(lib_mod, x, w, lora, ids, out, status, workspace=None):
     a.wq, a.sw = w.wq.data_ptr(), w.sw.data_ptr()
     a.lora_a_packed, a.lora_b_packed = lora.a.data_ptr(), lora.b.data_ptr()
     a.lora_scaling = lora.scaling.data_ptr()
+    a.lora_b_rows, a.lora_b_rows_rank = lora.b_rows.data_ptr(), lora.b_rows.shape[2]
     a.adapter_ids = ids.data_ptr()
     a.out, a.out_row_stride = out.data_ptr(), out.stride(0)
     a.status = status.data_ptr()

@@ -7,14 +7,19 @@
 //                                                          columns, z = three bf16 planes, quantized_lora.py:301-304)
 //   out        = epilogue(v)                              (one bf16 cast, then SwiGLU / residual)
 //
-// Roles (192 threads): warps 0-3 drain TMEM (warp w owns TMEM lanes 32w..32w+31),
-// warp 4 is the TMA producer, warp 5 issues the int8 MMAs and owns the TMEM
-// allocation.  Two accumulator stages of BN columns let the epilogue of tile t
+// Roles (320 threads): warps 0-3 and 6-9 drain TMEM (warp w owns TMEM lanes
+// 32 (w % 4) .. +31; the two warps of a lane quadrant split the tile's columns,
+// and two warps per scheduler hide each other's latencies in the SwiGLU math),
+// warp 4 is the TMA producer, warp 5 issues the MMAs and owns the TMEM allocation.  Two accumulator stages of BN columns let the epilogue of tile t
 // overlap the main loop of tile t+1.  The LoRA term does not get accumulator
 // columns of its own (2 x 256 int32 columns already fill the 512-column TMEM):
 // the epilogue rewrites the int32 accumulator in place as dequantised fp32,
-// then one elected epilogue thread issues the rank-r bf16 MMAs that accumulate
-// z @ B^T onto it, and the tile is read back a second time for the final cast.
+// the MMA warp then issues the rank-r bf16 MMAs that accumulate z @ B^T onto
+// it, and the tile is read back a second time for the final cast.  The LoRA
+// operands (three z planes, one B tile) have no shared memory of their own
+// either: they travel through two slots of the same TMA pipeline, injected
+// into the stream of the NEXT tile's K blocks, so the whole buffer serves
+// pipeline depth (the main loop is bound by bytes in flight per SM).
 //
 // Rows live in the adapter-sorted space: every 128-row M tile comes from the
 // tile list and holds rows of one adapter; rows past the tile's count are
@@ -29,23 +34,19 @@ namespace skyrl {
 constexpr int BM = 128;       // rows per tile == TMEM lanes
 constexpr int BK = 128;       // int8 elements (bytes) of K per pipeline stage: one 128-byte swizzled row
 constexpr int UMMA_K_I8 = 32; // K of one kind::i8 instruction
-constexpr int GEMM_THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int GEMM_THREADS = 320;  // warps 0-3 and 6-9 epilogue, warp 4 TMA producer, warp 5 MMA issuer
+constexpr int EPI_THREADS = 256;
 constexpr int LORA_ROW_BYTES = SKYRL_LORA_RANK_PAD * 2;  // 128-byte rows of z and packed B
+
+constexpr int STAGE_AREA_BYTES = 224 * 1024;  // shared memory given to the TMA pipeline stages
+constexpr int MAX_STAGES = 12;
+constexpr int Z_PLANE_BYTES = BM * LORA_ROW_BYTES;  // one bf16 plane of z for a tile: 128 rows x 128 bytes
+constexpr int LORA_INJECT_AFTER = 8;  // K blocks of the next tile issued before the previous tile's LoRA operands
 
 template <int BN>
 struct GemmCfg {
-  static constexpr int STAGES = (BN == 256) ? 3 : 5;
-  static constexpr int A_BYTES = BM * BK;
-  static constexpr int B_BYTES = BN * BK;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int Z_OFF = STAGES * STAGE_BYTES;        // three planes (hi, mid, lo) of BM x 128 bytes
-  static constexpr int Z_PLANE_BYTES = BM * LORA_ROW_BYTES;
-  static constexpr int BT_OFF = Z_OFF + 3 * Z_PLANE_BYTES;
-  static constexpr int LORA_BYTES = 3 * Z_PLANE_BYTES + BN * LORA_ROW_BYTES;
-  static constexpr int BAR_OFF = BT_OFF + BN * LORA_ROW_BYTES;
-  static constexpr int MAX_STAGES = 12;  // the LoRA-free variants reuse the LoRA operand space for extra stages
-  static constexpr int NUM_BARS = 2 * MAX_STAGES + 4 + 4;
+  static constexpr int BAR_OFF = STAGE_AREA_BYTES;
+  static constexpr int NUM_BARS = 2 * MAX_STAGES + 4 + 2;
   static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr/abort + alignment slack
   static constexpr int TMEM_COLS = 2 * BN;
 };
@@ -53,7 +54,7 @@ struct GemmCfg {
 struct GemmParams {
   CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
   CUtensorMap tm_w;    // int8 [K / 128, N, 128], box 128 x bn_eff x 1
-  CUtensorMap tm_z;    // bf16 [3, M, 64], box 64 x 128 x 3
+  CUtensorMap tm_z;    // bf16 [3, M, 64], box 64 x 128 x 1 (one plane of one tile)
   CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
   const float* sx;
   const float* sw;
@@ -105,12 +106,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + Cfg::MAX_STAGES;
-  uint64_t* tmem_full = bars + 2 * Cfg::MAX_STAGES;   // [2]
+  uint64_t* empty_bar = bars + MAX_STAGES;
+  uint64_t* tmem_full = bars + 2 * MAX_STAGES;        // [2]
   uint64_t* tmem_empty = tmem_full + 2;               // [2]
-  uint64_t* lora_full = tmem_empty + 2;               // TMA -> LoRA operands landed
-  uint64_t* lora_empty = lora_full + 1;               // LoRA MMAs done reading smem
-  uint64_t* conv_done = lora_empty + 1;               // 128 epilogue threads rewrote the accumulator
+  uint64_t* conv_done = tmem_empty + 2;               // 128 epilogue threads rewrote the accumulator
   uint64_t* lora_done = conv_done + 1;                // LoRA MMAs accumulated into TMEM
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
@@ -119,7 +118,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::MAX_STAGES; ++s) {
+    for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -127,8 +126,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       mbar_init(&tmem_full[s], 1);
       mbar_init(&tmem_empty[s], EPI_THREADS);
     }
-    mbar_init(lora_full, 1);
-    mbar_init(lora_empty, 1);
     mbar_init(conv_done, EPI_THREADS);
     mbar_init(lora_done, 1);
     *abort_flag = 0;
@@ -160,7 +157,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   const uint32_t stage_tx = a_bytes + bn_eff * BK;
   const int nstages = p.num_stages;
   const int stage_bytes = p.stage_bytes;
-  const uint32_t lora_tx = 3 * Cfg::Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES;
+
   const int kblocks = (p.k + BK - 1) / BK;
   const int band = min(p.band, max(tm, 1));
 
@@ -168,14 +165,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0, lora_it = 0;
-      bool ok = true;
+      uint32_t phase = 0;
+      bool ok = true, have_prev = false;
+      int prev_row0 = 0, prev_n0 = 0, prev_adapter = 0;
+      // LoRA operands of one tile: slot 1 = z planes lo and mid, slot 2 = z plane hi and the B tile
+      auto lora_slots = [&](int row0, int n0, int adapter) -> bool {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+        unsigned char* sa = smem + stage * stage_bytes;
+        mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
+        tma_load_3d(sa, &p.tm_z, 0, row0, 2, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, row0, 1, &full_bar[stage]);
+        if (++stage == nstages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+        sa = smem + stage * stage_bytes;
+        mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES);
+        tma_load_3d(sa, &p.tm_z, 0, row0, 0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
+        if (++stage == nstages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        return true;
+      };
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         const TileCoord c = tile_coord(t / ksplits, tm, tn, band);
         const int4 tile = __ldg(p.tiles + c.m_idx);
         const int n0 = c.n_idx * bn_eff;
         const int kb0 = (t % ksplits) * p.kb_per_split;
         const int kb1 = min(kblocks, kb0 + p.kb_per_split);
+        const int inject_at = min(LORA_INJECT_AFTER, kb1 - kb0);
+        int issued = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
           if (!ok) break;
@@ -187,26 +209,56 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             stage = 0;
             phase ^= 1u;
           }
+          if (HAS_LORA && have_prev && ++issued == inject_at) {
+            ok = lora_slots(prev_row0, prev_n0, prev_adapter);
+            if (!ok) break;
+          }
         }
-        if (HAS_LORA && ok) {
-          // Issued after the tile's main-loop loads so that waiting for the
-          // previous tile's LoRA MMAs never delays the weight stream.
-          ok = mbar_wait(lora_empty, (lora_it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
-          if (!ok) break;
-          mbar_expect_tx(lora_full, lora_tx);
-          tma_load_3d(smem + Cfg::Z_OFF, &p.tm_z, 0, tile.x, 0, lora_full);
-          tma_load_3d(smem + Cfg::BT_OFF, &p.tm_b, 0, n0, tile.z, lora_full);
-          ++lora_it;
-        }
+        prev_row0 = tile.x;
+        prev_n0 = n0;
+        prev_adapter = tile.z;
+        have_prev = true;
       }
+      if (HAS_LORA && have_prev && ok) lora_slots(prev_row0, prev_n0, prev_adapter);
     }
   } else if (warp == 5) {
-    // ------------------------------ int8 MMA issuer ---------------------------
+    // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
       const uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, BM, bn_eff);
+      const uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, bn_eff);
       int stage = 0;
-      uint32_t phase = 0, it = 0;
-      bool ok = true;
+      uint32_t phase = 0, it = 0, lora_rounds = 0;
+      bool ok = true, have_prev = false;
+      uint32_t prev_s = 0;
+      // rank-r bf16 MMAs of one tile, accumulated onto the accumulator the epilogue rewrote as fp32
+      auto lora_mma = [&](uint32_t acc_stage) -> bool {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        const int st1 = stage;
+        if (++stage == nstages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        const int st2 = stage;
+        if (++stage == nstages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (!mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        tc_fence_after_sync();
+        const uint32_t e1 = smem_u32(smem + st1 * stage_bytes), e2 = smem_u32(smem + st2 * stage_bytes);
+        const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
+        const uint64_t zd[3] = {make_desc_sw128(e1), make_desc_sw128(e1 + Z_PLANE_BYTES), make_desc_sw128(e2)};
+        const uint32_t d = tmem_base + acc_stage * BN;
+        // smallest plane first, so the low-order terms are not absorbed early
+        for (int plane = 0; plane < 3; ++plane)
+          for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16(d, zd[plane] + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+        mma_commit(&empty_bar[st1]);
+        mma_commit(&empty_bar[st2]);
+        mma_commit(lora_done);
+        ++lora_rounds;
+        return true;
+      };
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
         const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
         ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
@@ -215,6 +267,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         const uint32_t d = tmem_base + s * BN;
         const int kb0 = (t % ksplits) * p.kb_per_split;
         const int kb1 = min(kblocks, kb0 + p.kb_per_split);
+        const int inject_at = min(LORA_INJECT_AFTER, kb1 - kb0);
+        int issued = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
           if (!ok) break;
@@ -231,15 +285,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             stage = 0;
             phase ^= 1u;
           }
+          if (HAS_LORA && have_prev && ++issued == inject_at) {
+            ok = lora_mma(prev_s);
+            if (!ok) break;
+          }
         }
         if (ok) mma_commit(&tmem_full[s]);
+        prev_s = s;
+        have_prev = true;
       }
+      if (HAS_LORA && have_prev && ok) lora_mma(prev_s);
     }
   } else {
-    // ------------------------------ epilogue warps 0-3 -------------------------
-    const uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, bn_eff);
+    // ------------------------------ epilogue warps 0-3, 6-9 --------------------
     const int nchunks = (bn_eff + 31) / 32;
-    const int r = warp * 32 + lane;  // row of the tile == TMEM lane
+    const int quad = warp & 3;                        // TMEM lane quadrant this warp may access
+    const int c_begin = warp < 4 ? 0 : (nchunks + 1) / 2;  // column chunks [c_begin, c_end) of the tile
+    const int c_end = warp < 4 ? (nchunks + 1) / 2 : nchunks;
+    const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
@@ -256,12 +319,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[s], aphase, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t tbase = tmem_base + s * BN + (static_cast<uint32_t>(warp * 32) << 16);
+      const uint32_t tbase = tmem_base + s * BN + (static_cast<uint32_t>(quad * 32) << 16);
 
       if (HAS_LORA) {
         // pass 1: int32 accumulator -> dequantised fp32, in place
 #pragma unroll 1
-        for (int cc = 0; cc < nchunks; ++cc) {
+        for (int cc = c_begin; cc < c_end; ++cc) {
           uint32_t v[32];
           __syncwarp();
           tmem_ld32(tbase + cc * 32, v);
@@ -281,22 +344,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(conv_done);
-        if (threadIdx.x == 0) {
-          bool lok = mbar_wait(conv_done, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA);
-          lok = lok && mbar_wait(lora_full, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA);
-          if (lok) {
-            tc_fence_after_sync();
-            const uint64_t bd = make_desc_sw128(smem_u32(smem + Cfg::BT_OFF));
-            const uint32_t d = tmem_base + s * BN;
-            // smallest plane first, so the low-order terms are not absorbed early
-            for (int plane = 2; plane >= 0; --plane) {
-              const uint64_t zd = make_desc_sw128(smem_u32(smem + Cfg::Z_OFF + plane * Cfg::Z_PLANE_BYTES));
-              for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16(d, zd + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
-            }
-            mma_commit(lora_empty);
-            mma_commit(lora_done);
-          }
-        }
         __syncwarp();
         ok = __all_sync(0xffffffffu, mbar_wait(lora_done, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA));
         if (!ok) break;
@@ -306,7 +353,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 
       // pass 2: final values -> global memory
 #pragma unroll 1
-      for (int cc = 0; cc < nchunks; ++cc) {
+      for (int cc = c_begin; cc < c_end; ++cc) {
         uint32_t v[32];
         __syncwarp();
         tmem_ld32(tbase + cc * 32, v);
@@ -533,7 +580,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     return rc;
   if (lora) {
     if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, a.m, 3,
-                             LORA_ROW_BYTES, static_cast<uint64_t>(a.m) * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM, 3)))
+                             LORA_ROW_BYTES, static_cast<uint64_t>(a.m) * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM, 1)))
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
@@ -559,25 +606,19 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   p.rank_blocks = (a.rank + 15) / 16;
   p.band = 16;
   p.bn_eff = bn_eff;
-  if (lora) {
-    p.num_stages = bn == 256 ? GemmCfg<256>::STAGES : GemmCfg<128>::STAGES;
-    p.stage_bytes = bn == 256 ? GemmCfg<256>::STAGE_BYTES : GemmCfg<128>::STAGE_BYTES;
-  } else {
-    // no LoRA operands in shared memory: the whole buffer becomes pipeline stages (deep prefetch for the
-    // weight-streaming decode shapes, where bytes in flight per SM decide the achieved HBM bandwidth)
-    const int budget = bn == 256 ? GemmCfg<256>::BAR_OFF : GemmCfg<128>::BAR_OFF;
-    p.stage_bytes = (a.m <= 64 ? 64 : BM) * BK + (bn_eff * BK + 1023) / 1024 * 1024;
-    p.num_stages = budget / p.stage_bytes;
-    if (p.num_stages > GemmCfg<256>::MAX_STAGES) p.num_stages = GemmCfg<256>::MAX_STAGES;
-    if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_STAGES")) {  // tuning aid: cap the pipeline depth
-      const int v = atoi(dbg);
-      if (v >= 1 && v < p.num_stages) p.num_stages = v;
-    }
+  // The whole stage area is pipeline depth: the main loop is bound by bytes in flight per SM.
+  p.a_rows = (!lora && a.m <= 64) ? 64 : BM;
+  p.stage_bytes = p.a_rows * BK + (bn_eff * BK + 1023) / 1024 * 1024;
+  if (lora && p.stage_bytes < 2 * Z_PLANE_BYTES) p.stage_bytes = 2 * Z_PLANE_BYTES;  // a slot also carries two z planes
+  p.num_stages = STAGE_AREA_BYTES / p.stage_bytes;
+  if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
+  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_STAGES")) {  // tuning aid: cap the pipeline depth
+    const int v = atoi(dbg);
+    if (v >= 2 && v < p.num_stages) p.num_stages = v;
   }
   p.k_splits = k_splits;
   p.kb_per_split = kb_per_split;
   p.slab_stride = static_cast<int64_t>(a.m) * a.out_row_stride;
-  p.a_rows = (!lora && a.m <= 64) ? 64 : BM;
   const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff) * k_splits;
   const int grid = static_cast<int>(max_total < sms ? max_total : sms);
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)

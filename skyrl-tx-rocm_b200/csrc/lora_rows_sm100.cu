@@ -113,6 +113,7 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
 #pragma unroll
   for (int r = 0; r < ROWQ_CLUSTER; ++r) row_amax = fmaxf(row_amax, *cluster.map_shared_rank(&part_amax, r));
   const float scale = row_amax > 0.f ? __fdiv_rn(row_amax, 127.0f) : 1.0f;
+  const float rcp = quant_rcp(scale);
   if (crank == 0 && threadIdx.x == 0) sx[m] = scale;
 
   const int adapter = ids != nullptr ? ids[m] : 0;
@@ -126,19 +127,15 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     const uint4 u = slice[v];
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
     float xv[8];
-    uint32_t packed[2] = {0u, 0u};
+    int q[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       xv[2 * j] = bf16_lo(w[j]);
       xv[2 * j + 1] = bf16_hi(w[j]);
-      int qa = __float2int_rn(__fdiv_rn(xv[2 * j], scale));
-      int qb = __float2int_rn(__fdiv_rn(xv[2 * j + 1], scale));
-      qa = max(-127, min(127, qa));
-      qb = max(-127, min(127, qb));
-      const uint32_t two = (static_cast<uint32_t>(qa) & 0xffu) | ((static_cast<uint32_t>(qb) & 0xffu) << 8);
-      packed[j >> 1] |= two << ((j & 1) * 16);
+      q[2 * j] = quant_code(xv[2 * j], scale, rcp);
+      q[2 * j + 1] = quant_code(xv[2 * j + 1], scale, rcp);
     }
-    dst[v] = make_uint2(packed[0], packed[1]);
+    dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
 #pragma unroll
     for (int j = 0; j < R; ++j) {
       const uint4 aw = __ldg(a_base + static_cast<int64_t>(j) * nvec + v);

@@ -235,4 +235,28 @@ __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// int8 code of one activation: clip(rint(x / scale), -127, 127) with x / scale the IEEE fp32 quotient
+// (skyrl/tx/kernels/quantized_lora.py:209).  The quotient is first estimated as x * rcp with
+// rcp = RN(1 / scale): the estimate and the IEEE quotient both lie within 2.3e-5 of the exact value
+// for |x / scale| <= 127, so they round to the same integer unless the estimate is within that
+// distance of a half-integer; only then (about 1 element in 5000) the IEEE division is evaluated.
+// `rcp` is NaN for scales outside the range where that bound holds (quant_rcp), which sends every
+// element of such a row down the IEEE path.
+__device__ __forceinline__ float quant_rcp(float scale) {
+  return (scale > 1e-30f && scale < 1e30f) ? __frcp_rn(scale) : __int_as_float(0x7fc00000);
+}
+__device__ __forceinline__ int quant_code(float x, float scale, float rcp) {
+  float t = __fmul_rn(x, rcp);
+  if (!(fabsf(__fsub_rn(t, rintf(t))) <= 0.4999f)) t = __fdiv_rn(x, scale);
+  int q;  // round to nearest even and saturate to int8; |t| <= 127.00003, so -128 never appears
+  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(t));
+  return q;
+}
+// Four int8 codes (held sign-extended in 32-bit registers) -> one little-endian word.
+__device__ __forceinline__ uint32_t pack_codes4(int a, int b, int c, int d) {
+  const uint32_t lo = __byte_perm(static_cast<uint32_t>(a), static_cast<uint32_t>(b), 0x0040);
+  const uint32_t hi = __byte_perm(static_cast<uint32_t>(c), static_cast<uint32_t>(d), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
+
 }  // namespace skyrl

@@ -191,23 +191,20 @@ rms_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, cons
   }
   amax = block_reduce(amax, true, red);
   const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+  const float rcp = quant_rcp(scale);
   if (threadIdx.x == 0) sx[out_row] = scale;
 
   uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(out_row) * k);
   for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
     const uint4 u = row[v];
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-    uint32_t packed[2] = {0u, 0u};
+    int q[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      int qa = __float2int_rn(__fdiv_rn(bf16_lo(w[j]), scale));
-      int qb = __float2int_rn(__fdiv_rn(bf16_hi(w[j]), scale));
-      qa = max(-127, min(127, qa));
-      qb = max(-127, min(127, qb));
-      const uint32_t two = (static_cast<uint32_t>(qa) & 0xffu) | ((static_cast<uint32_t>(qb) & 0xffu) << 8);
-      packed[j >> 1] |= two << ((j & 1) * 16);
+      q[2 * j] = quant_code(bf16_lo(w[j]), scale, rcp);
+      q[2 * j + 1] = quant_code(bf16_hi(w[j]), scale, rcp);
     }
-    dst[v] = make_uint2(packed[0], packed[1]);
+    dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
   }
 }
 

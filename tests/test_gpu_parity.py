@@ -128,6 +128,26 @@ def test_activation_codes_and_scales_are_bit_exact(S, m, k):
     np.testing.assert_array_equal(to_np(xq), codes[:, 0, :])
 
 
+@pytest.mark.parametrize("m", [16, 200])
+def test_activation_codes_tiny_huge_and_tie_rows(S, m):
+    # rows scaled into the subnormal / near-overflow ranges, and rows full of exact .5 quotients
+    k = 512
+    rng = np.random.default_rng(m)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[0] *= 1e-38
+    x[1] *= 1e-41
+    x[2] *= 1e36
+    x[3] = (rng.integers(-254, 255, size=k) / 2.0)          # amax 127 -> scale 1.0 -> quotients k + 0.5
+    x[3, 0] = 127.0
+    x[4] = (rng.integers(-254, 255, size=k) / 2.0) * 0.25
+    x[4, 0] = 31.75
+    x = x.astype(BF16)
+    xq, sx, _ = S.rms_quant(to_dev(x))
+    codes, scales = O.dynamic_group_quantize(x, k)
+    np.testing.assert_array_equal(to_np(sx), scales[:, 0])
+    np.testing.assert_array_equal(to_np(xq), codes[:, 0, :])
+
+
 def test_quantiser_row_gather(S):
     rng = np.random.default_rng(3)
     x = rng.standard_normal((50, 256)).astype(np.float32).astype(BF16)

@@ -170,6 +170,8 @@ def run_device(args):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            del os.environ["NCCL_DEBUG"]  # its banner goes to stdout; this program prints exactly one JSON line
         dist.init_process_group("nccl", device_id=device)
 
     import skyrl_tx_rocm_b200 as S
@@ -205,11 +207,11 @@ def run_device(args):
             gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * ish, alpha, seed * 131 + rank * 7 + 3, device)
             dn_l = synth_lora(S, torch, wl["adapters"], ish, wl["rank"], hidden, alpha, seed * 131 + rank * 7 + 4, device)
             blocks.append((delta, gu_w, gu_l, dn_w, dn_l))
-        tp_blocks = None
+        tp_stack = None
         if tp > 1:
-            from skyrl_tx_rocm_b200.tp import TensorParallelMLP
+            from skyrl_tx_rocm_b200.tp import TensorParallelMLP, TensorParallelMLPStack
 
-            tp_blocks = [TensorParallelMLP(*b) for b in blocks]
+            tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks)
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
@@ -226,16 +228,15 @@ def run_device(args):
         launches_per_step = layers * (6 + (1 if tp > 1 else 0)) + 1
 
         def step(x_in, ids_in, events=None):
+            if tp > 1:
+                return tp_stack.forward(x_in, ids_in, timing_events=events)
             cur = x_in
             for l, (delta, gu_w, gu_l, dn_w, dn_l) in enumerate(blocks):
                 ev = events[l] if events is not None else None
                 dst = act[l & 1]
                 # adapter ids are the same for every layer of a step: route once, then reuse
-                if tp == 1:
-                    S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev,
-                                     reuse_routing=l > 0)
-                else:
-                    tp_blocks[l].forward(cur, ids_in, out=dst, timing_events=ev, reuse_routing=l > 0)
+                S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev,
+                                 reuse_routing=l > 0)
                 cur = dst
             return cur
     else:
@@ -411,7 +412,8 @@ def run_device(args):
         "data": "synthetic, seeded; random-init weights of the named shapes",
         "config": {"workload": args.workload, "kind": kind, "tokens": m, "layers": layers,
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
-                   "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None, "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
+                   "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
+                   **({"tp_chunks": args.tp_chunks} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -525,6 +527,8 @@ def main():
     ap.add_argument("--m", type=int, default=0, help="override the token count (debugging)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging / small ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-chunks", type=int, default=4,
+                    help="row chunks per block whose all-reduce overlaps the next chunk's kernels (N > 1)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()

@@ -148,7 +148,8 @@ typedef struct SkyrlW8A8GemmArgs {
                                (<= 1: no split).  The kernel may split K over up to that many CTAs per
                                tile; split s writes its partial sums to slab s and the caller adds the
                                skyrl_w8a8_gemm_k_splits(...) slabs (int32 addition is exact)      */
-  int32_t reserved;
+  int32_t cta_limit;        /* > 0: launch at most this many CTAs (one per SM otherwise), so that a
+                               collective running on another stream finds free SMs            */
 } SkyrlW8A8GemmArgs;
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
@@ -272,6 +273,13 @@ typedef struct SkyrlW8A8MlpArgs {
   int32_t b_rows_rank;       /* row length of the dense LoRA-B tables below */
   const void* gu_b_rows;     /* optional dense tables bf16 [A, 2I, b_rows_rank] / [A, H, b_rows_rank] for the */
   const void* dn_b_rows;     /* small-batch path (see SkyrlW8A8LinearArgs.lora_b_rows)                        */
+  int32_t num_chunks;        /* > 1 (and m > 128): the adapter-sorted rows are cut into this many chunks of   */
+  int32_t chunk_index;       /* ceil(m / num_chunks / 128) * 128 rows and this call computes chunk            */
+                             /* chunk_index only (rows [chunk_index * chunk_rows, ...) of the sorted order),  */
+                             /* so that a caller can reduce chunk c over ranks while chunk c + 1 computes.    */
+                             /* The first call of a block (without SKYRL_MLP_REUSE_ROUTING) routes all chunks. */
+  int32_t gemm_cta_limit;    /* > 0: cap on the CTAs of the GEMM launches (see SkyrlW8A8GemmArgs.cta_limit)   */
+  int32_t reserved;
 } SkyrlW8A8MlpArgs;
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);

@@ -41,7 +41,7 @@ class GemmArgs(C.Structure):
         ("tiles", C.c_void_p), ("num_tiles", C.c_void_p), ("out_row_map", C.c_void_p),
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
-        ("split_k_slabs", C.c_int32), ("reserved", C.c_int32),
+        ("split_k_slabs", C.c_int32), ("cta_limit", C.c_int32),
     ]
 
 
@@ -72,6 +72,7 @@ class MlpArgs(C.Structure):
         ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("timing_events", C.c_void_p * 4),
         ("flags", C.c_uint32), ("b_rows_rank", C.c_int32), ("gu_b_rows", C.c_void_p), ("dn_b_rows", C.c_void_p),
+        ("num_chunks", C.c_int32), ("chunk_index", C.c_int32), ("gemm_cta_limit", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

@@ -81,8 +81,19 @@ int sm_count() {
 // ---- workspace carving -------------------------------------------------------
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-static inline int max_tiles_for(int m, int num_adapters) {
-  return (m + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS + (num_adapters > 0 ? num_adapters : 1);
+constexpr int MAX_CHUNKS = 16;
+
+// Tiles one chunk of `rows` sorted rows can hold: every adapter may end a partial tile inside it.
+static inline int tile_cap(int rows, int num_adapters) {
+  return (rows + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS + (num_adapters > 0 ? num_adapters : 1) + 1;
+}
+static inline int max_tiles_for(int m, int num_adapters) { return tile_cap(m, num_adapters); }
+// Capacity of the tile buffer: the unchunked list, or MAX_CHUNKS per-chunk lists, whichever is larger.
+static inline size_t tile_buffer_slots(int m, int num_adapters) {
+  const size_t whole = static_cast<size_t>(max_tiles_for(m, num_adapters));
+  const size_t chunked = static_cast<size_t>(m) / SKYRL_TILE_ROWS + 2 * MAX_CHUNKS +
+                         static_cast<size_t>(MAX_CHUNKS) * ((num_adapters > 0 ? num_adapters : 1) + 1);
+  return whole > chunked ? whole : chunked;
 }
 
 struct Carver {
@@ -155,8 +166,9 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   MlpWs w;
   const int mt = max_tiles_for(m, num_adapters);
   w.perm = c.take<int32_t>(m);
-  w.tiles = c.take<int32_t>(4 * static_cast<size_t>(mt));
-  w.num_tiles = c.take<int32_t>(4);
+  (void)mt;
+  w.tiles = c.take<int32_t>(4 * tile_buffer_slots(m, num_adapters));
+  w.num_tiles = c.take<int32_t>(MAX_CHUNKS + 4);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
   w.sx = c.take<float>(m);
   w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
@@ -198,6 +210,8 @@ struct Projection {
   const int32_t* gather;  // row gather for the quantiser (sorted route) or NULL
   bool keep_xn;           // sorted route: x must be re-laid out (gathered / normalised) for the projection MMA
   int m, n, k, rank, na, mt;
+  int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
+  int cta_limit;
   const void* wq;
   const float* sw;
   const void* a_packed;
@@ -265,8 +279,13 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   }
   {
     const bool need_xn = lora && q.keep_xn;
-    if ((rc = launch_rms_quant(q.x, q.x_stride, q.rms_delta, q.eps, q.gather, q.m, q.k, q.xq, q.sx,
-                               need_xn ? q.xn : nullptr, stream)))
+    const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
+    // a gather reads rows perm[r0 ...] of x; without one the chunk's rows are rows r0 ... of x itself
+    const unsigned char* xsrc = static_cast<const unsigned char*>(q.x) +
+                                (q.gather != nullptr ? 0 : static_cast<size_t>(r0) * q.x_stride * 2);
+    if ((rc = launch_rms_quant(xsrc, q.x_stride, q.rms_delta, q.eps, q.gather != nullptr ? q.gather + r0 : nullptr,
+                               rows, q.k, q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
+                               need_xn ? q.xn + static_cast<size_t>(r0) * q.k : nullptr, stream)))
       return rc;
     if (lora) {
       const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
@@ -297,6 +316,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   g.out_row_stride = q.out_stride;
   g.residual_row_stride = q.residual_stride;
   g.status = q.status;
+  g.cta_limit = q.cta_limit;
   if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
   rc = launch_gemm(g, stream);
   if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
@@ -412,14 +432,26 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   const MlpWs w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, na);
   int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "mlp");
   if (rc) return rc;
-  const int mt = max_tiles_for(a->m, na);
   const bool rows_path = a->m <= ROWS_PATH_MAX_M;
   const bool routed = a->adapter_ids != nullptr && !rows_path;
   const int32_t* perm = routed ? w.perm : nullptr;
+  const bool chunked = a->num_chunks > 1 && !rows_path;
+  if (chunked && (a->num_chunks > MAX_CHUNKS || a->chunk_index < 0 || a->chunk_index >= a->num_chunks))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: num_chunks must be <= %d and chunk_index inside it", MAX_CHUNKS);
+  const int chunk_rows =
+      chunked ? ((a->m + a->num_chunks - 1) / a->num_chunks + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS * SKYRL_TILE_ROWS
+              : 0;
+  const int chunk_cap = chunked ? tile_cap(chunk_rows, na) : 0;
+  const int mt = chunked ? chunk_cap : max_tiles_for(a->m, na);
+  const int row0 = chunked ? a->chunk_index * chunk_rows : 0;
+  const int rows = chunked ? (a->m - row0 < chunk_rows ? a->m - row0 : chunk_rows) : a->m;
+  if (rows <= 0) return SKYRL_OK;  // more chunks than rows: nothing to do for this one
+  const int32_t* tiles = chunked ? w.tiles + 4 * static_cast<size_t>(a->chunk_index) * chunk_cap : w.tiles;
+  const int32_t* num_tiles = chunked ? w.num_tiles + a->chunk_index : w.num_tiles;
 
   if ((a->flags & SKYRL_MLP_REUSE_ROUTING) == 0) {
-    if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status,
-                           stream)))
+    if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles,
+                           static_cast<int>(tile_buffer_slots(a->m, na)), a->status, stream, chunk_rows, chunk_cap)))
       return rc;
   }
 
@@ -437,6 +469,9 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.rank = a->rank;
   q.na = na;
   q.mt = mt;
+  q.q_row0 = row0;
+  q.q_rows = rows;
+  q.cta_limit = a->gemm_cta_limit;
   q.wq = a->gu_wq;
   q.sw = a->gu_sw;
   q.a_packed = a->gu_a_packed;
@@ -450,8 +485,8 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.acc = w.acc;
   q.b_rows = a->gu_b_rows;
   q.b_rows_rank = a->b_rows_rank;
-  q.tiles = w.tiles;
-  q.num_tiles = w.num_tiles;
+  q.tiles = tiles;
+  q.num_tiles = num_tiles;
   q.epilogue = SKYRL_EPI_SWIGLU;
   q.out_row_map = nullptr;
   q.out = w.h;

@@ -27,7 +27,7 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 // kernel launchers implemented in the .cu files
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
-                 int max_tiles, int32_t* status, cudaStream_t stream);
+                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0);
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,

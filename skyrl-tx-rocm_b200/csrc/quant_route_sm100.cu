@@ -16,28 +16,40 @@ namespace skyrl {
 constexpr int ROUTE_THREADS = 1024;
 constexpr int ROUTE_MAX_ADAPTERS = 4096;
 
+// Tile lists.  With chunk_rows == 0 there is one list at `tiles` and its length at num_tiles[0].
+// With chunk_rows > 0 (a multiple of 128) the sorted row space is cut at multiples of chunk_rows and
+// chunk c gets its own list at tiles + 4 * c * chunk_cap with its length at num_tiles[c]; no tile
+// crosses a chunk boundary, so the chunks of a block can be computed and reduced independently.
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* __restrict__ perm,
-             int32_t* __restrict__ tiles, int32_t* __restrict__ num_tiles, int max_tiles, int32_t* status) {
+             int32_t* __restrict__ tiles, int32_t* __restrict__ num_tiles, int max_tiles, int chunk_rows,
+             int chunk_cap, int32_t* status) {
   __shared__ int counts[ROUTE_MAX_ADAPTERS];
   __shared__ int cursor[ROUTE_MAX_ADAPTERS];
   const int tid = threadIdx.x;
+  const int num_chunks = chunk_rows > 0 ? (m + chunk_rows - 1) / chunk_rows : 1;
+  const int cap = chunk_rows > 0 ? chunk_cap : max_tiles;
+  const int span = chunk_rows > 0 ? chunk_rows : m;
 
   if (ids == nullptr) {
     for (int i = tid; i < m; i += ROUTE_THREADS) perm[i] = i;
-    const int nt = (m + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS;
-    if (nt > max_tiles) {
-      if (tid == 0) {
-        atomicCAS(status, 0, STATUS_TILE_OVERFLOW);
-        *num_tiles = 0;
-      }
+    const int per_chunk = (span + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS;
+    if (per_chunk > cap) {
+      if (tid == 0) atomicCAS(status, 0, STATUS_TILE_OVERFLOW);
+      for (int c = tid; c < num_chunks; c += ROUTE_THREADS) num_tiles[c] = 0;
       return;
     }
+    const int nt = (m + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS;
     for (int t = tid; t < nt; t += ROUTE_THREADS) {
       const int r0 = t * SKYRL_TILE_ROWS;
-      reinterpret_cast<int4*>(tiles)[t] = make_int4(r0, min(SKYRL_TILE_ROWS, m - r0), 0, 0);
+      const int c = r0 / span;  // chunk_rows is a multiple of the tile height, so tiles never straddle
+      const int slot = c * cap + (r0 - c * span) / SKYRL_TILE_ROWS;
+      reinterpret_cast<int4*>(tiles)[slot] = make_int4(r0, min(SKYRL_TILE_ROWS, m - r0), 0, 0);
     }
-    if (tid == 0) *num_tiles = nt;
+    for (int c = tid; c < num_chunks; c += ROUTE_THREADS) {
+      const int rows = min(span, m - c * span);
+      num_tiles[c] = (rows + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS;
+    }
     return;
   }
 
@@ -53,26 +65,36 @@ route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* 
   }
   __syncthreads();
   if (tid == 0) {
-    int start = 0, t = 0;
+    int start = 0, chunk = 0, in_chunk = 0;
     bool overflow = false;
     for (int a = 0; a < num_adapters; ++a) {
       const int cnt = counts[a];
       cursor[a] = start;
-      for (int off = 0; off < cnt; off += SKYRL_TILE_ROWS) {
-        if (t < max_tiles) {
-          reinterpret_cast<int4*>(tiles)[t] = make_int4(start + off, min(SKYRL_TILE_ROWS, cnt - off), a, 0);
+      int off = 0;
+      while (off < cnt) {
+        const int r0 = start + off;
+        while (r0 >= (chunk + 1) * span) {  // close the chunks this row has passed
+          num_tiles[chunk] = in_chunk;
+          ++chunk;
+          in_chunk = 0;
+        }
+        const int rows = min(min(SKYRL_TILE_ROWS, cnt - off), (chunk + 1) * span - r0);
+        if (in_chunk < cap) {
+          reinterpret_cast<int4*>(tiles)[chunk * cap + in_chunk] = make_int4(r0, rows, a, 0);
         } else {
           overflow = true;
         }
-        ++t;
+        ++in_chunk;
+        off += rows;
       }
       start += cnt;
     }
+    num_tiles[chunk] = in_chunk;
+    for (int c = chunk + 1; c < num_chunks; ++c) num_tiles[c] = 0;
     if (overflow) {
       atomicCAS(status, 0, STATUS_TILE_OVERFLOW);
-      t = 0;
+      for (int c = 0; c < num_chunks; ++c) num_tiles[c] = 0;
     }
-    *num_tiles = t;
   }
   __syncthreads();
   if (tid < 32) {
@@ -93,7 +115,7 @@ route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* 
 }
 
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
-                 int max_tiles, int32_t* status, cudaStream_t stream) {
+                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows, int chunk_cap) {
   if (m <= 0 || perm == nullptr || tiles == nullptr || num_tiles == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: m must be positive and perm/tiles/num_tiles/status non-null");
   if (ids != nullptr && (num_adapters <= 0 || num_adapters > ROUTE_MAX_ADAPTERS))
@@ -101,7 +123,12 @@ int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int
                 num_adapters);
   if (max_tiles <= 0 || !aligned16(tiles))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: tiles must be 16-byte aligned with max_tiles > 0");
-  route_kernel<<<1, ROUTE_THREADS, 0, stream>>>(ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, status);
+  if (chunk_rows < 0 || chunk_rows % SKYRL_TILE_ROWS != 0 || (chunk_rows > 0 && chunk_cap <= 0))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: chunk_rows must be a multiple of %d", SKYRL_TILE_ROWS);
+  if (chunk_rows > 0 && static_cast<int64_t>((m + chunk_rows - 1) / chunk_rows) * chunk_cap > max_tiles)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: chunk lists do not fit in max_tiles");
+  route_kernel<<<1, ROUTE_THREADS, 0, stream>>>(ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, chunk_rows,
+                                                chunk_cap, status);
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "route launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
@@ -426,7 +453,7 @@ extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, 
                                          int32_t* tiles, int32_t* num_tiles, int32_t max_tiles, int32_t* status,
                                          skyrl_stream_t stream) {
   return launch_route(adapter_ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, status,
-                      static_cast<cudaStream_t>(stream));
+                      static_cast<cudaStream_t>(stream), 0, 0);
 }
 
 extern "C" int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, const void* rms_delta, float eps,

@@ -620,7 +620,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   p.kb_per_split = kb_per_split;
   p.slab_stride = static_cast<int64_t>(a.m) * a.out_row_stride;
   const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff) * k_splits;
-  const int grid = static_cast<int>(max_total < sms ? max_total : sms);
+  int grid = static_cast<int>(max_total < sms ? max_total : sms);
+  if (a.cta_limit > 0 && grid > a.cta_limit) grid = a.cta_limit;  // leave SMs to a concurrent collective
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
                    : launch_bn<128>(p, a.epilogue, lora, grid, stream);
 }

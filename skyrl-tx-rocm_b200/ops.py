@@ -31,6 +31,7 @@ __all__ = (
     "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
+    "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
     "check_status", "RMS_EPS",
 )
@@ -493,7 +494,8 @@ def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=
 def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: PackedLoRA | None,
                    down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
-                   timing_events=None, return_call: bool = False, reuse_routing: bool = False):
+                   timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
+                   gemm_cta_limit: int = 0):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only."""
@@ -559,11 +561,20 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
             a.timing_events[i] = ev.cuda_event
     if reuse_routing:
         a.flags = _lib.MLP_REUSE_ROUTING
+    if chunk is not None:
+        a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
+    a.gemm_cta_limit = int(gemm_cta_limit)
     _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
     if return_call:
         # keeps the argument block (and through it the workspace layout) for the tensor-parallel finalize
         return out, (a, x2, delta, ids, r2)
     return out.reshape(*x.shape[:-1], hidden) if out.shape[0] == m else out
+
+
+def chunk_rows(m: int, num_chunks: int) -> int:
+    """Rows per chunk of a chunked MLP block call: ceil(m / num_chunks) rounded up to the 128-row tile."""
+    per = (m + num_chunks - 1) // num_chunks
+    return (per + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
 
 
 def w8a8_mlp_tp_finalize(call, reduced: torch.Tensor, out: torch.Tensor, row_begin: int = 0, row_count: int | None = None):

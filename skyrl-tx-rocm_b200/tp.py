@@ -86,3 +86,69 @@ class TensorParallelMLP:
 
             dist.all_reduce(self._partial, group=self.group)
         return ops.w8a8_mlp_tp_finalize(call, self._partial, out)
+
+
+class TensorParallelMLPStack:
+    """A stack of tensor-parallel MLP blocks with the all-reduce hidden behind compute.
+
+    Every operation of the block is row-wise, so the adapter-sorted rows are cut
+    into `num_chunks` chunks: while NCCL reduces chunk c of a block on a second
+    stream, the kernels of chunk c + 1 (and then of the next block's chunk c)
+    run on the main stream.  The GEMMs leave `reserve_sms` SMs free so that the
+    collective's kernels can be resident at the same time.  Blocks shorter than
+    129 rows take the small-batch path and are not chunked.
+    """
+
+    def __init__(self, blocks, *, group=None, num_chunks: int = 4, reserve_sms: int = 16, sm_count: int = 148):
+        self.blocks = list(blocks)
+        self.group = group
+        self.num_chunks = num_chunks
+        self.cta_limit = max(1, sm_count - reserve_sms)
+        self._comm = None
+        self._partial = None
+        self._act = None
+
+    def forward(self, x, adapter_ids=None, *, timing_events=None):
+        import torch
+        import torch.distributed as dist
+
+        from . import ops
+
+        m, hidden = x.shape
+        chunks = self.num_chunks if m > ops.TILE_ROWS else 1
+        if self._comm is None:
+            self._comm = torch.cuda.Stream()
+        if self._partial is None or self._partial.shape != (m, hidden):
+            self._partial = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
+            self._act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
+        main = torch.cuda.current_stream()
+        rows = ops.chunk_rows(m, chunks)
+        spans = [(c * rows, min(rows, m - c * rows)) for c in range(chunks) if c * rows < m]
+        prev_done = [None] * len(spans)
+        cur = x
+        for l, blk in enumerate(self.blocks):
+            dst = self._act[l & 1]
+            done = []
+            for c, (r0, cnt) in enumerate(spans):
+                if prev_done[c] is not None:
+                    main.wait_event(prev_done[c])          # the rows this chunk gathers were finalized
+                ev = timing_events[l] if (timing_events is not None and c == 0) else None
+                _, call = ops.w8a8_mlp_block(
+                    cur, blk.rms_delta, blk.gate_up_weight, blk.gate_up_lora, blk.down_weight, blk.down_lora,
+                    adapter_ids, enabled=True, eps=blk.eps, out=self._partial, down_epilogue=ops.EPI_PARTIAL_F32,
+                    timing_events=ev, return_call=True, reuse_routing=(l > 0 or c > 0),
+                    chunk=(c, chunks) if chunks > 1 else None, gemm_cta_limit=self.cta_limit if chunks > 1 else 0)
+                computed = torch.cuda.Event()
+                computed.record(main)
+                with torch.cuda.stream(self._comm):
+                    self._comm.wait_event(computed)
+                    dist.all_reduce(self._partial[r0:r0 + cnt], group=self.group)
+                    ops.w8a8_mlp_tp_finalize(call, self._partial, dst, r0, cnt)
+                    fin = torch.cuda.Event()
+                    fin.record(self._comm)
+                done.append(fin)
+            prev_done = done
+            cur = dst
+        for fin in prev_done:
+            main.wait_event(fin)
+        return cur

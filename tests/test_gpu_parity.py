@@ -325,6 +325,28 @@ def test_mlp_block(S, m, hidden, inter, rank, na):
     assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
 
 
+@pytest.mark.parametrize("m,chunks", [(1000, 3), (700, 4), (300, 16)])
+def test_chunked_block_equals_whole_block(S, m, chunks):
+    # a block computed chunk by chunk (the form the tensor-parallel pipeline uses) is bit-identical
+    rng = np.random.default_rng(61)
+    hidden, inter, rank, na = 256, 384, 16, 5
+    x, wgu, ga, gb, s, ids = make_case(67 + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(71 + m, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    _, pgu = device_weight(S, wgu)
+    _, pd = device_weight(S, wd)
+    lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+    xd, dd, idd = to_dev(x), to_dev(delta), to_dev(ids)
+    whole = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True).clone()
+    out = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for c in range(chunks):
+        S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, out=out, chunk=(c, chunks),
+                         reuse_routing=c > 0, gemm_cta_limit=100)
+    S.check_status()
+    assert torch.equal(out.view(torch.int16), whole.view(torch.int16))
+
+
 @pytest.mark.parametrize("tp", [2, 4])
 def test_tensor_parallel_block_emulated_on_one_gpu(S, tp):
     # every rank's shard runs in turn on this GPU; the all-reduce is a sum of the fp32 partial buffers

@@ -211,7 +211,8 @@ def run_device(args):
         if tp > 1:
             from skyrl_tx_rocm_b200.tp import TensorParallelMLP, TensorParallelMLPStack
 
-            tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks)
+            tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks,
+                                              reserve_sms=args.tp_reserve_sms)
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
@@ -529,6 +530,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-chunks", type=int, default=4,
                     help="row chunks per block whose all-reduce overlaps the next chunk's kernels (N > 1)")
+    ap.add_argument("--tp-reserve-sms", type=int, default=16,
+                    help="SMs the GEMMs leave to the collective while chunks overlap (N > 1)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()

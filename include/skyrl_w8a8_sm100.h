@@ -120,6 +120,16 @@ SKYRL_API int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, co
                                const int32_t* num_tiles, int32_t max_tiles, void* z_parts, int32_t* status,
                                skyrl_stream_t stream);
 
+/* Grouped weights (group_size < K: GroupQuantizedWeight with several scale rows,
+ * skyrl/tx/kernels/quantized_lora.py:20-41; the reference's Pallas prototype uses
+ * group 64, skyrl/tx/kernels/rocm/w8a8_lora.py:44).  The caller runs one
+ * single-group GEMM per K group with SKYRL_EPI_PARTIAL_F32 into slab g of
+ * `slabs` (fp32 [groups, m, n], sorted rows); this adds the slabs in ascending
+ * group order (quantized_lora.py:253), casts once to bf16 and writes row i to
+ * out[row_map[i]].  A compatibility path: correct for any group size, not tuned. */
+SKYRL_API int skyrl_group_sum_cast_sm100_v1(const float* slabs, int32_t groups, int32_t m, int32_t n, const int32_t* row_map,
+                                  void* out, int64_t out_row_stride, skyrl_stream_t stream);
+
 /* Arguments of the int8 tensor-core GEMM with fused epilogue.  Computes
  *   acc = xq @ wq^T (int32, exact);  v = (f32(acc) * sx[m]) * sw[n] + z[m,:] @ B[a]^T
  * (skyrl/tx/kernels/quantized_lora.py:242-254, 298-304) and applies `epilogue`. */

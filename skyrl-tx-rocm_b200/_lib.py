@@ -87,6 +87,8 @@ SYMBOLS = {
     "skyrl_lora_a_proj_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
                                              C.c_void_p, C.c_void_p]),
+    "skyrl_group_sum_cast_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                                C.c_int64, C.c_void_p]),
     "skyrl_w8a8_gemm_sm100_v1": (C.c_int, [C.POINTER(GemmArgs), C.c_void_p]),
     "skyrl_w8a8_gemm_k_splits": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

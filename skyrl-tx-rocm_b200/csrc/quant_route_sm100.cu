@@ -302,6 +302,29 @@ int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* re
 }
 
 // ----------------------------------------------------------------------------
+// Grouped weights (group_size < K, the reference's native format): the caller
+// runs one single-group GEMM per K group into fp32 slabs (f32(acc) * sx_g) * sw_g;
+// this kernel adds the slabs in ascending group order, as the reference's
+// `sum(scaled, axis=1)` does (skyrl/tx/kernels/quantized_lora.py:248-253), casts
+// once to bf16 and scatters rows back to token order.
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+group_sum_cast_kernel(const float* __restrict__ slabs, int groups, int64_t slab_stride, int n,
+                      const int32_t* __restrict__ row_map, __nv_bfloat16* __restrict__ out, int64_t out_stride) {
+  const int64_t srow = blockIdx.x;
+  const int64_t orow = row_map != nullptr ? row_map[srow] : srow;
+  for (int c = threadIdx.x * 2; c < n; c += 2 * blockDim.x) {
+    float2 acc = *reinterpret_cast<const float2*>(slabs + srow * n + c);
+    for (int g = 1; g < groups; ++g) {
+      const float2 t = *reinterpret_cast<const float2*>(slabs + g * slab_stride + srow * n + c);
+      acc.x = __fadd_rn(acc.x, t.x);
+      acc.y = __fadd_rn(acc.y, t.y);
+    }
+    *reinterpret_cast<uint32_t*>(out + orow * out_stride + c) = pack_bf16x2(acc.x, acc.y);
+  }
+}
+
+// ----------------------------------------------------------------------------
 // Pack kernels (load time).  Tiled transposes through shared memory.
 // ----------------------------------------------------------------------------
 template <typename T>
@@ -447,6 +470,18 @@ extern "C" int skyrl_pack_lora_b_rows_sm100_v1(const void* b_arn, int32_t num_ad
   return run_transpose<uint16_t>(static_cast<const uint16_t*>(b_arn), static_cast<uint16_t*>(b_rows), num_adapters,
                                  rank, n, static_cast<int64_t>(n) * rr, rr,
                                  static_cast<size_t>(num_adapters) * n * rr * 2, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_group_sum_cast_sm100_v1(const float* slabs, int32_t groups, int32_t m, int32_t n,
+                                             const int32_t* row_map, void* out, int64_t out_row_stride,
+                                             skyrl_stream_t stream) {
+  if (slabs == nullptr || out == nullptr || groups <= 0 || m <= 0 || n <= 0 || n % 2 != 0 || out_row_stride < n)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "group_sum_cast: null buffer or bad shape");
+  group_sum_cast_kernel<<<m, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      slabs, groups, static_cast<int64_t>(m) * n, n, row_map, static_cast<__nv_bfloat16*>(out), out_row_stride);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "group_sum_cast launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
 }
 
 extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, int32_t num_adapters, int32_t* perm,

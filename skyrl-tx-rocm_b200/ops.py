@@ -66,6 +66,7 @@ class PackedW8Weight:
     sw: torch.Tensor
     in_features: int
     out_features: int
+    group_size: int = 0  # 0: one scale per output channel; > 0: sw is [K / group_size, Npad] (compatibility path)
 
     @property
     def padded_out_features(self) -> int:
@@ -143,11 +144,12 @@ def pack_weight(weight: GroupQuantizedWeight) -> PackedW8Weight:
         raise TypeError("W8 codes must be a rank-two INT8 array")
     if weight.scales.ndim != 2 or not weight.scales.is_floating_point():
         raise TypeError("W8 scales must be a rank-two floating-point array")
-    if weight.group_size != weight.padded_in_features or weight.scales.shape[0] != 1:
-        raise ValueError(
-            "pack_weight takes one scale per output channel (group_size == K); "
-            f"got group_size={weight.group_size} for K={weight.padded_in_features}"
-        )
+    grouped = weight.group_size != weight.padded_in_features
+    if weight.padded_in_features % weight.group_size or weight.scales.shape[0] != weight.padded_in_features // weight.group_size:
+        raise ValueError(f"scale shape {tuple(weight.scales.shape)} does not match K={weight.padded_in_features}, "
+                         f"group_size={weight.group_size}")
+    if grouped and weight.group_size % 16:
+        raise ValueError(f"grouped weights need group_size to be a multiple of 16, got {weight.group_size}")
     _require_cuda(weight.codes, "weight.codes")
     kpad, n = weight.codes.shape
     k = kpad
@@ -164,6 +166,12 @@ def pack_weight(weight: GroupQuantizedWeight) -> PackedW8Weight:
                      device=codes.device)
     lib = _lib.load()
     _lib.check(lib.skyrl_pack_weight_kn_sm100_v1(_ptr(codes), k, npad, _ptr(wq), _stream()), "pack_weight")
+    if grouped:
+        if k != kpad:
+            raise ValueError("grouped weights need K to be a multiple of 16")
+        sw = torch.zeros((weight.scales.shape[0], npad), dtype=torch.float32, device=codes.device)
+        sw[:, :n] = weight.scales.to(torch.float32)
+        return PackedW8Weight(wq, sw, k, n, weight.group_size)
     sw = torch.zeros((npad,), dtype=torch.float32, device=codes.device)
     sw[:n] = weight.scales[0].to(torch.float32)
     return PackedW8Weight(wq, sw, k, n)
@@ -329,8 +337,73 @@ def _lora_of(weight: PackedW8Weight, lora_a, lora_b, lora_scaling) -> PackedLoRA
     return lora
 
 
+def _run_linear_grouped(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids):
+    """Compatibility path for group_size < K: one single-group GEMM per K group into fp32 slabs, then the
+    ordered group sum, the LoRA term (accumulated by the last group's GEMM) and the single bf16 cast
+    (quantized_lora.py:242-254, 298-304).  Correct for every group size; not tuned."""
+    lib = _lib.load()
+    m, k, npad, g_size = x2.shape[0], weight.in_features, weight.padded_out_features, weight.group_size
+    groups = k // g_size
+    x2 = _pad_cols(x2, k)
+    dev = x2.device
+    na = lora.num_adapters if lora is not None else 1
+    st = _status_word(dev)
+    perm, tiles, num = prepare_routing(ids, m, na)
+    row_map = perm if ids is not None else None
+    max_tiles = tiles.shape[0]
+    z_parts = None
+    if lora is not None:
+        if ids is not None:
+            _, _, xs = rms_quant(x2, row_map=perm, want_normalized=True)  # rows gathered into sorted order
+        else:
+            xs = x2.contiguous()
+        z_parts = torch.empty((3, m, LORA_RANK_PAD), dtype=torch.bfloat16, device=dev)
+        _lib.check(lib.skyrl_lora_a_proj_sm100_v1(_ptr(xs), m, k, _ptr(lora.a), _ptr(lora.scaling), na, lora.rank,
+                                                  _ptr(tiles), _ptr(num), max_tiles, _ptr(z_parts), _ptr(st),
+                                                  _stream()), "lora_a_proj")
+    slabs = torch.empty((groups, m, npad), dtype=torch.float32, device=dev)
+    sliceable = g_size % _lib.WEIGHT_KBLOCK == 0  # whole K blocks of the packed weight per group
+    for j in range(groups):
+        xq_j, sx_j, _ = rms_quant(x2[:, j * g_size:(j + 1) * g_size], row_map=row_map)
+        a = _lib.GemmArgs()
+        a.struct_size = C.sizeof(_lib.GemmArgs)
+        a.epilogue = EPI_PARTIAL_F32
+        a.m, a.n = m, npad
+        if sliceable:
+            a.k = g_size
+            xq = xq_j
+            a.wq = weight.wq.data_ptr() + j * (g_size // _lib.WEIGHT_KBLOCK) * npad * _lib.WEIGHT_KBLOCK
+        else:
+            # a group that is not a whole number of 128-wide K blocks: full-K pass with the codes of the
+            # other groups zeroed, which contributes exactly nothing to the int32 accumulator
+            a.k = k
+            xq = torch.zeros((m, k), dtype=torch.int8, device=dev)
+            xq[:, j * g_size:(j + 1) * g_size] = xq_j
+            a.wq = weight.wq.data_ptr()
+        a.xq, a.sx, a.sw = xq.data_ptr(), sx_j.data_ptr(), weight.sw[j].data_ptr()
+        last = j == groups - 1
+        a.rank = lora.rank if (lora is not None and last) else 0
+        a.num_adapters = na
+        a.max_tiles = max_tiles
+        if a.rank:
+            a.z_parts, a.lora_b_packed = z_parts.data_ptr(), lora.b.data_ptr()
+        a.tiles, a.num_tiles = tiles.data_ptr(), num.data_ptr()
+        a.out, a.out_row_stride = slabs[j].data_ptr(), npad
+        a.status = st.data_ptr()
+        _lib.check(lib.skyrl_w8a8_gemm_sm100_v1(C.byref(a), _stream()), "w8a8_gemm (group)")
+    out = torch.empty((m, npad), dtype=torch.bfloat16, device=dev)
+    _lib.check(lib.skyrl_group_sum_cast_sm100_v1(_ptr(slabs), groups, m, npad, _ptr(row_map), _ptr(out), npad,
+                                                 _stream()), "group_sum_cast")
+    return out
+
+
 def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilogue, *, rms_delta=None, eps=RMS_EPS,
                 residual=None, out=None, timing_events=None):
+    if weight.group_size:
+        if epilogue != EPI_LINEAR or rms_delta is not None or residual is not None:
+            raise SkyrlKernelError("grouped weights (group_size < K) are served by w8a8_lora_linear and "
+                                   "w8a8_frozen_linear only; the fused operators take per-output-channel scales")
+        return _run_linear_grouped(x2, weight, lora, ids)
     lib = _lib.load()
     m = x2.shape[0]
     k, npad = weight.in_features, weight.padded_out_features

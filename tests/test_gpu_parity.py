@@ -261,6 +261,36 @@ def test_multi_adapter_linear(S, m, k, n, rank, na, mode):
     assert_bf16_close(to_np(y), want, what=f"multi-adapter m={m}")
 
 
+@pytest.mark.parametrize("m,k,n,g,rank,na", [(3, 128, 17, 64, 8, 1), (7, 128, 19, 64, 8, 1), (130, 256, 48, 128, 16, 3),
+                                             (40, 192, 32, 64, 8, 2)])
+def test_grouped_weight_compatibility_path(S, m, k, n, g, rank, na):
+    # the reference's native format: group_size 64 along K (tests/tx/kernels/rocm/test_w8a8_lora.py:95-124 shapes)
+    x, w, a, b, s, ids = make_case(77 + m, m, k, n, rank, na, w_std=0.05)
+    q = O.quantize_frozen_weight(w, group_size=g)
+    gq = S.GroupQuantizedWeight(to_dev(q.codes), to_dev(q.scales), k, k, 8, g)
+    if na == 1:
+        y = S.w8a8_lora_linear(to_dev(x), gq, to_dev(a[0]), to_dev(b[0]), float(s[0]), enabled=True)
+        want = O.quantized_lora_linear(x, q, a[0], b[0], s[0])
+    else:
+        y = S.w8a8_lora_linear(to_dev(x), gq, to_dev(a), to_dev(b), to_dev(s), to_dev(ids), enabled=True)
+        want = O.quantized_lora_linear(x, q, a, b, s, ids)
+    S.check_status()
+    assert_bf16_close(to_np(y), want, max_ulp_frac=0.02, what=f"group {g}")
+    frozen = S.w8a8_frozen_linear(to_dev(x), gq, enabled=True)
+    np.testing.assert_array_equal(to_np(frozen).view(np.uint16), O.quantized_lora_linear(x, q).view(np.uint16))
+
+
+def test_reference_group64_fixture(S):
+    z = np.load(GOLDEN / "w8a8_ref_oracle_cases.npz")
+    name = "group64_k128"
+    codes = z[f"{name}.weight_codes"]
+    gq = S.GroupQuantizedWeight(to_dev(codes), to_dev(z[f"{name}.weight_scales_bf16"].view(BF16)), 128, 128, 8, 64)
+    y = S.w8a8_lora_linear(to_dev(z[f"{name}.x_bf16"].view(BF16)), gq, to_dev(z[f"{name}.lora_a_bf16"].view(BF16)),
+                           to_dev(z[f"{name}.lora_b_bf16"].view(BF16)), float(z[f"{name}.lora_scaling"]), enabled=True)
+    S.check_status()
+    assert_bf16_close(to_np(y), z[f"{name}.expected_bf16"].view(BF16), max_ulp_frac=0.05, what=name)
+
+
 def test_zero_input_gives_exact_zeros(S):
     x, w, a, b, s, ids = make_case(5, 70, 128, 64, 8, 2)
     x = np.zeros_like(x)

@@ -222,6 +222,11 @@ def run_device(args):
             + wl["adapters"] * 2 * ish * wl["rank"] * 2 + m * ish * 2
         dn_bytes_launch = hidden * ish + m * ish + 4 * hidden + 4 * m + 3 * m * 64 * 2 \
             + wl["adapters"] * hidden * wl["rank"] * 2 + 2 * m * hidden * 2
+        if m <= 128:
+            # small-batch path: the GEMM reads weights + codes and writes the int32 accumulator; the LoRA
+            # tables are read by the row kernels, not by the GEMM
+            gu_bytes_launch = 2 * ish * hidden + m * hidden + 4 * m * 2 * ish
+            dn_bytes_launch = hidden * ish + m * ish + 4 * m * hidden * S._lib.load().skyrl_w8a8_gemm_k_splits(m, hidden, ish, 16)
         h2d = x_host.numel() * 2 + (ids_host.numel() * 4 if ids_host is not None else 0)
         d2h = m * hidden * 2
         out_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
@@ -397,9 +402,11 @@ def run_device(args):
                                        frac=dn_ops_launch / (dn_avg * 1e-3) / 1e12 / i8_peak) if kind == "mlp" else None)
     else:
         achieved = gu_bytes_launch / (gu_avg * 1e-3) / 1e9
-        roofline = dict(bound="hbm", kernel="w8a8_gemm_kernel<gate_up/SwiGLU epilogue>", achieved=achieved, peak=peaks["hbm_gbs"],
+        roofline = dict(bound="hbm", kernel="w8a8_gemm_kernel<int32 epilogue> (gate_up weights)", achieved=achieved, peak=peaks["hbm_gbs"],
                         unit="GB/s", frac=achieved / peaks["hbm_gbs"], traffic=None, peak_source=f"hbm_gbs of {peaks['source']}",
                         launch_ms=gu_avg, bytes_per_launch=gu_bytes_launch,
+                        step_bytes=layers * (hidden * 3 * inter + 2 * wl["adapters"] * wl["rank"] * (hidden + 2 * inter + inter + hidden)) if kind == "mlp" else None,
+                        step_frac=(layers * (hidden * 3 * inter + 2 * wl["adapters"] * wl["rank"] * (hidden + 2 * inter + inter + hidden)) / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"]) if kind == "mlp" else None,
                         down_gemm=dict(achieved=dn_bytes_launch / (dn_avg * 1e-3) / 1e9, launch_ms=dn_avg,
                                        frac=dn_bytes_launch / (dn_avg * 1e-3) / 1e9 / peaks["hbm_gbs"]))
     cpu = None

@@ -24,7 +24,6 @@ namespace skyrl {
 
 constexpr int ROWQ_THREADS = 128;
 constexpr int ROWQ_CLUSTER = 8;
-constexpr int ROWQ_MAX_SLICE_VECS = 512;  // 8 * 512 * 8 = 32768 in-features at most
 
 __device__ __forceinline__ float rowq_block_reduce(float v, bool is_max, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -42,14 +41,16 @@ __device__ __forceinline__ float rowq_block_reduce(float v, bool is_max, float* 
   return r;
 }
 
-template <int R>
+// Each thread owns up to VMAX 8-element vectors of its CTA's K slice and keeps them in registers; every
+// global load (activations, RMSNorm weights, and with PREFETCH_A the LoRA-A slice) is issued before the
+// first reduction, so the kernel pays one memory latency plus three cluster barriers.
+template <int R, int VMAX, bool PREFETCH_A>
 __global__ void __cluster_dims__(ROWQ_CLUSTER, 1, 1) __launch_bounds__(ROWQ_THREADS)
 rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
                       const __nv_bfloat16* __restrict__ delta, float eps, const int32_t* __restrict__ ids,
                       const __nv_bfloat16* __restrict__ a_packed, const float* __restrict__ scaling, int k,
                       int8_t* __restrict__ xq, float* __restrict__ sx, float* __restrict__ z_rows) {
   cg::cluster_group cluster = cg::this_cluster();
-  __shared__ __align__(16) uint4 slice[ROWQ_MAX_SLICE_VECS];
   __shared__ float red[ROWQ_THREADS / 32];
   __shared__ float zwarp[ROWQ_THREADS / 32][R];
   __shared__ float part_ss, part_amax;   // this CTA's partial results, read by the whole cluster
@@ -63,21 +64,36 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
   const int cnt = max(0, min(per, nvec - v0));
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * x_row_stride) + v0;
   const bool norm = delta != nullptr;
+  const int adapter = ids != nullptr ? __ldg(ids + m) : 0;
+  const uint4* a_base =
+      reinterpret_cast<const uint4*>(a_packed + static_cast<int64_t>(adapter) * SKYRL_LORA_RANK_PAD * k) + v0;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
+  uint4 xr[VMAX], dr[VMAX];
+  uint4 ar[PREFETCH_A ? VMAX : 1][PREFETCH_A ? R : 1];
+#pragma unroll
+  for (int i = 0; i < VMAX; ++i) {
+    const int v = threadIdx.x + i * ROWQ_THREADS;
+    const bool valid = v < cnt;
+    xr[i] = valid ? __ldg(src + v) : zero4;
+    dr[i] = (valid && norm) ? __ldg(reinterpret_cast<const uint4*>(delta) + v0 + v) : zero4;
+    if (PREFETCH_A) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) ar[i][j] = valid ? __ldg(a_base + static_cast<int64_t>(j) * nvec + v) : zero4;
+    }
+  }
+
+  float xv[VMAX][8];
   float ss = 0.f, amax = 0.f;
-  for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
-    const uint4 u = __ldg(src + v);
-    slice[v] = u;
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < VMAX; ++i) {
+    const uint32_t w[4] = {xr[i].x, xr[i].y, xr[i].z, xr[i].w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float a = bf16_lo(w[j]), b = bf16_hi(w[j]);
-      if (norm) {
-        ss = fmaf(a, a, ss);
-        ss = fmaf(b, b, ss);
-      } else {
-        amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
-      }
+      xv[i][2 * j] = bf16_lo(w[j]);
+      xv[i][2 * j + 1] = bf16_hi(w[j]);
+      ss = fmaf(xv[i][2 * j], xv[i][2 * j], ss);
+      ss = fmaf(xv[i][2 * j + 1], xv[i][2 * j + 1], ss);
     }
   }
   if (norm) {
@@ -89,23 +105,20 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     for (int r = 0; r < ROWQ_CLUSTER; ++r) total += *cluster.map_shared_rank(&part_ss, r);  // fixed order
     const float var = __fdiv_rn(total, static_cast<float>(k));
     const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
-    const uint4* dvec = reinterpret_cast<const uint4*>(delta) + v0;
-    for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
-      const uint4 u = slice[v];
-      const uint4 d = __ldg(dvec + v);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-      const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
-      uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < VMAX; ++i) {
+      const uint32_t dw[4] = {dr[i].x, dr[i].y, dr[i].z, dr[i].w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float a = __fmul_rn(__fmul_rn(bf16_lo(w[j]), rinv), __fadd_rn(1.0f, bf16_lo(dw[j])));
-        const float b = __fmul_rn(__fmul_rn(bf16_hi(w[j]), rinv), __fadd_rn(1.0f, bf16_hi(dw[j])));
-        o[j] = pack_bf16x2(a, b);
-        amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+        xv[i][2 * j] = round_bf16(__fmul_rn(__fmul_rn(xv[i][2 * j], rinv), __fadd_rn(1.0f, bf16_lo(dw[j]))));
+        xv[i][2 * j + 1] = round_bf16(__fmul_rn(__fmul_rn(xv[i][2 * j + 1], rinv), __fadd_rn(1.0f, bf16_hi(dw[j]))));
       }
-      slice[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
+#pragma unroll
+  for (int i = 0; i < VMAX; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(xv[i][e]));
   amax = rowq_block_reduce(amax, true, red);
   if (threadIdx.x == 0) part_amax = amax;
   cluster.sync();
@@ -116,34 +129,27 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
   const float rcp = quant_rcp(scale);
   if (crank == 0 && threadIdx.x == 0) sx[m] = scale;
 
-  const int adapter = ids != nullptr ? ids[m] : 0;
-  const uint4* a_base =
-      reinterpret_cast<const uint4*>(a_packed + static_cast<int64_t>(adapter) * SKYRL_LORA_RANK_PAD * k) + v0;
   float acc[R];
 #pragma unroll
   for (int j = 0; j < R; ++j) acc[j] = 0.f;
   uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k) + v0;
-  for (int v = threadIdx.x; v < cnt; v += ROWQ_THREADS) {
-    const uint4 u = slice[v];
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-    float xv[8];
-    int q[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      xv[2 * j] = bf16_lo(w[j]);
-      xv[2 * j + 1] = bf16_hi(w[j]);
-      q[2 * j] = quant_code(xv[2 * j], scale, rcp);
-      q[2 * j + 1] = quant_code(xv[2 * j + 1], scale, rcp);
-    }
-    dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+  for (int i = 0; i < VMAX; ++i) {
+    const int v = threadIdx.x + i * ROWQ_THREADS;
+    if (v < cnt) {
+      int q[8];
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
-      const uint4 aw = __ldg(a_base + static_cast<int64_t>(j) * nvec + v);
-      const uint32_t av[4] = {aw.x, aw.y, aw.z, aw.w};
+      for (int e = 0; e < 8; ++e) q[e] = quant_code(xv[i][e], scale, rcp);
+      dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        acc[j] = fmaf(xv[2 * q], bf16_lo(av[q]), acc[j]);
-        acc[j] = fmaf(xv[2 * q + 1], bf16_hi(av[q]), acc[j]);
+      for (int j = 0; j < R; ++j) {
+        const uint4 aw = PREFETCH_A ? ar[i][j] : __ldg(a_base + static_cast<int64_t>(j) * nvec + v);
+        const uint32_t av[4] = {aw.x, aw.y, aw.z, aw.w};
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          acc[j] = fmaf(xv[i][2 * qd], bf16_lo(av[qd]), acc[j]);
+          acc[j] = fmaf(xv[i][2 * qd + 1], bf16_hi(av[qd]), acc[j]);
+        }
       }
     }
   }
@@ -239,11 +245,11 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
   }
 }
 
-template <int R>
+template <int R, int VMAX, bool PREFETCH_A>
 static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                                const void* a_packed, const float* scaling, int m, int k, void* xq, float* sx,
                                float* z_rows, cudaStream_t stream) {
-  rms_quant_rows_kernel<R><<<m * ROWQ_CLUSTER, ROWQ_THREADS, 0, stream>>>(
+  rms_quant_rows_kernel<R, VMAX, PREFETCH_A><<<m * ROWQ_CLUSTER, ROWQ_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), x_row_stride, static_cast<const __nv_bfloat16*>(rms_delta), eps, ids,
       static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx, z_rows);
   cudaError_t e = cudaPeekAtLastError();
@@ -262,15 +268,22 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: row stride must be >= K and a multiple of 8 elements");
   if (!aligned16(x) || !aligned16(xq) || !aligned16(a_packed) || (rms_delta != nullptr && !aligned16(rms_delta)))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: buffers must be 16-byte aligned");
-  if ((k >> 3) > ROWQ_CLUSTER * ROWQ_MAX_SLICE_VECS)
-    return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: K=%d exceeds %d", k, ROWQ_CLUSTER * ROWQ_MAX_SLICE_VECS * 8);
+  const int per_cta = ((k >> 3) + ROWQ_CLUSTER - 1) / ROWQ_CLUSTER;  // 8-element vectors per CTA of the cluster
+  if (per_cta > 4 * ROWQ_THREADS)
+    return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: K=%d exceeds %d", k, 4 * ROWQ_THREADS * ROWQ_CLUSTER * 8);
   if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
-  if (rank <= 16)
-    return launch_rows_variant<16>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream);
-  if (rank <= 32)
-    return launch_rows_variant<32>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream);
-  return launch_rows_variant<64>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream);
+#define SKYRL_ROWS(R, V, P) \
+  return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream)
+  if (per_cta <= 2 * ROWQ_THREADS) {
+    if (rank <= 16) SKYRL_ROWS(16, 2, false);
+    if (rank <= 32) SKYRL_ROWS(32, 2, false);
+    SKYRL_ROWS(64, 2, false);
+  }
+  if (rank <= 16) SKYRL_ROWS(16, 4, false);
+  if (rank <= 32) SKYRL_ROWS(32, 4, false);
+  SKYRL_ROWS(64, 4, false);
+#undef SKYRL_ROWS
 }
 
 int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw,

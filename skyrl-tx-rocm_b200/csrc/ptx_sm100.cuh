@@ -233,7 +233,14 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
-__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// fp32 -> nearest-even bf16 -> fp32 with integer operations (the conversion instructions share the
+// quarter-rate pipe with exp and reciprocal, which the SwiGLU epilogue already saturates).  NaN payloads
+// are not preserved; the callers never produce NaN from finite inputs.
+__device__ __forceinline__ float round_bf16(float v) {
+  uint32_t b = __float_as_uint(v);
+  b += 0x7fffu + ((b >> 16) & 1u);
+  return __uint_as_float(b & 0xffff0000u);
+}
 
 // int8 code of one activation: clip(rint(x / scale), -127, 127) with x / scale the IEEE fp32 quotient
 // (skyrl/tx/kernels/quantized_lora.py:209).  The quotient is first estimated as x * rcp with
@@ -245,14 +252,17 @@ __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(_
 __device__ __forceinline__ float quant_rcp(float scale) {
   return (scale > 1e-30f && scale < 1e30f) ? __frcp_rn(scale) : __int_as_float(0x7fc00000);
 }
+// The rounding itself uses the 1.5 * 2^23 trick on the fp32 pipe (round-to-nearest-even, like rint):
+// the low byte of the biased sum is the two's-complement int8 code; |quotient| <= 127.00003 keeps it
+// inside [-127, 127] without a clamp.  Returns the biased word; pack_codes4 extracts the bytes.
 __device__ __forceinline__ int quant_code(float x, float scale, float rcp) {
-  float t = __fmul_rn(x, rcp);
-  if (!(fabsf(__fsub_rn(t, rintf(t))) <= 0.4999f)) t = __fdiv_rn(x, scale);
-  int q;  // round to nearest even and saturate to int8; |t| <= 127.00003, so -128 never appears
-  asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(q) : "f"(t));
-  return q;
+  constexpr float kBias = 12582912.0f;
+  const float t = __fmul_rn(x, rcp);
+  float u = __fadd_rn(t, kBias);
+  if (!(fabsf(__fsub_rn(t, __fsub_rn(u, kBias))) <= 0.4999f)) u = __fadd_rn(__fdiv_rn(x, scale), kBias);
+  return __float_as_int(u);
 }
-// Four int8 codes (held sign-extended in 32-bit registers) -> one little-endian word.
+// Four int8 codes (the low bytes of four 32-bit registers) -> one little-endian word.
 __device__ __forceinline__ uint32_t pack_codes4(int a, int b, int c, int d) {
   const uint32_t lo = __byte_perm(static_cast<uint32_t>(a), static_cast<uint32_t>(b), 0x0040);
   const uint32_t hi = __byte_perm(static_cast<uint32_t>(c), static_cast<uint32_t>(d), 0x0040);

@@ -97,6 +97,111 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tm, int tn, int band)
 
 __device__ __forceinline__ float silu_f32(float t) { return __fdiv_rn(t, 1.0f + expf(-t)); }
 
+
+// ---- epilogue building blocks (one 32-column chunk of one TMEM lane quadrant) ------------------------
+// pass 1 of the LoRA path: int32 accumulator -> (f32(acc) * sx[m]) * sw[n], written back in place
+__device__ __forceinline__ void epi_convert_chunk(uint32_t taddr, int nc, int n_end, float sxr,
+                                                  const float* __restrict__ sw) {
+  uint32_t v[32];
+  __syncwarp();
+  tmem_ld32(taddr, v);
+  tmem_wait_ld();
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(sw + nc) + g);
+    v[4 * g + 0] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x));
+    v[4 * g + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y));
+    v[4 * g + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z));
+    v[4 * g + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w));
+  }
+  tmem_st32(taddr, v);
+}
+
+// pass 2: final values of one chunk -> global memory (single bf16 cast, SwiGLU / residual / raw forms)
+template <int EPI, bool HAS_LORA>
+__device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t taddr, int nc, int n_end, float sxr,
+                                                bool row_valid, int64_t orow, int64_t slab_off) {
+  uint32_t v[32];
+  __syncwarp();
+  tmem_ld32(taddr, v);
+  tmem_wait_ld();
+  if (EPI == SKYRL_EPI_ACC_I32) {
+    if (row_valid) {
+      // split K: every split owns one [M, N] slab; the consumer adds the slabs (exact in int32)
+      int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + slab_off + orow * p.out_stride + nc);
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        if (nc + g * 4 < n_end) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    }
+    return;
+  }
+  float f[32];
+  if (HAS_LORA) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+  } else {
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
+      f[4 * g + 0] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x);
+      f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
+      f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
+      f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
+    }
+  }
+  if (!row_valid) return;
+  if (EPI == SKYRL_EPI_PARTIAL_F32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      if (nc + g * 4 < n_end) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+  } else if (EPI == SKYRL_EPI_LINEAR) {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (nc + g * 8 < n_end)
+        dst[g] = make_uint4(pack_bf16x2(f[8 * g], f[8 * g + 1]), pack_bf16x2(f[8 * g + 2], f[8 * g + 3]),
+                            pack_bf16x2(f[8 * g + 4], f[8 * g + 5]), pack_bf16x2(f[8 * g + 6], f[8 * g + 7]));
+  } else if (EPI == SKYRL_EPI_RESIDUAL) {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
+    const uint4* res = reinterpret_cast<const uint4*>(p.residual + orow * p.res_stride + nc);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (nc + g * 8 < n_end) {
+        const uint4 rv = __ldg(res + g);
+        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float a = __fadd_rn(round_bf16(f[8 * g + 2 * j]), bf16_lo(rw[j]));
+          const float b = __fadd_rn(round_bf16(f[8 * g + 2 * j + 1]), bf16_hi(rw[j]));
+          o[j] = pack_bf16x2(a, b);
+        }
+        dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  } else if (EPI == SKYRL_EPI_SWIGLU) {
+    // columns (2i, 2i+1) = (gate_i, up_i); 32 physical columns -> 16 outputs
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + (nc >> 1));
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      if (nc + g * 16 < n_end) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i0 = 16 * g + 4 * j;
+          const float h0 = __fmul_rn(silu_f32(round_bf16(f[i0])), round_bf16(f[i0 + 1]));
+          const float h1 = __fmul_rn(silu_f32(round_bf16(f[i0 + 2])), round_bf16(f[i0 + 3]));
+          o[j] = pack_bf16x2(h0, h1);
+        }
+        dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 template <int BN, int EPI, bool HAS_LORA>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -324,23 +429,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       if (HAS_LORA) {
         // pass 1: int32 accumulator -> dequantised fp32, in place
 #pragma unroll 1
-        for (int cc = c_begin; cc < c_end; ++cc) {
-          uint32_t v[32];
-          __syncwarp();
-          tmem_ld32(tbase + cc * 32, v);
-          tmem_wait_ld();
-          const int nc = n0 + cc * 32;
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
-            v[4 * g + 0] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x));
-            v[4 * g + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y));
-            v[4 * g + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z));
-            v[4 * g + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w));
-          }
-          tmem_st32(tbase + cc * 32, v);
-        }
+        for (int cc = c_begin; cc < c_end; ++cc)
+          epi_convert_chunk(tbase + cc * 32, n0 + cc * 32, n_end, sxr, p.sw);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(conv_done);
@@ -353,89 +443,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 
       // pass 2: final values -> global memory
 #pragma unroll 1
-      for (int cc = c_begin; cc < c_end; ++cc) {
-        uint32_t v[32];
-        __syncwarp();
-        tmem_ld32(tbase + cc * 32, v);
-        tmem_wait_ld();
-        const int nc = n0 + cc * 32;
-        if (EPI == SKYRL_EPI_ACC_I32) {
-          if (row_valid) {
-            // split K: every split owns one [M, N] slab; the consumer adds the slabs (exact in int32)
-            int4* dst = reinterpret_cast<int4*>(static_cast<int32_t*>(p.out) + (t % ksplits) * p.slab_stride +
-                                                orow * p.out_stride + nc);
-#pragma unroll
-            for (int g = 0; g < 8; ++g)
-              if (nc + g * 4 < n_end) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-          }
-          continue;
-        }
-        float f[32];
-        if (HAS_LORA) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-        } else {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (nc + g * 4 < n_end) w = __ldg(reinterpret_cast<const float4*>(p.sw + nc) + g);
-            f[4 * g + 0] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 0])), sxr), w.x);
-            f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
-            f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
-            f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
-          }
-        }
-        if (!row_valid) continue;
-        if (EPI == SKYRL_EPI_PARTIAL_F32) {
-          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            if (nc + g * 4 < n_end) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
-        } else if (EPI == SKYRL_EPI_LINEAR) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            if (nc + g * 8 < n_end)
-              dst[g] = make_uint4(pack_bf16x2(f[8 * g], f[8 * g + 1]), pack_bf16x2(f[8 * g + 2], f[8 * g + 3]),
-                                  pack_bf16x2(f[8 * g + 4], f[8 * g + 5]), pack_bf16x2(f[8 * g + 6], f[8 * g + 7]));
-        } else if (EPI == SKYRL_EPI_RESIDUAL) {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
-          const uint4* res = reinterpret_cast<const uint4*>(p.residual + orow * p.res_stride + nc);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (nc + g * 8 < n_end) {
-              const uint4 rv = __ldg(res + g);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-              uint32_t o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float a = __fadd_rn(round_bf16(f[8 * g + 2 * j]), bf16_lo(rw[j]));
-                const float b = __fadd_rn(round_bf16(f[8 * g + 2 * j + 1]), bf16_hi(rw[j]));
-                o[j] = pack_bf16x2(a, b);
-              }
-              dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        } else if (EPI == SKYRL_EPI_SWIGLU) {
-          // columns (2i, 2i+1) = (gate_i, up_i); 32 physical columns -> 16 outputs
-          uint4* dst =
-              reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + (nc >> 1));
-#pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            if (nc + g * 16 < n_end) {
-              uint32_t o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int i0 = 16 * g + 4 * j;
-                const float h0 = __fmul_rn(silu_f32(round_bf16(f[i0])), round_bf16(f[i0 + 1]));
-                const float h1 = __fmul_rn(silu_f32(round_bf16(f[i0 + 2])), round_bf16(f[i0 + 3]));
-                o[j] = pack_bf16x2(h0, h1);
-              }
-              dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
-        }
-      }
+      for (int cc = c_begin; cc < c_end; ++cc)
+        epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow,
+                                       (t % ksplits) * p.slab_stride);
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[s]);
     }
@@ -453,6 +463,296 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Paired-tile variant for large problems.  One CTA computes TWO 128-row M tiles against the same
+// 256-column weight tile: a K stage holds both activation tiles (2 x 16 KB) and one weight tile (32 KB)
+// and feeds two MMAs per K step, so the bytes a CTA must pull per unit of tensor-core work drop by a
+// third (64 KB per 1024 MMA cycles instead of 48 KB per 512) and three stages cover the TMA latency
+// that four 48 KB stages of the single-tile kernel do not.  The two accumulators fill TMEM
+// (2 x 256 columns), so the epilogue of a pair is not overlapped with the next pair's main loop; it is
+// kept short instead by sixteen epilogue warps (two tiles x four lane quadrants x two column halves).
+// The two tiles of a pair are neighbours in the tile list and may belong to different adapters: each
+// gets its own LoRA operands (two pipeline slots per tile, issued right after the pair's K loop).
+// ---------------------------------------------------------------------------------------------------
+constexpr int PAIR_THREADS = 576;      // warps 0-15 epilogue, warp 16 TMA producer, warp 17 MMA issuer
+constexpr int PAIR_EPI_THREADS = 512;
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_A_BYTES = 2 * BM * BK;
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_BN * BK;  // 64 KB
+constexpr int PAIR_STAGES = STAGE_AREA_BYTES / PAIR_STAGE_BYTES;  // 3
+constexpr int PAIR_SMEM_BYTES = STAGE_AREA_BYTES + (2 * PAIR_STAGES + 4) * 8 + 16 + 1024;
+
+template <int EPI, bool HAS_LORA>
+__global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGE_AREA_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + PAIR_STAGES;
+  uint64_t* tmem_full = bars + 2 * PAIR_STAGES;
+  uint64_t* tmem_empty = tmem_full + 1;
+  uint64_t* conv_done = tmem_empty + 1;
+  uint64_t* lora_done = conv_done + 1;
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(lora_done + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    mbar_init(tmem_empty, PAIR_EPI_THREADS);
+    mbar_init(conv_done, PAIR_EPI_THREADS);
+    mbar_init(lora_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 17) {
+    tmem_alloc(tmem_ptr_smem, 512);
+    tmem_relinquish();
+  }
+  if (warp == 16 && lane == 0) {
+    tma_prefetch_desc(&p.tm_xq);
+    tma_prefetch_desc(&p.tm_w);
+    if (HAS_LORA) {
+      tma_prefetch_desc(&p.tm_z);
+      tma_prefetch_desc(&p.tm_b);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int tm = *p.num_tiles;
+  const int tp = (tm + 1) / 2;  // tile pairs
+  const int tn = (p.n + PAIR_BN - 1) / PAIR_BN;
+  const int total = tp * tn;
+  const int kblocks = (p.k + BK - 1) / BK;
+  const int band = min(max(p.band / 2, 1), max(tp, 1));
+
+  if (warp == 16) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      auto lora_slots = [&](int row0, int n0, int adapter) -> bool {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+        unsigned char* sa = smem + stage * PAIR_STAGE_BYTES;
+        mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
+        tma_load_3d(sa, &p.tm_z, 0, row0, 2, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, row0, 1, &full_bar[stage]);
+        if (++stage == PAIR_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+        sa = smem + stage * PAIR_STAGE_BYTES;
+        mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + PAIR_BN * LORA_ROW_BYTES);
+        tma_load_3d(sa, &p.tm_z, 0, row0, 0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
+        if (++stage == PAIR_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        return true;
+      };
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const TileCoord c = tile_coord(t, tp, tn, band);
+        const int4 tile_a = __ldg(p.tiles + 2 * c.m_idx);
+        const bool has_b = 2 * c.m_idx + 1 < tm;
+        const int4 tile_b = has_b ? __ldg(p.tiles + 2 * c.m_idx + 1) : tile_a;
+        const int n0 = c.n_idx * PAIR_BN;
+        const uint32_t tx = (has_b ? 2 : 1) * BM * BK + PAIR_BN * BK;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          unsigned char* sa = smem + stage * PAIR_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], tx);
+          tma_load_2d(sa, &p.tm_xq, kb * BK, tile_a.x, &full_bar[stage]);
+          if (has_b) tma_load_2d(sa + BM * BK, &p.tm_xq, kb * BK, tile_b.x, &full_bar[stage]);
+          tma_load_3d(sa + PAIR_A_BYTES, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (HAS_LORA && ok) {
+          ok = lora_slots(tile_a.x, n0, tile_a.z);
+          if (ok && has_b) ok = lora_slots(tile_b.x, n0, tile_b.z);
+        }
+      }
+    }
+  } else if (warp == 17) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, BM, PAIR_BN);
+      const uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, BM, PAIR_BN);
+      int stage = 0;
+      uint32_t phase = 0, it = 0;
+      bool ok = true;
+      auto lora_mma = [&](uint32_t d, bool wait_conv, uint32_t conv_parity) -> bool {
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        const int st1 = stage;
+        if (++stage == PAIR_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        const int st2 = stage;
+        if (++stage == PAIR_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (wait_conv && !mbar_wait(conv_done, conv_parity, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        tc_fence_after_sync();
+        const uint32_t e1 = smem_u32(smem + st1 * PAIR_STAGE_BYTES), e2 = smem_u32(smem + st2 * PAIR_STAGE_BYTES);
+        const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
+        const uint64_t zd[3] = {make_desc_sw128(e1), make_desc_sw128(e1 + Z_PLANE_BYTES), make_desc_sw128(e2)};
+        for (int plane = 0; plane < 3; ++plane)
+          for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16(d, zd[plane] + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+        mma_commit(&empty_bar[st1]);
+        mma_commit(&empty_bar[st2]);
+        return true;
+      };
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+        const TileCoord c = tile_coord(t, tp, tn, band);
+        const bool has_b = 2 * c.m_idx + 1 < tm;
+        ok = mbar_wait(tmem_empty, (it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after_sync();
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+          const uint64_t a0 = make_desc_sw128(sa), a1 = make_desc_sw128(sa + BM * BK);
+          const uint64_t bdesc = make_desc_sw128(sa + PAIR_A_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K_I8; ++j) {
+            const uint32_t accumulate = (kb != 0 || j != 0) ? 1u : 0u;
+            mma_i8(tmem_base, a0 + 2 * j, bdesc + 2 * j, idesc, accumulate);
+            if (has_b) mma_i8(tmem_base + PAIR_BN, a1 + 2 * j, bdesc + 2 * j, idesc, accumulate);
+          }
+          mma_commit(&empty_bar[stage]);
+          if (++stage == PAIR_STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        mma_commit(tmem_full);
+        if (HAS_LORA) {
+          ok = lora_mma(tmem_base, true, it & 1u);
+          if (ok && has_b) ok = lora_mma(tmem_base + PAIR_BN, false, 0u);
+          if (ok) mma_commit(lora_done);
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps 0-15 -----------------------
+    const int which = warp >> 3;            // 0: first tile of the pair, 1: second
+    const int quad = warp & 3;              // TMEM lane quadrant this warp may access
+    const int c_begin = ((warp >> 2) & 1) * 4, c_end = c_begin + 4;  // column chunks of 32
+    const int r = quad * 32 + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      const TileCoord c = tile_coord(t, tp, tn, band);
+      const int tidx = 2 * c.m_idx + which;
+      const bool present = tidx < tm;
+      const int4 tile = present ? __ldg(p.tiles + tidx) : make_int4(0, 0, 0, 0);
+      const int n0 = c.n_idx * PAIR_BN;
+      const int n_end = min(p.n, n0 + PAIR_BN);
+      const bool row_valid = r < tile.y;
+      const int srow = tile.x + r;
+      const float sxr = row_valid ? __ldg(p.sx + srow) : 0.f;
+      const int64_t orow = row_valid ? (p.out_row_map != nullptr ? __ldg(p.out_row_map + srow) : srow) : 0;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_full, it & 1u, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tbase = tmem_base + which * PAIR_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      if (HAS_LORA) {
+        if (present) {
+#pragma unroll 1
+          for (int cc = c_begin; cc < c_end; ++cc)
+            epi_convert_chunk(tbase + cc * 32, n0 + cc * 32, n_end, sxr, p.sw);
+          tmem_wait_st();
+        }
+        tc_fence_before_sync();
+        mbar_arrive(conv_done);
+        __syncwarp();
+        ok = __all_sync(0xffffffffu, mbar_wait(lora_done, it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA));
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      if (present) {
+#pragma unroll 1
+        for (int cc = c_begin; cc < c_end; ++cc)
+          epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow, 0);
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tmem_empty);
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 17) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int EPI, bool HAS_LORA>
+static int launch_pair_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+  auto kernel = w8a8_gemm_pair_kernel<EPI, HAS_LORA>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
+    attr_set = true;
+  }
+  kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(p);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+static int launch_pair(const GemmParams& p, int epi, bool lora, int grid, cudaStream_t stream) {
+  switch (epi) {
+    case SKYRL_EPI_LINEAR:
+      return lora ? launch_pair_variant<SKYRL_EPI_LINEAR, true>(p, grid, stream)
+                  : launch_pair_variant<SKYRL_EPI_LINEAR, false>(p, grid, stream);
+    case SKYRL_EPI_SWIGLU:
+      return lora ? launch_pair_variant<SKYRL_EPI_SWIGLU, true>(p, grid, stream)
+                  : launch_pair_variant<SKYRL_EPI_SWIGLU, false>(p, grid, stream);
+    case SKYRL_EPI_RESIDUAL:
+      return lora ? launch_pair_variant<SKYRL_EPI_RESIDUAL, true>(p, grid, stream)
+                  : launch_pair_variant<SKYRL_EPI_RESIDUAL, false>(p, grid, stream);
+    case SKYRL_EPI_PARTIAL_F32:
+      return lora ? launch_pair_variant<SKYRL_EPI_PARTIAL_F32, true>(p, grid, stream)
+                  : launch_pair_variant<SKYRL_EPI_PARTIAL_F32, false>(p, grid, stream);
+    case SKYRL_EPI_ACC_I32:
+      return launch_pair_variant<SKYRL_EPI_ACC_I32, false>(p, grid, stream);
+    default:
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
   }
 }
 
@@ -493,6 +793,8 @@ static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStre
       return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
   }
 }
+
+static inline int kblocks_of(int k) { return (k + BK - 1) / BK; }
 
 GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs) {
   GemmPlan pl;
@@ -562,6 +864,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   const int sms = sm_count();
   if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
   const GemmPlan pl = plan_gemm(a.m, a.n, a.k, a.epilogue, a.split_k_slabs);
+  const int mt_est = (a.m + BM - 1) / BM;
   int bn_eff = pl.bn_eff;
   const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
   if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_BN")) {  // tuning aid: force the N tile width
@@ -622,6 +925,17 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff) * k_splits;
   int grid = static_cast<int>(max_total < sms ? max_total : sms);
   if (a.cta_limit > 0 && grid > a.cta_limit) grid = a.cta_limit;  // leave SMs to a concurrent collective
+  // Large problems with a long K loop: two M tiles per CTA.  The pair's epilogue is not overlapped with
+  // the next main loop, so this pays only when the K loop dwarfs it (measured: gain at K = 25600, loss at 5120).
+  bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 &&
+                static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
+  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_PAIR")) paired = paired && atoi(dbg) != 0;  // tuning aid
+  if (paired) {
+    const int64_t pair_total = static_cast<int64_t>((a.max_tiles + 1) / 2) * ((a.n + 255) / 256);
+    int pgrid = static_cast<int>(pair_total < sms ? pair_total : sms);
+    if (a.cta_limit > 0 && pgrid > a.cta_limit) pgrid = a.cta_limit;
+    return launch_pair(p, a.epilogue, lora, pgrid, stream);
+  }
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
                    : launch_bn<128>(p, a.epilogue, lora, grid, stream);
 }

@@ -46,7 +46,9 @@ def to_np(t):
     return t.numpy()
 
 
-def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what=""):
+def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what="", outliers=0):
+    """`outliers`: elements allowed beyond (max-abs AND one ulp).  Only the SwiGLU outputs use it: there a
+    one-ulp flip of a bf16 gate or up value, legitimate on its own, is amplified by the product."""
     got, want = np.asarray(got), np.asarray(want)
     assert got.shape == want.shape, (got.shape, want.shape)
     g32, w32 = got.astype(np.float32), want.astype(np.float32)
@@ -55,7 +57,8 @@ def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what=""):
     diff = np.abs(g32 - w32)
     ulp = O.bf16_ulp_distance(got, want)
     bad = (diff > MAX_ABS) & (ulp > 1)
-    assert not bad.any(), f"{what}: {int(bad.sum())} elements beyond max-abs {MAX_ABS} and 1 ulp; worst {diff.max()}"
+    assert int(bad.sum()) <= outliers, (
+        f"{what}: {int(bad.sum())} elements beyond max-abs {MAX_ABS} and 1 ulp; worst {diff.max()}")
     assert rel < REL_L2, f"{what}: relative L2 {rel} >= {REL_L2}"
     frac = float((ulp > 0).mean())
     assert frac <= max_ulp_frac, f"{what}: {frac:.2e} of the elements differ from the oracle"
@@ -289,6 +292,34 @@ def test_reference_group64_fixture(S):
                            to_dev(z[f"{name}.lora_b_bf16"].view(BF16)), float(z[f"{name}.lora_scaling"]), enabled=True)
     S.check_status()
     assert_bf16_close(to_np(y), z[f"{name}.expected_bf16"].view(BF16), max_ulp_frac=0.05, what=name)
+
+
+@pytest.mark.parametrize("kind", ["linear", "swiglu", "residual"])
+def test_large_problem_paired_tile_kernel(S, kind):
+    # enough 128x256 tiles (>= 4 per SM) and a long enough K loop (>= 64 blocks of 128) for the launcher to
+    # pick the two-tiles-per-CTA kernel; an odd number of M tiles and five adapters exercise the half-empty
+    # pair and per-tile LoRA operands
+    m, k, n, rank, na = 2200, 8192, 9728, 32, 5
+    x, w, a, b, s, ids = make_case(91, m, k, n, rank, na, w_std=0.05)
+    q, packed = device_weight(S, w)
+    xd, idd = to_dev(x), to_dev(ids)
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=k, padded_out_features=n)
+    if kind == "linear":
+        got = S.w8a8_lora_linear(xd, packed, lora, adapter_ids=idd, enabled=True)
+        want = O.quantized_lora_linear(x, q, a, b, s, ids)
+    elif kind == "swiglu":
+        got = S.w8a8_rms_gate_up_lora_swiglu(xd, None, packed, lora, adapter_ids=idd, enabled=True)
+        want = O.rms_gate_up_lora_swiglu(x, None, q, a, b, s, ids)
+    else:
+        res = np.random.default_rng(5).standard_normal((m, n)).astype(np.float32).astype(BF16)
+        got = S.w8a8_down_lora_residual(xd, packed, lora, residual=to_dev(res), adapter_ids=idd, enabled=True)
+        want = O.down_lora_residual(x, q, a, b, s, res, ids)
+    S.check_status()
+    assert_bf16_close(to_np(got), want, max_ulp_frac=5e-3, what=f"paired {kind}",
+                      outliers=want.size // 1000000 + 2 if kind == "swiglu" else 0)
+    acc = S.w8a8_int32_accumulator(xd, packed, enabled=True)
+    _, parts = O.quantized_lora_linear(x, q, return_parts=True)
+    np.testing.assert_array_equal(to_np(acc), parts["acc"][:, 0, :])
 
 
 def test_zero_input_gives_exact_zeros(S):

@@ -170,6 +170,9 @@ def run_device(args):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if args.tp_chunks > 1 and args.tp_reserve_sms > 0:
+            # the collective overlaps the GEMMs: keep it to the SMs the GEMMs leave free
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.tp_reserve_sms))
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             del os.environ["NCCL_DEBUG"]  # its banner goes to stdout; this program prints exactly one JSON line
         dist.init_process_group("nccl", device_id=device)

@@ -26,6 +26,8 @@
 // computed but never stored.  Every wait is bounded (see ptx_sm100.cuh).
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
@@ -47,7 +49,7 @@ template <int BN>
 struct GemmCfg {
   static constexpr int BAR_OFF = STAGE_AREA_BYTES;
   static constexpr int NUM_BARS = 2 * MAX_STAGES + 4 + 2;
-  static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 1024;  // + tmem ptr/abort + alignment slack
+  static constexpr int SMEM_BYTES = BAR_OFF + NUM_BARS * 8 + 16 + 128 + 1024;  // + tmem ptr/abort, tile ring, alignment slack
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -76,7 +78,47 @@ struct GemmParams {
   int kb_per_split;
   int64_t slab_stride;  // elements between slabs of the int32 output
   int a_rows;       // rows of the activation TMA box (64 when the batch has at most 64 rows, else 128)
+  int* sched;       // {tile claim counter, finished-CTA counter} of this launch, both zero on entry
 };
+
+// ---- dynamic tile scheduler --------------------------------------------------------------------------
+// Tiles are claimed from a global counter instead of a fixed stride, so a CTA that starts late (its SM
+// was held by another stream's kernel, e.g. a collective) simply takes fewer tiles.  The producer thread
+// claims tile numbers and hands them to the MMA and epilogue roles through a 4-slot ring in shared memory.
+constexpr int SCHED_SLOTS = 4;
+struct TileRing {
+  uint64_t full[SCHED_SLOTS];
+  uint64_t empty[SCHED_SLOTS];
+  int tile[SCHED_SLOTS];
+};
+__device__ __forceinline__ int sched_claim(TileRing* ring, uint32_t it, int* counter, int total,
+                                           volatile int* abort_flag, int* status, bool& ok) {
+  const uint32_t slot = it & (SCHED_SLOTS - 1);
+  ok = mbar_wait(&ring->empty[slot], ((it / SCHED_SLOTS) & 1u) ^ 1u, abort_flag, status, STATUS_TIMEOUT_PRODUCER);
+  if (!ok) return -1;
+  int t = atomicAdd(counter, 1);
+  if (t >= total) t = -1;
+  ring->tile[slot] = t;
+  mbar_arrive(&ring->full[slot]);  // release: the tile number is visible to whoever observes the phase
+  return t;
+}
+__device__ __forceinline__ int sched_read(TileRing* ring, uint32_t it, volatile int* abort_flag, int* status,
+                                          int code, bool& ok) {
+  const uint32_t slot = it & (SCHED_SLOTS - 1);
+  ok = mbar_wait(&ring->full[slot], (it / SCHED_SLOTS) & 1u, abort_flag, status, code);
+  return ok ? ring->tile[slot] : -1;
+}
+__device__ __forceinline__ void sched_release(TileRing* ring, uint32_t it) {
+  mbar_arrive(&ring->empty[it & (SCHED_SLOTS - 1)]);
+}
+// The last CTA of a launch puts the claim counter back to zero for the slot's next user.
+__device__ __forceinline__ void sched_finish(int* sched) {
+  if (atomicAdd(sched + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+    sched[0] = 0;
+    sched[1] = 0;
+    __threadfence();
+  }
+}
 
 struct TileCoord {
   int m_idx, n_idx;
@@ -218,11 +260,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
   uint64_t* lora_done = conv_done + 1;                // LoRA MMAs accumulated into TMEM
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  TileRing* ring = reinterpret_cast<TileRing*>(tmem_ptr_smem + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    for (int s = 0; s < SCHED_SLOTS; ++s) {
+      mbar_init(&ring->full[s], 1);
+      mbar_init(&ring->empty[s], 1 + EPI_THREADS / 32);  // the MMA thread and one lane of every epilogue warp
+    }
     for (int s = 0; s < MAX_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -295,7 +342,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         }
         return true;
       };
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (uint32_t it = 0; ok; ++it) {
+        const int t = sched_claim(ring, it, p.sched, total, abort_flag, p.status, ok);
+        if (t < 0) break;
         const TileCoord c = tile_coord(t / ksplits, tm, tn, band);
         const int4 tile = __ldg(p.tiles + c.m_idx);
         const int n0 = c.n_idx * bn_eff;
@@ -364,7 +413,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         ++lora_rounds;
         return true;
       };
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      for (; ok; ++it) {
+        const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_MMA, ok);
+        if (ok) sched_release(ring, it);
+        if (t < 0) break;
         const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
         ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
@@ -410,7 +462,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (; ok; ++it) {
+      const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE, ok);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) sched_release(ring, it);  // every lane has read the slot (warp-wide vote above)
+      if (t < 0) break;
       const TileCoord c = tile_coord(t / ksplits, tm, tn, band);
       const int4 tile = __ldg(p.tiles + c.m_idx);
       const int n0 = c.n_idx * bn_eff;
@@ -464,6 +521,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+  if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 
@@ -484,7 +542,7 @@ constexpr int PAIR_BN = 256;
 constexpr int PAIR_A_BYTES = 2 * BM * BK;
 constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_BN * BK;  // 64 KB
 constexpr int PAIR_STAGES = STAGE_AREA_BYTES / PAIR_STAGE_BYTES;  // 3
-constexpr int PAIR_SMEM_BYTES = STAGE_AREA_BYTES + (2 * PAIR_STAGES + 4) * 8 + 16 + 1024;
+constexpr int PAIR_SMEM_BYTES = STAGE_AREA_BYTES + (2 * PAIR_STAGES + 4) * 8 + 16 + 128 + 1024;
 
 template <int EPI, bool HAS_LORA>
 __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const __grid_constant__ GemmParams p) {
@@ -500,11 +558,16 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
   uint64_t* lora_done = conv_done + 1;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(lora_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+  TileRing* ring = reinterpret_cast<TileRing*>(tmem_ptr_smem + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    for (int s = 0; s < SCHED_SLOTS; ++s) {
+      mbar_init(&ring->full[s], 1);
+      mbar_init(&ring->empty[s], 1 + PAIR_EPI_THREADS / 32);
+    }
     for (int s = 0; s < PAIR_STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -567,7 +630,9 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         }
         return true;
       };
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (uint32_t it = 0; ok; ++it) {
+        const int t = sched_claim(ring, it, p.sched, total, abort_flag, p.status, ok);
+        if (t < 0) break;
         const TileCoord c = tile_coord(t, tp, tn, band);
         const int4 tile_a = __ldg(p.tiles + 2 * c.m_idx);
         const bool has_b = 2 * c.m_idx + 1 < tm;
@@ -625,7 +690,10 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         mma_commit(&empty_bar[st2]);
         return true;
       };
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+      for (; ok; ++it) {
+        const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_MMA, ok);
+        if (ok) sched_release(ring, it);
+        if (t < 0) break;
         const TileCoord c = tile_coord(t, tp, tn, band);
         const bool has_b = 2 * c.m_idx + 1 < tm;
         ok = mbar_wait(tmem_empty, (it & 1u) ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
@@ -667,7 +735,12 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
     const int r = quad * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
+    for (; ok; ++it) {
+      const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE, ok);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) sched_release(ring, it);
+      if (t < 0) break;
       const TileCoord c = tile_coord(t, tp, tn, band);
       const int tidx = 2 * c.m_idx + which;
       const bool present = tidx < tm;
@@ -718,6 +791,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+  if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
 template <int EPI, bool HAS_LORA>
@@ -795,6 +869,27 @@ static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStre
 }
 
 static inline int kblocks_of(int k) { return (k + BK - 1) / BK; }
+
+// Claim counters of the dynamic tile scheduler: one {claimed, finished} pair per launch, handed out round
+// robin.  A launch leaves its pair at zero (sched_finish), so a pair is ready again long before the ring
+// of SCHED_COUNTER_SLOTS launches comes back to it.
+constexpr int SCHED_COUNTER_SLOTS = 1024;
+static __device__ int g_sched_counters[SCHED_COUNTER_SLOTS][2];
+
+static int* next_sched_counter() {
+  static std::mutex mu;
+  static int* base[64] = {nullptr};
+  static unsigned seq = 0;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (base[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_sched_counters) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<int*>(ptr);
+  }
+  return base[dev] + 2 * (seq++ % SCHED_COUNTER_SLOTS);
+}
 
 GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs) {
   GemmPlan pl;
@@ -919,6 +1014,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     const int v = atoi(dbg);
     if (v >= 2 && v < p.num_stages) p.num_stages = v;
   }
+  p.sched = next_sched_counter();
+  if (p.sched == nullptr) return fail(SKYRL_ERR_LAUNCH, "gemm: scheduler counters unavailable");
   p.k_splits = k_splits;
   p.kb_per_split = kb_per_split;
   p.slab_stride = static_cast<int64_t>(a.m) * a.out_row_stride;

@@ -103,7 +103,7 @@ class TensorParallelMLPStack:
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
-        self.cta_limit = max(1, sm_count - reserve_sms)
+        self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self._comm = None
         self._partial = None
         self._act = None

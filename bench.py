@@ -538,10 +538,11 @@ def main():
     ap.add_argument("--m", type=int, default=0, help="override the token count (debugging)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging / small ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp-chunks", type=int, default=4,
+    ap.add_argument("--tp-chunks", type=int, default=2,
                     help="row chunks per block whose all-reduce overlaps the next chunk's kernels (N > 1)")
-    ap.add_argument("--tp-reserve-sms", type=int, default=16,
-                    help="SMs the GEMMs leave to the collective while chunks overlap (N > 1)")
+    ap.add_argument("--tp-reserve-sms", type=int, default=0,
+                    help="SMs the GEMMs leave to the collective while chunks overlap (N > 1); 0 = none: the GEMMs claim "
+                         "tiles dynamically, so CTAs displaced by the collective just take fewer tiles")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()

@@ -94,12 +94,15 @@ class TensorParallelMLPStack:
     Every operation of the block is row-wise, so the adapter-sorted rows are cut
     into `num_chunks` chunks: while NCCL reduces chunk c of a block on a second
     stream, the kernels of chunk c + 1 (and then of the next block's chunk c)
-    run on the main stream.  The GEMMs leave `reserve_sms` SMs free so that the
-    collective's kernels can be resident at the same time.  Blocks shorter than
-    129 rows take the small-batch path and are not chunked.
+    run on the main stream.  The GEMMs claim their tiles dynamically, so CTAs
+    whose SM is held by the collective's kernels simply take fewer tiles; with
+    `reserve_sms` > 0 the GEMMs additionally launch that many CTAs fewer.
+    Measured on 4 GPUs (c5): 2 chunks 18.4 ms per step, 4 chunks 19.9 ms,
+    unchunked 21.3 ms.  Blocks shorter than 129 rows take the small-batch path
+    and are not chunked.
     """
 
-    def __init__(self, blocks, *, group=None, num_chunks: int = 4, reserve_sms: int = 16, sm_count: int = 148):
+    def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 0, sm_count: int = 148):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks

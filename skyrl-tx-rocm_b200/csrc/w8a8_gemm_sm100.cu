@@ -41,6 +41,10 @@ constexpr int EPI_THREADS = 256;
 constexpr int LORA_ROW_BYTES = SKYRL_LORA_RANK_PAD * 2;  // 128-byte rows of z and packed B
 
 constexpr int STAGE_AREA_BYTES = 224 * 1024;  // shared memory given to the TMA pipeline stages
+constexpr int EPI_STAGE_PITCH = 80;           // bytes per row of an epilogue warp's store-staging tile (64 + pad)
+constexpr int EPI_STAGE_BYTES = 32 * EPI_STAGE_PITCH;
+// the single-tile kernel carves eight such tiles out of the top of the stage area
+constexpr int SINGLE_STAGE_AREA = STAGE_AREA_BYTES - 8 * EPI_STAGE_BYTES;
 constexpr int MAX_STAGES = 12;
 constexpr int Z_PLANE_BYTES = BM * LORA_ROW_BYTES;  // one bf16 plane of z for a tile: 128 rows x 128 bytes
 constexpr int LORA_INJECT_AFTER = 8;  // K blocks of the next tile issued before the previous tile's LoRA operands
@@ -79,6 +83,7 @@ struct GemmParams {
   int64_t slab_stride;  // elements between slabs of the int32 output
   int a_rows;       // rows of the activation TMA box (64 when the batch has at most 64 rows, else 128)
   int* sched;       // {tile claim counter, finished-CTA counter} of this launch, both zero on entry
+  int direct_stores;  // tuning aid: 1 = bf16 epilogues store from registers instead of through the staging tile
 };
 
 // ---- dynamic tile scheduler --------------------------------------------------------------------------
@@ -160,10 +165,49 @@ __device__ __forceinline__ void epi_convert_chunk(uint32_t taddr, int nc, int n_
   tmem_st32(taddr, v);
 }
 
+// Row r of an epilogue warp's chunk is held by lane r, so a register store instruction touches 32 rows
+// with 16 bytes each: half sectors, scattered.  With a staging tile the warp transposes the chunk and
+// every store instruction writes whole 32- or 64-byte runs of 8 or 16 rows (and reads the residual the
+// same way).  `stage` == nullptr keeps the direct form.
+__device__ __forceinline__ void epi_staged_store(unsigned char* stage, int lane, const uint32_t* packed, int words,
+                                                 bool row_valid, int64_t orow, __nv_bfloat16* out, int64_t out_stride,
+                                                 int col0, int cols_valid, const __nv_bfloat16* residual,
+                                                 int64_t res_stride) {
+  // `words` 32-bit words (2 bf16 each) per row: 16 (64 bytes) or 8 (32 bytes)
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * EPI_STAGE_PITCH);
+  for (int q = 0; q < words / 4; ++q) mine[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  __syncwarp();
+  const int pieces = words / 4;            // 16-byte pieces per row: 4 or 2
+  const int rows_per_round = 32 / pieces;  // 8 or 16
+  const int piece = lane % pieces, sub = lane / pieces;
+  const int orow_lo = static_cast<int>(orow & 0xffffffffll), orow_hi = static_cast<int>(orow >> 32);
+  for (int round = 0; round < pieces; ++round) {
+    const int r = sub + round * rows_per_round;
+    const bool valid = __shfl_sync(0xffffffffu, row_valid ? 1 : 0, r) != 0;
+    const int lo = __shfl_sync(0xffffffffu, orow_lo, r), hi = __shfl_sync(0xffffffffu, orow_hi, r);
+    if (valid && piece * 8 < cols_valid) {
+      const int64_t row = (static_cast<int64_t>(hi) << 32) | static_cast<uint32_t>(lo);
+      uint4 v = *reinterpret_cast<const uint4*>(stage + r * EPI_STAGE_PITCH + piece * 16);
+      if (residual != nullptr) {
+        const uint4 rv = __ldg(reinterpret_cast<const uint4*>(residual + row * res_stride + col0 + piece * 8));
+        const uint32_t vw[4] = {v.x, v.y, v.z, v.w}, rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2)
+          o[j2] = pack_bf16x2(__fadd_rn(bf16_lo(vw[j2]), bf16_lo(rw[j2])), __fadd_rn(bf16_hi(vw[j2]), bf16_hi(rw[j2])));
+        v = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      *reinterpret_cast<uint4*>(out + row * out_stride + col0 + piece * 8) = v;
+    }
+  }
+  __syncwarp();
+}
+
 // pass 2: final values of one chunk -> global memory (single bf16 cast, SwiGLU / residual / raw forms)
 template <int EPI, bool HAS_LORA>
 __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t taddr, int nc, int n_end, float sxr,
-                                                bool row_valid, int64_t orow, int64_t slab_off) {
+                                                bool row_valid, int64_t orow, int64_t slab_off,
+                                                unsigned char* stage = nullptr, int lane = 0) {
   uint32_t v[32];
   __syncwarp();
   tmem_ld32(taddr, v);
@@ -193,13 +237,36 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
       f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
     }
   }
-  if (!row_valid) return;
   if (EPI == SKYRL_EPI_PARTIAL_F32) {
+    if (!row_valid) return;
     float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
 #pragma unroll
     for (int g = 0; g < 8; ++g)
       if (nc + g * 4 < n_end) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
-  } else if (EPI == SKYRL_EPI_LINEAR) {
+    return;
+  }
+  if (stage != nullptr) {
+    // staged form: every lane takes part (shuffles), invalid rows are masked at the store
+    uint32_t o[16];
+    if (EPI == SKYRL_EPI_SWIGLU) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float h0 = __fmul_rn(silu_f32(round_bf16(f[4 * j])), round_bf16(f[4 * j + 1]));
+        const float h1 = __fmul_rn(silu_f32(round_bf16(f[4 * j + 2])), round_bf16(f[4 * j + 3]));
+        o[j] = pack_bf16x2(h0, h1);
+      }
+      epi_staged_store(stage, lane, o, 8, row_valid, orow, static_cast<__nv_bfloat16*>(p.out), p.out_stride, nc >> 1,
+                       (n_end - nc) >> 1, nullptr, 0);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+      epi_staged_store(stage, lane, o, 16, row_valid, orow, static_cast<__nv_bfloat16*>(p.out), p.out_stride, nc,
+                       n_end - nc, EPI == SKYRL_EPI_RESIDUAL ? p.residual : nullptr, p.res_stride);
+    }
+    return;
+  }
+  if (!row_valid) return;
+  if (EPI == SKYRL_EPI_LINEAR) {
     uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * p.out_stride + nc);
 #pragma unroll
     for (int g = 0; g < 4; ++g)
@@ -460,6 +527,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     const int c_begin = warp < 4 ? 0 : (nchunks + 1) / 2;  // column chunks [c_begin, c_end) of the tile
     const int c_end = warp < 4 ? (nchunks + 1) / 2 : nchunks;
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
+    unsigned char* store_stage =
+        p.direct_stores ? nullptr : smem + SINGLE_STAGE_AREA + (warp < 4 ? warp : warp - 2) * EPI_STAGE_BYTES;
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
     for (; ok; ++it) {
@@ -502,7 +571,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 #pragma unroll 1
       for (int cc = c_begin; cc < c_end; ++cc)
         epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow,
-                                       (t % ksplits) * p.slab_stride);
+                                       (t % ksplits) * p.slab_stride, store_stage, lane);
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[s]);
     }
@@ -1008,7 +1077,9 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   p.a_rows = (!lora && a.m <= 64) ? 64 : BM;
   p.stage_bytes = p.a_rows * BK + (bn_eff * BK + 1023) / 1024 * 1024;
   if (lora && p.stage_bytes < 2 * Z_PLANE_BYTES) p.stage_bytes = 2 * Z_PLANE_BYTES;  // a slot also carries two z planes
-  p.num_stages = STAGE_AREA_BYTES / p.stage_bytes;
+  p.num_stages = SINGLE_STAGE_AREA / p.stage_bytes;
+  p.direct_stores = 0;
+  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_DIRECT_STORES")) p.direct_stores = atoi(dbg) != 0;  // tuning aid
   if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
   if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_STAGES")) {  // tuning aid: cap the pipeline depth
     const int v = atoi(dbg);

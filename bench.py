@@ -134,9 +134,13 @@ def synth_weight(S, torch, n, k, seed, device):
     return S.pack_weight_nk(wq, sw)
 
 
-def synth_lora(S, torch, adapters, k, rank, n, alpha, seed, device):
+def synth_lora(S, torch, adapters, k, rank, n, alpha, seed, device, seed_b=None):
+    """`seed_b` seeds B separately: a tensor-parallel rank shares the replicated half of a LoRA pair with the
+    other ranks (A of gate_up, B of down) and draws only its shard of the other half from its own seed."""
     gen = torch.Generator(device=device).manual_seed(seed)
     a = (torch.randn((adapters, k, rank), generator=gen, device=device) / (k ** 0.5)).to(torch.bfloat16)
+    if seed_b is not None:
+        gen = torch.Generator(device=device).manual_seed(seed_b)
     b = (torch.randn((adapters, rank, n), generator=gen, device=device) * 0.02).to(torch.bfloat16)
     s = torch.full((adapters,), alpha / rank, dtype=torch.float32, device=device)
     return S.pack_lora(a, b, s, in_features=k, padded_out_features=n)
@@ -170,9 +174,8 @@ def run_device(args):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if args.tp_chunks > 1 and args.tp_reserve_sms > 0:
-            # the collective overlaps the GEMMs: keep it to the SMs the GEMMs leave free
-            os.environ.setdefault("NCCL_MAX_CTAS", str(args.tp_reserve_sms))
+        if args.nccl_max_ctas > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_max_ctas))
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             del os.environ["NCCL_DEBUG"]  # its banner goes to stdout; this program prints exactly one JSON line
         dist.init_process_group("nccl", device_id=device)
@@ -207,20 +210,26 @@ def run_device(args):
             delta = (torch.randn((hidden,), generator=gen, device=device) * 0.02).to(torch.bfloat16)
             gu_w = synth_weight(S, torch, 2 * ish, hidden, seed * 131 + rank * 7 + 1, device)
             dn_w = synth_weight(S, torch, hidden, ish, seed * 131 + rank * 7 + 2, device)
-            gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * ish, alpha, seed * 131 + rank * 7 + 3, device)
-            dn_l = synth_lora(S, torch, wl["adapters"], ish, wl["rank"], hidden, alpha, seed * 131 + rank * 7 + 4, device)
+            gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * ish, alpha, seed * 131 + 3, device,
+                              seed_b=seed * 131 + rank * 7 + 3)
+            dn_l = synth_lora(S, torch, wl["adapters"], ish, wl["rank"], hidden, alpha, seed * 131 + rank * 7 + 4, device,
+                              seed_b=seed * 131 + 4)
             blocks.append((delta, gu_w, gu_l, dn_w, dn_l))
         tp_stack = None
         if tp > 1:
             from skyrl_tx_rocm_b200.tp import TensorParallelMLP, TensorParallelMLPStack
 
             tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks,
-                                              reserve_sms=args.tp_reserve_sms)
+                                              reserve_sms=args.tp_reserve_sms,
+                                              sequence_parallel=bool(args.tp_sequence_parallel),
+                                              peer_scatter=bool(args.tp_peer_scatter))
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
-        gu_ops_launch = 2.0 * m * hidden * 2 * ish
-        dn_ops_launch = 2.0 * m * ish * hidden
+        # the timed GEMM launches are those of chunk 0 when the tensor-parallel stack cuts the rows into chunks
+        m_launch = min(m, S.chunk_rows(m, args.tp_chunks)) if (tp > 1 and m > 128) else m
+        gu_ops_launch = 2.0 * m_launch * hidden * 2 * ish
+        dn_ops_launch = 2.0 * m_launch * ish * hidden
         gu_bytes_launch = 2 * ish * hidden + m * hidden + 4 * (2 * ish) + 4 * m + 3 * m * 64 * 2 \
             + wl["adapters"] * 2 * ish * wl["rank"] * 2 + m * ish * 2
         dn_bytes_launch = hidden * ish + m * ish + 4 * hidden + 4 * m + 3 * m * 64 * 2 \
@@ -424,7 +433,9 @@ def run_device(args):
         "config": {"workload": args.workload, "kind": kind, "tokens": m, "layers": layers,
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
                    "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
-                   **({"tp_chunks": args.tp_chunks} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
+                   **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
+                       "tp_peer_scatter": bool(tp_stack.peer_scatter) if tp_stack is not None else False,
+                       "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -540,9 +551,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tp-chunks", type=int, default=2,
                     help="row chunks per block whose all-reduce overlaps the next chunk's kernels (N > 1)")
-    ap.add_argument("--tp-reserve-sms", type=int, default=0,
-                    help="SMs the GEMMs leave to the collective while chunks overlap (N > 1); 0 = none: the GEMMs claim "
-                         "tiles dynamically, so CTAs displaced by the collective just take fewer tiles")
+    ap.add_argument("--tp-sequence-parallel", type=int, default=1,
+                    help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
+                         "0: one fp32 all-reduce per chunk")
+    ap.add_argument("--tp-reserve-sms", type=int, default=4,
+                    help="SMs the GEMMs leave to the second stream's small kernels while chunks overlap (N > 1): the "
+                         "one-word all-reduce, the finalize / quantise kernels of the rank's own rows, the gathers")
+    ap.add_argument("--tp-peer-scatter", type=int, default=1,
+                    help="1: the down GEMM's epilogue stores each owner's fp32 partial sums into the owner's memory "
+                         "(symmetric memory over NVLink); 0: NCCL reduce-scatter")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="> 0: sets NCCL_MAX_CTAS (tuning aid)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()

@@ -114,7 +114,7 @@ SKYRL_API int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, cons
  * skyrl/tx/layers/lora.py:150 and `x.f32 @ lora_a.f32` of
  * skyrl/tx/kernels/quantized_lora.py:301.
  *   x bf16 [m, k] in sorted row order; lora_a_packed bf16 [A, 64, k];
- *   z_parts bf16 [3, m, 64]                                                   */
+ *   z_parts bf16 [m, 3, 64]: the three parts of a row side by side            */
 SKYRL_API int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
                                const float* lora_scaling, int32_t num_adapters, int32_t rank, const int32_t* tiles,
                                const int32_t* num_tiles, int32_t max_tiles, void* z_parts, int32_t* status,
@@ -144,7 +144,7 @@ typedef struct SkyrlW8A8GemmArgs {
   const float* sx;          /* fp32 [m]                                                */
   const void* wq;           /* int8 [ceil(k / 128), n, 128] packed                     */
   const float* sw;          /* fp32 [n]                                                */
-  const void* z_parts;      /* bf16 [3, m, 64] (hi, mid, lo planes) or NULL when rank == 0 */
+  const void* z_parts;      /* bf16 [m, 3, 64] (hi, mid, lo parts per row) or NULL when rank == 0 */
   const void* lora_b_packed;/* bf16 [A, n, 64]                                         */
   const int32_t* tiles;     /* int32 [4 * max_tiles] from skyrl_lora_route_sm100_v1    */
   const int32_t* num_tiles; /* device scalar                                           */
@@ -160,6 +160,14 @@ typedef struct SkyrlW8A8GemmArgs {
                                skyrl_w8a8_gemm_k_splits(...) slabs (int32 addition is exact)      */
   int32_t cta_limit;        /* > 0: launch at most this many CTAs (one per SM otherwise), so that a
                                collective running on another stream finds free SMs            */
+  void* scatter_bases[8];   /* SKYRL_EPI_PARTIAL_F32 with scatter_rows > 0: the reduce-scatter of a row-    */
+  int32_t scatter_row0;     /* parallel projection folded into the epilogue.  Sorted row i belongs to owner */
+  int32_t scatter_rows;     /* o = (i - scatter_row0) / scatter_rows and its fp32 partial sums are stored   */
+                            /* at scatter_bases[o] + (i - scatter_row0 - o * scatter_rows) * out_row_stride */
+                            /* instead of `out`; a base may point into another GPU's memory (peer mapping): */
+                            /* the kernel uses plain stores.  Rows below scatter_row0 must not occur in     */
+                            /* `tiles`.  XLA inserts a separate collective here                             */
+                            /* (skyrl/tx/models/qwen3_5.py:644, ("tp", "fsdp") sharding of down_proj).      */
 } SkyrlW8A8GemmArgs;
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
@@ -247,6 +255,11 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
 #define SKYRL_MLP_REUSE_ROUTING 1u /* the workspace still holds the routing (row permutation, tile list) of an
                                       earlier call with the same m and adapter_ids: skip the routing kernel.
                                       Adapter ids do not change between the layers of one forward pass. */
+#define SKYRL_MLP_INPUT_PREPARED 2u /* the workspace already holds the int8 codes, scales and LoRA-A projection of
+                                       this call's rows of rmsnorm(x) (written by skyrl_w8a8_mlp_tp_prepare_sm100_v1
+                                       here or, through a gather, on other ranks): skip that stage. */
+#define SKYRL_MLP_FINALIZE_SORTED 4u /* skyrl_w8a8_mlp_tp_finalize_sm100_v1 writes row i to out[i] (sorted order)
+                                        instead of out[perm[i]]; the residual is still read at perm[i]. */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
@@ -289,7 +302,10 @@ typedef struct SkyrlW8A8MlpArgs {
                              /* so that a caller can reduce chunk c over ranks while chunk c + 1 computes.    */
                              /* The first call of a block (without SKYRL_MLP_REUSE_ROUTING) routes all chunks. */
   int32_t gemm_cta_limit;    /* > 0: cap on the CTAs of the GEMM launches (see SkyrlW8A8GemmArgs.cta_limit)   */
-  int32_t reserved;
+  int32_t tp_scatter_rows;   /* > 0 (down_epilogue PARTIAL_F32): the down GEMM scatters this call's rows to   */
+  void* tp_scatter_bases[8]; /* their owners, tp_scatter_rows consecutive sorted rows each starting at the    */
+                             /* first row of the call's chunk (see SkyrlW8A8GemmArgs.scatter_bases); `out` is  */
+                             /* then not written.                                                             */
 } SkyrlW8A8MlpArgs;
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
@@ -304,6 +320,39 @@ SKYRL_API int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* args, skyrl_
  * workspace: it holds the row permutation); `reduced` is fp32 [m, H] in sorted order. */
 SKYRL_API int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* args, const float* reduced, void* out,
                                         int32_t row_begin, int32_t row_count, skyrl_stream_t stream);
+/* The same for partial sums that were scattered to their owner (tp_scatter_bases) and not yet added:
+ * slabs[s] holds rank s's fp32 partial sums of sorted rows [row_begin, row_begin + row_count), row i at
+ * slabs[s] + (i - row_begin) * H.  The slabs are added in ascending s in fp32, the order of the group sum
+ * of skyrl/tx/kernels/quantized_lora.py:253, then cast and finalized as above. */
+SKYRL_API int skyrl_w8a8_mlp_tp_finalize_slabs_sm100_v1(const SkyrlW8A8MlpArgs* args, const float* const* slabs,
+                                              int32_t num_slabs, void* out, int32_t row_begin, int32_t row_count,
+                                              skyrl_stream_t stream);
+
+/* Sequence-parallel form of the tensor-parallel block.  Every stage but the two GEMMs is row-wise, so a
+ * rank of a tensor-parallel group need only run the stage in front of gate_up (RMSNorm, int8 codes,
+ * scales, LoRA-A projection) on ITS share of the sorted rows and gather the other ranks' results, which
+ * are a quarter of the bytes of the bf16 rows; behind down_proj a reduce-scatter replaces the all-reduce
+ * and each rank finalizes its share only.  The reference leaves this choice to GSPMD (activations carry no
+ * "tp" axis in skyrl/tx/models/qwen3_5.py:633,644, so XLA is free to shard them by rows between the two
+ * collectives); the values computed per row are the same either way.
+ *
+ * skyrl_w8a8_mlp_tp_prepare_sm100_v1 runs that front stage for sorted rows [row_begin, row_begin +
+ * row_count), which must lie inside the chunk (num_chunks, chunk_index) of `args`, and routes first unless
+ * SKYRL_MLP_REUSE_ROUTING is set.  It reads args->x at perm[i] for the rows i of the range only, so x may
+ * be a buffer in which only this rank's rows are current.  The caller then gathers the three regions
+ * named by skyrl_w8a8_mlp_workspace_regions over the ranks and calls skyrl_w8a8_mlp_block_sm100_v1 with
+ * SKYRL_MLP_INPUT_PREPARED. */
+SKYRL_API int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* args, int32_t row_begin, int32_t row_count,
+                                       skyrl_stream_t stream);
+/* Byte offsets inside an MLP workspace of the regions a gather moves, each indexed by sorted row:
+ * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 3, 64]. */
+SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
+                                     size_t* offsets);
+/* out[perm[i], :] = sorted_rows[i, :] for all m rows of a bf16 [m, H] matrix (perm from the workspace of
+ * `args`): the last block of a sequence-parallel stack gathers its rows in sorted order, then restores
+ * token order with this. */
+SKYRL_API int skyrl_w8a8_mlp_tp_unsort_sm100_v1(const SkyrlW8A8MlpArgs* args, const void* sorted_rows, void* out,
+                                      skyrl_stream_t stream);
 
 /* ------------------------------------------------------------------------- *
  * Pack helpers (load-time, device to device)

@@ -18,6 +18,8 @@ LIB_PATH = PKG / "lib" / "libskyrl_w8a8_sm100.so"
 EPI_LINEAR, EPI_SWIGLU, EPI_RESIDUAL, EPI_ACC_I32, EPI_PARTIAL_F32 = 0, 1, 2, 3, 4
 NOALLOC_SCRATCH_BYTES = 32 << 20
 MLP_REUSE_ROUTING = 1
+MLP_INPUT_PREPARED = 2
+MLP_FINALIZE_SORTED = 4
 LORA_RANK_PAD = 64
 TILE_ROWS = 128
 WEIGHT_KBLOCK = 128
@@ -28,7 +30,7 @@ ERROR_NAMES = {
 STATUS_NAMES = {
     101: "bounded wait ran out in the TMA producer", 102: "bounded wait ran out in the MMA issuer",
     103: "bounded wait ran out in the epilogue", 104: "bounded wait ran out in the LoRA step",
-    201: "adapter id outside [0, num_adapters)", 202: "tile list overflow",
+    201: "adapter id outside [0, num_adapters)", 202: "tile list overflow", 203: "scattered partial-sum row without an owner",
 }
 
 
@@ -42,6 +44,7 @@ class GemmArgs(C.Structure):
         ("residual", C.c_void_p), ("out", C.c_void_p),
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
         ("split_k_slabs", C.c_int32), ("cta_limit", C.c_int32),
+        ("scatter_bases", C.c_void_p * 8), ("scatter_row0", C.c_int32), ("scatter_rows", C.c_int32),
     ]
 
 
@@ -72,7 +75,8 @@ class MlpArgs(C.Structure):
         ("adapter_ids", C.c_void_p), ("out", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p), ("timing_events", C.c_void_p * 4),
         ("flags", C.c_uint32), ("b_rows_rank", C.c_int32), ("gu_b_rows", C.c_void_p), ("dn_b_rows", C.c_void_p),
-        ("num_chunks", C.c_int32), ("chunk_index", C.c_int32), ("gemm_cta_limit", C.c_int32), ("reserved", C.c_int32),
+        ("num_chunks", C.c_int32), ("chunk_index", C.c_int32), ("gemm_cta_limit", C.c_int32), ("tp_scatter_rows", C.c_int32),
+        ("tp_scatter_bases", C.c_void_p * 8),
     ]
 
 
@@ -98,6 +102,12 @@ SYMBOLS = {
     "skyrl_w8a8_mlp_block_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_tp_finalize_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_int32,
                                                       C.c_int32, C.c_void_p]),
+    "skyrl_w8a8_mlp_tp_finalize_slabs_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.POINTER(C.c_void_p), C.c_int32,
+                                                            C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "skyrl_w8a8_mlp_tp_prepare_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_int32, C.c_int32, C.c_void_p]),
+    "skyrl_w8a8_mlp_workspace_regions": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                   C.POINTER(C.c_size_t)]),
+    "skyrl_w8a8_mlp_tp_unsort_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_void_p]),
     "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_weight_nk_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_lora_a_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),

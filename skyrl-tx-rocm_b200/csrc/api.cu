@@ -211,7 +211,10 @@ struct Projection {
   bool keep_xn;           // sorted route: x must be re-laid out (gathered / normalised) for the projection MMA
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
+  bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
   int cta_limit;
+  void* const* scatter_bases;  // row scatter of the fp32 partial sums (see SkyrlW8A8GemmArgs) or NULL
+  int scatter_row0, scatter_rows;
   const void* wq;
   const float* sw;
   const void* a_packed;
@@ -237,6 +240,29 @@ struct Projection {
   void* ev_begin;
   void* ev_end;
 };
+
+// Quantiser stage of the sorted route for rows [q_row0, q_row0 + q_rows): RMSNorm + int8 codes + scales
+// (+ the normalised bf16 rows the LoRA-A projection reads), then the LoRA-A projection of those rows.
+static int run_quant_stage(const Projection& q, cudaStream_t stream) {
+  const bool lora = q.rank > 0;
+  const bool need_xn = lora && q.keep_xn;
+  const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
+  int rc;
+  // a gather reads rows perm[r0 ...] of x; without one the chunk's rows are rows r0 ... of x itself
+  const unsigned char* xsrc = static_cast<const unsigned char*>(q.x) +
+                              (q.gather != nullptr ? 0 : static_cast<size_t>(r0) * q.x_stride * 2);
+  if ((rc = launch_rms_quant(xsrc, q.x_stride, q.rms_delta, q.eps, q.gather != nullptr ? q.gather + r0 : nullptr,
+                             rows, q.k, q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
+                             need_xn ? q.xn + static_cast<size_t>(r0) * q.k : nullptr, stream)))
+    return rc;
+  if (lora) {
+    const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
+    if ((rc = launch_lora_a_proj(xa, q.m, q.k, q.a_packed, q.scaling, q.na, q.rank, q.tiles, q.num_tiles, q.mt,
+                                 q.z_parts, q.status, stream, r0, r0 + rows)))
+      return rc;
+  }
+  return SKYRL_OK;
+}
 
 static int run_projection(const Projection& q, cudaStream_t stream) {
   const bool lora = q.rank > 0;
@@ -278,21 +304,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
                                 q.residual_stride, q.out, q.out_stride, stream);
   }
   {
-    const bool need_xn = lora && q.keep_xn;
-    const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
-    // a gather reads rows perm[r0 ...] of x; without one the chunk's rows are rows r0 ... of x itself
-    const unsigned char* xsrc = static_cast<const unsigned char*>(q.x) +
-                                (q.gather != nullptr ? 0 : static_cast<size_t>(r0) * q.x_stride * 2);
-    if ((rc = launch_rms_quant(xsrc, q.x_stride, q.rms_delta, q.eps, q.gather != nullptr ? q.gather + r0 : nullptr,
-                               rows, q.k, q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
-                               need_xn ? q.xn + static_cast<size_t>(r0) * q.k : nullptr, stream)))
-      return rc;
-    if (lora) {
-      const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
-      if ((rc = launch_lora_a_proj(xa, q.m, q.k, q.a_packed, q.scaling, q.na, q.rank, q.tiles, q.num_tiles, q.mt,
-                                   q.z_parts, q.status, stream)))
-        return rc;
-    }
+    if (!q.skip_quant && (rc = run_quant_stage(q, stream))) return rc;
     g.rank = q.rank;
     g.z_parts = lora ? q.z_parts : nullptr;
   }
@@ -317,6 +329,11 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   g.residual_row_stride = q.residual_stride;
   g.status = q.status;
   g.cta_limit = q.cta_limit;
+  if (q.scatter_bases != nullptr && q.scatter_rows > 0) {
+    for (int o = 0; o < 8; ++o) g.scatter_bases[o] = q.scatter_bases[o];
+    g.scatter_row0 = q.scatter_row0;
+    g.scatter_rows = q.scatter_rows;
+  }
   if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
   rc = launch_gemm(g, stream);
   if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
@@ -408,69 +425,84 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   return run_projection(q, stream);
 }
 
-extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_stream_t stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: args is null");
+namespace skyrl {
+
+// What one MLP call works on: the carved workspace and the chunk of sorted rows with its tile list.
+struct MlpPlan {
+  MlpWs w;
+  int na;
+  bool rows_path, routed, chunked;
+  const int32_t* perm;
+  int chunk_rows, chunk_cap, mt, row0, rows;
+  const int32_t* tiles;
+  const int32_t* num_tiles;
+};
+
+static int plan_mlp(const SkyrlW8A8MlpArgs* a, const char* who, MlpPlan* pl) {
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: args is null", who);
   if (a->struct_size != sizeof(SkyrlW8A8MlpArgs))
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: struct_size %u does not match ABI v%d (%zu)", a->struct_size,
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: struct_size %u does not match ABI v%d (%zu)", who, a->struct_size,
                 SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8MlpArgs));
-  if (a->m <= 0 || a->hidden <= 0 || a->inter <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: non-positive shape");
+  if (a->m <= 0 || a->hidden <= 0 || a->inter <= 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: non-positive shape", who);
   if (a->x == nullptr || a->gu_wq == nullptr || a->gu_sw == nullptr || a->dn_wq == nullptr || a->dn_sw == nullptr ||
       a->out == nullptr || a->status == nullptr)
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: null buffer");
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: null buffer", who);
   if (a->down_epilogue != SKYRL_EPI_RESIDUAL && a->down_epilogue != SKYRL_EPI_PARTIAL_F32 &&
       a->down_epilogue != SKYRL_EPI_LINEAR)
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: down_epilogue must be RESIDUAL, LINEAR or PARTIAL_F32");
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: down_epilogue must be RESIDUAL, LINEAR or PARTIAL_F32", who);
   if (a->rank < 0 || a->rank > SKYRL_LORA_RANK_PAD)
-    return fail(SKYRL_ERR_UNSUPPORTED, "mlp: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a->rank);
+    return fail(SKYRL_ERR_UNSUPPORTED, "%s: LoRA rank must be in [0, %d], got %d", who, SKYRL_LORA_RANK_PAD, a->rank);
   const bool lora = a->rank > 0;
   if (lora && (a->gu_a_packed == nullptr || a->gu_b_packed == nullptr || a->gu_scaling == nullptr ||
                a->dn_a_packed == nullptr || a->dn_b_packed == nullptr || a->dn_scaling == nullptr ||
                a->num_adapters <= 0))
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: LoRA tables missing");
-  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
-  const MlpWs w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, na);
-  int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "mlp");
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: LoRA tables missing", who);
+  pl->na = a->num_adapters > 0 ? a->num_adapters : 1;
+  pl->w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, pl->na);
+  int rc = check_ws(a->workspace, a->workspace_bytes, pl->w.bytes, who);
   if (rc) return rc;
-  const bool rows_path = a->m <= ROWS_PATH_MAX_M;
-  const bool routed = a->adapter_ids != nullptr && !rows_path;
-  const int32_t* perm = routed ? w.perm : nullptr;
-  const bool chunked = a->num_chunks > 1 && !rows_path;
-  if (chunked && (a->num_chunks > MAX_CHUNKS || a->chunk_index < 0 || a->chunk_index >= a->num_chunks))
-    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: num_chunks must be <= %d and chunk_index inside it", MAX_CHUNKS);
-  const int chunk_rows =
-      chunked ? ((a->m + a->num_chunks - 1) / a->num_chunks + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS * SKYRL_TILE_ROWS
-              : 0;
-  const int chunk_cap = chunked ? tile_cap(chunk_rows, na) : 0;
-  const int mt = chunked ? chunk_cap : max_tiles_for(a->m, na);
-  const int row0 = chunked ? a->chunk_index * chunk_rows : 0;
-  const int rows = chunked ? (a->m - row0 < chunk_rows ? a->m - row0 : chunk_rows) : a->m;
-  if (rows <= 0) return SKYRL_OK;  // more chunks than rows: nothing to do for this one
-  const int32_t* tiles = chunked ? w.tiles + 4 * static_cast<size_t>(a->chunk_index) * chunk_cap : w.tiles;
-  const int32_t* num_tiles = chunked ? w.num_tiles + a->chunk_index : w.num_tiles;
+  pl->rows_path = a->m <= ROWS_PATH_MAX_M;
+  pl->routed = a->adapter_ids != nullptr && !pl->rows_path;
+  pl->perm = pl->routed ? pl->w.perm : nullptr;
+  pl->chunked = a->num_chunks > 1 && !pl->rows_path;
+  if (pl->chunked && (a->num_chunks > MAX_CHUNKS || a->chunk_index < 0 || a->chunk_index >= a->num_chunks))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "%s: num_chunks must be <= %d and chunk_index inside it", who, MAX_CHUNKS);
+  pl->chunk_rows = pl->chunked ? ((a->m + a->num_chunks - 1) / a->num_chunks + SKYRL_TILE_ROWS - 1) / SKYRL_TILE_ROWS *
+                                     SKYRL_TILE_ROWS
+                               : 0;
+  pl->chunk_cap = pl->chunked ? tile_cap(pl->chunk_rows, pl->na) : 0;
+  pl->mt = pl->chunked ? pl->chunk_cap : max_tiles_for(a->m, pl->na);
+  pl->row0 = pl->chunked ? a->chunk_index * pl->chunk_rows : 0;
+  pl->rows = pl->chunked ? (a->m - pl->row0 < pl->chunk_rows ? a->m - pl->row0 : pl->chunk_rows) : a->m;
+  pl->tiles = pl->chunked ? pl->w.tiles + 4 * static_cast<size_t>(a->chunk_index) * pl->chunk_cap : pl->w.tiles;
+  pl->num_tiles = pl->chunked ? pl->w.num_tiles + a->chunk_index : pl->w.num_tiles;
+  return SKYRL_OK;
+}
 
-  if ((a->flags & SKYRL_MLP_REUSE_ROUTING) == 0) {
-    if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles,
-                           static_cast<int>(tile_buffer_slots(a->m, na)), a->status, stream, chunk_rows, chunk_cap)))
-      return rc;
-  }
+static int route_mlp(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl, cudaStream_t stream) {
+  if ((a->flags & SKYRL_MLP_REUSE_ROUTING) != 0) return SKYRL_OK;
+  return launch_route(pl.routed ? a->adapter_ids : nullptr, a->m, pl.na, pl.w.perm, pl.w.tiles, pl.w.num_tiles,
+                      static_cast<int>(tile_buffer_slots(a->m, pl.na)), a->status, stream, pl.chunk_rows, pl.chunk_cap);
+}
 
-  // front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU; h keeps the row order of the GEMM
+// front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU; h keeps the row order of the GEMM
+static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl) {
+  const MlpWs& w = pl.w;
   Projection q = {};
   q.x = a->x;
   q.x_stride = a->hidden;
   q.rms_delta = a->rms_delta;
   q.eps = a->rms_eps;
-  q.gather = perm;
-  q.keep_xn = routed || a->rms_delta != nullptr;
+  q.gather = pl.perm;
+  q.keep_xn = pl.routed || a->rms_delta != nullptr;
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;
   q.rank = a->rank;
-  q.na = na;
-  q.mt = mt;
-  q.q_row0 = row0;
-  q.q_rows = rows;
+  q.na = pl.na;
+  q.mt = pl.mt;
+  q.q_row0 = pl.row0;
+  q.q_rows = pl.rows;
   q.cta_limit = a->gemm_cta_limit;
   q.wq = a->gu_wq;
   q.sw = a->gu_sw;
@@ -485,8 +517,8 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.acc = w.acc;
   q.b_rows = a->gu_b_rows;
   q.b_rows_rank = a->b_rows_rank;
-  q.tiles = tiles;
-  q.num_tiles = num_tiles;
+  q.tiles = pl.tiles;
+  q.num_tiles = pl.num_tiles;
   q.epilogue = SKYRL_EPI_SWIGLU;
   q.out_row_map = nullptr;
   q.out = w.h;
@@ -494,9 +526,29 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.status = a->status;
   q.ev_begin = a->timing_events[0];
   q.ev_end = a->timing_events[1];
+  return q;
+}
+
+}  // namespace skyrl
+
+extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MlpPlan pl;
+  int rc = plan_mlp(a, "mlp", &pl);
+  if (rc) return rc;
+  if (pl.rows <= 0) return SKYRL_OK;  // more chunks than rows: nothing to do for this one
+  const bool prepared = (a->flags & SKYRL_MLP_INPUT_PREPARED) != 0;
+  if (prepared && pl.rows_path)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: SKYRL_MLP_INPUT_PREPARED needs more than %d rows", ROWS_PATH_MAX_M);
+  if ((rc = route_mlp(a, pl, stream))) return rc;
+  const MlpWs& w = pl.w;
+
+  Projection q = front_projection(a, pl);
+  q.skip_quant = prepared;
   if ((rc = run_projection(q, stream))) return rc;
 
   // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
+  q.skip_quant = false;
   q.x = w.h;
   q.x_stride = a->inter;
   q.rms_delta = nullptr;
@@ -513,14 +565,61 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.xq = w.hq;
   q.sx = w.sh;
   q.epilogue = a->down_epilogue;
-  q.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : perm;
+  q.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : pl.perm;
   q.residual = a->residual != nullptr ? a->residual : a->x;
   q.residual_stride = a->hidden;
   q.out = a->out;
   q.out_stride = a->hidden;
+  if (a->tp_scatter_rows > 0) {
+    if (a->down_epilogue != SKYRL_EPI_PARTIAL_F32 || pl.rows_path)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "mlp: tp_scatter_rows needs down_epilogue PARTIAL_F32 and more than %d rows",
+                  ROWS_PATH_MAX_M);
+    q.scatter_bases = a->tp_scatter_bases;
+    q.scatter_row0 = pl.row0;
+    q.scatter_rows = a->tp_scatter_rows;
+  }
   q.ev_begin = a->timing_events[2];
   q.ev_end = a->timing_events[3];
   return run_projection(q, stream);
+}
+
+extern "C" int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* a, int32_t row_begin, int32_t row_count,
+                                                   skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MlpPlan pl;
+  int rc = plan_mlp(a, "tp_prepare", &pl);
+  if (rc) return rc;
+  if (pl.rows_path)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_prepare: needs more than %d rows", ROWS_PATH_MAX_M);
+  if (row_count <= 0 || row_begin < pl.row0 || row_begin + row_count > pl.row0 + pl.rows)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_prepare: rows [%d, %d) are not inside chunk rows [%d, %d)", row_begin,
+                row_begin + row_count, pl.row0, pl.row0 + pl.rows);
+  if ((rc = route_mlp(a, pl, stream))) return rc;
+  Projection q = front_projection(a, pl);
+  q.q_row0 = row_begin;
+  q.q_rows = row_count;
+  return run_quant_stage(q, stream);
+}
+
+extern "C" int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
+                                                 size_t* offsets) {
+  if (m <= 0 || hidden <= 0 || inter <= 0 || offsets == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "workspace_regions: bad argument");
+  unsigned char* const base = reinterpret_cast<unsigned char*>(static_cast<uintptr_t>(1024));
+  const MlpWs w = carve_mlp(base, m, hidden, inter, num_adapters > 0 ? num_adapters : 1);
+  offsets[0] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.xq) - base);
+  offsets[1] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.sx) - base);
+  offsets[2] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.z_parts) - base);
+  return SKYRL_OK;
+}
+
+extern "C" int skyrl_w8a8_mlp_tp_unsort_sm100_v1(const SkyrlW8A8MlpArgs* a, const void* sorted_rows, void* out,
+                                                  skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  MlpPlan pl;
+  int rc = plan_mlp(a, "tp_unsort", &pl);
+  if (rc) return rc;
+  return launch_unsort_rows(sorted_rows, pl.perm, out, a->m, a->hidden, stream);
 }
 
 extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, const float* reduced, void* out,
@@ -539,7 +638,30 @@ extern "C" int skyrl_w8a8_mlp_tp_finalize_sm100_v1(const SkyrlW8A8MlpArgs* a, co
   if (rc) return rc;
   const void* residual = a->residual != nullptr ? a->residual : a->x;
   const bool routed = a->adapter_ids != nullptr && a->m > ROWS_PATH_MAX_M;
-  return launch_tp_finalize(reduced, routed ? w.perm : nullptr, residual, out, a->hidden, row_begin, row_count, stream);
+  return launch_tp_finalize(reduced, routed ? w.perm : nullptr, residual, out, a->hidden, row_begin, row_count, stream,
+                            (a->flags & SKYRL_MLP_FINALIZE_SORTED) != 0);
+}
+
+extern "C" int skyrl_w8a8_mlp_tp_finalize_slabs_sm100_v1(const SkyrlW8A8MlpArgs* a, const float* const* slabs,
+                                                          int32_t num_slabs, void* out, int32_t row_begin,
+                                                          int32_t row_count, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || slabs == nullptr || out == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: null argument");
+  if (a->struct_size != sizeof(SkyrlW8A8MlpArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: struct_size does not match ABI v%d",
+                SKYRL_W8A8_ABI_VERSION);
+  if (a->m <= 0 || a->hidden <= 0 || a->hidden % 8 != 0 || row_begin < 0 || row_count <= 0 ||
+      row_begin + row_count > a->m)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: bad shape or row range");
+  const int na = a->num_adapters > 0 ? a->num_adapters : 1;
+  const MlpWs w = carve_mlp(a->workspace, a->m, a->hidden, a->inter, na);
+  int rc = check_ws(a->workspace, a->workspace_bytes, w.bytes, "tp_finalize_slabs");
+  if (rc) return rc;
+  const void* residual = a->residual != nullptr ? a->residual : a->x;
+  const bool routed = a->adapter_ids != nullptr && a->m > ROWS_PATH_MAX_M;
+  return launch_tp_finalize_slabs(slabs, num_slabs, routed ? w.perm : nullptr, residual, out, a->hidden, row_begin,
+                                  row_count, stream, (a->flags & SKYRL_MLP_FINALIZE_SORTED) != 0);
 }
 
 // ---------------------------------------------------------------------------

@@ -32,7 +32,7 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
-                       int32_t* status, cudaStream_t stream);
+                       int32_t* status, cudaStream_t stream, int row_lo = 0, int row_hi = -1);
 // Tile width and K split the GEMM launcher chooses for a shape (deterministic per device).
 struct GemmPlan {
   int bn_eff;
@@ -50,6 +50,9 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
                          int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
                          cudaStream_t stream);
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
-                       int row_begin, int row_count, cudaStream_t stream);
+                       int row_begin, int row_count, cudaStream_t stream, bool out_sorted = false);
+int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int32_t* perm, const void* residual,
+                             void* out, int hidden, int row_begin, int row_count, cudaStream_t stream, bool out_sorted);
+int launch_unsort_rows(const void* sorted_rows, const int32_t* perm, void* out, int m, int hidden, cudaStream_t stream);
 
 }  // namespace skyrl

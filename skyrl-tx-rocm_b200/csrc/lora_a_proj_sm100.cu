@@ -1,9 +1,13 @@
 // LoRA-A projection on the tensor cores: for every 128-row tile of the
 // adapter-sorted row space, z = s[a] * (x_tile @ A[a]) with a bf16 tcgen05 MMA
 // (fp32 accumulator in TMEM, products of bf16 inputs are exact), written out as
-// three bf16 planes (hi, mid, lo) that sum to the fp32 value exactly, so that the
-// rank-r contraction of the GEMM epilogue sees z at full fp32 precision.  HBM-bound: x is streamed once through a 6-stage
-// TMA pipeline, one CTA per tile.
+// three bf16 parts (hi, mid, lo) that sum to the fp32 value exactly, so that the
+// rank-r contraction of the GEMM epilogue sees z at full fp32 precision.  The parts of a row sit side by
+// side, z_parts[row][part][64], so that a range of rows is one contiguous block (a rank of a
+// tensor-parallel group computes a range and gathers the rest).  HBM-bound: x is streamed once through a
+// 6-stage TMA pipeline, one CTA per tile.  A row window [row_lo, row_hi) limits the rows written: tiles
+// outside it are skipped, tiles that straddle its edge compute all their rows (rows of an MMA are
+// independent, so whatever the unowned rows of x hold cannot reach an owned row) and store the owned ones.
 //
 // Reference arithmetic: `x.astype(f32) @ lora_a.astype(f32)`
 // (skyrl/tx/kernels/quantized_lora.py:301) and the first ragged_dot of
@@ -32,8 +36,8 @@ struct ProjParams {
   const float* scaling;
   const int4* tiles;
   const int32_t* num_tiles;
-  __nv_bfloat16* z_parts;  // [3, m, 64]
-  int64_t plane;           // m * 64
+  __nv_bfloat16* z_parts;  // [m, 3, 64]
+  int row_lo, row_hi;      // rows written
   int32_t* status;
   int k;
 };
@@ -51,6 +55,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   if (static_cast<int>(blockIdx.x) >= *p.num_tiles) return;  // uniform for the CTA
+  const int4 tile = __ldg(p.tiles + blockIdx.x);
+  if (tile.x >= p.row_hi || tile.x + tile.y <= p.row_lo) return;  // outside the row window, also uniform
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PROJ_STAGES; ++s) {
@@ -70,7 +76,6 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const int4 tile = __ldg(p.tiles + blockIdx.x);
   const int kblocks = (p.k + PROJ_BK - 1) / PROJ_BK;
 
   if (warp == 4) {
@@ -120,8 +125,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
     if (ok) {
       tc_fence_after_sync();
       const float s = __ldg(p.scaling + tile.z);
-      const bool row_valid = r < tile.y;
       const int64_t row = tile.x + r;
+      const bool row_valid = r < tile.y && row >= p.row_lo && row < p.row_hi;
 #pragma unroll
       for (int cc = 0; cc < PROJ_N / 32; ++cc) {
         uint32_t v[32];
@@ -141,9 +146,9 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
             mid[i] = pack_bf16x2(m0, m1);
             lo[i] = pack_bf16x2(__fsub_rn(r0, m0), __fsub_rn(r1, m1));  // <= 8 bits left: exact in bf16
           }
-          uint4* dh = reinterpret_cast<uint4*>(p.z_parts + row * PROJ_N + cc * 32);
-          uint4* dm = reinterpret_cast<uint4*>(p.z_parts + p.plane + row * PROJ_N + cc * 32);
-          uint4* dl = reinterpret_cast<uint4*>(p.z_parts + 2 * p.plane + row * PROJ_N + cc * 32);
+          uint4* dh = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + cc * 32);
+          uint4* dm = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + PROJ_N + cc * 32);
+          uint4* dl = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + 2 * PROJ_N + cc * 32);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
@@ -170,7 +175,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
 
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
-                       int32_t* status, cudaStream_t stream) {
+                       int32_t* status, cudaStream_t stream, int row_lo, int row_hi) {
   if (x == nullptr || a_packed == nullptr || scaling == nullptr || tiles == nullptr || num_tiles == nullptr ||
       z_parts == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: null buffer");
@@ -195,7 +200,8 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
   p.tiles = reinterpret_cast<const int4*>(tiles);
   p.num_tiles = num_tiles;
   p.z_parts = static_cast<__nv_bfloat16*>(z_parts);
-  p.plane = static_cast<int64_t>(m) * PROJ_N;
+  p.row_lo = row_lo;
+  p.row_hi = row_hi < 0 ? m : row_hi;
   p.status = status;
   p.k = k;
   static bool attr_set = false;

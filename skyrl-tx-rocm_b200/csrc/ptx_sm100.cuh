@@ -22,6 +22,7 @@ enum : int {
   STATUS_TIMEOUT_LORA = 104,
   STATUS_BAD_ADAPTER_ID = 201,
   STATUS_TILE_OVERFLOW = 202,
+  STATUS_BAD_SCATTER = 203,  // a row of a scattered partial-sum store has no owner
 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s

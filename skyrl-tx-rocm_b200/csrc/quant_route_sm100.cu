@@ -270,12 +270,12 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
 __global__ void __launch_bounds__(256)
 tp_finalize_kernel(const float* __restrict__ reduced, const int32_t* __restrict__ perm,
                    const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int hidden,
-                   int row_begin) {
+                   int row_begin, int out_sorted) {
   const int64_t srow = row_begin + blockIdx.x;
   const int64_t orow = perm != nullptr ? perm[srow] : srow;
   const float4* src = reinterpret_cast<const float4*>(reduced + srow * hidden);
   const uint4* res = reinterpret_cast<const uint4*>(residual + orow * hidden);
-  uint4* dst = reinterpret_cast<uint4*>(out + orow * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + (out_sorted ? srow : orow) * hidden);
   for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
     const float4 a = __ldg(src + 2 * v), b = __ldg(src + 2 * v + 1);
     const uint4 r = __ldg(res + v);
@@ -291,13 +291,92 @@ tp_finalize_kernel(const float* __restrict__ reduced, const int32_t* __restrict_
 }
 
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
-                       int row_begin, int row_count, cudaStream_t stream) {
+                       int row_begin, int row_count, cudaStream_t stream, bool out_sorted) {
   if (residual == nullptr || !aligned16(reduced) || !aligned16(residual) || !aligned16(out))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize: residual missing or buffers not 16-byte aligned");
   tp_finalize_kernel<<<row_count, 256, 0, stream>>>(reduced, perm, static_cast<const __nv_bfloat16*>(residual),
-                                                    static_cast<__nv_bfloat16*>(out), hidden, row_begin);
+                                                    static_cast<__nv_bfloat16*>(out), hidden, row_begin,
+                                                    out_sorted ? 1 : 0);
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_finalize launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+// The same with the ranks' partial sums still apart: slab s holds rank s's fp32 partial sums of the rows
+// [row_begin, row_begin + gridDim.x), each rank having stored them into this GPU's memory from its down
+// GEMM epilogue.  Added in ascending rank order in fp32 (quantized_lora.py:253), then as above.
+struct SlabList {
+  const float* slab[8];
+  int count;
+};
+
+__global__ void __launch_bounds__(256)
+tp_finalize_slabs_kernel(const SlabList slabs, const int32_t* __restrict__ perm,
+                         const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out, int hidden,
+                         int row_begin, int out_sorted) {
+  const int64_t srow = row_begin + blockIdx.x;
+  const int64_t orow = perm != nullptr ? perm[srow] : srow;
+  const int64_t off = static_cast<int64_t>(blockIdx.x) * hidden;
+  const uint4* res = reinterpret_cast<const uint4*>(residual + orow * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + (out_sorted ? srow : orow) * hidden);
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    const float4* src = reinterpret_cast<const float4*>(slabs.slab[0] + off);
+    float4 a = __ldg(src + 2 * v), b = __ldg(src + 2 * v + 1);
+    for (int s = 1; s < slabs.count; ++s) {
+      src = reinterpret_cast<const float4*>(slabs.slab[s] + off);
+      const float4 c = __ldg(src + 2 * v), d = __ldg(src + 2 * v + 1);
+      a.x = __fadd_rn(a.x, c.x); a.y = __fadd_rn(a.y, c.y); a.z = __fadd_rn(a.z, c.z); a.w = __fadd_rn(a.w, c.w);
+      b.x = __fadd_rn(b.x, d.x); b.y = __fadd_rn(b.y, d.y); b.z = __fadd_rn(b.z, d.z); b.w = __fadd_rn(b.w, d.w);
+    }
+    const uint4 r = __ldg(res + v);
+    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])),
+                         __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
+    dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int32_t* perm, const void* residual,
+                             void* out, int hidden, int row_begin, int row_count, cudaStream_t stream, bool out_sorted) {
+  if (slabs == nullptr || num_slabs < 1 || num_slabs > 8)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: 1 to 8 slabs wanted, got %d", num_slabs);
+  SlabList list = {};
+  list.count = num_slabs;
+  for (int s = 0; s < num_slabs; ++s) {
+    if (slabs[s] == nullptr || !aligned16(slabs[s]))
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: slab %d is null or not 16-byte aligned", s);
+    list.slab[s] = slabs[s];
+  }
+  if (residual == nullptr || !aligned16(residual) || !aligned16(out))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_finalize_slabs: residual missing or buffers not 16-byte aligned");
+  tp_finalize_slabs_kernel<<<row_count, 256, 0, stream>>>(list, perm, static_cast<const __nv_bfloat16*>(residual),
+                                                          static_cast<__nv_bfloat16*>(out), hidden, row_begin,
+                                                          out_sorted ? 1 : 0);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_finalize_slabs launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+// Rows of a bf16 [m, hidden] matrix in adapter-sorted order back to token order: out[perm[i]] = in[i].
+__global__ void __launch_bounds__(256)
+unsort_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ perm, uint4* __restrict__ out, int vecs) {
+  const int64_t srow = blockIdx.x;
+  const int64_t orow = perm != nullptr ? perm[srow] : srow;
+  for (int v = threadIdx.x; v < vecs; v += blockDim.x) out[orow * vecs + v] = __ldg(in + srow * vecs + v);
+}
+
+int launch_unsort_rows(const void* sorted_rows, const int32_t* perm, void* out, int m, int hidden, cudaStream_t stream) {
+  if (sorted_rows == nullptr || out == nullptr || sorted_rows == out || !aligned16(sorted_rows) || !aligned16(out) ||
+      hidden % 8 != 0 || m <= 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "unsort_rows: distinct 16-byte aligned buffers and hidden % 8 == 0 wanted");
+  unsort_rows_kernel<<<m, 256, 0, stream>>>(static_cast<const uint4*>(sorted_rows), perm, static_cast<uint4*>(out),
+                                            hidden / 8);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "unsort_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
 

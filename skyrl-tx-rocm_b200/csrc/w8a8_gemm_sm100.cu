@@ -41,8 +41,8 @@ constexpr int EPI_THREADS = 256;
 constexpr int LORA_ROW_BYTES = SKYRL_LORA_RANK_PAD * 2;  // 128-byte rows of z and packed B
 
 constexpr int STAGE_AREA_BYTES = 224 * 1024;  // shared memory given to the TMA pipeline stages
-constexpr int EPI_STAGE_PITCH = 80;           // bytes per row of an epilogue warp's store-staging tile (64 + pad)
-constexpr int EPI_STAGE_BYTES = 32 * EPI_STAGE_PITCH;
+constexpr int EPI_STAGE_PITCH = 80;           // bytes per row of an epilogue warp's bf16 store-staging tile (64 + pad)
+constexpr int EPI_STAGE_BYTES = 32 * 128;     // the fp32 form holds 32 rows x 128 bytes, swizzled instead of padded
 // the single-tile kernel carves eight such tiles out of the top of the stage area
 constexpr int SINGLE_STAGE_AREA = STAGE_AREA_BYTES - 8 * EPI_STAGE_BYTES;
 constexpr int MAX_STAGES = 12;
@@ -60,7 +60,7 @@ struct GemmCfg {
 struct GemmParams {
   CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
   CUtensorMap tm_w;    // int8 [K / 128, N, 128], box 128 x bn_eff x 1
-  CUtensorMap tm_z;    // bf16 [3, M, 64], box 64 x 128 x 1 (one plane of one tile)
+  CUtensorMap tm_z;    // bf16 [M, 3, 64], box 64 x 1 x 128 (one part of one tile's rows)
   CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
   const float* sx;
   const float* sw;
@@ -84,7 +84,29 @@ struct GemmParams {
   int a_rows;       // rows of the activation TMA box (64 when the batch has at most 64 rows, else 128)
   int* sched;       // {tile claim counter, finished-CTA counter} of this launch, both zero on entry
   int direct_stores;  // tuning aid: 1 = bf16 epilogues store from registers instead of through the staging tile
+  // Row scatter of the fp32 partial sums (tensor-parallel reduce-scatter folded into the epilogue): row i of
+  // the sorted order belongs to owner o = (i - scatter_row0) / scatter_rows and is written to
+  // scatter_base[o] + (i - scatter_row0 - o * scatter_rows) * out_stride, which may be another GPU's memory
+  // (plain stores over NVLink).  scatter_rows == 0: rows go to `out`.
+  float* scatter_base[8];
+  int scatter_row0;
+  int scatter_rows;
 };
+
+// NULL (and status STATUS_BAD_SCATTER) for a row that has no owner: the caller skips the store.
+__device__ __forceinline__ float* partial_row_ptr(const GemmParams& p, int64_t orow) {
+  if (p.scatter_rows > 0) {
+    const int rel = static_cast<int>(orow) - p.scatter_row0;
+    const int o = rel >= 0 ? rel / p.scatter_rows : 8;
+    float* base = o < 8 ? p.scatter_base[o] : nullptr;
+    if (base == nullptr) {
+      atomicCAS(p.status, 0, STATUS_BAD_SCATTER);
+      return nullptr;
+    }
+    return base + static_cast<int64_t>(rel - o * p.scatter_rows) * p.out_stride;
+  }
+  return static_cast<float*>(p.out) + orow * p.out_stride;
+}
 
 // ---- dynamic tile scheduler --------------------------------------------------------------------------
 // Tiles are claimed from a global counter instead of a fixed stride, so a CTA that starts late (its SM
@@ -238,8 +260,34 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
     }
   }
   if (EPI == SKYRL_EPI_PARTIAL_F32) {
+    if (stage != nullptr) {
+      // transposed through the staging tile (16-byte pieces XOR-swizzled by row): eight lanes then write the
+      // 128 contiguous bytes of one row, whole lines for local memory and for NVLink alike
+      float4* tile = reinterpret_cast<float4*>(stage);
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        tile[lane * 8 + (g ^ (lane & 7))] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
+      __syncwarp();
+      const int piece = lane & 7, sub = lane >> 3;
+      const int orow_lo = static_cast<int>(orow & 0xffffffffll), orow_hi = static_cast<int>(orow >> 32);
+#pragma unroll
+      for (int round = 0; round < 8; ++round) {
+        const int r = sub + round * 4;
+        const bool valid = __shfl_sync(0xffffffffu, row_valid ? 1 : 0, r) != 0;
+        const int lo = __shfl_sync(0xffffffffu, orow_lo, r), hi = __shfl_sync(0xffffffffu, orow_hi, r);
+        if (valid && nc + piece * 4 < n_end) {
+          const int64_t row = (static_cast<int64_t>(hi) << 32) | static_cast<uint32_t>(lo);
+          float* rowp = partial_row_ptr(p, row);
+          if (rowp != nullptr) *reinterpret_cast<float4*>(rowp + nc + piece * 4) = tile[r * 8 + (piece ^ (r & 7))];
+        }
+      }
+      __syncwarp();
+      return;
+    }
     if (!row_valid) return;
-    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * p.out_stride + nc);
+    float* rowp = partial_row_ptr(p, orow);
+    if (rowp == nullptr) return;
+    float4* dst = reinterpret_cast<float4*>(rowp + nc);
 #pragma unroll
     for (int g = 0; g < 8; ++g)
       if (nc + g * 4 < n_end) dst[g] = make_float4(f[4 * g], f[4 * g + 1], f[4 * g + 2], f[4 * g + 3]);
@@ -392,8 +440,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         unsigned char* sa = smem + stage * stage_bytes;
         mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, row0, 2, &full_bar[stage]);
-        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, row0, 1, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 2, row0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 1, row0, &full_bar[stage]);
         if (++stage == nstages) {
           stage = 0;
           phase ^= 1u;
@@ -401,7 +449,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         sa = smem + stage * stage_bytes;
         mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, row0, 0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 0, row0, &full_bar[stage]);
         tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
         if (++stage == nstages) {
           stage = 0;
@@ -682,8 +730,8 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         unsigned char* sa = smem + stage * PAIR_STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, row0, 2, &full_bar[stage]);
-        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, row0, 1, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 2, row0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 1, row0, &full_bar[stage]);
         if (++stage == PAIR_STAGES) {
           stage = 0;
           phase ^= 1u;
@@ -691,7 +739,7 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         sa = smem + stage * PAIR_STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + PAIR_BN * LORA_ROW_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, row0, 0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 0, row0, &full_bar[stage]);
         tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
         if (++stage == PAIR_STAGES) {
           stage = 0;
@@ -1046,8 +1094,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
                            static_cast<uint64_t>(a.n) * BK, BK, bn_eff)))
     return rc;
   if (lora) {
-    if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, a.m, 3,
-                             LORA_ROW_BYTES, static_cast<uint64_t>(a.m) * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, BM, 1)))
+    if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, 3, a.m,
+                             LORA_ROW_BYTES, 3 * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, 1, BM)))
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
@@ -1078,6 +1126,22 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   p.stage_bytes = p.a_rows * BK + (bn_eff * BK + 1023) / 1024 * 1024;
   if (lora && p.stage_bytes < 2 * Z_PLANE_BYTES) p.stage_bytes = 2 * Z_PLANE_BYTES;  // a slot also carries two z planes
   p.num_stages = SINGLE_STAGE_AREA / p.stage_bytes;
+  p.scatter_rows = 0;
+  p.scatter_row0 = 0;
+  for (int o = 0; o < 8; ++o) p.scatter_base[o] = nullptr;
+  if (a.scatter_rows > 0) {
+    if (a.epilogue != SKYRL_EPI_PARTIAL_F32 || a.scatter_row0 < 0)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: a row scatter needs SKYRL_EPI_PARTIAL_F32 and scatter_row0 >= 0");
+    // owners are the leading non-null bases; a row whose owner has none is skipped and flagged in `status`
+    if (a.scatter_bases[0] == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: scatter base 0 is null");
+    for (int o = 0; o < 8; ++o) {
+      if (!aligned16(a.scatter_bases[o]))
+        return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: scatter base %d is not 16-byte aligned", o);
+      p.scatter_base[o] = static_cast<float*>(a.scatter_bases[o]);
+    }
+    p.scatter_rows = a.scatter_rows;
+    p.scatter_row0 = a.scatter_row0;
+  }
   p.direct_stores = 0;
   if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_DIRECT_STORES")) p.direct_stores = atoi(dbg) != 0;  // tuning aid
   if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
@@ -1095,7 +1159,9 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
   if (a.cta_limit > 0 && grid > a.cta_limit) grid = a.cta_limit;  // leave SMs to a concurrent collective
   // Large problems with a long K loop: two M tiles per CTA.  The pair's epilogue is not overlapped with
   // the next main loop, so this pays only when the K loop dwarfs it (measured: gain at K = 25600, loss at 5120).
-  bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 &&
+  // Not with a row scatter: the pair's epilogue stores 16 bytes per row from registers, which NVLink carries
+  // poorly; the single-tile kernel writes whole 128-byte lines through its staging tiles.
+  bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
                 static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
   if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_PAIR")) paired = paired && atoi(dbg) != 0;  // tuning aid
   if (paired) {

@@ -31,7 +31,7 @@ __all__ = (
     "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
-    "chunk_rows",
+    "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
     "check_status", "RMS_EPS",
 )
@@ -357,7 +357,7 @@ def _run_linear_grouped(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids
             _, _, xs = rms_quant(x2, row_map=perm, want_normalized=True)  # rows gathered into sorted order
         else:
             xs = x2.contiguous()
-        z_parts = torch.empty((3, m, LORA_RANK_PAD), dtype=torch.bfloat16, device=dev)
+        z_parts = torch.empty((m, 3, LORA_RANK_PAD), dtype=torch.bfloat16, device=dev)
         _lib.check(lib.skyrl_lora_a_proj_sm100_v1(_ptr(xs), m, k, _ptr(lora.a), _ptr(lora.scaling), na, lora.rank,
                                                   _ptr(tiles), _ptr(num), max_tiles, _ptr(z_parts), _ptr(st),
                                                   _stream()), "lora_a_proj")
@@ -568,10 +568,19 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
-                   gemm_cta_limit: int = 0):
+                   gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
-    order (qwen3_5.py:786-826).  Takes packed weights and tables only."""
+    order (qwen3_5.py:786-826).  Takes packed weights and tables only.
+
+    Sequence-parallel callers split the call: `prepare_rows=(row_begin, row_count)`
+    runs only the stage in front of the gate_up GEMM (RMSNorm, codes, scales,
+    LoRA-A projection) for those sorted rows and returns the call handle;
+    `input_prepared=True` runs the rest on a workspace whose regions
+    (`w8a8_mlp_workspace_regions`) already hold that stage's results.
+    `scatter=(rows_per_owner, [address of owner 0's slab, ...])` makes the down
+    GEMM store each owner's rows of the fp32 partial sums straight into that
+    owner's slab (device addresses, possibly peer mappings) instead of `out`."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
         raise RuntimeError("the W8A8 MLP block is disabled by default")
@@ -633,10 +642,22 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         for i, ev in enumerate(timing_events):
             a.timing_events[i] = ev.cuda_event
     if reuse_routing:
-        a.flags = _lib.MLP_REUSE_ROUTING
+        a.flags |= _lib.MLP_REUSE_ROUTING
+    if input_prepared:
+        a.flags |= _lib.MLP_INPUT_PREPARED
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)
+    if scatter is not None:
+        a.tp_scatter_rows = int(scatter[0])
+        if len(scatter[1]) > 8:
+            raise ValueError("at most 8 scatter owners")
+        for i, addr in enumerate(scatter[1]):
+            a.tp_scatter_bases[i] = int(addr)
+    if prepare_rows is not None:
+        _lib.check(lib.skyrl_w8a8_mlp_tp_prepare_sm100_v1(C.byref(a), int(prepare_rows[0]), int(prepare_rows[1]),
+                                                        _stream()), "w8a8_mlp_tp_prepare")
+        return out, (a, x2, delta, ids, r2)
     _lib.check(lib.skyrl_w8a8_mlp_block_sm100_v1(C.byref(a), _stream()), "w8a8_mlp_block")
     if return_call:
         # keeps the argument block (and through it the workspace layout) for the tensor-parallel finalize
@@ -650,18 +671,65 @@ def chunk_rows(m: int, num_chunks: int) -> int:
     return (per + TILE_ROWS - 1) // TILE_ROWS * TILE_ROWS
 
 
-def w8a8_mlp_tp_finalize(call, reduced: torch.Tensor, out: torch.Tensor, row_begin: int = 0, row_count: int | None = None):
+def w8a8_mlp_tp_finalize(call, reduced: torch.Tensor, out: torch.Tensor, row_begin: int = 0,
+                         row_count: int | None = None, *, sorted_out: bool = False):
     """Second half of a row-parallel block: out[perm[i]] = bf16(bf16(reduced[i]) + residual[perm[i]]).
 
     `call` is the handle returned by `w8a8_mlp_block(..., down_epilogue=EPI_PARTIAL_F32, return_call=True)`;
-    `reduced` is the all-reduced fp32 [M, H] partial-sum buffer in adapter-sorted row order."""
+    `reduced` is the reduced fp32 [M, H] partial-sum buffer in adapter-sorted row order.  With
+    `sorted_out` row i goes to out[i] instead (a later `w8a8_mlp_tp_unsort` restores token order)."""
     a = call[0]
     lib = _lib.load()
     if row_count is None:
         row_count = a.m - row_begin
-    _lib.check(lib.skyrl_w8a8_mlp_tp_finalize_sm100_v1(C.byref(a), _ptr(reduced), _ptr(out), row_begin, row_count,
-                                                     _stream()), "w8a8_mlp_tp_finalize")
+    flags = a.flags
+    a.flags = (flags | _lib.MLP_FINALIZE_SORTED) if sorted_out else (flags & ~_lib.MLP_FINALIZE_SORTED)
+    try:
+        _lib.check(lib.skyrl_w8a8_mlp_tp_finalize_sm100_v1(C.byref(a), _ptr(reduced), _ptr(out), row_begin, row_count,
+                                                         _stream()), "w8a8_mlp_tp_finalize")
+    finally:
+        a.flags = flags
     return out
+
+
+def w8a8_mlp_tp_finalize_slabs(call, slab_addresses, out: torch.Tensor, row_begin: int, row_count: int, *,
+                               sorted_out: bool = False):
+    """Finalize rows whose partial sums were scattered to this rank and not yet added: slab s (a device
+    address) holds rank s's fp32 sums of sorted rows [row_begin, row_begin + row_count); the slabs are added
+    in ascending s, then as `w8a8_mlp_tp_finalize`."""
+    a = call[0]
+    lib = _lib.load()
+    ptrs = (C.c_void_p * len(slab_addresses))(*[int(p) for p in slab_addresses])
+    flags = a.flags
+    a.flags = (flags | _lib.MLP_FINALIZE_SORTED) if sorted_out else (flags & ~_lib.MLP_FINALIZE_SORTED)
+    try:
+        _lib.check(lib.skyrl_w8a8_mlp_tp_finalize_slabs_sm100_v1(C.byref(a), ptrs, len(slab_addresses), _ptr(out),
+                                                               row_begin, row_count, _stream()),
+                   "w8a8_mlp_tp_finalize_slabs")
+    finally:
+        a.flags = flags
+    return out
+
+
+def w8a8_mlp_tp_unsort(call, sorted_rows: torch.Tensor, out: torch.Tensor):
+    """out[perm[i]] = sorted_rows[i]: bf16 [M, H] rows from adapter-sorted back to token order."""
+    _lib.check(_lib.load().skyrl_w8a8_mlp_tp_unsort_sm100_v1(C.byref(call[0]), _ptr(sorted_rows), _ptr(out), _stream()),
+               "w8a8_mlp_tp_unsort")
+    return out
+
+
+def w8a8_mlp_workspace_regions(m: int, hidden: int, inter: int, num_adapters: int, device):
+    """Views of the workspace regions a sequence-parallel gather moves, indexed by sorted row:
+    (codes int8 [m, hidden], scales fp32 [m], LoRA-A parts bf16 [m, 192])."""
+    lib = _lib.load()
+    na = max(int(num_adapters), 1)
+    ws = _workspace(device, lib.skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na))
+    off = (C.c_size_t * 3)()
+    _lib.check(lib.skyrl_w8a8_mlp_workspace_regions(m, hidden, inter, na, off), "w8a8_mlp_workspace_regions")
+    xq = ws[off[0]: off[0] + m * hidden].view(torch.int8).view(m, hidden)
+    sx = ws[off[1]: off[1] + 4 * m].view(torch.float32)
+    z = ws[off[2]: off[2] + m * 3 * LORA_RANK_PAD * 2].view(torch.bfloat16).view(m, 3 * LORA_RANK_PAD)
+    return xq, sx, z
 
 
 # --------------------------------------------------------------------------- #

@@ -89,27 +89,110 @@ class TensorParallelMLP:
 
 
 class TensorParallelMLPStack:
-    """A stack of tensor-parallel MLP blocks with the all-reduce hidden behind compute.
+    """A stack of tensor-parallel MLP blocks with the collectives hidden behind compute.
 
-    Every operation of the block is row-wise, so the adapter-sorted rows are cut
-    into `num_chunks` chunks: while NCCL reduces chunk c of a block on a second
-    stream, the kernels of chunk c + 1 (and then of the next block's chunk c)
-    run on the main stream.  The GEMMs claim their tiles dynamically, so CTAs
-    whose SM is held by the collective's kernels simply take fewer tiles; with
-    `reserve_sms` > 0 the GEMMs additionally launch that many CTAs fewer.
-    Measured on 4 GPUs (c5): 2 chunks 18.4 ms per step, 4 chunks 19.9 ms,
-    unchunked 21.3 ms.  Blocks shorter than 129 rows take the small-batch path
-    and are not chunked.
+    Every operation of the block but the two GEMMs is row-wise, so the adapter-sorted
+    rows are cut into `num_chunks` chunks and a second stream carries chunk c's
+    collectives while the GEMMs of chunk c + 1 (then of the next block's chunk c) run
+    on the main stream.  The GEMMs claim their tiles dynamically, so CTAs whose SM is
+    held by a collective's kernels simply take fewer tiles; with `reserve_sms` > 0 the
+    GEMMs additionally launch that many CTAs fewer.
+
+    Two forms of the exchange:
+
+    * `sequence_parallel=True` (default; needs every chunk's row count to divide by the
+      group size): each rank owns 1/tp of a chunk's sorted rows between the blocks.
+      Behind down_proj a reduce-scatter of the fp32 partial sums leaves a rank the sums
+      of its rows, it adds the residual for them, runs the NEXT block's RMSNorm, int8
+      quantisation and LoRA-A projection on them, and an all-gather hands every rank
+      the codes, scales and projections of all rows (1.08 bytes per element instead of
+      the 4 + 4 of an fp32 all-reduce, and none of the row-wise work is replicated).
+      The last block gathers its bf16 rows in sorted order and restores token order.
+    * otherwise: one fp32 all-reduce per chunk, every rank finalizes all rows and
+      repeats the row-wise stages.
+
+    With `peer_scatter` (default, sequence-parallel form only) the reduce-scatter is not a
+    collective at all: every rank's down GEMM stores each owner's rows of its fp32
+    partial sums straight into a slab in the owner's memory (symmetric memory, plain
+    stores over NVLink from the GEMM epilogue, tile by tile while the tensor cores
+    work on the next tile), a one-word all-reduce orders the ranks, and the owner adds
+    the slabs in rank order while finalizing.  If symmetric memory cannot be set up
+    the NCCL reduce-scatter is used.
+
+    Blocks of fewer than 129 rows take the small-batch path and are not chunked.
     """
 
-    def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 0, sm_count: int = 148):
+    def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 4, sm_count: int = 148,
+                 sequence_parallel: bool = True, peer_scatter: bool = True):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
+        self.sequence_parallel = sequence_parallel
+        self.peer_scatter = peer_scatter
+        self._slabs = None        # (shape key, local tensor, handle, per-rank base addresses)
+        self._token = None
         self._comm = None
         self._partial = None
         self._act = None
+        self._sorted = None
+        self.trace = None   # set to a list to collect (label, stream name, event) marks of the next forward
+
+    def _mark(self, label, stream, name):
+        if self.trace is not None:
+            import torch
+
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            self.trace.append((label, name, ev))
+
+    def trace_ms(self):
+        """Marks of the traced forward as (label, stream name, milliseconds since the first mark)."""
+        t0 = self.trace[0][2]
+        return [(label, name, t0.elapsed_time(ev)) for label, name, ev in self.trace]
+
+    def _buffers(self, x):
+        import torch
+
+        m, hidden = x.shape
+        if self._comm is None:
+            self._comm = torch.cuda.Stream()
+        if self._partial is None or self._partial.shape != (m, hidden):
+            self._partial = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
+            self._act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
+            self._sorted = torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device)
+
+    def _peer_slabs(self, x, tp):
+        """Symmetric fp32 [source rank, m / tp own rows, hidden] slab buffer; returns every rank's base
+        address as seen from this process, or None when symmetric memory is unavailable (decided together)."""
+        import torch
+        import torch.distributed as dist
+
+        m, hidden = x.shape
+        key = (m, hidden, tp, x.device)
+        if self._slabs is not None and self._slabs[0] == key:
+            return self._slabs[3]
+        ptrs, ok = None, 1
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            local = symm.empty((tp * (m // tp) * hidden,), dtype=torch.float32, device=x.device)
+            handle = symm.rendezvous(local, self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            if len(ptrs) != tp or ptrs[dist.get_rank(self.group)] != local.data_ptr():
+                ok = 0
+        except Exception as exc:  # noqa: BLE001 - any failure means "use the collective"
+            import warnings
+
+            warnings.warn(f"symmetric memory unavailable ({exc}); using the NCCL reduce-scatter")
+            ok = 0
+        flag = torch.tensor([ok], device=x.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.peer_scatter = False
+            return None
+        self._slabs = (key, local, handle, ptrs)
+        return ptrs
 
     def forward(self, x, adapter_ids=None, *, timing_events=None):
         import torch
@@ -119,14 +202,14 @@ class TensorParallelMLPStack:
 
         m, hidden = x.shape
         chunks = self.num_chunks if m > ops.TILE_ROWS else 1
-        if self._comm is None:
-            self._comm = torch.cuda.Stream()
-        if self._partial is None or self._partial.shape != (m, hidden):
-            self._partial = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
-            self._act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
-        main = torch.cuda.current_stream()
         rows = ops.chunk_rows(m, chunks)
         spans = [(c * rows, min(rows, m - c * rows)) for c in range(chunks) if c * rows < m]
+        tp = dist.get_world_size(self.group)
+        self._buffers(x)
+        if (self.sequence_parallel and tp > 1 and m > ops.TILE_ROWS and self.blocks
+                and all(cnt % tp == 0 for _, cnt in spans)):
+            return self._forward_sequence_parallel(x, adapter_ids, spans, chunks, tp, timing_events)
+        main = torch.cuda.current_stream()
         prev_done = [None] * len(spans)
         cur = x
         for l, blk in enumerate(self.blocks):
@@ -155,3 +238,110 @@ class TensorParallelMLPStack:
         for fin in prev_done:
             main.wait_event(fin)
         return cur
+
+    def _forward_sequence_parallel(self, x, adapter_ids, spans, chunks, tp, timing_events):
+        import torch
+        import torch.distributed as dist
+
+        from . import ops
+
+        m, hidden = x.shape
+        rank = dist.get_rank(self.group)
+        main, comm = torch.cuda.current_stream(), self._comm
+        chunk_arg = lambda c: (c, chunks) if chunks > 1 else None
+        own = [(r0 + rank * (cnt // tp), cnt // tp) for r0, cnt in spans]
+        first = self.blocks[0]
+        na = first.gate_up_lora.num_adapters if first.gate_up_lora is not None else 1
+        codes, scales, parts = ops.w8a8_mlp_workspace_regions(m, hidden, first.down_weight.in_features, na, x.device)
+        lora = first.gate_up_lora is not None
+        slab_ptrs = self._peer_slabs(x, tp) if self.peer_scatter else None
+        own_rows = m // tp
+        own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(len(spans))]
+        row_bytes = hidden * 4
+        if slab_ptrs is not None and self._token is None:
+            self._token = torch.zeros(1, dtype=torch.int32, device=x.device)
+
+        def scatter_arg(c):
+            # owner o keeps source rank s's rows at [s, own rows of chunk 0, own rows of chunk 1, ...]
+            if slab_ptrs is None:
+                return None
+            return (own[c][1], [slab_ptrs[o] + (rank * own_rows + own_off[c]) * row_bytes for o in range(tp)])
+
+        def my_slabs(c):
+            return [slab_ptrs[rank] + (s * own_rows + own_off[c]) * row_bytes for s in range(tp)]
+
+        def block_call(blk, src, c, **kw):
+            return ops.w8a8_mlp_block(
+                src, blk.rms_delta, blk.gate_up_weight, blk.gate_up_lora, blk.down_weight, blk.down_lora, adapter_ids,
+                enabled=True, eps=blk.eps, out=self._partial, down_epilogue=ops.EPI_PARTIAL_F32, return_call=True,
+                chunk=chunk_arg(c), gemm_cta_limit=self.cta_limit if chunks > 1 else 0, **kw)[1]
+
+        def gather_prepared(c):
+            (r0, cnt), (o0, ocnt) = spans[c], own[c]
+            dist.all_gather_into_tensor(codes[r0:r0 + cnt], codes[o0:o0 + ocnt], group=self.group)
+            dist.all_gather_into_tensor(scales[r0:r0 + cnt], scales[o0:o0 + ocnt], group=self.group)
+            if lora:
+                dist.all_gather_into_tensor(parts[r0:r0 + cnt], parts[o0:o0 + ocnt], group=self.group)
+            ev = torch.cuda.Event()
+            ev.record(comm)
+            return ev
+
+        # block 0: x is complete on every rank; each prepares its rows, the gathers run on the second stream
+        gathered = []
+        self._mark("begin", main, "main")
+        for c in range(len(spans)):
+            block_call(first, x, c, reuse_routing=c > 0, prepare_rows=own[c])
+            prepared = torch.cuda.Event()
+            prepared.record(main)
+            with torch.cuda.stream(comm):
+                comm.wait_event(prepared)
+                gathered.append(gather_prepared(c))
+        cur = x
+        final = []
+        for l, blk in enumerate(self.blocks):
+            dst = self._act[l & 1]
+            last = l + 1 == len(self.blocks)
+            for c, (r0, cnt) in enumerate(spans):
+                o0, ocnt = own[c]
+                main.wait_event(gathered[c])
+                self._mark(f"L{l}c{c} gemms>", main, "main")
+                ev = timing_events[l] if (timing_events is not None and c == 0) else None
+                call = block_call(blk, cur, c, reuse_routing=True, input_prepared=True, timing_events=ev,
+                                  scatter=scatter_arg(c))
+                self._mark(f"L{l}c{c} gemms<", main, "main")
+                computed = torch.cuda.Event()
+                computed.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(computed)
+                    self._mark(f"L{l}c{c} reduce_scatter>", comm, "comm")
+                    if slab_ptrs is None:
+                        dist.reduce_scatter_tensor(self._partial[o0:o0 + ocnt], self._partial[r0:r0 + cnt],
+                                                   group=self.group)
+
+                        def finalize(dst_rows, **kw):
+                            return ops.w8a8_mlp_tp_finalize(call, self._partial, dst_rows, o0, ocnt, **kw)
+                    else:
+                        # every rank's down GEMM of this chunk has finished once this one-word sum returns, and
+                        # with it the stores into this rank's slabs
+                        dist.all_reduce(self._token, group=self.group)
+
+                        def finalize(dst_rows, **kw):
+                            return ops.w8a8_mlp_tp_finalize_slabs(call, my_slabs(c), dst_rows, o0, ocnt, **kw)
+                    self._mark(f"L{l}c{c} reduce_scatter<", comm, "comm")
+                    if last:
+                        finalize(self._sorted, sorted_out=True)
+                        dist.all_gather_into_tensor(self._sorted[r0:r0 + cnt], self._sorted[o0:o0 + ocnt],
+                                                    group=self.group)
+                        fin = torch.cuda.Event()
+                        fin.record(comm)
+                        final.append((fin, call))
+                    else:
+                        finalize(dst)
+                        block_call(self.blocks[l + 1], dst, c, reuse_routing=True, prepare_rows=own[c])
+                        self._mark(f"L{l}c{c} finalize+prepare<", comm, "comm")
+                        gathered[c] = gather_prepared(c)
+                        self._mark(f"L{l}c{c} gather<", comm, "comm")
+            cur = dst
+        for fin, _ in final:
+            main.wait_event(fin)
+        return ops.w8a8_mlp_tp_unsort(final[-1][1], self._sorted, cur)

@@ -445,6 +445,99 @@ def test_tensor_parallel_block_emulated_on_one_gpu(S, tp):
     assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
 
 
+@pytest.mark.parametrize("tp", [2, 4])
+def test_sequence_parallel_stages_emulated_on_one_gpu(S, tp):
+    # The sequence-parallel exchange, with every rank's work done in turn on this GPU: each "rank" prepares
+    # its window of a chunk's sorted rows (windows cut through tiles), the gather is the shared workspace,
+    # the reduce-scatter is a sum of the partial buffers, and every window is finalized in sorted order and
+    # then un-sorted.  Must be bit-identical to the all-reduce form on the same shards.
+    from skyrl_tx_rocm_b200 import tp as T
+
+    rng = np.random.default_rng(151)
+    m, hidden, inter, rank, na, chunks = 520, 256, 512, 16, 5, 2
+    x, wgu, ga, gb, s, ids = make_case(153, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(159, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    qgu = O.quantize_frozen_weight(wgu, group_size=hidden)
+    xd, idd, dd = to_dev(x), to_dev(ids), to_dev(delta)
+    rows = S.chunk_rows(m, chunks)
+    spans = [(c * rows, min(rows, m - c * rows)) for c in range(chunks)]
+    assert all(cnt % tp == 0 for _, cnt in spans)
+    shards = []
+    for r in range(tp):
+        codes, scales, gb_r = T.shard_gate_up(qgu.codes, qgu.scales, gb, tp, r)
+        pgu = S.pack_weight(S.GroupQuantizedWeight(to_dev(codes), to_dev(scales), hidden, hidden, 8, hidden))
+        lo, hi = T.shard_bounds(inter, tp, r)
+        qd = O.quantize_frozen_weight(wd[lo:hi], group_size=hi - lo)
+        pd = S.pack_weight(S.GroupQuantizedWeight(to_dev(qd.codes), to_dev(qd.scales), hi - lo, hi - lo, 8, hi - lo))
+        _, da_r = T.shard_down(wd, da, tp, r)
+        lgu = S.pack_lora(to_dev(ga), to_dev(gb_r), to_dev(s), in_features=hidden, padded_out_features=2 * (hi - lo))
+        ld = S.pack_lora(to_dev(da_r), to_dev(db), to_dev(s), in_features=hi - lo, padded_out_features=hidden)
+        shards.append((pgu, lgu, pd, ld))
+
+    # all-reduce form
+    total = torch.zeros((m, hidden), dtype=torch.float32, device="cuda")
+    for pgu, lgu, pd, ld in shards:
+        part, call = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, down_epilogue=S.EPI_PARTIAL_F32,
+                                      return_call=True)
+        total += part
+    want = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+    S.w8a8_mlp_tp_finalize(call, total, want)
+
+    # sequence-parallel form
+    total2 = torch.zeros((m, hidden), dtype=torch.float32, device="cuda")
+    part = torch.empty((m, hidden), dtype=torch.float32, device="cuda")
+    first = True
+    for pgu, lgu, pd, ld in shards:
+        for c, (r0, cnt) in enumerate(spans):
+            for wdw in range(tp):     # what the other ranks would have prepared and the gather delivered
+                S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, out=part,
+                                 down_epilogue=S.EPI_PARTIAL_F32, chunk=(c, chunks), reuse_routing=not first,
+                                 prepare_rows=(r0 + wdw * (cnt // tp), cnt // tp))
+                first = False
+            _, call = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, out=part,
+                                       down_epilogue=S.EPI_PARTIAL_F32, chunk=(c, chunks), reuse_routing=True,
+                                       input_prepared=True, return_call=True)
+        total2 += part
+    assert torch.equal(total2, total)
+    srt = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for r0, cnt in spans:
+        for wdw in range(tp):
+            S.w8a8_mlp_tp_finalize(call, total2, srt, r0 + wdw * (cnt // tp), cnt // tp, sorted_out=True)
+    got = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    S.w8a8_mlp_tp_unsort(call, srt, got)
+    S.check_status()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    xq, sx, parts = S.w8a8_mlp_workspace_regions(m, hidden, inter // tp, na, xd.device)
+    assert xq.shape == (m, hidden) and sx.shape == (m,) and parts.shape == (m, 192)
+
+    # the reduce-scatter folded into the down GEMM: every "rank" stores owner o's rows into o's slab
+    # [source rank][own rows, chunk after chunk]; the owners add the slabs in rank order and finalize
+    own_rows = m // tp
+    slabs = torch.full((tp, tp, own_rows, hidden), float("nan"), dtype=torch.float32, device="cuda")
+    own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(chunks)]
+    for r, (pgu, lgu, pd, ld) in enumerate(shards):
+        for c, (r0, cnt) in enumerate(spans):
+            for wdw in range(tp):
+                S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, out=part,
+                                 down_epilogue=S.EPI_PARTIAL_F32, chunk=(c, chunks), reuse_routing=True,
+                                 prepare_rows=(r0 + wdw * (cnt // tp), cnt // tp))
+            bases = [slabs[o, r, own_off[c]].data_ptr() for o in range(tp)]
+            _, call = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, out=part,
+                                       down_epilogue=S.EPI_PARTIAL_F32, chunk=(c, chunks), reuse_routing=True,
+                                       input_prepared=True, return_call=True, scatter=(cnt // tp, bases))
+    srt2 = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    for o in range(tp):
+        for c, (r0, cnt) in enumerate(spans):
+            S.w8a8_mlp_tp_finalize_slabs(call, [slabs[o, q, own_off[c]].data_ptr() for q in range(tp)], srt2,
+                                         r0 + o * (cnt // tp), cnt // tp, sorted_out=True)
+    got2 = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    S.w8a8_mlp_tp_unsort(call, srt2, got2)
+    S.check_status()
+    assert not torch.isnan(slabs).any()
+    assert torch.equal(got2.view(torch.int16), want.view(torch.int16))
+
+
 # ----------------------------------------------------------------------------- full benchmark sizes, sampled
 def test_config3_accumulator_sampled_tiles(S):
     # Config 3 shape (M=8192, K=4096, 2I=24576): 64 sampled 128x128 tiles of the int32 accumulator

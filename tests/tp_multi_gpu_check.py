@@ -1,0 +1,104 @@
+"""Run under torchrun on 2+ GPUs: the sequence-parallel stack against the all-reduce stack and the oracle.
+
+Every rank builds the same seeded case, keeps its shard, runs a three-block stack three ways (all-reduce,
+sequence-parallel with the NCCL reduce-scatter, sequence-parallel with the reduce-scatter folded into the
+down GEMM's epilogue over peer memory) and checks
+(rank 0 prints one line, every rank exits non-zero on a mismatch):
+  * sequence-parallel output == all-reduce output (bit-identical for 2 ranks, where the fp32 sum has one
+    order; relative L2 below 1e-3 with under 1 % of elements differing for more ranks),
+  * both within the bf16 tolerance of the oracle's tensor-parallel statement of the same stack.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import ml_dtypes  # noqa: E402
+
+import skyrl_tx_rocm_b200 as S  # noqa: E402
+from oracle import w8a8_oracle as O  # noqa: E402
+from skyrl_tx_rocm_b200 import tp as T  # noqa: E402
+
+BF16 = ml_dtypes.bfloat16
+
+
+def to_dev(a):
+    if a.dtype == BF16:
+        return torch.from_numpy(a.view(np.int16).copy()).cuda().view(torch.bfloat16)
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dist.init_process_group("nccl")
+    m, hidden, inter, r, na, layers = 1024, 512, 1024, 16, 6, 3
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((m, hidden)).astype(np.float32).astype(BF16)
+    ids = rng.integers(0, na, size=m).astype(np.int32)
+    scal = np.full((na,), 2.0, np.float32)
+    blocks, host = [], []
+    for l in range(layers):
+        wgu = (rng.standard_normal((hidden, 2 * inter)) * 0.04).astype(np.float32)
+        wd = (rng.standard_normal((inter, hidden)) * 0.04).astype(np.float32)
+        ga = (rng.standard_normal((na, hidden, r)) / np.sqrt(hidden)).astype(np.float32).astype(BF16)
+        gb = (rng.standard_normal((na, r, 2 * inter)) * 0.02).astype(np.float32).astype(BF16)
+        da = (rng.standard_normal((na, inter, r)) / np.sqrt(inter)).astype(np.float32).astype(BF16)
+        db = (rng.standard_normal((na, r, hidden)) * 0.02).astype(np.float32).astype(BF16)
+        delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+        qgu = O.quantize_frozen_weight(wgu, group_size=hidden)
+        host.append((delta, qgu, ga, gb, wd, da, db))
+        codes, scales, gb_r = T.shard_gate_up(qgu.codes, qgu.scales, gb, world, rank)
+        lo, hi = T.shard_bounds(inter, world, rank)
+        pgu = S.pack_weight(S.GroupQuantizedWeight(to_dev(codes), to_dev(scales), hidden, hidden, 8, hidden))
+        qd = O.quantize_frozen_weight(wd[lo:hi], group_size=hi - lo)
+        pd = S.pack_weight(S.GroupQuantizedWeight(to_dev(qd.codes), to_dev(qd.scales), hi - lo, hi - lo, 8, hi - lo))
+        _, da_r = T.shard_down(wd, da, world, rank)
+        lgu = S.pack_lora(to_dev(ga), to_dev(gb_r), to_dev(scal), in_features=hidden,
+                          padded_out_features=2 * (hi - lo))
+        ld = S.pack_lora(to_dev(da_r), to_dev(db), to_dev(scal), in_features=hi - lo, padded_out_features=hidden)
+        blocks.append(T.TensorParallelMLP(to_dev(delta), pgu, lgu, pd, ld))
+    xd, idd = to_dev(x), to_dev(ids)
+    outs = {}
+    for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False), ("peer_scatter", True, True)):
+        stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
+        for _ in range(2):                      # the second pass reuses buffers and a warm workspace
+            y = stack.forward(xd, idd)
+        torch.cuda.synchronize()
+        S.check_status()
+        outs[name] = y.clone()
+        if name == "peer_scatter":
+            used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
+    a = outs["all_reduce"].float()
+    ok, mismatched, between = True, 0, 0.0
+    for name in ("sequence_parallel", "peer_scatter"):
+        b = outs[name].float()
+        mism = int(((a - b).abs() > 0).sum())
+        # more than two ranks: the collectives may add the fp32 partial sums in different orders, and a
+        # one-step difference in a block's output can move int8 codes of the next block
+        rel_b = float((a - b).norm() / a.norm())
+        ok = ok and (mism == 0 if world == 2 else (mism <= a.numel() // 100 and rel_b < 1e-3))
+        mismatched, between = max(mismatched, mism), max(between, rel_b)
+    want = x
+    for delta, qgu, ga, gb, wd, da, db in host:
+        want = O.tp_shard_mlp_reference(want, delta, qgu, ga, gb, scal, wd, da, db, scal, ids, world)
+    rel = 0.0
+    for name in ("sequence_parallel", "peer_scatter"):
+        got = outs[name].cpu().view(torch.int16).numpy().view(BF16)
+        rel = max(rel, O.relative_l2(got, want))
+    ok = ok and rel < 2e-3
+    flag = torch.tensor([0 if ok else 1], device="cuda")
+    dist.all_reduce(flag)
+    if rank == 0:
+        print(f"tp_multi_gpu_check world={world} mismatched={mismatched}/{a.numel()} rel_l2_between={between:.2e} "
+              f"rel_l2_vs_oracle={rel:.2e} peer_scatter_used={used_peer} "
+              f"{'OK' if int(flag) == 0 else 'FAILED'}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,6 +66,15 @@ int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, 
   return encode(map, dtype, 3, base, dims, strides, box);
 }
 
+bool pdl_enabled() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* dbg = getenv("SKYRL_W8A8_DEBUG_NO_PDL");
+    cached = (dbg != nullptr && atoi(dbg) != 0) ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -215,6 +224,7 @@ struct Projection {
   int cta_limit;
   void* const* scatter_bases;  // row scatter of the fp32 partial sums (see SkyrlW8A8GemmArgs) or NULL
   int scatter_row0, scatter_rows;
+
   const void* wq;
   const float* sw;
   const void* a_packed;
@@ -272,7 +282,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   if (rows_path && lora && q.epilogue != SKYRL_EPI_ACC_I32) {
     float* z_rows = reinterpret_cast<float*>(q.z_parts);
     if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.a_packed, q.scaling, q.rank, q.m, q.k,
-                                    q.xq, q.sx, z_rows, stream)))
+                                    q.xq, q.sx, z_rows, stream, pdl_enabled())))
       return rc;
     const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     g.struct_size = sizeof(g);
@@ -294,14 +304,16 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
     g.out_row_stride = q.n;
     g.status = q.status;
     if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
-    rc = launch_gemm(g, stream);
+    // timing events between the launches would cut the programmatic chain: use ordinary launches then
+    const bool chain = pdl_enabled() && q.ev_begin == nullptr && q.ev_end == nullptr;
+    rc = launch_gemm(g, stream, chain);
     if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
     if (rc) return rc;
     const bool dense = q.b_rows != nullptr;
     const int brow = dense ? q.b_rows_rank : SKYRL_LORA_RANK_PAD;
     return launch_finalize_rows(q.epilogue, q.acc, slabs, q.sx, q.sw, z_rows, q.ids, dense ? q.b_rows : q.b_packed,
                                 static_cast<int64_t>(q.n) * brow, brow, q.rank, q.m, q.n, q.residual,
-                                q.residual_stride, q.out, q.out_stride, stream);
+                                q.residual_stride, q.out, q.out_stride, stream, chain);
   }
   {
     if (!q.skip_quant && (rc = run_quant_stage(q, stream))) return rc;

@@ -25,6 +25,28 @@ int sm_count();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Kernel launch, optionally with programmatic stream serialization (see pdl_wait / pdl_trigger): the
+// kernel may then begin, up to its pdl_wait, before the previous kernel of the stream has finished.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool programmatic, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+// SKYRL_W8A8_DEBUG_NO_PDL=1 turns programmatic launches off (tuning aid).
+bool pdl_enabled();
+#endif
+
 // kernel launchers implemented in the .cu files
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
                  int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0);
@@ -41,14 +63,15 @@ struct GemmPlan {
 };
 GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs);
 constexpr int MAX_SPLIT_K_SLABS = 16;
-int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream);
+int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmatic = false);
+// `programmatic`: launch with programmatic stream serialization (small-batch chain of short kernels)
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                           const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
-                          float* z_rows, cudaStream_t stream);
+                          float* z_rows, cudaStream_t stream, bool programmatic = false);
 int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw, const float* z_rows,
                          const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
                          int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
-                         cudaStream_t stream);
+                         cudaStream_t stream, bool programmatic = false);
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
                        int row_begin, int row_count, cudaStream_t stream, bool out_sorted = false);
 int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int32_t* perm, const void* residual,

@@ -71,16 +71,23 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
 
   uint4 xr[VMAX], dr[VMAX];
   uint4 ar[PREFETCH_A ? VMAX : 1][PREFETCH_A ? R : 1];
+  // parameters (RMSNorm weights, LoRA-A) first; the activations are the previous kernel's output
 #pragma unroll
   for (int i = 0; i < VMAX; ++i) {
     const int v = threadIdx.x + i * ROWQ_THREADS;
     const bool valid = v < cnt;
-    xr[i] = valid ? __ldg(src + v) : zero4;
     dr[i] = (valid && norm) ? __ldg(reinterpret_cast<const uint4*>(delta) + v0 + v) : zero4;
     if (PREFETCH_A) {
 #pragma unroll
       for (int j = 0; j < R; ++j) ar[i][j] = valid ? __ldg(a_base + static_cast<int64_t>(j) * nvec + v) : zero4;
     }
+  }
+  pdl_wait();
+  pdl_trigger();
+#pragma unroll
+  for (int i = 0; i < VMAX; ++i) {
+    const int v = threadIdx.x + i * ROWQ_THREADS;
+    xr[i] = v < cnt ? ld_stream16(src + v) : zero4;
   }
 
   float xv[VMAX][8];
@@ -195,24 +202,18 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
     zs[threadIdx.x] = z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x];
   __syncthreads();
   const int n0 = 2 * (blockIdx.x * 256 + threadIdx.x);  // this thread owns columns n0 and n0 + 1
-  if (n0 >= n) return;
+  if (n0 >= n) return;  // (a thread that leaves counts as having passed pdl_wait / pdl_trigger)
+  // everything that does not come from the GEMM just before this kernel is fetched and the LoRA term
+  // computed while that GEMM may still be running; only the accumulator is read after the wait
   const float sxm = __ldg(sx + m);
-  int2 a2 = __ldg(reinterpret_cast<const int2*>(acc + static_cast<int64_t>(m) * n + n0));
-  for (int sl = 1; sl < slabs; ++sl) {  // split-K partial sums: int32 addition is exact
-    const int2 t2 = __ldg(reinterpret_cast<const int2*>(acc + sl * slab_stride + static_cast<int64_t>(m) * n + n0));
-    a2.x += t2.x;
-    a2.y += t2.y;
-  }
   const float2 w2 = __ldg(reinterpret_cast<const float2*>(sw + n0));
-  float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a2.x), sxm), w2.x);
-  float f1 = __fmul_rn(__fmul_rn(__int2float_rn(a2.y), sxm), w2.y);
+  float l0 = 0.f, l1 = 0.f;
   if (rank_vecs > 0) {
     const int adapter = ids != nullptr ? ids[m] : 0;
     const __nv_bfloat16* b0 = b_table + static_cast<int64_t>(adapter) * b_adapter_stride +
                               static_cast<int64_t>(n0) * b_row_stride;
     const uint4* r0 = reinterpret_cast<const uint4*>(b0);
     const uint4* r1 = reinterpret_cast<const uint4*>(b0 + b_row_stride);
-    float l0 = 0.f, l1 = 0.f;
     for (int q = 0; q < rank_vecs; ++q) {
       const uint4 u0 = __ldg(r0 + q), u1 = __ldg(r1 + q);
       const uint32_t c0[4] = {u0.x, u0.y, u0.z, u0.w};
@@ -225,6 +226,21 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
         l1 = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(c1[j]), l1);
       }
     }
+  }
+  uint32_t rv = 0u;
+  if (EPI == SKYRL_EPI_RESIDUAL)
+    rv = __ldg(reinterpret_cast<const uint32_t*>(residual + static_cast<int64_t>(m) * res_stride + n0));
+  pdl_wait();
+  pdl_trigger();
+  int2 a2 = ld_stream_int2(acc + static_cast<int64_t>(m) * n + n0);
+  for (int sl = 1; sl < slabs; ++sl) {  // split-K partial sums: int32 addition is exact
+    const int2 t2 = ld_stream_int2(acc + sl * slab_stride + static_cast<int64_t>(m) * n + n0);
+    a2.x += t2.x;
+    a2.y += t2.y;
+  }
+  float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a2.x), sxm), w2.x);
+  float f1 = __fmul_rn(__fmul_rn(__int2float_rn(a2.y), sxm), w2.y);
+  if (rank_vecs > 0) {
     f0 = __fadd_rn(f0, l0);
     f1 = __fadd_rn(f1, l1);
   }
@@ -236,7 +252,6 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
     const float h = __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u);
     static_cast<__nv_bfloat16*>(out)[static_cast<int64_t>(m) * out_stride + (n0 >> 1)] = __float2bfloat16_rn(h);
   } else if (EPI == SKYRL_EPI_RESIDUAL) {
-    const uint32_t rv = __ldg(reinterpret_cast<const uint32_t*>(residual + static_cast<int64_t>(m) * res_stride + n0));
     *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
         pack_bf16x2(__fadd_rn(round_bf16(f0), bf16_lo(rv)), __fadd_rn(round_bf16(f1), bf16_hi(rv)));
   } else {
@@ -248,18 +263,20 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
 template <int R, int VMAX, bool PREFETCH_A>
 static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                                const void* a_packed, const float* scaling, int m, int k, void* xq, float* sx,
-                               float* z_rows, cudaStream_t stream) {
-  rms_quant_rows_kernel<R, VMAX, PREFETCH_A><<<m * ROWQ_CLUSTER, ROWQ_THREADS, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), x_row_stride, static_cast<const __nv_bfloat16*>(rms_delta), eps, ids,
-      static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx, z_rows);
-  cudaError_t e = cudaPeekAtLastError();
+                               float* z_rows, cudaStream_t stream, bool programmatic) {
+  cudaError_t e = launch_kernel(rms_quant_rows_kernel<R, VMAX, PREFETCH_A>, dim3(m * ROWQ_CLUSTER), dim3(ROWQ_THREADS), 0,
+                                stream, programmatic, static_cast<const __nv_bfloat16*>(x), x_row_stride,
+                                static_cast<const __nv_bfloat16*>(rms_delta), eps, ids,
+                                static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx,
+                                z_rows);
+  if (e == cudaSuccess) e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
 
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                           const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
-                          float* z_rows, cudaStream_t stream) {
+                          float* z_rows, cudaStream_t stream, bool programmatic) {
   if (x == nullptr || xq == nullptr || sx == nullptr || a_packed == nullptr || scaling == nullptr ||
       z_rows == nullptr || m <= 0 || k <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: null buffer or non-positive shape");
@@ -274,7 +291,8 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
   if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
 #define SKYRL_ROWS(R, V, P) \
-  return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream)
+  return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream, \
+                                      programmatic)
   if (per_cta <= 2 * ROWQ_THREADS) {
     if (rank <= 16) SKYRL_ROWS(16, 2, false);
     if (rank <= 32) SKYRL_ROWS(32, 2, false);
@@ -290,7 +308,7 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
                          const float* z_rows,
                          const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
                          int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, bool programmatic) {
   if (acc == nullptr || sx == nullptr || sw == nullptr || out == nullptr || m <= 0 || n <= 0 || n % 2 != 0 ||
       m > 65535)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: null buffer or bad shape");
@@ -302,10 +320,11 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
   const int rank_vecs = (rank + 7) / 8;
   const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(b_table);
   const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(residual);
-#define SKYRL_FINALIZE(E)                                                                                        \
-  finalize_rows_kernel<E><<<grid, 256, 0, stream>>>(acc, slabs, static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, bt, \
-                                                    b_adapter_stride, b_row_stride, rank_vecs, n, res, res_stride,   \
-                                                    out, out_stride)
+  cudaError_t le = cudaSuccess;
+#define SKYRL_FINALIZE(E)                                                                                            \
+  le = launch_kernel(finalize_rows_kernel<E>, grid, dim3(256), 0, stream, programmatic, acc, slabs,                  \
+                     static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, bt, b_adapter_stride, b_row_stride, rank_vecs, \
+                     n, res, res_stride, out, out_stride)
   switch (epilogue) {
     case SKYRL_EPI_LINEAR: SKYRL_FINALIZE(SKYRL_EPI_LINEAR); break;
     case SKYRL_EPI_SWIGLU: SKYRL_FINALIZE(SKYRL_EPI_SWIGLU); break;
@@ -314,7 +333,7 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
     default: return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: unsupported epilogue %d", epilogue);
   }
 #undef SKYRL_FINALIZE
-  cudaError_t e = cudaPeekAtLastError();
+  cudaError_t e = le != cudaSuccess ? le : cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "finalize_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }

@@ -27,6 +27,27 @@ enum : int {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream serialization may start
+// while its predecessor in the stream still runs; `pdl_wait` returns once that predecessor has finished
+// and its writes are visible, `pdl_trigger` lets the successor start.  Rule kept by every kernel here:
+// trigger only after the own wait, so that whatever a successor touches before ITS wait was written at
+// least two kernels back and is complete.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Loads of data the previous kernel wrote, issued after pdl_wait: plain (coherent) global loads, not the
+// read-only path, which is reserved for data that is constant for the kernel's whole lifetime.
+__device__ __forceinline__ uint4 ld_stream16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int2 ld_stream_int2(const int32_t* p) {
+  int2 v;
+  asm volatile("ld.global.v2.s32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -434,6 +434,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true, have_prev = false;
+      bool dep_ready = false;  // the previous kernel of the stream has finished (programmatic launch)
+      int held = 0, held_stage[MAX_STAGES], held_kb[MAX_STAGES];
       int prev_row0 = 0, prev_n0 = 0, prev_adapter = 0;
       // LoRA operands of one tile: slot 1 = z planes lo and mid, slot 2 = z plane hi and the B tile
       auto lora_slots = [&](int row0, int n0, int adapter) -> bool {
@@ -472,8 +474,26 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           if (!ok) break;
           unsigned char* sa = smem + stage * stage_bytes;
           mbar_expect_tx(&full_bar[stage], stage_tx);
-          tma_load_2d(sa, &p.tm_xq, kb * BK, tile.x, &full_bar[stage]);
-          tma_load_3d(sa + a_bytes, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+          if (!dep_ready) {
+            // The weights never depend on the kernel before this one, the activations do: until the
+            // pipeline is full only the weight half of each stage is requested, then the producer waits
+            // for the previous kernel and requests the activation halves.
+            tma_load_3d(sa + a_bytes, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+            held_stage[held] = stage;
+            held_kb[held] = kb;
+            ++held;
+            if (held == nstages || kb + 1 == kb1) {
+              pdl_wait();
+              pdl_trigger();
+              dep_ready = true;
+              for (int hq = 0; hq < held; ++hq)
+                tma_load_2d(smem + held_stage[hq] * stage_bytes, &p.tm_xq, held_kb[hq] * BK, tile.x,
+                            &full_bar[held_stage[hq]]);
+            }
+          } else {
+            tma_load_2d(sa, &p.tm_xq, kb * BK, tile.x, &full_bar[stage]);
+            tma_load_3d(sa + a_bytes, &p.tm_w, 0, n0, kb, &full_bar[stage]);
+          }
           if (++stage == nstages) {
             stage = 0;
             phase ^= 1u;
@@ -948,7 +968,7 @@ static int launch_pair(const GemmParams& p, int epi, bool lora, int grid, cudaSt
 }
 
 template <int BN, int EPI, bool HAS_LORA>
-static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream, bool programmatic) {
   using Cfg = GemmCfg<BN>;
   auto kernel = w8a8_gemm_kernel<BN, EPI, HAS_LORA>;
   static bool attr_set = false;
@@ -957,29 +977,29 @@ static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
     attr_set = true;
   }
-  kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
-  cudaError_t e = cudaPeekAtLastError();
+  cudaError_t e = launch_kernel(kernel, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, programmatic, p);
+  if (e == cudaSuccess) e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
 
 template <int BN>
-static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStream_t stream) {
+static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStream_t stream, bool programmatic) {
   switch (epi) {
     case SKYRL_EPI_LINEAR:
-      return lora ? launch_variant<BN, SKYRL_EPI_LINEAR, true>(p, grid, stream)
-                  : launch_variant<BN, SKYRL_EPI_LINEAR, false>(p, grid, stream);
+      return lora ? launch_variant<BN, SKYRL_EPI_LINEAR, true>(p, grid, stream, programmatic)
+                  : launch_variant<BN, SKYRL_EPI_LINEAR, false>(p, grid, stream, programmatic);
     case SKYRL_EPI_SWIGLU:
-      return lora ? launch_variant<BN, SKYRL_EPI_SWIGLU, true>(p, grid, stream)
-                  : launch_variant<BN, SKYRL_EPI_SWIGLU, false>(p, grid, stream);
+      return lora ? launch_variant<BN, SKYRL_EPI_SWIGLU, true>(p, grid, stream, programmatic)
+                  : launch_variant<BN, SKYRL_EPI_SWIGLU, false>(p, grid, stream, programmatic);
     case SKYRL_EPI_RESIDUAL:
-      return lora ? launch_variant<BN, SKYRL_EPI_RESIDUAL, true>(p, grid, stream)
-                  : launch_variant<BN, SKYRL_EPI_RESIDUAL, false>(p, grid, stream);
+      return lora ? launch_variant<BN, SKYRL_EPI_RESIDUAL, true>(p, grid, stream, programmatic)
+                  : launch_variant<BN, SKYRL_EPI_RESIDUAL, false>(p, grid, stream, programmatic);
     case SKYRL_EPI_PARTIAL_F32:
-      return lora ? launch_variant<BN, SKYRL_EPI_PARTIAL_F32, true>(p, grid, stream)
-                  : launch_variant<BN, SKYRL_EPI_PARTIAL_F32, false>(p, grid, stream);
+      return lora ? launch_variant<BN, SKYRL_EPI_PARTIAL_F32, true>(p, grid, stream, programmatic)
+                  : launch_variant<BN, SKYRL_EPI_PARTIAL_F32, false>(p, grid, stream, programmatic);
     case SKYRL_EPI_ACC_I32:
-      return launch_variant<BN, SKYRL_EPI_ACC_I32, false>(p, grid, stream);
+      return launch_variant<BN, SKYRL_EPI_ACC_I32, false>(p, grid, stream, programmatic);
     default:
       return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
   }
@@ -1042,7 +1062,7 @@ GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs) {
   return pl;
 }
 
-int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
+int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmatic) {
   if (a.struct_size != sizeof(SkyrlW8A8GemmArgs))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: struct_size %u does not match ABI v%d (%zu)", a.struct_size,
                 SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8GemmArgs));
@@ -1170,15 +1190,15 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream) {
     if (a.cta_limit > 0 && pgrid > a.cta_limit) pgrid = a.cta_limit;
     return launch_pair(p, a.epilogue, lora, pgrid, stream);
   }
-  return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream)
-                   : launch_bn<128>(p, a.epilogue, lora, grid, stream);
+  return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream, programmatic)
+                   : launch_bn<128>(p, a.epilogue, lora, grid, stream, programmatic);
 }
 
 }  // namespace skyrl
 
 extern "C" int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream) {
   if (args == nullptr) return skyrl::fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: args is null");
-  return skyrl::launch_gemm(*args, static_cast<cudaStream_t>(stream));
+  return skyrl::launch_gemm(*args, static_cast<cudaStream_t>(stream), false);
 }
 
 extern "C" int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t split_k_slabs) {

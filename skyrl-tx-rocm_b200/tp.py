@@ -156,7 +156,9 @@ class TensorParallelMLPStack:
 
         m, hidden = x.shape
         if self._comm is None:
-            self._comm = torch.cuda.Stream()
+            # high priority: its short kernels (finalize, quantise, the collectives) take the SMs first
+            # whenever a GEMM launch of the main stream ends
+            self._comm = torch.cuda.Stream(priority=-1)
         if self._partial is None or self._partial.shape != (m, hidden):
             self._partial = torch.empty((m, hidden), dtype=torch.float32, device=x.device)
             self._act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=x.device) for _ in range(2)]

@@ -11,6 +11,8 @@ number of such elements is bounded as well.
 from pathlib import Path
 
 import ml_dtypes
+import os
+
 import numpy as np
 import pytest
 

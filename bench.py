@@ -222,7 +222,7 @@ def run_device(args):
             tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks,
                                               reserve_sms=args.tp_reserve_sms,
                                               sequence_parallel=bool(args.tp_sequence_parallel),
-                                              peer_scatter=bool(args.tp_peer_scatter))
+                                              peer_scatter=False if args.tp_peer_scatter == "off" else args.tp_peer_scatter)
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
@@ -239,7 +239,8 @@ def run_device(args):
             # tables are read by the row kernels, not by the GEMM
             gu_bytes_launch = 2 * ish * hidden + m * hidden + 4 * m * 2 * ish
             dn_bytes_launch = hidden * ish + m * ish + 4 * m * hidden * S._lib.load().skyrl_w8a8_gemm_k_splits(m, hidden, ish, 16)
-        h2d = x_host.numel() * 2 + (ids_host.numel() * 4 if ids_host is not None else 0)
+        # whole job per step: the rows of x once (shared out over the ranks), the adapter ids on every rank
+        h2d = x_host.numel() * 2 + (ids_host.numel() * 4 * tp if ids_host is not None else 0)
         d2h = m * hidden * 2
         out_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
         # per layer: 2 quantiser, 2 LoRA-A / LoRA-B-rows, 2 GEMM launches (+ finalize under TP); one routing launch per step
@@ -374,8 +375,16 @@ def run_device(args):
             graph.replay()
             out_host.copy_(graph_out[0], non_blocking=True)
             return
-        xd = x_host.to(device, non_blocking=True)
         idd = ids_host.to(device, non_blocking=True) if ids_host is not None else None
+        if tp > 1 and m % tp == 0:
+            # one job, one host input: every rank uploads its share of the rows and NVLink replicates them
+            # (all-gather in place); every rank reads back its share of the result
+            r0, r1 = rank * (m // tp), (rank + 1) * (m // tp)
+            x_dev[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+            dist.all_gather_into_tensor(x_dev, x_dev[r0:r1])
+            out_host[r0:r1].copy_(step(x_dev, idd)[r0:r1], non_blocking=True)
+            return
+        xd = x_host.to(device, non_blocking=True)
         if kind == "down":
             res_holder[0] = res_host.to(device, non_blocking=True)
         out_host.copy_(step(xd, idd), non_blocking=True)
@@ -434,7 +443,7 @@ def run_device(args):
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
                    "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
                    **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
-                       "tp_peer_scatter": bool(tp_stack.peer_scatter) if tp_stack is not None else False,
+                       "tp_peer_scatter": (tp_stack.peer_scatter or "off") if tp_stack is not None else "off",
                        "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
@@ -554,12 +563,13 @@ def main():
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
                     help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
                          "0: one fp32 all-reduce per chunk")
-    ap.add_argument("--tp-reserve-sms", type=int, default=4,
+    ap.add_argument("--tp-reserve-sms", type=int, default=8,
                     help="SMs the GEMMs leave to the second stream's small kernels while chunks overlap (N > 1): the "
                          "one-word all-reduce, the finalize / quantise kernels of the rank's own rows, the gathers")
-    ap.add_argument("--tp-peer-scatter", type=int, default=1,
-                    help="1: the down GEMM's epilogue stores each owner's fp32 partial sums into the owner's memory "
-                         "(symmetric memory over NVLink); 0: NCCL reduce-scatter")
+    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "epilogue", "copy", "off"],
+                    help="how the fp32 partial sums reach the rank that owns the rows: stores from the down GEMM's "
+                         "epilogue into the owner's memory, copy-engine pushes on the second stream, or (off) the "
+                         "NCCL reduce-scatter; auto = epilogue on 2 GPUs, copy on more")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="> 0: sets NCCL_MAX_CTAS (tuning aid)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")

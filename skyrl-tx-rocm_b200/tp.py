@@ -111,26 +111,35 @@ class TensorParallelMLPStack:
     * otherwise: one fp32 all-reduce per chunk, every rank finalizes all rows and
       repeats the row-wise stages.
 
-    With `peer_scatter` (default, sequence-parallel form only) the reduce-scatter is not a
-    collective at all: every rank's down GEMM stores each owner's rows of its fp32
-    partial sums straight into a slab in the owner's memory (symmetric memory, plain
-    stores over NVLink from the GEMM epilogue, tile by tile while the tensor cores
-    work on the next tile), a one-word all-reduce orders the ranks, and the owner adds
-    the slabs in rank order while finalizing.  If symmetric memory cannot be set up
-    the NCCL reduce-scatter is used.
+    With `peer_scatter` (sequence-parallel form only) the reduce-scatter is not a
+    collective at all: each owner has a slab per source rank in symmetric memory, the
+    ranks deliver their fp32 partial sums of the owner's rows into it, a one-word
+    all-reduce orders the ranks, and the owner adds the slabs in rank order while
+    finalizing.  Two ways to deliver:
+      "epilogue"  the down GEMM's epilogue stores the rows straight into the owner's slab
+                  (plain stores over NVLink, tile by tile while the tensor cores work on
+                  the next tile); best while the GEMM is long enough to cover the
+                  transfer (2 ranks);
+      "copy"      the GEMM writes its partial sums locally and the copy engines push each
+                  owner's rows on the second stream (no SM involved), so the transfer
+                  also overlaps the other chunk's gate_up GEMM; best once the transfer
+                  outlasts the down GEMM (4 and 8 ranks).
+    "auto" (default) picks by group size.  If symmetric memory cannot be set up the
+    NCCL reduce-scatter is used.
 
     Blocks of fewer than 129 rows take the small-batch path and are not chunked.
     """
 
-    def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 4, sm_count: int = 148,
-                 sequence_parallel: bool = True, peer_scatter: bool = True):
+    def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 8, sm_count: int = 148,
+                 sequence_parallel: bool = True, peer_scatter="auto"):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self.sequence_parallel = sequence_parallel
         self.peer_scatter = peer_scatter
-        self._slabs = None        # (shape key, local tensor, handle, per-rank base addresses)
+        self._slabs = None        # (shape key, local tensor, handle, per-rank base addresses, peer views)
+        self._coalesce = True     # gathers of the three prepared regions go out as one NCCL group
         self._token = None
         self._comm = None
         self._partial = None
@@ -193,7 +202,8 @@ class TensorParallelMLPStack:
         if int(flag.item()) == 0:
             self.peer_scatter = False
             return None
-        self._slabs = (key, local, handle, ptrs)
+        peers = [handle.get_buffer(r, (tp, m // tp, hidden), torch.float32) for r in range(tp)]
+        self._slabs = (key, local, handle, ptrs, peers)
         return ptrs
 
     def forward(self, x, adapter_ids=None, *, timing_events=None):
@@ -257,6 +267,10 @@ class TensorParallelMLPStack:
         codes, scales, parts = ops.w8a8_mlp_workspace_regions(m, hidden, first.down_weight.in_features, na, x.device)
         lora = first.gate_up_lora is not None
         slab_ptrs = self._peer_slabs(x, tp) if self.peer_scatter else None
+        mode = self.peer_scatter if slab_ptrs is not None else False
+        if mode in (True, "auto"):
+            mode = "epilogue" if tp <= 2 else "copy"
+        peers = self._slabs[4] if slab_ptrs is not None else None
         own_rows = m // tp
         own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(len(spans))]
         row_bytes = hidden * 4
@@ -265,12 +279,25 @@ class TensorParallelMLPStack:
 
         def scatter_arg(c):
             # owner o keeps source rank s's rows at [s, own rows of chunk 0, own rows of chunk 1, ...]
-            if slab_ptrs is None:
+            if mode != "epilogue":
                 return None
             return (own[c][1], [slab_ptrs[o] + (rank * own_rows + own_off[c]) * row_bytes for o in range(tp)])
 
+        def push_partial(c):
+            # copy engines: this rank's partial sums of owner o's rows -> o's slab for this rank.  One stream:
+            # alternating the pushes between two streams made their duration erratic on 8 GPUs (0.3 to 1.1 ms
+            # per chunk instead of a steady 0.3 ms).
+            (r0, cnt), ocnt = spans[c], own[c][1]
+            for step in range(1, tp):
+                o = (rank + step) % tp       # every rank starts with a different owner
+                peers[o][rank, own_off[c]:own_off[c] + ocnt].copy_(
+                    self._partial[r0 + o * ocnt:r0 + (o + 1) * ocnt], non_blocking=True)
+
         def my_slabs(c):
-            return [slab_ptrs[rank] + (s * own_rows + own_off[c]) * row_bytes for s in range(tp)]
+            ptrs = [slab_ptrs[rank] + (s * own_rows + own_off[c]) * row_bytes for s in range(tp)]
+            if mode == "copy":
+                ptrs[rank] = self._partial.data_ptr() + own[c][0] * row_bytes   # own rows were never moved
+            return ptrs
 
         def block_call(blk, src, c, **kw):
             return ops.w8a8_mlp_block(
@@ -280,10 +307,22 @@ class TensorParallelMLPStack:
 
         def gather_prepared(c):
             (r0, cnt), (o0, ocnt) = spans[c], own[c]
-            dist.all_gather_into_tensor(codes[r0:r0 + cnt], codes[o0:o0 + ocnt], group=self.group)
-            dist.all_gather_into_tensor(scales[r0:r0 + cnt], scales[o0:o0 + ocnt], group=self.group)
+            pairs = [(codes[r0:r0 + cnt], codes[o0:o0 + ocnt]), (scales[r0:r0 + cnt], scales[o0:o0 + ocnt])]
             if lora:
-                dist.all_gather_into_tensor(parts[r0:r0 + cnt], parts[o0:o0 + ocnt], group=self.group)
+                pairs.append((parts[r0:r0 + cnt], parts[o0:o0 + ocnt]))
+            done = False
+            if self._coalesce:
+                # one NCCL group launch for the three regions instead of three kernels
+                try:
+                    with dist._coalescing_manager(group=self.group, device=x.device):
+                        for full, mine in pairs:
+                            dist.all_gather_into_tensor(full, mine, group=self.group)
+                    done = True
+                except (AttributeError, RuntimeError, ValueError, TypeError):
+                    self._coalesce = False
+            if not done:
+                for full, mine in pairs:
+                    dist.all_gather_into_tensor(full, mine, group=self.group)
             ev = torch.cuda.Event()
             ev.record(comm)
             return ev
@@ -323,8 +362,10 @@ class TensorParallelMLPStack:
                         def finalize(dst_rows, **kw):
                             return ops.w8a8_mlp_tp_finalize(call, self._partial, dst_rows, o0, ocnt, **kw)
                     else:
-                        # every rank's down GEMM of this chunk has finished once this one-word sum returns, and
-                        # with it the stores into this rank's slabs
+                        if mode == "copy":
+                            push_partial(c)
+                        # every rank's down GEMM (or copies) of this chunk has finished once this one-word sum
+                        # returns, and with it the stores into this rank's slabs
                         dist.all_reduce(self._token, group=self.group)
 
                         def finalize(dst_rows, **kw):

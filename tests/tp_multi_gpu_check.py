@@ -1,8 +1,8 @@
 """Run under torchrun on 2+ GPUs: the sequence-parallel stack against the all-reduce stack and the oracle.
 
-Every rank builds the same seeded case, keeps its shard, runs a three-block stack three ways (all-reduce,
-sequence-parallel with the NCCL reduce-scatter, sequence-parallel with the reduce-scatter folded into the
-down GEMM's epilogue over peer memory) and checks
+Every rank builds the same seeded case, keeps its shard, runs a three-block stack four ways (all-reduce,
+sequence-parallel with the NCCL reduce-scatter, with the reduce-scatter folded into the down GEMM's epilogue
+over peer memory, and with copy-engine pushes into peer memory) and checks
 (rank 0 prints one line, every rank exits non-zero on a mismatch):
   * sequence-parallel output == all-reduce output (bit-identical for 2 ranks, where the fp32 sum has one
     order; relative L2 below 1e-3 with under 1 % of elements differing for more ranks),
@@ -63,18 +63,19 @@ def main():
         blocks.append(T.TensorParallelMLP(to_dev(delta), pgu, lgu, pd, ld))
     xd, idd = to_dev(x), to_dev(ids)
     outs = {}
-    for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False), ("peer_scatter", True, True)):
+    for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False),
+                           ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy")):
         stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
         for _ in range(2):                      # the second pass reuses buffers and a warm workspace
             y = stack.forward(xd, idd)
         torch.cuda.synchronize()
         S.check_status()
         outs[name] = y.clone()
-        if name == "peer_scatter":
+        if name == "peer_copy":
             used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
     a = outs["all_reduce"].float()
     ok, mismatched, between = True, 0, 0.0
-    for name in ("sequence_parallel", "peer_scatter"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy"):
         b = outs[name].float()
         mism = int(((a - b).abs() > 0).sum())
         # more than two ranks: the collectives may add the fp32 partial sums in different orders, and a
@@ -86,7 +87,7 @@ def main():
     for delta, qgu, ga, gb, wd, da, db in host:
         want = O.tp_shard_mlp_reference(want, delta, qgu, ga, gb, scal, wd, da, db, scal, ids, world)
     rel = 0.0
-    for name in ("sequence_parallel", "peer_scatter"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy"):
         got = outs[name].cpu().view(torch.int16).numpy().view(BF16)
         rel = max(rel, O.relative_l2(got, want))
     ok = ok and rel < 2e-3

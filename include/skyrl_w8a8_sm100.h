@@ -52,7 +52,8 @@ extern "C" {
 
 #define SKYRL_W8A8_ABI_VERSION 1
 #define SKYRL_LORA_RANK_PAD 64 /* packed LoRA tables hold 64 rank slots            */
-#define SKYRL_TILE_ROWS 128    /* rows of one M tile (one adapter per tile)         */
+#define SKYRL_TILE_ROWS 128
+#define SKYRL_Z_PARTS 6 /* bf16 parts of a row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo) */    /* rows of one M tile (one adapter per tile)         */
 #define SKYRL_WEIGHT_KBLOCK 128 /* K values per block of the packed weight layout   */
 
 #define SKYRL_OK 0
@@ -87,7 +88,10 @@ SKYRL_API const char* skyrl_w8a8_last_error(void);
  * row space.  Replaces prepare_routing (skyrl/tx/layers/util.py:66-87: argsort,
  * bincount, unsort) and the ragged grouping of skyrl/tx/layers/lora.py:142-157.
  *   perm[i]      original row of sorted position i                 int32 [m]
- *   tiles[4*t..] (first sorted row, row count <= 128, adapter, 0)  int32 [4*max_tiles]
+ *   tiles[4*t..] (first sorted row, row count <= 128, adapter, second)  int32 [4*max_tiles]
+ *                A tile holds rows of at most two adapters, so that the end of an adapter's run does
+ *                not leave a partly empty tile: second == 0 for one adapter, else
+ *                (second adapter + 1) | (rows of the first adapter << 16).
  *   num_tiles    device scalar, number of tiles written
  * adapter_ids == NULL: identity permutation, uniform tiles of adapter 0.
  * status: device int32, set non-zero on a bad id or tile overflow.            */
@@ -114,7 +118,11 @@ SKYRL_API int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, cons
  * skyrl/tx/layers/lora.py:150 and `x.f32 @ lora_a.f32` of
  * skyrl/tx/kernels/quantized_lora.py:301.
  *   x bf16 [m, k] in sorted row order; lora_a_packed bf16 [A, 64, k];
- *   z_parts bf16 [m, 3, 64]: the three parts of a row side by side            */
+ *   z_parts bf16 [m, 6, 64]: per row two adapter slots of three parts each.  A row's value sits in
+ *   the slot of its adapter within its tile (0 = the tile's first adapter, 1 = its second) and, in a
+ *   tile of two adapters, the other slot holds zeros; the GEMM then adds slot 0 times the first
+ *   adapter's B and slot 1 times the second's for all rows of the tile.  Tiles of one adapter
+ *   neither write nor read slot 1.                                            */
 SKYRL_API int skyrl_lora_a_proj_sm100_v1(const void* x, int32_t m, int32_t k, const void* lora_a_packed,
                                const float* lora_scaling, int32_t num_adapters, int32_t rank, const int32_t* tiles,
                                const int32_t* num_tiles, int32_t max_tiles, void* z_parts, int32_t* status,
@@ -144,7 +152,7 @@ typedef struct SkyrlW8A8GemmArgs {
   const float* sx;          /* fp32 [m]                                                */
   const void* wq;           /* int8 [ceil(k / 128), n, 128] packed                     */
   const float* sw;          /* fp32 [n]                                                */
-  const void* z_parts;      /* bf16 [m, 3, 64] (hi, mid, lo parts per row) or NULL when rank == 0 */
+  const void* z_parts;      /* bf16 [m, 6, 64] (see skyrl_lora_a_proj_sm100_v1) or NULL when rank == 0 */
   const void* lora_b_packed;/* bf16 [A, n, 64]                                         */
   const int32_t* tiles;     /* int32 [4 * max_tiles] from skyrl_lora_route_sm100_v1    */
   const int32_t* num_tiles; /* device scalar                                           */
@@ -345,7 +353,7 @@ SKYRL_API int skyrl_w8a8_mlp_tp_finalize_slabs_sm100_v1(const SkyrlW8A8MlpArgs* 
 SKYRL_API int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* args, int32_t row_begin, int32_t row_count,
                                        skyrl_stream_t stream);
 /* Byte offsets inside an MLP workspace of the regions a gather moves, each indexed by sorted row:
- * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 3, 64]. */
+ * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 6, 64]. */
 SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                      size_t* offsets);
 /* out[perm[i], :] = sorted_rows[i, :] for all m rows of a bf16 [m, H] matrix (perm from the workspace of

@@ -129,7 +129,7 @@ struct LinearWs {
   int8_t* xq;
   float* sx;
   uint16_t* xn;
-  uint16_t* z_parts;  // bf16 [3, m, 64]; the row-wise path keeps fp32 [m, 64] here instead
+  uint16_t* z_parts;  // bf16 [m, 6, 64]; the row-wise path keeps fp32 [m, 64] here instead
   int32_t* acc;       // int32 [m, n] accumulator, row-wise path only
   size_t bytes;
 };
@@ -143,7 +143,7 @@ static LinearWs carve_linear(void* ws, int m, int n, int k, int num_adapters) {
   w.num_tiles = c.take<int32_t>(4);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * k);
   w.sx = c.take<float>(m);
-  w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_parts = c.take<uint16_t>(SKYRL_Z_PARTS * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   if (m <= ROWS_PATH_MAX_M) {
     w.xn = nullptr;
     w.acc = c.take<int32_t>(static_cast<size_t>(m) * n * plan_gemm(m, n, k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits);
@@ -180,7 +180,7 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   w.num_tiles = c.take<int32_t>(MAX_CHUNKS + 4);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
   w.sx = c.take<float>(m);
-  w.z_parts = c.take<uint16_t>(3 * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
+  w.z_parts = c.take<uint16_t>(SKYRL_Z_PARTS * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
   w.h = c.take<uint16_t>(static_cast<size_t>(m) * inter);
   w.hq = c.take<int8_t>(static_cast<size_t>(m) * inter);
   w.sh = c.take<float>(m);

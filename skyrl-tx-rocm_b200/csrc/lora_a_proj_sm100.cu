@@ -20,15 +20,17 @@ namespace skyrl {
 
 constexpr int PROJ_BM = 128;
 constexpr int PROJ_BK = 64;  // bf16 elements per stage row (128 bytes)
-constexpr int PROJ_N = SKYRL_LORA_RANK_PAD;
+constexpr int PROJ_N = SKYRL_LORA_RANK_PAD;  // columns of one adapter; a tile of two adapters uses 2 * PROJ_N
 constexpr int PROJ_STAGES = 6;
 constexpr int PROJ_A_BYTES = PROJ_BM * 128;
-constexpr int PROJ_B_BYTES = PROJ_N * 128;
+constexpr int PROJ_B1_BYTES = PROJ_N * 128;   // one adapter's slice of A for one K block
+constexpr int PROJ_B_BYTES = 2 * PROJ_B1_BYTES;
 constexpr int PROJ_STAGE_BYTES = PROJ_A_BYTES + PROJ_B_BYTES;
 constexpr int PROJ_BAR_OFF = PROJ_STAGES * PROJ_STAGE_BYTES;
 constexpr int PROJ_SMEM_BYTES = PROJ_BAR_OFF + (2 * PROJ_STAGES + 1) * 8 + 16 + 1024;
 constexpr int PROJ_THREADS = 192;
-constexpr int PROJ_TMEM_COLS = 64;
+constexpr int PROJ_TMEM_COLS = 128;
+constexpr int PROJ_Z_ROW = SKYRL_Z_PARTS * PROJ_N;  // bf16 elements of one row of z_parts
 
 struct ProjParams {
   CUtensorMap tm_x;  // bf16 [M, K], box 64 x 128
@@ -36,7 +38,7 @@ struct ProjParams {
   const float* scaling;
   const int4* tiles;
   const int32_t* num_tiles;
-  __nv_bfloat16* z_parts;  // [m, 3, 64]
+  __nv_bfloat16* z_parts;  // [m, 6, 64]: adapter slot 0 parts (hi, mid, lo), adapter slot 1 parts
   int row_lo, row_hi;      // rows written
   int32_t* status;
   int k;
@@ -77,6 +79,11 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
   const uint32_t tmem_base = *tmem_ptr_smem;
 
   const int kblocks = (p.k + PROJ_BK - 1) / PROJ_BK;
+  // a tile of two adapters: rows [0, split) belong to tile.z, the rest to `second`; both projections are
+  // computed for all rows in one MMA of twice the width and every row keeps the one of its adapter
+  const bool mixed = tile.w != 0;
+  const int second = mixed ? (tile.w & 0xffff) - 1 : tile.z;
+  const int split = mixed ? (tile.w >> 16) : PROJ_BM;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -87,9 +94,10 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
       for (int kb = 0; kb < kblocks; ++kb) {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) break;
         unsigned char* sa = smem + stage * PROJ_STAGE_BYTES;
-        mbar_expect_tx(&full_bar[stage], PROJ_STAGE_BYTES);
+        mbar_expect_tx(&full_bar[stage], PROJ_A_BYTES + (mixed ? 2 : 1) * PROJ_B1_BYTES);
         tma_load_2d(sa, &p.tm_x, kb * PROJ_BK, tile.x, &full_bar[stage]);
         tma_load_3d(sa + PROJ_A_BYTES, &p.tm_a, kb * PROJ_BK, 0, tile.z, &full_bar[stage]);
+        if (mixed) tma_load_3d(sa + PROJ_A_BYTES + PROJ_B1_BYTES, &p.tm_a, kb * PROJ_BK, 0, second, &full_bar[stage]);
         if (++stage == PROJ_STAGES) {
           stage = 0;
           phase ^= 1u;
@@ -98,7 +106,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, PROJ_BM, PROJ_N);
+      const uint32_t idesc = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, PROJ_BM, mixed ? 2 * PROJ_N : PROJ_N);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -124,21 +132,24 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
     const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0u, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
     if (ok) {
       tc_fence_after_sync();
-      const float s = __ldg(p.scaling + tile.z);
       const int64_t row = tile.x + r;
       const bool row_valid = r < tile.y && row >= p.row_lo && row < p.row_hi;
-#pragma unroll
-      for (int cc = 0; cc < PROJ_N / 32; ++cc) {
+      const int slot = r >= split ? 1 : 0;  // adapter slot of this row inside its tile
+      const float s = __ldg(p.scaling + (slot ? second : tile.z));
+      const int nchunks = (mixed ? 2 : 1) * (PROJ_N / 32);
+      for (int cc = 0; cc < nchunks; ++cc) {
         uint32_t v[32];
         __syncwarp();
         tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + cc * 32, v);
         tmem_wait_ld();
         if (row_valid) {
+          const int dslot = cc / (PROJ_N / 32);      // the slot these 32 columns belong to
+          const bool mine = dslot == slot;           // the other slot of a two-adapter tile is zeroed
           uint32_t hi[16], mid[16], lo[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float z0 = __fmul_rn(__uint_as_float(v[2 * i]), s);
-            const float z1 = __fmul_rn(__uint_as_float(v[2 * i + 1]), s);
+            const float z0 = mine ? __fmul_rn(__uint_as_float(v[2 * i]), s) : 0.f;
+            const float z1 = mine ? __fmul_rn(__uint_as_float(v[2 * i + 1]), s) : 0.f;
             const float h0 = round_bf16(z0), h1 = round_bf16(z1);
             const float r0 = __fsub_rn(z0, h0), r1 = __fsub_rn(z1, h1);  // exact
             const float m0 = round_bf16(r0), m1 = round_bf16(r1);
@@ -146,9 +157,10 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
             mid[i] = pack_bf16x2(m0, m1);
             lo[i] = pack_bf16x2(__fsub_rn(r0, m0), __fsub_rn(r1, m1));  // <= 8 bits left: exact in bf16
           }
-          uint4* dh = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + cc * 32);
-          uint4* dm = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + PROJ_N + cc * 32);
-          uint4* dl = reinterpret_cast<uint4*>(p.z_parts + row * (3 * PROJ_N) + 2 * PROJ_N + cc * 32);
+          __nv_bfloat16* base = p.z_parts + row * PROJ_Z_ROW + dslot * 3 * PROJ_N + (cc % (PROJ_N / 32)) * 32;
+          uint4* dh = reinterpret_cast<uint4*>(base);
+          uint4* dm = reinterpret_cast<uint4*>(base + PROJ_N);
+          uint4* dl = reinterpret_cast<uint4*>(base + 2 * PROJ_N);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);

@@ -1,6 +1,6 @@
 // HBM-bound front-end kernels of the W8A8 multi-LoRA path:
 //   * route_kernel ....... stable counting sort of token rows by adapter id and
-//                          the list of 128-row M tiles (one adapter per tile)
+//                          the list of 128-row M tiles (at most two adapters per tile)
 //   * rms_quant_kernel ... optional RMSNorm(1 + delta), per-token absmax, int8 codes
 //   * pack kernels ....... one-time layout changes of weights and LoRA tables
 #include "common.cuh"
@@ -65,29 +65,43 @@ route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* 
   }
   __syncthreads();
   if (tid == 0) {
-    int start = 0, chunk = 0, in_chunk = 0;
-    bool overflow = false;
+    int start = 0;
     for (int a = 0; a < num_adapters; ++a) {
-      const int cnt = counts[a];
       cursor[a] = start;
-      int off = 0;
-      while (off < cnt) {
-        const int r0 = start + off;
-        while (r0 >= (chunk + 1) * span) {  // close the chunks this row has passed
-          num_tiles[chunk] = in_chunk;
-          ++chunk;
-          in_chunk = 0;
-        }
-        const int rows = min(min(SKYRL_TILE_ROWS, cnt - off), (chunk + 1) * span - r0);
-        if (in_chunk < cap) {
-          reinterpret_cast<int4*>(tiles)[chunk * cap + in_chunk] = make_int4(r0, rows, a, 0);
-        } else {
-          overflow = true;
-        }
-        ++in_chunk;
-        off += rows;
+      start += counts[a];
+    }
+    // Greedy packing of the sorted rows into tiles of up to 128 rows and at most two adapters: where an
+    // adapter's run ends inside a tile, the tile is filled up with rows of the next adapter.
+    int chunk = 0, in_chunk = 0, pos = 0, a = 0;
+    bool overflow = false;
+    while (a < num_adapters && counts[a] == 0) ++a;
+    while (pos < m && a < num_adapters) {
+      while (pos >= (chunk + 1) * span) {  // close the chunks this row has passed
+        num_tiles[chunk] = in_chunk;
+        ++chunk;
+        in_chunk = 0;
       }
-      start += cnt;
+      const int cend = min(m, (chunk + 1) * span);
+      const int aend = cursor[a] + counts[a];
+      const int take = min(SKYRL_TILE_ROWS, min(aend, cend) - pos);
+      int rows = take, second = 0;
+      if (take < SKYRL_TILE_ROWS && pos + take == aend && pos + take < cend) {
+        int b = a + 1;
+        while (b < num_adapters && counts[b] == 0) ++b;
+        if (b < num_adapters) {
+          const int bend = cursor[b] + counts[b];
+          rows = take + min(SKYRL_TILE_ROWS - take, min(bend, cend) - (pos + take));
+          second = (b + 1) | (take << 16);
+        }
+      }
+      if (in_chunk < cap) {
+        reinterpret_cast<int4*>(tiles)[chunk * cap + in_chunk] = make_int4(pos, rows, a, second);
+      } else {
+        overflow = true;
+      }
+      ++in_chunk;
+      pos += rows;
+      while (a < num_adapters && pos >= cursor[a] + counts[a]) ++a;  // the adapter that owns row `pos`
     }
     num_tiles[chunk] = in_chunk;
     for (int c = chunk + 1; c < num_chunks; ++c) num_tiles[c] = 0;

@@ -60,7 +60,7 @@ struct GemmCfg {
 struct GemmParams {
   CUtensorMap tm_xq;   // int8 [M, K], box 128 x 128
   CUtensorMap tm_w;    // int8 [K / 128, N, 128], box 128 x bn_eff x 1
-  CUtensorMap tm_z;    // bf16 [M, 3, 64], box 64 x 1 x 128 (one part of one tile's rows)
+  CUtensorMap tm_z;    // bf16 [M, 6, 64], box 64 x 1 x 128 (one part of one adapter slot of one tile's rows)
   CUtensorMap tm_b;    // bf16 [A, N, 64], box 64 x BN x 1
   const float* sx;
   const float* sw;
@@ -436,14 +436,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       bool ok = true, have_prev = false;
       bool dep_ready = false;  // the previous kernel of the stream has finished (programmatic launch)
       int held = 0, held_stage[MAX_STAGES], held_kb[MAX_STAGES];
-      int prev_row0 = 0, prev_n0 = 0, prev_adapter = 0;
-      // LoRA operands of one tile: slot 1 = z planes lo and mid, slot 2 = z plane hi and the B tile
-      auto lora_slots = [&](int row0, int n0, int adapter) -> bool {
+      int prev_row0 = 0, prev_n0 = 0, prev_adapter = 0, prev_second = 0;
+      // LoRA operands of one adapter slot of one tile: pipeline slot 1 = z parts lo and mid, pipeline
+      // slot 2 = z part hi and the adapter's B tile
+      auto lora_slots_of = [&](int row0, int n0, int adapter, int zslot) -> bool {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         unsigned char* sa = smem + stage * stage_bytes;
         mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, 2, row0, &full_bar[stage]);
-        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 1, row0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 3 * zslot + 2, row0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 3 * zslot + 1, row0, &full_bar[stage]);
         if (++stage == nstages) {
           stage = 0;
           phase ^= 1u;
@@ -451,13 +452,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         sa = smem + stage * stage_bytes;
         mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + bn_eff * LORA_ROW_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, 0, row0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 3 * zslot, row0, &full_bar[stage]);
         tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
         if (++stage == nstages) {
           stage = 0;
           phase ^= 1u;
         }
         return true;
+      };
+      // a tile of two adapters (second != 0) brings both slots: z(slot 0) with the first adapter's B,
+      // z(slot 1) with the second's; each row is zero in the slot that is not its own
+      auto lora_slots = [&](int row0, int n0, int adapter, int second) -> bool {
+        if (!lora_slots_of(row0, n0, adapter, 0)) return false;
+        return second == 0 || lora_slots_of(row0, n0, (second & 0xffff) - 1, 1);
       };
       for (uint32_t it = 0; ok; ++it) {
         const int t = sched_claim(ring, it, p.sched, total, abort_flag, p.status, ok);
@@ -499,16 +506,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             phase ^= 1u;
           }
           if (HAS_LORA && have_prev && ++issued == inject_at) {
-            ok = lora_slots(prev_row0, prev_n0, prev_adapter);
+            ok = lora_slots(prev_row0, prev_n0, prev_adapter, prev_second);
             if (!ok) break;
           }
         }
         prev_row0 = tile.x;
         prev_n0 = n0;
         prev_adapter = tile.z;
+        prev_second = tile.w;
         have_prev = true;
       }
-      if (HAS_LORA && have_prev && ok) lora_slots(prev_row0, prev_n0, prev_adapter);
+      if (HAS_LORA && have_prev && ok) lora_slots(prev_row0, prev_n0, prev_adapter, prev_second);
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer --------------------------------
@@ -519,8 +527,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       uint32_t phase = 0, it = 0, lora_rounds = 0;
       bool ok = true, have_prev = false;
       uint32_t prev_s = 0;
-      // rank-r bf16 MMAs of one tile, accumulated onto the accumulator the epilogue rewrote as fp32
-      auto lora_mma = [&](uint32_t acc_stage) -> bool {
+      int prev_second = 0;
+      // rank-r bf16 MMAs of one adapter slot of one tile, accumulated onto the accumulator the epilogue
+      // rewrote as fp32; `first` waits for that rewrite, `last` hands the accumulator back to the epilogue
+      auto lora_mma_of = [&](uint32_t acc_stage, bool first, bool last) -> bool {
         if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
         const int st1 = stage;
         if (++stage == nstages) {
@@ -533,7 +543,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           stage = 0;
           phase ^= 1u;
         }
-        if (!mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        if (first && !mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
         tc_fence_after_sync();
         const uint32_t e1 = smem_u32(smem + st1 * stage_bytes), e2 = smem_u32(smem + st2 * stage_bytes);
         const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
@@ -544,9 +554,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16(d, zd[plane] + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
         mma_commit(&empty_bar[st1]);
         mma_commit(&empty_bar[st2]);
-        mma_commit(lora_done);
-        ++lora_rounds;
+        if (last) {
+          mma_commit(lora_done);
+          ++lora_rounds;
+        }
         return true;
+      };
+      auto lora_mma = [&](uint32_t acc_stage, int second) -> bool {
+        if (!lora_mma_of(acc_stage, true, second == 0)) return false;
+        return second == 0 || lora_mma_of(acc_stage, false, true);
       };
       for (; ok; ++it) {
         const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_MMA, ok);
@@ -560,6 +576,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         const int kb0 = (t % ksplits) * p.kb_per_split;
         const int kb1 = min(kblocks, kb0 + p.kb_per_split);
         const int inject_at = min(LORA_INJECT_AFTER, kb1 - kb0);
+        const int second = HAS_LORA ? __ldg(p.tiles + tile_coord(t / ksplits, tm, tn, band).m_idx).w : 0;
         int issued = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
@@ -578,15 +595,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
             phase ^= 1u;
           }
           if (HAS_LORA && have_prev && ++issued == inject_at) {
-            ok = lora_mma(prev_s);
+            ok = lora_mma(prev_s, prev_second);
             if (!ok) break;
           }
         }
         if (ok) mma_commit(&tmem_full[s]);
         prev_s = s;
+        prev_second = second;
         have_prev = true;
       }
-      if (HAS_LORA && have_prev && ok) lora_mma(prev_s);
+      if (HAS_LORA && have_prev && ok) lora_mma(prev_s, prev_second);
     }
   } else {
     // ------------------------------ epilogue warps 0-3, 6-9 --------------------
@@ -746,12 +764,12 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      auto lora_slots = [&](int row0, int n0, int adapter) -> bool {
+      auto lora_slots_of = [&](int row0, int n0, int adapter, int zslot) -> bool {
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         unsigned char* sa = smem + stage * PAIR_STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], 2 * Z_PLANE_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, 2, row0, &full_bar[stage]);
-        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 1, row0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 3 * zslot + 2, row0, &full_bar[stage]);
+        tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_z, 0, 3 * zslot + 1, row0, &full_bar[stage]);
         if (++stage == PAIR_STAGES) {
           stage = 0;
           phase ^= 1u;
@@ -759,13 +777,17 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
         sa = smem + stage * PAIR_STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], Z_PLANE_BYTES + PAIR_BN * LORA_ROW_BYTES);
-        tma_load_3d(sa, &p.tm_z, 0, 0, row0, &full_bar[stage]);
+        tma_load_3d(sa, &p.tm_z, 0, 3 * zslot, row0, &full_bar[stage]);
         tma_load_3d(sa + Z_PLANE_BYTES, &p.tm_b, 0, n0, adapter, &full_bar[stage]);
         if (++stage == PAIR_STAGES) {
           stage = 0;
           phase ^= 1u;
         }
         return true;
+      };
+      auto lora_slots = [&](const int4& tile, int n0) -> bool {  // both adapter slots of a two-adapter tile
+        if (!lora_slots_of(tile.x, n0, tile.z, 0)) return false;
+        return tile.w == 0 || lora_slots_of(tile.x, n0, (tile.w & 0xffff) - 1, 1);
       };
       for (uint32_t it = 0; ok; ++it) {
         const int t = sched_claim(ring, it, p.sched, total, abort_flag, p.status, ok);
@@ -790,8 +812,8 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
           }
         }
         if (HAS_LORA && ok) {
-          ok = lora_slots(tile_a.x, n0, tile_a.z);
-          if (ok && has_b) ok = lora_slots(tile_b.x, n0, tile_b.z);
+          ok = lora_slots(tile_a, n0);
+          if (ok && has_b) ok = lora_slots(tile_b, n0);
         }
       }
     }
@@ -858,8 +880,12 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         if (!ok) break;
         mma_commit(tmem_full);
         if (HAS_LORA) {
+          const int second_a = __ldg(p.tiles + 2 * c.m_idx).w;
+          const int second_b = has_b ? __ldg(p.tiles + 2 * c.m_idx + 1).w : 0;
           ok = lora_mma(tmem_base, true, it & 1u);
+          if (ok && second_a != 0) ok = lora_mma(tmem_base, false, 0u);
           if (ok && has_b) ok = lora_mma(tmem_base + PAIR_BN, false, 0u);
+          if (ok && second_b != 0) ok = lora_mma(tmem_base + PAIR_BN, false, 0u);
           if (ok) mma_commit(lora_done);
         }
       }
@@ -1114,8 +1140,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
                            static_cast<uint64_t>(a.n) * BK, BK, bn_eff)))
     return rc;
   if (lora) {
-    if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, 3, a.m,
-                             LORA_ROW_BYTES, 3 * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, 1, BM)))
+    if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, SKYRL_Z_PARTS,
+                             a.m, LORA_ROW_BYTES, SKYRL_Z_PARTS * LORA_ROW_BYTES, SKYRL_LORA_RANK_PAD, 1, BM)))
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,

@@ -23,7 +23,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS,
+from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS, Z_PARTS,
                    WEIGHT_KBLOCK, SkyrlKernelError)
 
 __all__ = (
@@ -357,7 +357,7 @@ def _run_linear_grouped(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids
             _, _, xs = rms_quant(x2, row_map=perm, want_normalized=True)  # rows gathered into sorted order
         else:
             xs = x2.contiguous()
-        z_parts = torch.empty((m, 3, LORA_RANK_PAD), dtype=torch.bfloat16, device=dev)
+        z_parts = torch.empty((m, Z_PARTS, LORA_RANK_PAD), dtype=torch.bfloat16, device=dev)
         _lib.check(lib.skyrl_lora_a_proj_sm100_v1(_ptr(xs), m, k, _ptr(lora.a), _ptr(lora.scaling), na, lora.rank,
                                                   _ptr(tiles), _ptr(num), max_tiles, _ptr(z_parts), _ptr(st),
                                                   _stream()), "lora_a_proj")
@@ -720,7 +720,7 @@ def w8a8_mlp_tp_unsort(call, sorted_rows: torch.Tensor, out: torch.Tensor):
 
 def w8a8_mlp_workspace_regions(m: int, hidden: int, inter: int, num_adapters: int, device):
     """Views of the workspace regions a sequence-parallel gather moves, indexed by sorted row:
-    (codes int8 [m, hidden], scales fp32 [m], LoRA-A parts bf16 [m, 192])."""
+    (codes int8 [m, hidden], scales fp32 [m], LoRA-A parts bf16 [m, 384])."""
     lib = _lib.load()
     na = max(int(num_adapters), 1)
     ws = _workspace(device, lib.skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na))
@@ -728,7 +728,7 @@ def w8a8_mlp_workspace_regions(m: int, hidden: int, inter: int, num_adapters: in
     _lib.check(lib.skyrl_w8a8_mlp_workspace_regions(m, hidden, inter, na, off), "w8a8_mlp_workspace_regions")
     xq = ws[off[0]: off[0] + m * hidden].view(torch.int8).view(m, hidden)
     sx = ws[off[1]: off[1] + 4 * m].view(torch.float32)
-    z = ws[off[2]: off[2] + m * 3 * LORA_RANK_PAD * 2].view(torch.bfloat16).view(m, 3 * LORA_RANK_PAD)
+    z = ws[off[2]: off[2] + m * Z_PARTS * LORA_RANK_PAD * 2].view(torch.bfloat16).view(m, Z_PARTS * LORA_RANK_PAD)
     return xq, sx, z
 
 

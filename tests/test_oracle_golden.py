@@ -206,6 +206,16 @@ def test_multi_adapter_gather_equals_per_token_formula():
     np.testing.assert_array_equal(sort_idx[unsort], np.arange(m))
     tiles = O.row_tiles(sizes, 8)
     assert tiles[:, 1].sum() == m and np.all(tiles[:, 1] <= 8)
+    sorted_ids = ids[sort_idx]
+    for first, rows, adapter, second in tiles.tolist():
+        owners = sorted_ids[first:first + rows]
+        if second == 0:
+            assert np.all(owners == adapter)
+        else:
+            split = second >> 16
+            assert np.all(owners[:split] == adapter) and np.all(owners[split:] == (second & 0xffff) - 1)
+    # at most one tile more than a dense packing per adapter boundary that a third adapter would cross
+    assert tiles.shape[0] <= -(-m // 8) + na
 
 
 def test_gate_then_up_pairing():

@@ -75,6 +75,13 @@ typedef void* skyrl_stream_t; /* cudaStream_t */
 SKYRL_API int skyrl_w8a8_abi_version(void);
 SKYRL_API const char* skyrl_w8a8_last_error(void);
 
+/* Self-test of failure detection (no counterpart in the reference).  Every wait inside the kernels of
+ * this library is bounded: when a limit runs out the kernel writes a code into the caller's device status
+ * word, drains and returns, and the CUDA context stays usable.  This entry point launches one CTA that
+ * waits, for `limit_ns` (at most 2 s), on a barrier nothing ever arrives at; afterwards *status holds
+ * 190 and later launches on the device work as before.  Nothing faults, traps or hangs. */
+SKYRL_API int skyrl_w8a8_bounded_wait_selftest_sm100_v1(int32_t* status, uint64_t limit_ns, skyrl_stream_t stream);
+
 /* ------------------------------------------------------------------------- *
  * Stage kernels
  * ------------------------------------------------------------------------- */

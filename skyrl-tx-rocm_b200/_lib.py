@@ -31,7 +31,7 @@ ERROR_NAMES = {
 STATUS_NAMES = {
     101: "bounded wait ran out in the TMA producer", 102: "bounded wait ran out in the MMA issuer",
     103: "bounded wait ran out in the epilogue", 104: "bounded wait ran out in the LoRA step",
-    201: "adapter id outside [0, num_adapters)", 202: "tile list overflow", 203: "scattered partial-sum row without an owner",
+    190: "self-test wait ran out (expected)", 201: "adapter id outside [0, num_adapters)", 202: "tile list overflow", 203: "scattered partial-sum row without an owner",
 }
 
 
@@ -85,6 +85,7 @@ class MlpArgs(C.Structure):
 SYMBOLS = {
     "skyrl_w8a8_abi_version": (C.c_int, []),
     "skyrl_w8a8_last_error": (C.c_char_p, []),
+    "skyrl_w8a8_bounded_wait_selftest_sm100_v1": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     "skyrl_lora_route_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
                                             C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_rms_quant_sm100_v1": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_int32,

@@ -22,6 +22,7 @@ enum : int {
   STATUS_TIMEOUT_LORA = 104,
   STATUS_BAD_ADAPTER_ID = 201,
   STATUS_TILE_OVERFLOW = 202,
+  STATUS_SELFTEST_TIMEOUT = 190,  // the wait of the self-test kernel ran out, as it is meant to
   STATUS_BAD_SCATTER = 203,  // a row of a scattered partial-sum store has no owner
 };
 
@@ -104,7 +105,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit ran out or another role of the
 // CTA already aborted; the caller must then leave its loop.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, unsigned long long limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
@@ -115,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       unsigned long long now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > WAIT_LIMIT_NS) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         if (status != nullptr) atomicCAS(status, 0, code);
         return false;

@@ -375,6 +375,30 @@ int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int
   return SKYRL_OK;
 }
 
+// Self-test of the bounded wait every kernel of this library uses: one CTA waits on an mbarrier that
+// nothing ever arrives at, for `limit_ns`.  The wait gives up, writes its code into the status word and
+// the kernel returns normally; the context stays usable.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(int32_t* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  mbar_wait(&bar, 0u, &abort_flag, status, STATUS_SELFTEST_TIMEOUT, limit_ns);
+}
+
+int launch_bounded_wait_selftest(int32_t* status, unsigned long long limit_ns, cudaStream_t stream) {
+  if (status == nullptr || limit_ns == 0 || limit_ns > WAIT_LIMIT_NS)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "selftest: status must be non-null and the limit within (0, 2 s]");
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_ns);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "selftest launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
 // Rows of a bf16 [m, hidden] matrix in adapter-sorted order back to token order: out[perm[i]] = in[i].
 __global__ void __launch_bounds__(256)
 unsort_rows_kernel(const uint4* __restrict__ in, const int32_t* __restrict__ perm, uint4* __restrict__ out, int vecs) {
@@ -575,6 +599,10 @@ extern "C" int skyrl_group_sum_cast_sm100_v1(const float* slabs, int32_t groups,
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "group_sum_cast launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
+}
+
+extern "C" int skyrl_w8a8_bounded_wait_selftest_sm100_v1(int32_t* status, uint64_t limit_ns, skyrl_stream_t stream) {
+  return skyrl::launch_bounded_wait_selftest(status, limit_ns, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, int32_t num_adapters, int32_t* perm,

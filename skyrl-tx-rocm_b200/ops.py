@@ -33,7 +33,7 @@ __all__ = (
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
     "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
-    "check_status", "RMS_EPS",
+    "check_status", "bounded_wait_selftest", "RMS_EPS",
 )
 
 RMS_EPS = 1e-6
@@ -276,6 +276,16 @@ def check_status(device=None) -> None:
     if code != 0:
         st.zero_()
         raise SkyrlKernelError(f"device status {code}: {_lib.STATUS_NAMES.get(code, 'unknown')}")
+
+
+def bounded_wait_selftest(limit_ms: float = 50.0, device=None) -> None:
+    """Launch the library's failure-detection self-test: one CTA waits `limit_ms` on a barrier nothing
+    arrives at, gives up and records status 190.  The next `check_status()` raises for it; the device
+    stays usable."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _status_word(device)
+    _lib.check(_lib.load().skyrl_w8a8_bounded_wait_selftest_sm100_v1(st.data_ptr(), int(limit_ms * 1e6), _stream()),
+               "bounded_wait_selftest")
 
 
 # --------------------------------------------------------------------------- #

@@ -120,6 +120,18 @@ def test_routing_flags_bad_adapter_id(S):
         S.check_status()
 
 
+def test_bounded_wait_gives_up_and_reports(S):
+    # failure detection without a fault: a wait that nothing will ever satisfy runs into its limit, the
+    # kernel returns, the status word names the cause, and the device keeps working
+    S.bounded_wait_selftest(limit_ms=20.0)
+    with pytest.raises(S.SkyrlKernelError, match="self-test"):
+        S.check_status()
+    perm, _, num = S.prepare_routing(None, 300, 1)
+    S.check_status()
+    np.testing.assert_array_equal(to_np(perm), np.arange(300))
+    assert int(to_np(num)[0]) == 3
+
+
 # ----------------------------------------------------------------------------- quantiser
 @pytest.mark.parametrize("m,k", [(3, 64), (64, 4096), (257, 1024), (40, 12288), (8, 25600), (5, 48)])
 def test_activation_codes_and_scales_are_bit_exact(S, m, k):

@@ -183,6 +183,10 @@ typedef struct SkyrlW8A8GemmArgs {
                             /* the kernel uses plain stores.  Rows below scatter_row0 must not occur in     */
                             /* `tiles`.  XLA inserts a separate collective here                             */
                             /* (skyrl/tx/models/qwen3_5.py:644, ("tp", "fsdp") sharding of down_proj).      */
+  float* row_amax;          /* SKYRL_EPI_SWIGLU without out_row_map: fp32 [m], zeroed by the caller; the     */
+                            /* epilogue leaves max |out[i, :]| of every row in it (the absmax that           */
+                            /* _dynamic_group_quantize, quantized_lora.py:205, takes of the next projection's */
+                            /* input), so the quantiser need not read the rows twice.  NULL: not collected.  */
 } SkyrlW8A8GemmArgs;
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);

@@ -46,6 +46,7 @@ class GemmArgs(C.Structure):
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
         ("split_k_slabs", C.c_int32), ("cta_limit", C.c_int32),
         ("scatter_bases", C.c_void_p * 8), ("scatter_row0", C.c_int32), ("scatter_rows", C.c_int32),
+        ("row_amax", C.c_void_p),
     ]
 
 

@@ -167,6 +167,7 @@ struct MlpWs {
   int8_t* hq;
   float* sh;
   int32_t* acc;  // int32 [m, max(2I, H)] accumulator, row-wise path only
+  float* h_amax; // fp32 [m]: absmax of every row of h, collected by the gate_up epilogue
   size_t bytes;
 };
 
@@ -195,6 +196,7 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
     w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
     w.acc = nullptr;
   }
+  w.h_amax = c.take<float>(m);
   w.bytes = c.total();
   return w;
 }
@@ -221,6 +223,8 @@ struct Projection {
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
   bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
+  const float* known_amax;  // absmax of every source row, if the producer of x collected it (sorted route)
+  float* row_amax;          // SwiGLU epilogue: collect the absmax of every output row here
   int cta_limit;
   void* const* scatter_bases;  // row scatter of the fp32 partial sums (see SkyrlW8A8GemmArgs) or NULL
   int scatter_row0, scatter_rows;
@@ -261,10 +265,17 @@ static int run_quant_stage(const Projection& q, cudaStream_t stream) {
   // a gather reads rows perm[r0 ...] of x; without one the chunk's rows are rows r0 ... of x itself
   const unsigned char* xsrc = static_cast<const unsigned char*>(q.x) +
                               (q.gather != nullptr ? 0 : static_cast<size_t>(r0) * q.x_stride * 2);
-  if ((rc = launch_rms_quant(xsrc, q.x_stride, q.rms_delta, q.eps, q.gather != nullptr ? q.gather + r0 : nullptr,
-                             rows, q.k, q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
-                             need_xn ? q.xn + static_cast<size_t>(r0) * q.k : nullptr, stream)))
+  if (q.known_amax != nullptr && q.rms_delta == nullptr && q.gather == nullptr && !need_xn && q.x_stride == q.k) {
+    // the rows' absmax came with them: one streaming pass
+    if ((rc = launch_quant_stream(xsrc, q.known_amax + r0, rows, q.k, q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
+                                  stream)))
+      return rc;
+  } else if ((rc = launch_rms_quant(xsrc, q.x_stride, q.rms_delta, q.eps,
+                                    q.gather != nullptr ? q.gather + r0 : nullptr, rows, q.k,
+                                    q.xq + static_cast<size_t>(r0) * q.k, q.sx + r0,
+                                    need_xn ? q.xn + static_cast<size_t>(r0) * q.k : nullptr, stream))) {
     return rc;
+  }
   if (lora) {
     const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
     if ((rc = launch_lora_a_proj(xa, q.m, q.k, q.a_packed, q.scaling, q.na, q.rank, q.tiles, q.num_tiles, q.mt,
@@ -341,6 +352,12 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   g.residual_row_stride = q.residual_stride;
   g.status = q.status;
   g.cta_limit = q.cta_limit;
+  if (q.row_amax != nullptr && q.epilogue == SKYRL_EPI_SWIGLU) {
+    const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
+    cudaError_t e = cudaMemsetAsync(q.row_amax + r0, 0, static_cast<size_t>(rows) * sizeof(float), stream);
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "row_amax memset: %s", cudaGetErrorString(e));
+    g.row_amax = q.row_amax;
+  }
   if (q.scatter_bases != nullptr && q.scatter_rows > 0) {
     for (int o = 0; o < 8; ++o) g.scatter_bases[o] = q.scatter_bases[o];
     g.scatter_row0 = q.scatter_row0;
@@ -557,10 +574,17 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
 
   Projection q = front_projection(a, pl);
   q.skip_quant = prepared;
+  // sorted route: the gate_up epilogue collects the absmax of every row of h, so that quantising h is one
+  // streaming pass (SKYRL_W8A8_DEBUG_NO_ROW_AMAX=1, a tuning aid, keeps the two-pass quantiser)
+  const char* no_amax = getenv("SKYRL_W8A8_DEBUG_NO_ROW_AMAX");
+  const bool collect = !pl.rows_path && !(no_amax != nullptr && atoi(no_amax) != 0);
+  q.row_amax = collect ? w.h_amax : nullptr;
   if ((rc = run_projection(q, stream))) return rc;
 
   // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
   q.skip_quant = false;
+  q.row_amax = nullptr;
+  q.known_amax = collect ? w.h_amax : nullptr;
   q.x = w.h;
   q.x_stride = a->inter;
   q.rms_delta = nullptr;

@@ -52,6 +52,8 @@ int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int
                  int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0);
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
+// rows [m, k] contiguous (row pitch k) with their absmax known: codes and scales in one streaming pass
+int launch_quant_stream(const void* x, const float* row_amax, int m, int k, void* xq, float* sx, cudaStream_t stream);
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream, int row_lo = 0, int row_hi = -1);

@@ -276,6 +276,55 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
   return SKYRL_OK;
 }
 
+// Per-token int8 quantisation of rows whose absmax is already known (the GEMM that produced the rows
+// collected it in its epilogue): nothing is row-wide any more, so every thread streams two 8-element
+// vectors, HBM in -> codes out, with no shared memory and no barrier.  Same arithmetic as
+// rms_quant_kernel (scale = amax / 127 or 1, exact rint(x / scale)).
+__global__ void __launch_bounds__(256)
+quant_stream_kernel(const uint4* __restrict__ x, const float* __restrict__ row_amax, int nvec, int64_t total_vecs,
+                    uint2* __restrict__ xq, float* __restrict__ sx) {
+  const int64_t v0 = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) * 2;
+  if (v0 >= total_vecs) return;
+  const bool two = v0 + 1 < total_vecs;
+  const uint4 u0 = __ldg(x + v0);
+  const uint4 u1 = two ? __ldg(x + v0 + 1) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (i == 1 && !two) break;
+    const int64_t v = v0 + i;
+    const int64_t row = v / nvec;
+    const float amax = __ldg(row_amax + row);
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float rcp = quant_rcp(scale);
+    if (v - row * nvec == 0) sx[row] = scale;
+    const uint4 u = i == 0 ? u0 : u1;
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    int q[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      q[2 * j] = quant_code(bf16_lo(w[j]), scale, rcp);
+      q[2 * j + 1] = quant_code(bf16_hi(w[j]), scale, rcp);
+    }
+    xq[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+  }
+}
+
+int launch_quant_stream(const void* x, const float* row_amax, int m, int k, void* xq, float* sx, cudaStream_t stream) {
+  if (x == nullptr || row_amax == nullptr || xq == nullptr || sx == nullptr || m <= 0 || k <= 0 || k % 16 != 0)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "quant_stream: null buffer or bad shape");
+  if (!aligned16(x) || !aligned16(xq) || x == xq)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "quant_stream: buffers must be distinct and 16-byte aligned");
+  const int nvec = k >> 3;
+  const int64_t total = static_cast<int64_t>(m) * nvec;
+  const int64_t ctas = (total + 511) / 512;
+  if (ctas > 0x7fffffffll) return fail(SKYRL_ERR_UNSUPPORTED, "quant_stream: too many rows");
+  quant_stream_kernel<<<static_cast<unsigned>(ctas), 256, 0, stream>>>(static_cast<const uint4*>(x), row_amax, nvec, total,
+                                                                      static_cast<uint2*>(xq), sx);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "quant_stream launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
 // ----------------------------------------------------------------------------
 // Row-parallel finalize: out[perm[i]] = bf16(bf16(sum[i]) + residual[perm[i]]).
 // The two roundings are the reference's: the projection is cast to bf16 once

@@ -91,6 +91,10 @@ struct GemmParams {
   float* scatter_base[8];
   int scatter_row0;
   int scatter_rows;
+  // SwiGLU epilogue: absmax of every output row, collected with atomicMax on the bit pattern (the values
+  // are >= 0) so that the quantiser of the next projection needs no pass of its own to find it.
+  // Indexed by sorted row; the caller zeroes it before the launch.  NULL: not collected.
+  float* row_amax;
 };
 
 // NULL (and status STATUS_BAD_SCATTER) for a row that has no owner: the caller skips the store.
@@ -229,7 +233,8 @@ __device__ __forceinline__ void epi_staged_store(unsigned char* stage, int lane,
 template <int EPI, bool HAS_LORA>
 __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t taddr, int nc, int n_end, float sxr,
                                                 bool row_valid, int64_t orow, int64_t slab_off,
-                                                unsigned char* stage = nullptr, int lane = 0) {
+                                                unsigned char* stage = nullptr, int lane = 0,
+                                                float* amax_acc = nullptr) {
   uint32_t v[32];
   __syncwarp();
   tmem_ld32(taddr, v);
@@ -302,6 +307,10 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
         const float h0 = __fmul_rn(silu_f32(round_bf16(f[4 * j])), round_bf16(f[4 * j + 1]));
         const float h1 = __fmul_rn(silu_f32(round_bf16(f[4 * j + 2])), round_bf16(f[4 * j + 3]));
         o[j] = pack_bf16x2(h0, h1);
+        if (amax_acc != nullptr) {  // columns past the tile's end hold whatever TMEM held: leave them out
+          if (nc + 4 * j < n_end) *amax_acc = fmaxf(*amax_acc, fabsf(h0));
+          if (nc + 4 * j + 2 < n_end) *amax_acc = fmaxf(*amax_acc, fabsf(h1));
+        }
       }
       epi_staged_store(stage, lane, o, 8, row_valid, orow, static_cast<__nv_bfloat16*>(p.out), p.out_stride, nc >> 1,
                        (n_end - nc) >> 1, nullptr, 0);
@@ -352,6 +361,10 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
           const float h0 = __fmul_rn(silu_f32(round_bf16(f[i0])), round_bf16(f[i0 + 1]));
           const float h1 = __fmul_rn(silu_f32(round_bf16(f[i0 + 2])), round_bf16(f[i0 + 3]));
           o[j] = pack_bf16x2(h0, h1);
+          if (amax_acc != nullptr) {
+            if (nc + i0 < n_end) *amax_acc = fmaxf(*amax_acc, fabsf(h0));
+            if (nc + i0 + 2 < n_end) *amax_acc = fmaxf(*amax_acc, fabsf(h1));
+          }
         }
         dst[g] = make_uint4(o[0], o[1], o[2], o[3]);
       }
@@ -654,10 +667,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       }
 
       // pass 2: final values -> global memory
+      float tile_amax = 0.f;
+      float* amax_acc = (EPI == SKYRL_EPI_SWIGLU && p.row_amax != nullptr) ? &tile_amax : nullptr;
 #pragma unroll 1
       for (int cc = c_begin; cc < c_end; ++cc)
         epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow,
-                                       (t % ksplits) * p.slab_stride, store_stage, lane);
+                                       (t % ksplits) * p.slab_stride, store_stage, lane, amax_acc);
+      // rounding to bf16 is monotonic, so the absmax of the stored values is the rounded absmax
+      if (amax_acc != nullptr && row_valid && tile_amax > 0.f)
+        atomicMax(reinterpret_cast<int*>(p.row_amax) + srow, __float_as_int(round_bf16(tile_amax)));
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[s]);
     }
@@ -934,9 +952,14 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
         tc_fence_after_sync();
       }
       if (present) {
+        float tile_amax = 0.f;
+        float* amax_acc = (EPI == SKYRL_EPI_SWIGLU && p.row_amax != nullptr) ? &tile_amax : nullptr;
 #pragma unroll 1
         for (int cc = c_begin; cc < c_end; ++cc)
-          epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow, 0);
+          epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow, 0, nullptr, 0,
+                                         amax_acc);
+        if (amax_acc != nullptr && row_valid && tile_amax > 0.f)
+          atomicMax(reinterpret_cast<int*>(p.row_amax) + srow, __float_as_int(round_bf16(tile_amax)));
       }
       tc_fence_before_sync();
       mbar_arrive(tmem_empty);
@@ -1187,6 +1210,12 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
     }
     p.scatter_rows = a.scatter_rows;
     p.scatter_row0 = a.scatter_row0;
+  }
+  p.row_amax = nullptr;
+  if (a.row_amax != nullptr) {
+    if (a.epilogue != SKYRL_EPI_SWIGLU || a.out_row_map != nullptr)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: row_amax needs the SwiGLU epilogue and rows left in sorted order");
+    p.row_amax = a.row_amax;
   }
   p.direct_stores = 0;
   if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_DIRECT_STORES")) p.direct_stores = atoi(dbg) != 0;  // tuning aid

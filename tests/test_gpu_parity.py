@@ -403,6 +403,29 @@ def test_mlp_block(S, m, hidden, inter, rank, na):
     assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
 
 
+@pytest.mark.parametrize("m,hidden,inter,rank,na", [(300, 512, 640, 32, 4), (1000, 256, 400, 16, 9)])
+def test_row_absmax_from_epilogue_equals_two_pass_quantiser(S, m, hidden, inter, rank, na):
+    # the gate_up epilogue collects max |h[i, :]| with atomics and the quantiser of h streams once;
+    # against the quantiser that finds the absmax itself the block must be bit-identical
+    rng = np.random.default_rng(191 + m)
+    x, wgu, ga, gb, s, ids = make_case(193 + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(197 + m, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    _, pgu = device_weight(S, wgu)
+    _, pd = device_weight(S, wd)
+    lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+    xd, dd, idd = to_dev(x), to_dev(delta), to_dev(ids)
+    os.environ["SKYRL_W8A8_DEBUG_NO_ROW_AMAX"] = "1"
+    try:
+        want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True).clone()
+    finally:
+        del os.environ["SKYRL_W8A8_DEBUG_NO_ROW_AMAX"]
+    got = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True)
+    S.check_status()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
 @pytest.mark.parametrize("m,chunks", [(1000, 3), (700, 4), (300, 16)])
 def test_chunked_block_equals_whole_block(S, m, chunks):
     # a block computed chunk by chunk (the form the tensor-parallel pipeline uses) is bit-identical

@@ -443,7 +443,7 @@ def run_device(args):
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
                    "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
                    **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
-                       "tp_peer_scatter": (tp_stack.peer_scatter or "off") if tp_stack is not None else "off",
+                       "tp_peer_scatter": (tp_stack.scatter_mode or "all_reduce") if tp_stack is not None else "off",
                        "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),

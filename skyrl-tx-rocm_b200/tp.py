@@ -138,6 +138,7 @@ class TensorParallelMLPStack:
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self.sequence_parallel = sequence_parallel
         self.peer_scatter = peer_scatter
+        self.scatter_mode = None
         self._slabs = None        # (shape key, local tensor, handle, per-rank base addresses, peer views)
         self._coalesce = True     # gathers of the three prepared regions go out as one NCCL group
         self._token = None
@@ -271,6 +272,7 @@ class TensorParallelMLPStack:
         if mode in (True, "auto"):
             mode = "epilogue" if tp <= 2 else "copy"
         peers = self._slabs[4] if slab_ptrs is not None else None
+        self.scatter_mode = mode or "nccl"     # what actually delivers the partial sums, for reports
         own_rows = m // tp
         own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(len(spans))]
         row_bytes = hidden * 4

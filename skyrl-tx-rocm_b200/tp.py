@@ -105,7 +105,7 @@ class TensorParallelMLPStack:
       Behind down_proj a reduce-scatter of the fp32 partial sums leaves a rank the sums
       of its rows, it adds the residual for them, runs the NEXT block's RMSNorm, int8
       quantisation and LoRA-A projection on them, and an all-gather hands every rank
-      the codes, scales and projections of all rows (1.08 bytes per element instead of
+      the codes, scales and projections of all rows (1.15 bytes per element instead of
       the 4 + 4 of an fp32 all-reduce, and none of the row-wise work is replicated).
       The last block gathers its bf16 rows in sorted order and restores token order.
     * otherwise: one fp32 all-reduce per chunk, every rank finalizes all rows and

@@ -46,6 +46,26 @@ def shard_down(codes_kn, lora_a, tp: int, rank: int):
     return codes_kn[lo:hi], lora_a[:, lo:hi, :]
 
 
+def exchange_plan(m: int, num_chunks: int, tp: int, rank: int, tile_rows: int = 128):
+    """Row bookkeeping of the sequence-parallel exchange, as plain integers.
+
+    The sorted rows are cut into chunks of ceil(m / num_chunks) rows rounded up to the tile height; inside a
+    chunk rank r owns the r-th of tp equal runs of rows.  Returns a dict with
+      spans    [(first row, rows)] of the chunks,
+      own      [(first row, rows)] of this rank's run in every chunk,
+      own_off  offset of each chunk's run inside the rank's [m / tp]-row slab (runs stored chunk after chunk),
+      own_rows m // tp, rows of one slab,
+      even     whether every chunk divides by tp (otherwise the all-reduce form is used).
+    """
+    per = (m + num_chunks - 1) // num_chunks
+    rows = (per + tile_rows - 1) // tile_rows * tile_rows
+    spans = [(c * rows, min(rows, m - c * rows)) for c in range(num_chunks) if c * rows < m]
+    even = all(cnt % tp == 0 for _, cnt in spans)
+    own = [(r0 + rank * (cnt // tp), cnt // tp) for r0, cnt in spans]
+    own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(len(spans))]
+    return {"spans": spans, "own": own, "own_off": own_off, "own_rows": m // tp, "even": even}
+
+
 class TensorParallelMLP:
     """One rank's share of an MLP block: partial sums -> all-reduce -> finalize.
 
@@ -215,12 +235,11 @@ class TensorParallelMLPStack:
 
         m, hidden = x.shape
         chunks = self.num_chunks if m > ops.TILE_ROWS else 1
-        rows = ops.chunk_rows(m, chunks)
-        spans = [(c * rows, min(rows, m - c * rows)) for c in range(chunks) if c * rows < m]
         tp = dist.get_world_size(self.group)
+        plan = exchange_plan(m, chunks, tp, dist.get_rank(self.group), ops.TILE_ROWS)
+        spans = plan["spans"]
         self._buffers(x)
-        if (self.sequence_parallel and tp > 1 and m > ops.TILE_ROWS and self.blocks
-                and all(cnt % tp == 0 for _, cnt in spans)):
+        if self.sequence_parallel and tp > 1 and m > ops.TILE_ROWS and self.blocks and plan["even"]:
             return self._forward_sequence_parallel(x, adapter_ids, spans, chunks, tp, timing_events)
         main = torch.cuda.current_stream()
         prev_done = [None] * len(spans)
@@ -262,7 +281,8 @@ class TensorParallelMLPStack:
         rank = dist.get_rank(self.group)
         main, comm = torch.cuda.current_stream(), self._comm
         chunk_arg = lambda c: (c, chunks) if chunks > 1 else None
-        own = [(r0 + rank * (cnt // tp), cnt // tp) for r0, cnt in spans]
+        plan = exchange_plan(m, chunks, tp, rank, ops.TILE_ROWS)
+        own, own_off, own_rows = plan["own"], plan["own_off"], plan["own_rows"]
         first = self.blocks[0]
         na = first.gate_up_lora.num_adapters if first.gate_up_lora is not None else 1
         codes, scales, parts = ops.w8a8_mlp_workspace_regions(m, hidden, first.down_weight.in_features, na, x.device)
@@ -273,8 +293,6 @@ class TensorParallelMLPStack:
             mode = "epilogue" if tp <= 2 else "copy"
         peers = self._slabs[4] if slab_ptrs is not None else None
         self.scatter_mode = mode or "nccl"     # what actually delivers the partial sums, for reports
-        own_rows = m // tp
-        own_off = [sum(cnt // tp for _, cnt in spans[:c]) for c in range(len(spans))]
         row_bytes = hidden * 4
         if slab_ptrs is not None and self._token is None:
             self._token = torch.zeros(1, dtype=torch.int32, device=x.device)

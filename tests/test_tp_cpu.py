@@ -101,3 +101,65 @@ def test_shard_helpers():
     # rank 1 of 2 owns pairs 4..7 = physical columns 8..15 (gate and up of each pair together)
     np.testing.assert_array_equal(c, codes[:, 8:16])
     assert sc.shape == (1, 8) and b.shape == (2, 3, 8)
+
+
+def _exchange_rank(rank, world, port, result_path):
+    """The sequence-parallel exchange with NumPy rows instead of kernels: every rank holds fp32 partial sums of
+    all rows, pushes each owner's runs into the owner's [source rank, own rows] slab, the
+    owner adds the slabs in rank order, and the owned runs are gathered back into sorted order."""
+    import torch.distributed as dist
+
+    from skyrl_tx_rocm_b200 import tp as T
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    m, hidden, chunks = 1280, 8, 3
+    plans = [T.exchange_plan(m, chunks, world, r) for r in range(world)]
+    me = plans[rank]
+    assert me["even"] and me["own_rows"] == m // world
+    part = torch.from_numpy(np.random.default_rng(100 + rank).standard_normal((m, hidden)).astype(np.float32))
+    # what this rank sends to owner o: o's runs of every chunk, laid out as o stores them (chunk after chunk)
+    send = []
+    for o in range(world):
+        buf = torch.empty((me["own_rows"], hidden))
+        for (r0, cnt), off in zip(plans[o]["own"], plans[o]["own_off"]):
+            buf[off:off + cnt] = part[r0:r0 + cnt]
+        send.append(buf)
+    # the pushes: gloo has no all_to_all, so every rank publishes all it sends and an owner picks its part
+    outbox = torch.stack(send)
+    boxes = [torch.empty_like(outbox) for _ in range(world)]
+    dist.all_gather(boxes, outbox)
+    slabs = [boxes[src][rank] for src in range(world)]                      # [source rank] of this owner
+    total = slabs[0].clone()
+    for s in range(1, world):
+        total += slabs[s]                                                   # ascending rank order
+    gathered = [torch.empty_like(total) for _ in range(world)]
+    dist.all_gather(gathered, total)
+    full = torch.empty((m, hidden))
+    for o in range(world):
+        for (r0, cnt), off in zip(plans[o]["own"], plans[o]["own_off"]):
+            full[r0:r0 + cnt] = gathered[o][off:off + cnt]
+    if rank == 0:
+        np.save(result_path, full.numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sequence_parallel_exchange_bookkeeping(tmp_path):
+    import torch.multiprocessing as mp
+
+    from skyrl_tx_rocm_b200 import tp as T
+
+    result = str(tmp_path / "exchange.npy")
+    mp.spawn(_exchange_rank, args=(2, _free_port(), result), nprocs=2, join=True)
+    got = np.load(result)
+    want = sum(np.random.default_rng(100 + r).standard_normal((1280, 8)).astype(np.float32) for r in range(2))
+    np.testing.assert_array_equal(got, want)
+
+    plan = T.exchange_plan(16384, 2, 8, 3)
+    assert plan["spans"] == [(0, 8192), (8192, 8192)] and plan["own"] == [(3072, 1024), (11264, 1024)]
+    assert plan["own_off"] == [0, 1024] and plan["own_rows"] == 2048 and plan["even"]
+    assert not T.exchange_plan(1001, 2, 8, 0)["even"]          # 512 + 489 rows: the second chunk does not divide
+    runs = sorted(r for k in range(4) for r in T.exchange_plan(1280, 3, 4, k)["own"])
+    assert runs[0][0] == 0 and all(a[0] + a[1] == b[0] for a, b in zip(runs, runs[1:])) and sum(r[1] for r in runs) == 1280

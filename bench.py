@@ -244,7 +244,12 @@ def run_device(args):
         d2h = m * hidden * 2
         out_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
         # per layer: 2 quantiser, 2 LoRA-A / LoRA-B-rows, 2 GEMM launches (+ finalize under TP); one routing launch per step
-        launches_per_step = layers * (6 + (1 if tp > 1 else 0)) + 1
+        if tp > 1 and m > 128:
+            # per layer and row chunk: quantiser of h, LoRA-A of h, two GEMMs, finalize, next layer's quantiser and
+            # LoRA-A projection of the own rows; one routing launch and one row un-sort per step
+            launches_per_step = layers * args.tp_chunks * 7 + 2
+        else:
+            launches_per_step = layers * 6 + 1
 
         def step(x_in, ids_in, events=None):
             if tp > 1:

@@ -421,7 +421,11 @@ def run_device(args):
     if wl["bound"] == "tensor":
         achieved = gu_ops_launch / (gu_avg * 1e-3) / 1e12
         roofline = dict(bound="tensor", kernel="w8a8_gemm_kernel<gate_up/SwiGLU epilogue>" if kind in ("mlp", "gate_up") else "w8a8_gemm_kernel",
-                        achieved=achieved, peak=i8_peak, unit="TFLOP/s", frac=achieved / i8_peak, traffic=None,
+                        achieved=achieved, peak=i8_peak, unit="TFLOP/s", frac=achieved / i8_peak,
+                        # DRAM bytes of one gate_up launch: ncu capture at M = 4096 (660.5 MB read + 195.9 MB written,
+                        # profiles/w8a8_gemm_c5_layer_m4096.md) scaled by the rows, which every term grows with
+                        traffic=(856.3e6 * m / 4096 if (args.workload == "c5" and tp == 1) else None),
+                        traffic_unit="bytes per launch (ncu at M=4096, scaled by M)",
                         peak_source=f"2 x bf16_tflops_sustained of {peaks['source']} (int8 tcgen05 rate is twice bf16); 1 int8 multiply-add = 2 ops",
                         launch_ms=gu_avg, ops_per_launch=gu_ops_launch,
                         down_gemm=dict(achieved=dn_ops_launch / (dn_avg * 1e-3) / 1e12, launch_ms=dn_avg,

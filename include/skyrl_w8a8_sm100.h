@@ -11,8 +11,11 @@
  *
  * Naming and versioning follow the reference's native-ABI convention
  * (rocm/compile_probes/down_lora_residual_gfx1100_abi.h:12-85: versioned
- * symbols, explicit device addresses + dimensions, layout asserted at compile
- * time).  Citations below are file:line inside the reference project.
+ * symbols, explicit device addresses + dimensions, and the layout of every
+ * argument block asserted at compile time: the SKYRL_ABI_ASSERT lines behind
+ * each struct below, as down_lora_residual_gfx1100_abi.h:77-85 does).
+ * Citations are file:line inside the reference project.  The header is plain
+ * C (C11) and C++.
  *
  * Device data layouts
  *   activations ........ bf16 [M, K] row-major
@@ -52,9 +55,15 @@ extern "C" {
 
 #define SKYRL_W8A8_ABI_VERSION 1
 #define SKYRL_LORA_RANK_PAD 64 /* packed LoRA tables hold 64 rank slots            */
-#define SKYRL_TILE_ROWS 128
-#define SKYRL_Z_PARTS 6 /* bf16 parts of a row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo) */    /* rows of one M tile (one adapter per tile)         */
-#define SKYRL_WEIGHT_KBLOCK 128 /* K values per block of the packed weight layout   */
+#define SKYRL_TILE_ROWS 128     /* rows of one M tile (rows of at most two adapters) */
+#define SKYRL_Z_PARTS 6         /* bf16 parts of a row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo) */
+#define SKYRL_WEIGHT_KBLOCK 128 /* K values per block of the packed weight layout    */
+
+#if defined(__cplusplus)
+#define SKYRL_ABI_ASSERT(cond, msg) static_assert(cond, msg)
+#else
+#define SKYRL_ABI_ASSERT(cond, msg) _Static_assert(cond, msg)
+#endif
 
 #define SKYRL_OK 0
 #define SKYRL_ERR_INVALID_ARGUMENT (-1) /* shape / alignment / null / alias violation    */
@@ -187,7 +196,19 @@ typedef struct SkyrlW8A8GemmArgs {
                             /* epilogue leaves max |out[i, :]| of every row in it (the absmax that           */
                             /* _dynamic_group_quantize, quantized_lora.py:205, takes of the next projection's */
                             /* input), so the quantiser need not read the rows twice.  NULL: not collected.  */
+  int32_t* sched;           /* two device words {tiles claimed, CTAs finished} of the kernel's dynamic tile   */
+                            /* scheduler: zero when the kernel starts, left at zero when it ends, and not     */
+                            /* shared with a launch that may run at the same time.  NULL: the library hands   */
+                            /* out a pair from a ring of 1024 per device; that is safe while the GEMM         */
+                            /* launches of a process on one device are ordered (one stream, or events), and   */
+                            /* NOT safe for a captured graph replayed next to eager launches on another       */
+                            /* stream (the graph keeps its pairs).  The operator entry points below keep      */
+                            /* their pairs in the caller's workspace and have no such constraint.             */
 } SkyrlW8A8GemmArgs;
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8GemmArgs) == 240, "SkyrlW8A8GemmArgs layout");
+SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8GemmArgs, xq) == 32 && offsetof(SkyrlW8A8GemmArgs, out_row_stride) == 120 &&
+                     offsetof(SkyrlW8A8GemmArgs, scatter_bases) == 152 && offsetof(SkyrlW8A8GemmArgs, sched) == 232,
+                 "SkyrlW8A8GemmArgs layout");
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
 /* Number of K splits (slabs written) the GEMM uses for this shape when given `split_k_slabs` slabs. */
@@ -235,9 +256,32 @@ typedef struct SkyrlW8A8LinearArgs {
   int32_t lora_b_rows_rank;
   int32_t reserved2;
 } SkyrlW8A8LinearArgs;
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8LinearArgs) == 200, "SkyrlW8A8LinearArgs layout");
+SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8LinearArgs, x) == 32 && offsetof(SkyrlW8A8LinearArgs, wq) == 64 &&
+                     offsetof(SkyrlW8A8LinearArgs, out) == 128 && offsetof(SkyrlW8A8LinearArgs, workspace) == 144 &&
+                     offsetof(SkyrlW8A8LinearArgs, timing_events) == 168 &&
+                     offsetof(SkyrlW8A8LinearArgs, lora_b_rows) == 184,
+                 "SkyrlW8A8LinearArgs layout");
 
 SKYRL_API size_t skyrl_w8a8_linear_workspace_bytes(int32_t m, int32_t n, int32_t k, int32_t num_adapters);
 SKYRL_API int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
+
+/* One exported target per fused variant, so that a custom-call layer binds each operator to its own
+ * symbol and no epilogue selector travels through the hot path (rocm/QUANTIZED_FFI.md:579-580).  Both
+ * take the argument block above; `epilogue` is ignored and fixed by the entry point.
+ *
+ *   skyrl_rms_gate_up_w8a8_lora_swiglu_sm100_v1   h[m, n/2] = swiglu(W8A8-LoRA gate_up(rmsnorm(x))) on
+ *       interleaved (gate, up) columns; `rms_delta` may be NULL (no normalisation), `residual` must be.
+ *       Successor of bf16_rms_gate_up_lora_swiglu_contiguous
+ *       (skyrl/tx/kernels/rocm/bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757) and of the traced
+ *       kernel skyrl_qwen35_bf16_contiguous_gate_up_lora_swiglu_forward
+ *       (rocm/probe_bf16_rms_gate_up_lora_swiglu.py:143-188).
+ *   skyrl_down_w8a8_lora_residual_sm100_v1        out[m, n] = bf16(W8A8-LoRA down(x)) + residual;
+ *       `residual` is required, `rms_delta` must be NULL.  Successor of bf16_lora_residual
+ *       (skyrl/tx/kernels/rocm/bf16_lora_residual.py:507-566) and of
+ *       skyrl_qwen35_bf16_down_lora_residual_forward (rocm/probe_bf16_down_lora_residual.py:416-469). */
+SKYRL_API int skyrl_rms_gate_up_w8a8_lora_swiglu_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
+SKYRL_API int skyrl_down_w8a8_lora_residual_sm100_v1(const SkyrlW8A8LinearArgs* args, skyrl_stream_t stream);
 
 /* The same W8A8 LoRA linear for callers that cannot hand over a workspace.
  * This entry point has no counterpart in the reference.
@@ -279,6 +323,8 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
                                        here or, through a gather, on other ranks): skip that stage. */
 #define SKYRL_MLP_FINALIZE_SORTED 4u /* skyrl_w8a8_mlp_tp_finalize_sm100_v1 writes row i to out[i] (sorted order)
                                         instead of out[perm[i]]; the residual is still read at perm[i]. */
+#define SKYRL_MLP_NO_ROW_AMAX 8u /* the quantiser of h finds the row absmax itself (two passes over h) instead of
+                                    taking it from the gate_up epilogue; results are bit-identical (a cross-check). */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
@@ -326,6 +372,12 @@ typedef struct SkyrlW8A8MlpArgs {
                              /* first row of the call's chunk (see SkyrlW8A8GemmArgs.scatter_bases); `out` is  */
                              /* then not written.                                                             */
 } SkyrlW8A8MlpArgs;
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8MlpArgs) == 312, "SkyrlW8A8MlpArgs layout");
+SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8MlpArgs, x) == 32 && offsetof(SkyrlW8A8MlpArgs, gu_wq) == 56 &&
+                     offsetof(SkyrlW8A8MlpArgs, out) == 144 && offsetof(SkyrlW8A8MlpArgs, timing_events) == 176 &&
+                     offsetof(SkyrlW8A8MlpArgs, flags) == 208 && offsetof(SkyrlW8A8MlpArgs, num_chunks) == 232 &&
+                     offsetof(SkyrlW8A8MlpArgs, tp_scatter_bases) == 248,
+                 "SkyrlW8A8MlpArgs layout");
 
 SKYRL_API size_t skyrl_w8a8_mlp_workspace_bytes(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters);
 SKYRL_API int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* args, skyrl_stream_t stream);
@@ -367,6 +419,13 @@ SKYRL_API int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* args, i
  * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 6, 64]. */
 SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                      size_t* offsets);
+/* Byte offsets of the intermediate results a finished skyrl_w8a8_mlp_block_sm100_v1 call leaves in its
+ * workspace, for stage-by-stage parity checks: offsets[0] row permutation int32 [m] (sorted position ->
+ * token row; meaningful for m > 128 with adapter ids, otherwise rows keep token order), offsets[1]
+ * h = swiglu(gate_up(...)) bf16 [m, inter] in the GEMM's row order, offsets[2] int8 codes of h [m, inter],
+ * offsets[3] fp32 scales of h [m]. */
+SKYRL_API int skyrl_w8a8_mlp_workspace_stage_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
+                                           size_t* offsets);
 /* out[perm[i], :] = sorted_rows[i, :] for all m rows of a bf16 [m, H] matrix (perm from the workspace of
  * `args`): the last block of a sequence-parallel stack gathers its rows in sorted order, then restores
  * token order with this. */

@@ -20,6 +20,7 @@ NOALLOC_SCRATCH_BYTES = 32 << 20
 MLP_REUSE_ROUTING = 1
 MLP_INPUT_PREPARED = 2
 MLP_FINALIZE_SORTED = 4
+MLP_NO_ROW_AMAX = 8
 LORA_RANK_PAD = 64
 Z_PARTS = 6            # bf16 parts per row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo)
 TILE_ROWS = 128
@@ -46,7 +47,7 @@ class GemmArgs(C.Structure):
         ("out_row_stride", C.c_int64), ("residual_row_stride", C.c_int64), ("status", C.c_void_p),
         ("split_k_slabs", C.c_int32), ("cta_limit", C.c_int32),
         ("scatter_bases", C.c_void_p * 8), ("scatter_row0", C.c_int32), ("scatter_rows", C.c_int32),
-        ("row_amax", C.c_void_p),
+        ("row_amax", C.c_void_p), ("sched", C.c_void_p),
     ]
 
 
@@ -101,6 +102,8 @@ SYMBOLS = {
     "skyrl_w8a8_linear_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_lora_forward_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_lora_forward_noalloc_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "skyrl_rms_gate_up_w8a8_lora_swiglu_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
+    "skyrl_down_w8a8_lora_residual_sm100_v1": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "skyrl_w8a8_mlp_block_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p]),
     "skyrl_w8a8_mlp_tp_finalize_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_int32,
@@ -110,6 +113,8 @@ SYMBOLS = {
     "skyrl_w8a8_mlp_tp_prepare_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_int32, C.c_int32, C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_regions": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                    C.POINTER(C.c_size_t)]),
+    "skyrl_w8a8_mlp_workspace_stage_regions": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                                         C.POINTER(C.c_size_t)]),
     "skyrl_w8a8_mlp_tp_unsort_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_void_p]),
     "skyrl_pack_weight_kn_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_pack_weight_nk_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),

@@ -35,7 +35,8 @@ def _nvcc() -> str:
 
 def _digest() -> str:
     h = hashlib.sha256()
-    for path in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list((PKG.parent / "include").glob("*.h"))):
+    for path in sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.c")) +
+                       list((PKG.parent / "include").glob("*.h"))):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
@@ -66,8 +67,20 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
             raise RuntimeError(f"nvcc failed on {src}")
     link = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(link, check=True)
+    build_abi_check()
     stamp.write_text(digest + "\n")
     return LIB_PATH
+
+
+def build_abi_check() -> Path:
+    """Plain-C consumer of the public header (csrc/abi_check.c), linked against the library."""
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        raise RuntimeError("gcc not found; the C-ABI check cannot be built")
+    exe = LIB_DIR / "abi_check"
+    subprocess.run([gcc, "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", str(CSRC / "abi_check.c"), "-o", str(exe),
+                    f"-L{LIB_DIR}", "-lskyrl_w8a8_sm100", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN"], check=True)
+    return exe
 
 
 if __name__ == "__main__":

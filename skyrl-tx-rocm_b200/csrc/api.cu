@@ -66,15 +66,6 @@ int encode_tmap_3d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, 
   return encode(map, dtype, 3, base, dims, strides, box);
 }
 
-bool pdl_enabled() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* dbg = getenv("SKYRL_W8A8_DEBUG_NO_PDL");
-    cached = (dbg != nullptr && atoi(dbg) != 0) ? 0 : 1;
-  }
-  return cached == 1;
-}
-
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -91,6 +82,7 @@ int sm_count() {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 constexpr int MAX_CHUNKS = 16;
+constexpr int SCHED_WORDS = 8;  // room for four {claimed, finished} pairs of the GEMMs' dynamic tile scheduler
 
 // Tiles one chunk of `rows` sorted rows can hold: every adapter may end a partial tile inside it.
 static inline int tile_cap(int rows, int num_adapters) {
@@ -131,6 +123,7 @@ struct LinearWs {
   uint16_t* xn;
   uint16_t* z_parts;  // bf16 [m, 6, 64]; the row-wise path keeps fp32 [m, 64] here instead
   int32_t* acc;       // int32 [m, n] accumulator, row-wise path only
+  int32_t* sched;     // tile-claim counters of the GEMM launch (zeroed by the routing kernel, left at zero by the GEMM)
   size_t bytes;
 };
 
@@ -141,6 +134,7 @@ static LinearWs carve_linear(void* ws, int m, int n, int k, int num_adapters) {
   w.perm = c.take<int32_t>(m);
   w.tiles = c.take<int32_t>(4 * static_cast<size_t>(mt));
   w.num_tiles = c.take<int32_t>(4);
+  w.sched = c.take<int32_t>(SCHED_WORDS);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * k);
   w.sx = c.take<float>(m);
   w.z_parts = c.take<uint16_t>(SKYRL_Z_PARTS * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
@@ -168,6 +162,7 @@ struct MlpWs {
   float* sh;
   int32_t* acc;  // int32 [m, max(2I, H)] accumulator, row-wise path only
   float* h_amax; // fp32 [m]: absmax of every row of h, collected by the gate_up epilogue
+  int32_t* sched; // tile-claim counters: words 0-1 gate_up GEMM, 2-3 down GEMM (zeroed by the routing kernel)
   size_t bytes;
 };
 
@@ -179,6 +174,7 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   (void)mt;
   w.tiles = c.take<int32_t>(4 * tile_buffer_slots(m, num_adapters));
   w.num_tiles = c.take<int32_t>(MAX_CHUNKS + 4);
+  w.sched = c.take<int32_t>(SCHED_WORDS);
   w.xq = c.take<int8_t>(static_cast<size_t>(m) * hidden);
   w.sx = c.take<float>(m);
   w.z_parts = c.take<uint16_t>(SKYRL_Z_PARTS * static_cast<size_t>(m) * SKYRL_LORA_RANK_PAD);
@@ -251,6 +247,7 @@ struct Projection {
   void* out;
   int64_t out_stride;
   int32_t* status;
+  int32_t* sched;         // {claimed, finished} words of the GEMM launch inside the caller's workspace
   void* ev_begin;
   void* ev_end;
 };
@@ -292,8 +289,8 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   SkyrlW8A8GemmArgs g = {};
   if (rows_path && lora && q.epilogue != SKYRL_EPI_ACC_I32) {
     float* z_rows = reinterpret_cast<float*>(q.z_parts);
-    if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.a_packed, q.scaling, q.rank, q.m, q.k,
-                                    q.xq, q.sx, z_rows, stream, pdl_enabled())))
+    if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.na, q.a_packed, q.scaling, q.rank, q.m,
+                                    q.k, q.xq, q.sx, z_rows, q.status, stream, true)))
       return rc;
     const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     g.struct_size = sizeof(g);
@@ -314,17 +311,18 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
     g.out = q.acc;
     g.out_row_stride = q.n;
     g.status = q.status;
+    g.sched = q.sched;
     if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
     // timing events between the launches would cut the programmatic chain: use ordinary launches then
-    const bool chain = pdl_enabled() && q.ev_begin == nullptr && q.ev_end == nullptr;
+    const bool chain = q.ev_begin == nullptr && q.ev_end == nullptr;
     rc = launch_gemm(g, stream, chain);
     if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
     if (rc) return rc;
     const bool dense = q.b_rows != nullptr;
     const int brow = dense ? q.b_rows_rank : SKYRL_LORA_RANK_PAD;
-    return launch_finalize_rows(q.epilogue, q.acc, slabs, q.sx, q.sw, z_rows, q.ids, dense ? q.b_rows : q.b_packed,
-                                static_cast<int64_t>(q.n) * brow, brow, q.rank, q.m, q.n, q.residual,
-                                q.residual_stride, q.out, q.out_stride, stream, chain);
+    return launch_finalize_rows(q.epilogue, q.acc, slabs, q.sx, q.sw, z_rows, q.ids, q.na,
+                                dense ? q.b_rows : q.b_packed, static_cast<int64_t>(q.n) * brow, brow, q.rank, q.m, q.n,
+                                q.residual, q.residual_stride, q.out, q.out_stride, q.status, stream, chain);
   }
   {
     if (!q.skip_quant && (rc = run_quant_stage(q, stream))) return rc;
@@ -351,6 +349,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   g.out_row_stride = q.out_stride;
   g.residual_row_stride = q.residual_stride;
   g.status = q.status;
+  g.sched = q.sched;
   g.cta_limit = q.cta_limit;
   if (q.row_amax != nullptr && q.epilogue == SKYRL_EPI_SWIGLU) {
     const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
@@ -412,7 +411,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   const bool routed = a->adapter_ids != nullptr && !rows_path;
 
   if ((rc = launch_route(routed ? a->adapter_ids : nullptr, a->m, na, w.perm, w.tiles, w.num_tiles, mt, a->status,
-                         stream)))
+                         stream, 0, 0, w.sched, SCHED_WORDS)))
     return rc;
   Projection q = {};
   q.x = a->x;
@@ -449,9 +448,35 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.out = a->out;
   q.out_stride = a->out_row_stride;
   q.status = a->status;
+  q.sched = w.sched;
   q.ev_begin = a->timing_events[0];
   q.ev_end = a->timing_events[1];
   return run_projection(q, stream);
+}
+
+// One exported target per fused variant: thin wrappers that check what the variant needs and fix the epilogue.
+extern "C" int skyrl_rms_gate_up_w8a8_lora_swiglu_sm100_v1(const SkyrlW8A8LinearArgs* a, skyrl_stream_t stream) {
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_gate_up_swiglu: args is null");
+  if (a->struct_size != sizeof(SkyrlW8A8LinearArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_gate_up_swiglu: struct_size %u does not match ABI v%d (%zu)",
+                a->struct_size, SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8LinearArgs));
+  if (a->residual != nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_gate_up_swiglu: takes no residual");
+  if (a->n % 2 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_gate_up_swiglu: n must count (gate, up) pairs");
+  SkyrlW8A8LinearArgs b = *a;
+  b.epilogue = SKYRL_EPI_SWIGLU;
+  return skyrl_w8a8_lora_forward_sm100_v1(&b, stream);
+}
+
+extern "C" int skyrl_down_w8a8_lora_residual_sm100_v1(const SkyrlW8A8LinearArgs* a, skyrl_stream_t stream) {
+  if (a == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "down_residual: args is null");
+  if (a->struct_size != sizeof(SkyrlW8A8LinearArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "down_residual: struct_size %u does not match ABI v%d (%zu)",
+                a->struct_size, SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8LinearArgs));
+  if (a->residual == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "down_residual: residual is null");
+  if (a->rms_delta != nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "down_residual: takes no RMSNorm weights");
+  SkyrlW8A8LinearArgs b = *a;
+  b.epilogue = SKYRL_EPI_RESIDUAL;
+  return skyrl_w8a8_lora_forward_sm100_v1(&b, stream);
 }
 
 namespace skyrl {
@@ -511,7 +536,8 @@ static int plan_mlp(const SkyrlW8A8MlpArgs* a, const char* who, MlpPlan* pl) {
 static int route_mlp(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl, cudaStream_t stream) {
   if ((a->flags & SKYRL_MLP_REUSE_ROUTING) != 0) return SKYRL_OK;
   return launch_route(pl.routed ? a->adapter_ids : nullptr, a->m, pl.na, pl.w.perm, pl.w.tiles, pl.w.num_tiles,
-                      static_cast<int>(tile_buffer_slots(a->m, pl.na)), a->status, stream, pl.chunk_rows, pl.chunk_cap);
+                      static_cast<int>(tile_buffer_slots(a->m, pl.na)), a->status, stream, pl.chunk_rows, pl.chunk_cap,
+                      pl.w.sched, SCHED_WORDS);
 }
 
 // front half: RMSNorm -> quant -> gate_up W8A8 LoRA -> SwiGLU; h keeps the row order of the GEMM
@@ -553,6 +579,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.out = w.h;
   q.out_stride = a->inter;
   q.status = a->status;
+  q.sched = w.sched;
   q.ev_begin = a->timing_events[0];
   q.ev_end = a->timing_events[1];
   return q;
@@ -575,9 +602,8 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   Projection q = front_projection(a, pl);
   q.skip_quant = prepared;
   // sorted route: the gate_up epilogue collects the absmax of every row of h, so that quantising h is one
-  // streaming pass (SKYRL_W8A8_DEBUG_NO_ROW_AMAX=1, a tuning aid, keeps the two-pass quantiser)
-  const char* no_amax = getenv("SKYRL_W8A8_DEBUG_NO_ROW_AMAX");
-  const bool collect = !pl.rows_path && !(no_amax != nullptr && atoi(no_amax) != 0);
+  // streaming pass (SKYRL_MLP_NO_ROW_AMAX keeps the two-pass quantiser; the two must agree bit for bit)
+  const bool collect = !pl.rows_path && (a->flags & SKYRL_MLP_NO_ROW_AMAX) == 0;
   q.row_amax = collect ? w.h_amax : nullptr;
   if ((rc = run_projection(q, stream))) return rc;
 
@@ -600,6 +626,7 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.scaling = a->dn_scaling;
   q.xq = w.hq;
   q.sx = w.sh;
+  q.sched = w.sched + 2;
   q.epilogue = a->down_epilogue;
   q.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : pl.perm;
   q.residual = a->residual != nullptr ? a->residual : a->x;
@@ -646,6 +673,19 @@ extern "C" int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32
   offsets[0] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.xq) - base);
   offsets[1] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.sx) - base);
   offsets[2] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.z_parts) - base);
+  return SKYRL_OK;
+}
+
+extern "C" int skyrl_w8a8_mlp_workspace_stage_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
+                                                       size_t* offsets) {
+  if (m <= 0 || hidden <= 0 || inter <= 0 || offsets == nullptr)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "workspace_stage_regions: bad argument");
+  unsigned char* const base = reinterpret_cast<unsigned char*>(static_cast<uintptr_t>(1024));
+  const MlpWs w = carve_mlp(base, m, hidden, inter, num_adapters > 0 ? num_adapters : 1);
+  offsets[0] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.perm) - base);
+  offsets[1] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.h) - base);
+  offsets[2] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.hq) - base);
+  offsets[3] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.sh) - base);
   return SKYRL_OK;
 }
 

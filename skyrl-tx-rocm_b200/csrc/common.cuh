@@ -43,13 +43,29 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   cfg.numAttrs = programmatic ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
-// SKYRL_W8A8_DEBUG_NO_PDL=1 turns programmatic launches off (tuning aid).
-bool pdl_enabled();
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of the function PER DEVICE
+// (a single process may drive several GPUs, as an XLA host does): `done` is the caller's
+// function-local `static bool[MAX_DEVICES]`, indexed by the current device.  A benign race only
+// repeats the idempotent call.
+constexpr int MAX_DEVICES = 64;
+template <typename Kernel>
+inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[MAX_DEVICES]) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= MAX_DEVICES) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (done[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done[dev] = true;
+  return e;
+}
 #endif
 
 // kernel launchers implemented in the .cu files
+// `zero_words` (nullable): `zero_count` int32 words the routing kernel clears (the workspace's tile-claim counters).
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
-                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0);
+                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0,
+                 int32_t* zero_words = nullptr, int zero_count = 0);
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
 // rows [m, k] contiguous (row pitch k) with their absmax known: codes and scales in one streaming pass
@@ -67,13 +83,14 @@ GemmPlan plan_gemm(int m, int n, int k, int epilogue, int max_slabs);
 constexpr int MAX_SPLIT_K_SLABS = 16;
 int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmatic = false);
 // `programmatic`: launch with programmatic stream serialization (small-batch chain of short kernels)
+// Adapter ids outside [0, num_adapters) are clamped and STATUS_BAD_ADAPTER_ID is recorded in `status`.
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
-                          const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
-                          float* z_rows, cudaStream_t stream, bool programmatic = false);
+                          int num_adapters, const void* a_packed, const float* scaling, int rank, int m, int k, void* xq,
+                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic = false);
 int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw, const float* z_rows,
-                         const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
-                         int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
-                         cudaStream_t stream, bool programmatic = false);
+                         const int32_t* ids, int num_adapters, const void* b_table, int64_t b_adapter_stride,
+                         int b_row_stride, int rank, int m, int n, const void* residual, int64_t res_stride, void* out,
+                         int64_t out_stride, int32_t* status, cudaStream_t stream, bool programmatic = false);
 int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* residual, void* out, int hidden,
                        int row_begin, int row_count, cudaStream_t stream, bool out_sorted = false);
 int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int32_t* perm, const void* residual,

@@ -216,15 +216,11 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
   p.row_hi = row_hi < 0 ? m : row_hi;
   p.status = status;
   p.k = k;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e =
-        cudaFuncSetAttribute(lora_a_proj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PROJ_SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static bool attr_set[MAX_DEVICES] = {};
+  cudaError_t e = ensure_dynamic_smem(lora_a_proj_kernel, PROJ_SMEM_BYTES, attr_set);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj attribute: %s", cudaGetErrorString(e));
   lora_a_proj_kernel<<<max_tiles, PROJ_THREADS, PROJ_SMEM_BYTES, stream>>>(p);
-  cudaError_t e = cudaPeekAtLastError();
+  e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }

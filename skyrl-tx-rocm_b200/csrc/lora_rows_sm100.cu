@@ -48,8 +48,9 @@ template <int R, int VMAX, bool PREFETCH_A>
 __global__ void __cluster_dims__(ROWQ_CLUSTER, 1, 1) __launch_bounds__(ROWQ_THREADS)
 rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
                       const __nv_bfloat16* __restrict__ delta, float eps, const int32_t* __restrict__ ids,
-                      const __nv_bfloat16* __restrict__ a_packed, const float* __restrict__ scaling, int k,
-                      int8_t* __restrict__ xq, float* __restrict__ sx, float* __restrict__ z_rows) {
+                      int num_adapters, const __nv_bfloat16* __restrict__ a_packed,
+                      const float* __restrict__ scaling, int k, int8_t* __restrict__ xq, float* __restrict__ sx,
+                      float* __restrict__ z_rows, int32_t* status) {
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[ROWQ_THREADS / 32];
   __shared__ float zwarp[ROWQ_THREADS / 32][R];
@@ -64,7 +65,12 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
   const int cnt = max(0, min(per, nvec - v0));
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(m) * x_row_stride) + v0;
   const bool norm = delta != nullptr;
-  const int adapter = ids != nullptr ? __ldg(ids + m) : 0;
+  // an id outside the tables is clamped (so that no load leaves them) and reported, as the routing kernel does
+  int adapter = ids != nullptr ? __ldg(ids + m) : 0;
+  if (adapter < 0 || adapter >= num_adapters) {
+    if (threadIdx.x == 0 && crank == 0) atomicCAS(status, 0, STATUS_BAD_ADAPTER_ID);
+    adapter = min(max(adapter, 0), num_adapters - 1);
+  }
   const uint4* a_base =
       reinterpret_cast<const uint4*>(a_packed + static_cast<int64_t>(adapter) * SKYRL_LORA_RANK_PAD * k) + v0;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -192,10 +198,10 @@ template <int EPI>
 __global__ void __launch_bounds__(256)
 finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_stride, const float* __restrict__ sx,
                      const float* __restrict__ sw,
-                     const float* __restrict__ z_rows, const int32_t* __restrict__ ids,
+                     const float* __restrict__ z_rows, const int32_t* __restrict__ ids, int num_adapters,
                      const __nv_bfloat16* __restrict__ b_table, int64_t b_adapter_stride, int b_row_stride,
                      int rank_vecs, int n, const __nv_bfloat16* __restrict__ residual, int64_t res_stride,
-                     void* __restrict__ out, int64_t out_stride) {
+                     void* __restrict__ out, int64_t out_stride, int32_t* status) {
   __shared__ float zs[SKYRL_LORA_RANK_PAD];
   const int m = blockIdx.y;
   if (rank_vecs > 0 && threadIdx.x < SKYRL_LORA_RANK_PAD)
@@ -209,7 +215,11 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
   const float2 w2 = __ldg(reinterpret_cast<const float2*>(sw + n0));
   float l0 = 0.f, l1 = 0.f;
   if (rank_vecs > 0) {
-    const int adapter = ids != nullptr ? ids[m] : 0;
+    int adapter = ids != nullptr ? ids[m] : 0;
+    if (adapter < 0 || adapter >= num_adapters) {  // clamped and reported, never used as an index
+      if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, STATUS_BAD_ADAPTER_ID);
+      adapter = min(max(adapter, 0), num_adapters - 1);
+    }
     const __nv_bfloat16* b0 = b_table + static_cast<int64_t>(adapter) * b_adapter_stride +
                               static_cast<int64_t>(n0) * b_row_stride;
     const uint4* r0 = reinterpret_cast<const uint4*>(b0);
@@ -262,23 +272,23 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
 
 template <int R, int VMAX, bool PREFETCH_A>
 static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
-                               const void* a_packed, const float* scaling, int m, int k, void* xq, float* sx,
-                               float* z_rows, cudaStream_t stream, bool programmatic) {
+                               int num_adapters, const void* a_packed, const float* scaling, int m, int k, void* xq,
+                               float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic) {
   cudaError_t e = launch_kernel(rms_quant_rows_kernel<R, VMAX, PREFETCH_A>, dim3(m * ROWQ_CLUSTER), dim3(ROWQ_THREADS), 0,
                                 stream, programmatic, static_cast<const __nv_bfloat16*>(x), x_row_stride,
-                                static_cast<const __nv_bfloat16*>(rms_delta), eps, ids,
+                                static_cast<const __nv_bfloat16*>(rms_delta), eps, ids, num_adapters,
                                 static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx,
-                                z_rows);
+                                z_rows, status);
   if (e == cudaSuccess) e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
 
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
-                          const void* a_packed, const float* scaling, int rank, int m, int k, void* xq, float* sx,
-                          float* z_rows, cudaStream_t stream, bool programmatic) {
+                          int num_adapters, const void* a_packed, const float* scaling, int rank, int m, int k, void* xq,
+                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic) {
   if (x == nullptr || xq == nullptr || sx == nullptr || a_packed == nullptr || scaling == nullptr ||
-      z_rows == nullptr || m <= 0 || k <= 0)
+      z_rows == nullptr || status == nullptr || m <= 0 || k <= 0 || num_adapters <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: null buffer or non-positive shape");
   if (k % 16 != 0) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: K must be a multiple of 16, got %d", k);
   if (x_row_stride < k || x_row_stride % 8 != 0)
@@ -291,8 +301,8 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
   if (rank <= 0 || rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
 #define SKYRL_ROWS(R, V, P) \
-  return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, a_packed, scaling, m, k, xq, sx, z_rows, stream, \
-                                      programmatic)
+  return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, num_adapters, a_packed, scaling, m, k, xq, sx, \
+                                      z_rows, status, stream, programmatic)
   if (per_cta <= 2 * ROWQ_THREADS) {
     if (rank <= 16) SKYRL_ROWS(16, 2, false);
     if (rank <= 32) SKYRL_ROWS(32, 2, false);
@@ -305,12 +315,12 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
 }
 
 int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw,
-                         const float* z_rows,
-                         const int32_t* ids, const void* b_table, int64_t b_adapter_stride, int b_row_stride, int rank,
-                         int m, int n, const void* residual, int64_t res_stride, void* out, int64_t out_stride,
-                         cudaStream_t stream, bool programmatic) {
-  if (acc == nullptr || sx == nullptr || sw == nullptr || out == nullptr || m <= 0 || n <= 0 || n % 2 != 0 ||
-      m > 65535)
+                         const float* z_rows, const int32_t* ids, int num_adapters, const void* b_table,
+                         int64_t b_adapter_stride, int b_row_stride, int rank, int m, int n, const void* residual,
+                         int64_t res_stride, void* out, int64_t out_stride, int32_t* status, cudaStream_t stream,
+                         bool programmatic) {
+  if (acc == nullptr || sx == nullptr || sw == nullptr || out == nullptr || status == nullptr || m <= 0 || n <= 0 ||
+      n % 2 != 0 || m > 65535 || num_adapters <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: null buffer or bad shape");
   if (rank > 0 && (z_rows == nullptr || b_table == nullptr || !aligned16(b_table) || b_row_stride % 8 != 0))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: LoRA operands missing or misaligned");
@@ -323,8 +333,8 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
   cudaError_t le = cudaSuccess;
 #define SKYRL_FINALIZE(E)                                                                                            \
   le = launch_kernel(finalize_rows_kernel<E>, grid, dim3(256), 0, stream, programmatic, acc, slabs,                  \
-                     static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, bt, b_adapter_stride, b_row_stride, rank_vecs, \
-                     n, res, res_stride, out, out_stride)
+                     static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, num_adapters, bt, b_adapter_stride, b_row_stride, \
+                     rank_vecs, n, res, res_stride, out, out_stride, status)
   switch (epilogue) {
     case SKYRL_EPI_LINEAR: SKYRL_FINALIZE(SKYRL_EPI_LINEAR); break;
     case SKYRL_EPI_SWIGLU: SKYRL_FINALIZE(SKYRL_EPI_SWIGLU); break;

@@ -23,10 +23,11 @@ constexpr int ROUTE_MAX_ADAPTERS = 4096;
 __global__ void __launch_bounds__(ROUTE_THREADS)
 route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* __restrict__ perm,
              int32_t* __restrict__ tiles, int32_t* __restrict__ num_tiles, int max_tiles, int chunk_rows,
-             int chunk_cap, int32_t* status) {
+             int chunk_cap, int32_t* status, int32_t* __restrict__ zero_words, int zero_count) {
   __shared__ int counts[ROUTE_MAX_ADAPTERS];
   __shared__ int cursor[ROUTE_MAX_ADAPTERS];
   const int tid = threadIdx.x;
+  if (zero_words != nullptr && tid < zero_count) zero_words[tid] = 0;
   const int num_chunks = chunk_rows > 0 ? (m + chunk_rows - 1) / chunk_rows : 1;
   const int cap = chunk_rows > 0 ? chunk_cap : max_tiles;
   const int span = chunk_rows > 0 ? chunk_rows : m;
@@ -129,7 +130,8 @@ route_kernel(const int32_t* __restrict__ ids, int m, int num_adapters, int32_t* 
 }
 
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
-                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows, int chunk_cap) {
+                 int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows, int chunk_cap, int32_t* zero_words,
+                 int zero_count) {
   if (m <= 0 || perm == nullptr || tiles == nullptr || num_tiles == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: m must be positive and perm/tiles/num_tiles/status non-null");
   if (ids != nullptr && (num_adapters <= 0 || num_adapters > ROUTE_MAX_ADAPTERS))
@@ -141,8 +143,10 @@ int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: chunk_rows must be a multiple of %d", SKYRL_TILE_ROWS);
   if (chunk_rows > 0 && static_cast<int64_t>((m + chunk_rows - 1) / chunk_rows) * chunk_cap > max_tiles)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: chunk lists do not fit in max_tiles");
+  if (zero_count < 0 || zero_count > ROUTE_THREADS)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "route: at most %d words can be cleared", ROUTE_THREADS);
   route_kernel<<<1, ROUTE_THREADS, 0, stream>>>(ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, chunk_rows,
-                                                chunk_cap, status);
+                                                chunk_cap, status, zero_words, zero_count);
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "route launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
@@ -262,16 +266,13 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
   if (x == xq || x == xn) return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant: inputs and outputs must not alias");
   const size_t smem = static_cast<size_t>(k) * 2;
   if (smem > 200 * 1024) return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant: K=%d exceeds the staged-row limit", k);
-  static bool attr_set = false;  // idempotent; a benign race only repeats the call
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(rms_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static bool attr_set[MAX_DEVICES] = {};
+  cudaError_t e = ensure_dynamic_smem(rms_quant_kernel, 200 * 1024, attr_set);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant attribute: %s", cudaGetErrorString(e));
   rms_quant_kernel<<<m, QUANT_THREADS, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(x), x_row_stride, static_cast<const __nv_bfloat16*>(rms_delta), eps, row_map,
       k, static_cast<int8_t*>(xq), sx, static_cast<__nv_bfloat16*>(xn));
-  cudaError_t e = cudaPeekAtLastError();
+  e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
@@ -658,7 +659,7 @@ extern "C" int skyrl_lora_route_sm100_v1(const int32_t* adapter_ids, int32_t m, 
                                          int32_t* tiles, int32_t* num_tiles, int32_t max_tiles, int32_t* status,
                                          skyrl_stream_t stream) {
   return launch_route(adapter_ids, m, num_adapters, perm, tiles, num_tiles, max_tiles, status,
-                      static_cast<cudaStream_t>(stream), 0, 0);
+                      static_cast<cudaStream_t>(stream), 0, 0, nullptr, 0);
 }
 
 extern "C" int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, const void* rms_delta, float eps,

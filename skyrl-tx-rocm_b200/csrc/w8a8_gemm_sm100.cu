@@ -10,7 +10,8 @@
 // Roles (320 threads): warps 0-3 and 6-9 drain TMEM (warp w owns TMEM lanes
 // 32 (w % 4) .. +31; the two warps of a lane quadrant split the tile's columns,
 // and two warps per scheduler hide each other's latencies in the SwiGLU math),
-// warp 4 is the TMA producer, warp 5 issues the MMAs and owns the TMEM allocation.  Two accumulator stages of BN columns let the epilogue of tile t
+// warp 4 is the TMA producer, warp 5 issues the MMAs and owns the TMEM
+// allocation.  Two accumulator stages of BN columns let the epilogue of tile t
 // overlap the main loop of tile t+1.  The LoRA term does not get accumulator
 // columns of its own (2 x 256 int32 columns already fill the 512-column TMEM):
 // the epilogue rewrites the int32 accumulator in place as dequantised fp32,
@@ -22,7 +23,8 @@
 // pipeline depth (the main loop is bound by bytes in flight per SM).
 //
 // Rows live in the adapter-sorted space: every 128-row M tile comes from the
-// tile list and holds rows of one adapter; rows past the tile's count are
+// tile list and holds rows of at most two adapters (each row's z is zero in the
+// slot of the adapter that is not its own); rows past the tile's count are
 // computed but never stored.  Every wait is bounded (see ptx_sm100.cuh).
 #include <stdlib.h>
 
@@ -983,14 +985,11 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
 template <int EPI, bool HAS_LORA>
 static int launch_pair_variant(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kernel = w8a8_gemm_pair_kernel<EPI, HAS_LORA>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
+  static bool attr_set[MAX_DEVICES] = {};
+  cudaError_t e = ensure_dynamic_smem(kernel, PAIR_SMEM_BYTES, attr_set);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
   kernel<<<grid, PAIR_THREADS, PAIR_SMEM_BYTES, stream>>>(p);
-  cudaError_t e = cudaPeekAtLastError();
+  e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
 }
@@ -1020,13 +1019,10 @@ template <int BN, int EPI, bool HAS_LORA>
 static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream, bool programmatic) {
   using Cfg = GemmCfg<BN>;
   auto kernel = w8a8_gemm_kernel<BN, EPI, HAS_LORA>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
-    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
-    attr_set = true;
-  }
-  cudaError_t e = launch_kernel(kernel, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, programmatic, p);
+  static bool attr_set[MAX_DEVICES] = {};
+  cudaError_t e = ensure_dynamic_smem(kernel, Cfg::SMEM_BYTES, attr_set);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
+  e = launch_kernel(kernel, dim3(grid), dim3(GEMM_THREADS), Cfg::SMEM_BYTES, stream, programmatic, p);
   if (e == cudaSuccess) e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
@@ -1146,12 +1142,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
   const GemmPlan pl = plan_gemm(a.m, a.n, a.k, a.epilogue, a.split_k_slabs);
   const int mt_est = (a.m + BM - 1) / BM;
-  int bn_eff = pl.bn_eff;
+  const int bn_eff = pl.bn_eff;
   const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
-  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_BN")) {  // tuning aid: force the N tile width
-    const int v = atoi(dbg);
-    if (v >= 16 && v <= 256 && v % 16 == 0) bn_eff = v;
-  }
   const int bn = bn_eff > 128 ? 256 : 128;
 
   GemmParams p;
@@ -1218,13 +1210,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
     p.row_amax = a.row_amax;
   }
   p.direct_stores = 0;
-  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_DIRECT_STORES")) p.direct_stores = atoi(dbg) != 0;  // tuning aid
   if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
-  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_STAGES")) {  // tuning aid: cap the pipeline depth
-    const int v = atoi(dbg);
-    if (v >= 2 && v < p.num_stages) p.num_stages = v;
-  }
-  p.sched = next_sched_counter();
+  p.sched = a.sched != nullptr ? a.sched : next_sched_counter();
   if (p.sched == nullptr) return fail(SKYRL_ERR_LAUNCH, "gemm: scheduler counters unavailable");
   p.k_splits = k_splits;
   p.kb_per_split = kb_per_split;
@@ -1236,9 +1223,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   // the next main loop, so this pays only when the K loop dwarfs it (measured: gain at K = 25600, loss at 5120).
   // Not with a row scatter: the pair's epilogue stores 16 bytes per row from registers, which NVLink carries
   // poorly; the single-tile kernel writes whole 128-byte lines through its staging tiles.
-  bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
+  const bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
                 static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
-  if (const char* dbg = getenv("SKYRL_W8A8_DEBUG_PAIR")) paired = paired && atoi(dbg) != 0;  // tuning aid
   if (paired) {
     const int64_t pair_total = static_cast<int64_t>((a.max_tiles + 1) / 2) * ((a.n + 255) / 256);
     int pgrid = static_cast<int>(pair_total < sms ? pair_total : sms);

@@ -31,7 +31,8 @@ __all__ = (
     "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
-    "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "chunk_rows",
+    "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "w8a8_mlp_stage_regions",
+    "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
     "check_status", "bounded_wait_selftest", "RMS_EPS",
 )
@@ -462,7 +463,13 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
     a.status = st.data_ptr()
     if timing_events is not None:
         a.timing_events[0], a.timing_events[1] = timing_events[0].cuda_event, timing_events[1].cuda_event
-    _lib.check(lib.skyrl_w8a8_lora_forward_sm100_v1(C.byref(a), _stream()), "w8a8_lora_forward")
+    # every fused variant has its own exported target (one symbol per operator, as a custom-call layer binds them)
+    if epilogue == EPI_SWIGLU:
+        _lib.check(lib.skyrl_rms_gate_up_w8a8_lora_swiglu_sm100_v1(C.byref(a), _stream()), "rms_gate_up_w8a8_lora_swiglu")
+    elif epilogue == EPI_RESIDUAL:
+        _lib.check(lib.skyrl_down_w8a8_lora_residual_sm100_v1(C.byref(a), _stream()), "down_w8a8_lora_residual")
+    else:
+        _lib.check(lib.skyrl_w8a8_lora_forward_sm100_v1(C.byref(a), _stream()), "w8a8_lora_forward")
     return out
 
 
@@ -578,7 +585,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    down_weight: PackedW8Weight, down_lora: PackedLoRA | None, adapter_ids=None, *, residual=None,
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
-                   gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None):
+                   gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
+                   row_amax_from_epilogue: bool = True):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -590,7 +598,9 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     (`w8a8_mlp_workspace_regions`) already hold that stage's results.
     `scatter=(rows_per_owner, [address of owner 0's slab, ...])` makes the down
     GEMM store each owner's rows of the fp32 partial sums straight into that
-    owner's slab (device addresses, possibly peer mappings) instead of `out`."""
+    owner's slab (device addresses, possibly peer mappings) instead of `out`.
+    `row_amax_from_epilogue=False` makes the quantiser of h find the row absmax itself (a cross-check:
+    both forms give identical bits)."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
         raise RuntimeError("the W8A8 MLP block is disabled by default")
@@ -655,6 +665,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         a.flags |= _lib.MLP_REUSE_ROUTING
     if input_prepared:
         a.flags |= _lib.MLP_INPUT_PREPARED
+    if not row_amax_from_epilogue:
+        a.flags |= _lib.MLP_NO_ROW_AMAX
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)
@@ -740,6 +752,23 @@ def w8a8_mlp_workspace_regions(m: int, hidden: int, inter: int, num_adapters: in
     sx = ws[off[1]: off[1] + 4 * m].view(torch.float32)
     z = ws[off[2]: off[2] + m * Z_PARTS * LORA_RANK_PAD * 2].view(torch.bfloat16).view(m, Z_PARTS * LORA_RANK_PAD)
     return xq, sx, z
+
+
+def w8a8_mlp_stage_regions(m: int, hidden: int, inter: int, num_adapters: int, device):
+    """Views of what the last `w8a8_mlp_block` call of these sizes left in the workspace, for stage-by-stage
+    checks: (perm int32 [m], h bf16 [m, inter], codes of h int8 [m, inter], scales of h fp32 [m]).  h and its
+    codes are in the GEMM's row order: adapter-sorted (row i = token perm[i]) for m > 128 with adapter
+    ids, token order otherwise."""
+    lib = _lib.load()
+    na = max(int(num_adapters), 1)
+    ws = _workspace(device, lib.skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na))
+    off = (C.c_size_t * 4)()
+    _lib.check(lib.skyrl_w8a8_mlp_workspace_stage_regions(m, hidden, inter, na, off), "w8a8_mlp_workspace_stage_regions")
+    perm = ws[off[0]: off[0] + 4 * m].view(torch.int32)
+    h = ws[off[1]: off[1] + 2 * m * inter].view(torch.bfloat16).view(m, inter)
+    hq = ws[off[2]: off[2] + m * inter].view(torch.int8).view(m, inter)
+    sh = ws[off[3]: off[3] + 4 * m].view(torch.float32)
+    return perm, h, hq, sh
 
 
 # --------------------------------------------------------------------------- #

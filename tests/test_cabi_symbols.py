@@ -44,14 +44,34 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert loaded.skyrl_w8a8_abi_version() == 1
 
 
+def test_header_is_plain_c_and_size_queries_run_without_a_gpu():
+    # csrc/abi_check.c includes the public header as C11 (-Wall -Wextra -Werror -pedantic, so the
+    # _Static_assert layout checks are evaluated by a C compiler) and calls the size queries
+    import subprocess
+
+    from skyrl_tx_rocm_b200 import _lib
+
+    exe = _lib.LIB_PATH.parent / "abi_check"
+    assert exe.exists(), "build.py did not produce the C-ABI check"
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "abi=1" in res.stdout and "rc=-1" in res.stdout
+
+
+def test_header_asserts_struct_layouts():
+    text = HEADER.read_text()
+    for name in ("SkyrlW8A8GemmArgs", "SkyrlW8A8LinearArgs", "SkyrlW8A8MlpArgs"):
+        assert f"SKYRL_ABI_ASSERT(sizeof({name})" in text and f"offsetof({name}," in text
+
+
 def test_struct_sizes_are_stable():
     from skyrl_tx_rocm_b200 import _lib
 
     # Natural alignment, no packing: these sizes are part of ABI v1 and are
     # checked against struct_size by every entry point.
-    assert ctypes.sizeof(_lib.GemmArgs) == 32 + 11 * 8 + 2 * 8 + 8 + 8 + 8 * 8 + 8 + 8
-    assert ctypes.sizeof(_lib.LinearArgs) == 32 + 3 * 8 + 8 + 7 * 8 + 8 + 8 + 8 + 8 + 8 + 8 + 2 * 8 + 16
-    assert ctypes.sizeof(_lib.MlpArgs) == 32 + 18 * 8 + 4 * 8 + 8 + 16 + 16 + 8 * 8
+    assert ctypes.sizeof(_lib.GemmArgs) == 32 + 11 * 8 + 2 * 8 + 8 + 8 + 8 * 8 + 8 + 8 + 8 == 240
+    assert ctypes.sizeof(_lib.LinearArgs) == 32 + 3 * 8 + 8 + 7 * 8 + 8 + 8 + 8 + 8 + 8 + 8 + 2 * 8 + 16 == 200
+    assert ctypes.sizeof(_lib.MlpArgs) == 32 + 18 * 8 + 4 * 8 + 8 + 16 + 16 + 8 * 8 == 312
 
 
 def test_disabled_by_default_and_exact_bool():

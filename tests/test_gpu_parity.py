@@ -416,11 +416,7 @@ def test_row_absmax_from_epilogue_equals_two_pass_quantiser(S, m, hidden, inter,
     lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
     ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
     xd, dd, idd = to_dev(x), to_dev(delta), to_dev(ids)
-    os.environ["SKYRL_W8A8_DEBUG_NO_ROW_AMAX"] = "1"
-    try:
-        want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True).clone()
-    finally:
-        del os.environ["SKYRL_W8A8_DEBUG_NO_ROW_AMAX"]
+    want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, row_amax_from_epilogue=False).clone()
     got = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True)
     S.check_status()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))

@@ -118,32 +118,77 @@ class ClockSampler:
 # --------------------------------------------------------------------------- #
 # synthetic, seeded inputs (generated on the device in the packed layout)
 # --------------------------------------------------------------------------- #
-def synth_weight(S, torch, n, k, seed, device):
-    """W ~ N(0, 0.02) bf16 [n, k], per-output-channel absmax int8 (quantized_lora.py:150-171 with group = K)."""
+def full_weight(torch, n, k, seed, device):
+    """W ~ N(0, 0.02) bf16 [n, k] ([out, in]), the whole projection from ONE seed (every tensor-parallel rank
+    draws the same matrix and cuts its shard from it, so that all GPU counts compute the same model)."""
     gen = torch.Generator(device=device).manual_seed(seed)
-    wq = torch.empty((n, k), dtype=torch.int8, device=device)
-    sw = torch.empty((n,), dtype=torch.float32, device=device)
+    w = torch.empty((n, k), dtype=torch.bfloat16, device=device)
     rows = max(1, (64 << 20) // k)
     for r0 in range(0, n, rows):
         r1 = min(n, r0 + rows)
-        w = (torch.randn((r1 - r0, k), generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16).float()
-        amax = w.abs().amax(dim=1)
-        scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
-        wq[r0:r1] = torch.clamp(torch.round(w / scale[:, None]), -127, 127).to(torch.int8)
+        w[r0:r1] = (torch.randn((r1 - r0, k), generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    return w
+
+
+def quantize_nk(torch, w):
+    """Per-output-channel absmax int8 of a bf16 [n, k] matrix (quantized_lora.py:150-171 with one group over
+    all of K: codes from the fp32 scale, stored scale rounded to bf16).  Returns (codes int8 [n, k], fp32 [n])."""
+    n, k = w.shape
+    wq = torch.empty((n, k), dtype=torch.int8, device=w.device)
+    sw = torch.empty((n,), dtype=torch.float32, device=w.device)
+    rows = max(1, (64 << 20) // k)
+    for r0 in range(0, n, rows):
+        r1 = min(n, r0 + rows)
+        wf = w[r0:r1].float()
+        amax = wf.abs().amax(dim=1)
+        qmax = torch.full((), 127.0, dtype=torch.float32, device=w.device)   # tensor divisor: a true fp32 division
+        scale = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
+        wq[r0:r1] = torch.clamp(torch.round(wf / scale[:, None]), -127, 127).to(torch.int8)
         sw[r0:r1] = scale.to(torch.bfloat16).float()
-    return S.pack_weight_nk(wq, sw)
+    return wq, sw
 
 
-def synth_lora(S, torch, adapters, k, rank, n, alpha, seed, device, seed_b=None):
-    """`seed_b` seeds B separately: a tensor-parallel rank shares the replicated half of a LoRA pair with the
-    other ranks (A of gate_up, B of down) and draws only its shard of the other half from its own seed."""
+def synth_weight(S, torch, n, k, seed, device, keep_host=False):
+    """Packed per-output-channel W8 weight of a seeded [n, k] matrix; with `keep_host` also the oracle's view of
+    it (codes [K, N], bf16 scales [1, N]) for the parity check."""
+    wq, sw = quantize_nk(torch, full_weight(torch, n, k, seed, device))
+    packed = S.pack_weight_nk(wq, sw)
+    return (packed, host_weight(torch, [wq], [sw])) if keep_host else packed
+
+
+def host_weight(torch, codes_nk_groups, scales_groups):
+    """Oracle storage (quantized_lora.py:20-41) of a weight given as K groups of [n, k_g] codes with fp32 [n]
+    scales each: codes int8 [K, N], scales bf16 [groups, N], group_size = k_g."""
+    import ml_dtypes
+    import numpy as np
+
+    from oracle import w8a8_oracle as O
+
+    codes = np.concatenate([c.t().contiguous().cpu().numpy() for c in codes_nk_groups], axis=0)
+    scales = np.stack([s_.cpu().numpy() for s_ in scales_groups], axis=0).astype(ml_dtypes.bfloat16)
+    k = codes.shape[0]
+    return O.GroupQuantizedWeight(codes, scales, k, k, 8, k // len(codes_nk_groups))
+
+
+def synth_lora(S, torch, adapters, k, rank, n, alpha, seed, device, rows=None, cols=None, keep_host=False):
+    """LoRA tables A [adapters, k, rank] ~ N(0, 1/sqrt(k)), B [adapters, rank, n] ~ N(0, 0.02) from one seed.
+    A tensor-parallel rank keeps rows [rows[0], rows[1]) of A's K axis or columns [cols[0], cols[1]) of B's N
+    axis (skyrl/tx/layers/lora.py:264-265: A follows the in-feature sharding, B the out-feature sharding)."""
     gen = torch.Generator(device=device).manual_seed(seed)
     a = (torch.randn((adapters, k, rank), generator=gen, device=device) / (k ** 0.5)).to(torch.bfloat16)
-    if seed_b is not None:
-        gen = torch.Generator(device=device).manual_seed(seed_b)
     b = (torch.randn((adapters, rank, n), generator=gen, device=device) * 0.02).to(torch.bfloat16)
     s = torch.full((adapters,), alpha / rank, dtype=torch.float32, device=device)
-    return S.pack_lora(a, b, s, in_features=k, padded_out_features=n)
+    host = None
+    if keep_host:
+        import ml_dtypes
+
+        bf16 = ml_dtypes.bfloat16
+        host = (a.cpu().view(torch.uint16).numpy().view(bf16), b.cpu().view(torch.uint16).numpy().view(bf16),
+                s.cpu().numpy())
+    a_sh = a[:, rows[0]:rows[1]].contiguous() if rows is not None else a
+    b_sh = b[:, :, cols[0]:cols[1]].contiguous() if cols is not None else b
+    packed = S.pack_lora(a_sh, b_sh, s, in_features=a_sh.shape[1], padded_out_features=b_sh.shape[2])
+    return (packed, host) if keep_host else packed
 
 
 def synth_ids(torch, m, adapters, mode, seed):
@@ -159,7 +204,26 @@ def synth_ids(torch, m, adapters, mode, seed):
 # --------------------------------------------------------------------------- #
 # the device arm
 # --------------------------------------------------------------------------- #
-def run_device(args):
+def load_traffic(workload, m):
+    """DRAM bytes of one launch of the dominant kernel, from a committed ncu capture (profiles/gemm_traffic.json:
+    dram__bytes_read.sum + dram__bytes_write.sum of one launch at `m` rows, scaled by the rows when the bench
+    runs more, which every term of the traffic grows with).  None when no capture of this workload is committed."""
+    path = os.path.join(ROOT, "profiles", "gemm_traffic.json")
+    if not os.path.exists(path):
+        return None, None
+    try:
+        with open(path) as f:
+            entry = json.load(f).get(workload)
+    except (OSError, ValueError):
+        return None, None
+    if not entry:
+        return None, None
+    scale = m / entry["m"]
+    note = f"ncu capture at M={entry['m']}" + ("" if scale == 1 else f", scaled by {scale:g} (rows)")
+    return (entry["dram_bytes_read"] + entry["dram_bytes_write"]) * scale, note
+
+
+def init_distributed(args):
     import torch
 
     rank = int(os.environ.get("RANK", "0"))
@@ -179,13 +243,36 @@ def run_device(args):
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
             del os.environ["NCCL_DEBUG"]  # its banner goes to stdout; this program prints exactly one JSON line
         dist.init_process_group("nccl", device_id=device)
+    return rank, local_rank, world, device, dist
+
+
+def run_device(args):
+    rank, local_rank, world, device, dist = init_distributed(args)
+    line, ok = measure(args, args.workload, args.steps, rank, local_rank, world, device, dist)
+    if rank == 0 and world == 1 and args.workload == "c5" and not args.no_decode:
+        # the HBM-bound decode configuration beside the tensor-bound headline, outside its timed region
+        sub, sub_ok = measure(args, "c2", max(args.steps, 300), rank, local_rank, world, device, dist, sub=True)
+        line["decode"] = {k_: sub[k_] for k_ in ("value", "unit", "ms_per_step", "steps", "config", "roofline", "clocks",
+                                                 "e2e", "gpu_launches", "parity")}
+        ok = ok and sub_ok
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    if not ok:
+        raise SystemExit(3)   # the line above says which parity check failed
+
+
+def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=False):
+    """Build one workload, check it against the oracle on sampled rows, time it.  Returns (line dict, parity ok)."""
+    import torch
 
     import skyrl_tx_rocm_b200 as S
 
-    wl = dict(WORKLOADS[args.workload])
-    if args.m:
+    wl = dict(WORKLOADS[workload])
+    if args.m and not sub:
         wl["m"] = args.m
-    if args.layers:
+    if args.layers and not sub:
         wl["layers"] = args.layers
     kind, m, layers = wl["kind"], wl["m"], wl["layers"]
     tp = world
@@ -193,36 +280,64 @@ def run_device(args):
         raise SystemExit("tensor parallelism is benchmarked on the MLP workloads (c5, c2)")
     peaks = load_peaks()
     alpha = 2.0 * wl["rank"]
+    want_parity = not args.no_parity
 
     # ---------------- build the workload ----------------
     ids_host = synth_ids(torch, m, wl["adapters"], wl["ids"], 7)
     ids = ids_host.to(device) if ids_host is not None else None
+    ids_np = ids_host.numpy() if ids_host is not None else None
     gen = torch.Generator(device=device).manual_seed(11)
+    parity_inputs = None
     if kind == "mlp":
         hidden, inter = wl["hidden"], wl["inter"]
         if inter % tp or (inter // tp) % 16:
             raise SystemExit("intermediate size must split into multiples of 16 per rank")
         ish = inter // tp
+        lo, hi = rank * ish, (rank + 1) * ish
         x_host = torch.randn((m, hidden), generator=torch.Generator().manual_seed(5), dtype=torch.float32).to(torch.bfloat16).pin_memory()
         blocks = []
         for l in range(layers):
-            seed = (5000 if args.workload == "c5" else 1000) + l
+            seed = ((5000 if workload == "c5" else 1000) + l) * 131
+            keep = want_parity and l == 0 and rank == 0
             delta = (torch.randn((hidden,), generator=gen, device=device) * 0.02).to(torch.bfloat16)
-            gu_w = synth_weight(S, torch, 2 * ish, hidden, seed * 131 + rank * 7 + 1, device)
-            dn_w = synth_weight(S, torch, hidden, ish, seed * 131 + rank * 7 + 2, device)
-            gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * ish, alpha, seed * 131 + 3, device,
-                              seed_b=seed * 131 + rank * 7 + 3)
-            dn_l = synth_lora(S, torch, wl["adapters"], ish, wl["rank"], hidden, alpha, seed * 131 + rank * 7 + 4, device,
-                              seed_b=seed * 131 + 4)
+            # ONE seeded full weight per projection; a rank keeps gate/up pairs [lo, hi) (rows 2 lo .. 2 hi of the
+            # interleaved [2I, H] matrix) and columns [lo, hi) of down's [H, I], quantised over its own K slice
+            w_full = full_weight(torch, 2 * inter, hidden, seed + 1, device)
+            gq, gs = quantize_nk(torch, w_full[2 * lo:2 * hi])
+            gu_w = S.pack_weight_nk(gq, gs)
+            gu_host = None
+            if keep:
+                gu_host = host_weight(torch, [gq], [gs]) if tp == 1 else host_weight(torch, *[[t] for t in quantize_nk(torch, w_full)])
+            del w_full, gq, gs
+            w_full = full_weight(torch, hidden, inter, seed + 2, device)
+            dq, ds = quantize_nk(torch, w_full[:, lo:hi].contiguous())
+            dn_w = S.pack_weight_nk(dq, ds)
+            dn_host = None
+            if keep:
+                shards = [quantize_nk(torch, w_full[:, r * ish:(r + 1) * ish].contiguous()) for r in range(tp)] if tp > 1 else [(dq, ds)]
+                dn_host = host_weight(torch, [c for c, _ in shards], [s_ for _, s_ in shards])
+                del shards
+            del w_full, dq, ds
+            gu_l = synth_lora(S, torch, wl["adapters"], hidden, wl["rank"], 2 * inter, alpha, seed + 3, device,
+                              cols=(2 * lo, 2 * hi), keep_host=keep)
+            dn_l = synth_lora(S, torch, wl["adapters"], inter, wl["rank"], hidden, alpha, seed + 4, device,
+                              rows=(lo, hi), keep_host=keep)
+            if keep:
+                parity_inputs = dict(delta=delta, gate_up=(gu_host, gu_w, gu_l[1], gu_l[0]), down=(dn_host, dn_w, dn_l[1], dn_l[0]))
+                gu_l, dn_l = gu_l[0], dn_l[0]
             blocks.append((delta, gu_w, gu_l, dn_w, dn_l))
+            torch.cuda.empty_cache()
         tp_stack = None
         if tp > 1:
             from skyrl_tx_rocm_b200.tp import TensorParallelMLP, TensorParallelMLPStack
 
-            tp_stack = TensorParallelMLPStack([TensorParallelMLP(*b) for b in blocks], num_chunks=args.tp_chunks,
+            def make_stack(blks):
+                return TensorParallelMLPStack([TensorParallelMLP(*b) for b in blks], num_chunks=args.tp_chunks,
                                               reserve_sms=args.tp_reserve_sms,
                                               sequence_parallel=bool(args.tp_sequence_parallel),
                                               peer_scatter=False if args.tp_peer_scatter == "off" else args.tp_peer_scatter)
+
+            tp_stack = make_stack(blocks)
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
@@ -243,12 +358,12 @@ def run_device(args):
         h2d = x_host.numel() * 2 + (ids_host.numel() * 4 * tp if ids_host is not None else 0)
         d2h = m * hidden * 2
         out_host = torch.empty((m, hidden), dtype=torch.bfloat16).pin_memory()
-        # per layer: 2 quantiser, 2 LoRA-A / LoRA-B-rows, 2 GEMM launches (+ finalize under TP); one routing launch per step
         if tp > 1 and m > 128:
             # per layer and row chunk: quantiser of h, LoRA-A of h, two GEMMs, finalize, next layer's quantiser and
             # LoRA-A projection of the own rows; one routing launch and one row un-sort per step
             launches_per_step = layers * args.tp_chunks * 7 + 2
         else:
+            # per layer: two quantiser launches, two LoRA-A (or LoRA-B row) launches, two GEMMs; one routing launch
             launches_per_step = layers * 6 + 1
 
         def step(x_in, ids_in, events=None):
@@ -271,8 +386,10 @@ def run_device(args):
             x_host = torch.nn.functional.silu(x_host) * g
         x_host = x_host.to(torch.bfloat16).pin_memory()
         x_dev = x_host.to(device)
-        w = synth_weight(S, torch, n, k, 3 if kind == "gate_up" else 4, device)
-        lora = synth_lora(S, torch, wl["adapters"], k, wl["rank"], n, alpha, 9, device)
+        w = synth_weight(S, torch, n, k, 3 if kind == "gate_up" else 4, device, keep_host=want_parity)
+        lora = synth_lora(S, torch, wl["adapters"], k, wl["rank"], n, alpha, 9, device, keep_host=want_parity)
+        if want_parity:
+            (w, w_host), (lora, lora_host) = w, lora
         delta = (torch.randn((k,), generator=gen, device=device) * 0.02).to(torch.bfloat16) if kind == "gate_up" else None
         res_host = torch.randn((m, n), generator=torch.Generator().manual_seed(8), dtype=torch.float32).to(torch.bfloat16).pin_memory() if kind == "down" else None
         res_dev = res_host.to(device) if res_host is not None else None
@@ -310,6 +427,13 @@ def run_device(args):
             evs.append(quad)
         return evs
 
+    # ---------------- parity of the timed configuration, before anything is timed ----------------
+    parity, ok = None, True
+    if want_parity:
+        parity, ok = parity_check(S, torch, dist, workload, wl, tp, rank, device, x_dev, ids, ids_np, parity_inputs,
+                                  locals())
+    parity_inputs = None
+
     # ---------------- warm-up ----------------
     for _ in range(max(args.warmup, 3)):
         step(x_dev, ids)
@@ -336,7 +460,8 @@ def run_device(args):
         torch.cuda.synchronize()
 
     # ---------------- timed region: inputs resident in HBM ----------------
-    step_events = [make_events() for _ in range(args.steps)]
+    event_steps = min(steps, 20)   # per-kernel events of the first steps only (a decode run has hundreds of steps)
+    step_events = [make_events() for _ in range(event_steps)]
     torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -345,11 +470,11 @@ def run_device(args):
     t_begin = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
     t_begin.record()
-    for i in range(args.steps):
+    for i in range(steps):
         if graph is not None:
             graph.replay()
         else:
-            step(x_dev, ids, step_events[i])
+            step(x_dev, ids, step_events[i] if i < event_steps else None)
     t_end.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -357,20 +482,20 @@ def run_device(args):
     S.check_status(device)
     if graph is not None:
         # per-kernel durations cannot be read from events inside a graph: take them from an eager pass
-        for i in range(args.steps):
+        for i in range(event_steps):
             step(x_dev, ids, step_events[i])
         torch.cuda.synchronize()
     if dist is not None:
         t = torch.tensor([elapsed_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = elapsed_ms / steps
     gu_ms = [q[0].elapsed_time(q[1]) for evs in step_events for q in evs]
     dn_ms = [q[2].elapsed_time(q[3]) for evs in step_events for q in evs] if kind == "mlp" else gu_ms
     gu_avg, dn_avg = sum(gu_ms) / len(gu_ms), sum(dn_ms) / len(dn_ms)
 
     # ---------------- end to end: host buffers, copies inside the timed region ----------------
-    e2e_steps = max(2, min(args.steps, 5))
+    e2e_steps = max(2, min(steps, 5)) if m > 128 else min(steps, 50)
 
     def e2e_once():
         if graph is not None:
@@ -412,43 +537,41 @@ def run_device(args):
     S.check_status(device)
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
-        return
+        return None, ok
 
     tokens_per_s = m / (ms_per_step * 1e-3)
     i8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     if wl["bound"] == "tensor":
         achieved = gu_ops_launch / (gu_avg * 1e-3) / 1e12
+        traffic, traffic_note = load_traffic(workload, m_launch if kind == "mlp" else m) if tp == 1 else (None, None)
         roofline = dict(bound="tensor", kernel="w8a8_gemm_kernel<gate_up/SwiGLU epilogue>" if kind in ("mlp", "gate_up") else "w8a8_gemm_kernel",
                         achieved=achieved, peak=i8_peak, unit="TFLOP/s", frac=achieved / i8_peak,
-                        # DRAM bytes of one gate_up launch: ncu capture at M = 4096 (660.5 MB read + 195.9 MB written,
-                        # profiles/w8a8_gemm_c5_layer_m4096.md) scaled by the rows, which every term grows with
-                        traffic=(856.3e6 * m / 4096 if (args.workload == "c5" and tp == 1) else None),
-                        traffic_unit="bytes per launch (ncu at M=4096, scaled by M)",
-                        peak_source=f"2 x bf16_tflops_sustained of {peaks['source']} (int8 tcgen05 rate is twice bf16); 1 int8 multiply-add = 2 ops",
+                        traffic=traffic, traffic_unit="bytes per launch" + (f" ({traffic_note})" if traffic_note else ""),
+                        algorithmic_bytes=gu_bytes_launch,
+                        peak_source=f"2 x bf16_tflops_sustained of {peaks['source']} (no int8 figure is measured; the int8 tcgen05 rate is twice bf16); 1 int8 multiply-add = 2 ops",
                         launch_ms=gu_avg, ops_per_launch=gu_ops_launch,
                         down_gemm=dict(achieved=dn_ops_launch / (dn_avg * 1e-3) / 1e12, launch_ms=dn_avg,
                                        frac=dn_ops_launch / (dn_avg * 1e-3) / 1e12 / i8_peak) if kind == "mlp" else None)
     else:
         achieved = gu_bytes_launch / (gu_avg * 1e-3) / 1e9
-        roofline = dict(bound="hbm", kernel="w8a8_gemm_kernel<int32 epilogue> (gate_up weights)", achieved=achieved, peak=peaks["hbm_gbs"],
+        step_bytes = layers * (hidden * 3 * inter + 2 * wl["adapters"] * wl["rank"] * (hidden + 2 * inter + inter + hidden)) if kind == "mlp" else None
+        roofline = dict(bound="hbm", kernel="w8a8_gemm_kernel (gate_up weights)", achieved=achieved, peak=peaks["hbm_gbs"],
                         unit="GB/s", frac=achieved / peaks["hbm_gbs"], traffic=None, peak_source=f"hbm_gbs of {peaks['source']}",
                         launch_ms=gu_avg, bytes_per_launch=gu_bytes_launch,
-                        step_bytes=layers * (hidden * 3 * inter + 2 * wl["adapters"] * wl["rank"] * (hidden + 2 * inter + inter + hidden)) if kind == "mlp" else None,
-                        step_frac=(layers * (hidden * 3 * inter + 2 * wl["adapters"] * wl["rank"] * (hidden + 2 * inter + inter + hidden)) / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"]) if kind == "mlp" else None,
+                        step_bytes=step_bytes,
+                        step_frac=(step_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"]) if kind == "mlp" else None,
                         down_gemm=dict(achieved=dn_bytes_launch / (dn_avg * 1e-3) / 1e9, launch_ms=dn_avg,
                                        frac=dn_bytes_launch / (dn_avg * 1e-3) / 1e9 / peaks["hbm_gbs"]))
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline(args.workload, wl)
+    if world == 1 and not args.no_cpu_baseline and not sub:
+        cpu = cpu_baseline(workload, wl)
 
     line = {
         "metric": "tokens_per_s_w8a8_lora_mlp", "value": tokens_per_s, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong" if kind == "mlp" else "replicas", "vs_baseline": None, "dtype": "int8 x int8 -> int32 (+ bf16 LoRA, fp32 epilogue)",
-        "data": "synthetic, seeded; random-init weights of the named shapes",
-        "config": {"workload": args.workload, "kind": kind, "tokens": m, "layers": layers,
+        "data": "synthetic, seeded; random-init weights of the named shapes (one seeded model, sharded for N > 1)",
+        "config": {"workload": workload, "kind": kind, "tokens": m, "layers": layers,
                    **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
                    "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
                    **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
@@ -458,14 +581,92 @@ def run_device(args):
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * steps,
         "clocks": clocks,
+        # time x clock: what a comparison across runs at different SM clocks (a power-capped 1-GPU run against an
+        # 8-GPU run at full clock) should divide by
+        "ms_x_sm_mhz": (ms_per_step * clocks["sm_mhz"]) if clocks and clocks.get("sm_mhz") else None,
         "roofline": roofline,
+        "parity": parity,
         "cpu_baseline": cpu,
     }
-    print(json.dumps(line), flush=True)
+    return line, ok
+
+
+def parity_check(S, torch, dist, workload, wl, tp, rank, device, x_dev, ids, ids_np, inputs, env):
+    """Sampled-row check of the configured workload against the oracle, run before the timed region.
+    Returns (dict for the JSON line, ok).  A failed bar is reported in the line, not raised."""
+    from oracle import parity_checks as P
+    from oracle import w8a8_oracle as O
+
+    kind, m = wl["kind"], wl["m"]
+    rows = min(m, 192)   # more than one 128-row tile, so that the sampled rows take the same kernels as the full launch
+    try:
+        if kind == "mlp" and tp == 1:
+            res = P.check_mlp_layer(S, x_dev, inputs["delta"], ids_np, inputs["gate_up"], inputs["down"], rows=rows, seed=1)
+            res.update(scope=f"layer 0 of {wl['layers']} at the full launch shape, {res['rows']} sampled token rows, stage by stage")
+        elif kind == "mlp":
+            # tensor-parallel: block 0 through the same exchange the timed stack uses, against the oracle's statement
+            # of the sharded block (per-shard activation scales = group_size I / tp) on sampled rows
+            stack = env["make_stack"](env["blocks"][:1])
+            out = stack.forward(x_dev, ids)
+            torch.cuda.synchronize()
+            S.check_status(device)
+            res = None
+            if rank == 0:
+                import numpy as np
+
+                sampled = P.sample_rows(m, rows, 1)
+                rt = torch.from_numpy(sampled).to(device)
+                gu_host, _, gu_tab, _ = inputs["gate_up"]
+                dn_host, _, dn_tab, _ = inputs["down"]
+                want = O.tp_shard_mlp_reference(P.to_np(x_dev[rt]), P.to_np(inputs["delta"]), gu_host, *gu_tab, dn_host,
+                                                *dn_tab, ids_np[sampled], tp)
+                got = P.to_np(out[rt])
+                diff = np.abs(got.astype(np.float32) - want.astype(np.float32))
+                ulp = O.bf16_ulp_distance(got, want)
+                res = {"rows": int(len(sampled)), "rel_l2": O.relative_l2(got, want), "max_abs": float(diff.max()),
+                       "max_ulp_ge1": int(ulp[np.abs(want.astype(np.float32)) >= 1.0].max()),
+                       "beyond_bar": int(((diff > P.MAX_ABS) & (ulp > 1)).sum()),
+                       "exchange": stack.scatter_mode,
+                       "scope": f"tp_parity: block 0 through the {tp}-rank exchange against the oracle's sharded block "
+                                f"(activation scales per shard, group_size I/{tp}), {len(sampled)} sampled rows"}
+                assert res["rel_l2"] < P.REL_L2 and res["beyond_bar"] == 0, res
+            del stack
+        else:
+            import numpy as np
+
+            sampled = P.sample_rows(m, rows, 1)
+            rt = torch.from_numpy(sampled).to(device)
+            got = env["step"](x_dev, ids)
+            S.check_status(device)
+            ids_r = ids_np[sampled] if ids_np is not None else None
+            xin = x_dev[rt].contiguous()
+            if kind == "gate_up":
+                xin = S.rms_quant(xin, env["delta"], want_normalized=True)[2]
+            res = P.check_projection_chain(
+                S, workload, P.to_np(xin), env["w_host"], env["w"], env["lora_host"], env["lora"], ids_r, P.to_np(got[rt]),
+                {"linear": "linear", "gate_up": "swiglu", "down": "residual"}[kind],
+                residual=P.to_np(env["res_dev"][rt]) if kind == "down" else None)
+            acc = S.w8a8_int32_accumulator(xin if m <= 128 else (S.rms_quant(x_dev, env["delta"], want_normalized=True)[2]
+                                                                  if kind == "gate_up" else x_dev), env["w"], enabled=True)
+            codes, _ = O.dynamic_group_quantize(P.to_np(xin), wl["k"])
+            want_acc = O.int8_group_gemm(codes, env["w_host"].codes.reshape(1, wl["k"], wl["n"]))[:, 0, :]
+            res["acc_bit_exact"] = bool(np.array_equal(P.to_np(acc if m <= 128 else acc[rt]), want_acc))
+            res["rows"] = int(len(sampled))
+            res["scope"] = f"{res['rows']} sampled token rows of the full launch shape"
+            assert res["acc_bit_exact"], "int32 accumulator is not bit-exact"
+        ok = True
+        if res is not None:
+            res["ok"] = True
+    except AssertionError as exc:
+        res, ok = {"ok": False, "failed": str(exc)[:400]}, False
     if dist is not None:
-        dist.destroy_process_group()
+        flag = torch.tensor([0 if ok else 1], device=device, dtype=torch.int32)
+        dist.all_reduce(flag)
+        ok = int(flag.item()) == 0
+    torch.cuda.empty_cache()
+    return res, ok
 
 
 # --------------------------------------------------------------------------- #
@@ -518,7 +719,7 @@ def cpu_sample(workload: str, wl: dict, rows: int):
 
 
 def cpu_baseline(workload: str, wl: dict, rows: int | None = None, reps: int = 2):
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = host_threads()
     rows = rows or min(wl["m"], 256)
     cpu_sample(workload, wl, min(rows, 16))  # warm BLAS threads
     secs = min(cpu_sample(workload, wl, rows) for _ in range(reps))
@@ -530,7 +731,15 @@ def cpu_baseline(workload: str, wl: dict, rows: int | None = None, reps: int = 2
             "seconds": secs}
 
 
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
 def run_reference(args):
+    """The reference's CPU path for the same workload: the NumPy port of its pure-JAX quantised-LoRA functions
+    (JAX itself cannot be installed here), on all host threads.  Launchers that start one process per GPU pin
+    every process to ONE OpenMP thread (OMP_NUM_THREADS=1); main() lifts that before NumPy is imported, so the
+    figure is the same whatever N the arm is launched with."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -538,19 +747,22 @@ def run_reference(args):
     rows = min(wl["m"], 256)
     for _ in range(max(args.warmup, 1)):
         cpu_sample(args.workload, wl, min(rows, 16))
-    times = [cpu_sample(args.workload, wl, rows) for _ in range(max(1, min(args.steps, 3)))]
+    times = [cpu_sample(args.workload, wl, rows) for _ in range(max(1, min(args.steps, 30)))]
     secs = sum(times) / len(times)
     value = rows / secs / wl["layers"]
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    cores = host_threads()
+    threads = {k_: os.environ.get(k_) for k_ in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS")}
     sample = (f"{rows} token rows through 1 of {wl['layers']} layers per step, NumPy port of the reference's pure-JAX "
-              f"quantised-LoRA path (JAX is not installable here), scaled by 1/{wl['layers']} layers")
+              f"quantised-LoRA path (JAX is not installable here; the int8 contraction runs through float64 BLAS, which is "
+              f"exact and faster than the reference's int32 einsum), scaled by 1/{wl['layers']} layers; thread settings {threads}")
     line = {
         "impl": "reference", "metric": "tokens_per_s_w8a8_lora_mlp", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": len(times), "warmup": max(args.warmup, 1), "ms_per_step": secs * 1e3,
         "higher_is_better": True, "scaling": "strong" if wl["kind"] == "mlp" else "replicas", "vs_baseline": None,
         "dtype": "int8 x int8 -> int32 (+ fp32 LoRA)", "data": "synthetic, seeded",
         "config": {"workload": args.workload, "kind": wl["kind"], "tokens": wl["m"], "layers": wl["layers"],
-                   "parallelism": "cpu"},
+                   **{k_: wl[k_] for k_ in ("hidden", "inter", "k", "n", "rank", "adapters") if k_ in wl},
+                   "adapter_ids": wl["ids"], "parallelism": "cpu"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -567,6 +779,8 @@ def main():
     ap.add_argument("--m", type=int, default=0, help="override the token count (debugging)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging / small ncu captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row oracle check in front of the timed region")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode (c2) sub-benchmark of the default c5 line")
     ap.add_argument("--tp-chunks", type=int, default=2,
                     help="row chunks per block whose all-reduce overlaps the next chunk's kernels (N > 1)")
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
@@ -584,6 +798,9 @@ def main():
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
+        # before NumPy loads its BLAS: all host threads, whatever the launcher set for its per-GPU workers
+        for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+            os.environ[var] = str(host_threads())
         run_reference(args)
     else:
         run_device(args)

@@ -326,6 +326,10 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
 #define SKYRL_MLP_NO_ROW_AMAX 8u /* the quantiser of h finds the row absmax itself (two passes over h) instead of
                                     taking it from the gate_up epilogue; results are bit-identical (a cross-check). */
 
+#define SKYRL_MLP_KEEP_NORMALIZED 16u /* batches of at most SKYRL_TILE_ROWS rows: also store the normalised bf16
+                                         activations rmsnorm(x) in the workspace (larger batches always do), so that
+                                         a stage-by-stage check can feed the oracle what the kernels saw. */
+
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,
  * skyrl/tx/models/qwen3_5.py:786-826; Qwen3MLP, skyrl/tx/models/qwen3.py:100-131). */
@@ -423,7 +427,8 @@ SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_
  * workspace, for stage-by-stage parity checks: offsets[0] row permutation int32 [m] (sorted position ->
  * token row; meaningful for m > 128 with adapter ids, otherwise rows keep token order), offsets[1]
  * h = swiglu(gate_up(...)) bf16 [m, inter] in the GEMM's row order, offsets[2] int8 codes of h [m, inter],
- * offsets[3] fp32 scales of h [m]. */
+ * offsets[3] fp32 scales of h [m], offsets[4] normalised activations rmsnorm(x) bf16 [m, hidden] in the same
+ * row order (batches of at most SKYRL_TILE_ROWS rows: only with SKYRL_MLP_KEEP_NORMALIZED). */
 SKYRL_API int skyrl_w8a8_mlp_workspace_stage_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                            size_t* offsets);
 /* out[perm[i], :] = sorted_rows[i, :] for all m rows of a bf16 [m, H] matrix (perm from the workspace of

@@ -1,0 +1,223 @@
+"""Checker routines built on the CPU oracle: stage-by-stage parity of the CUDA path on sampled rows.
+
+TEST INFRASTRUCTURE, NOT PRODUCT CODE: used by tests/, by the smoke check and by the parity leg of
+bench.py (which runs before its timed region).  `S` is the product package (skyrl_tx_rocm_b200), always
+called through its public operators; nothing here is on a timed or shipped path.
+"""
+
+import ml_dtypes
+import numpy as np
+import torch
+
+from oracle import w8a8_oracle as O
+
+BF16 = ml_dtypes.bfloat16
+MAX_ABS = 2e-2
+REL_L2 = 1e-3
+
+
+def to_np(t):
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.uint16).numpy().view(BF16)
+    return t.numpy()
+
+
+def to_dev(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == BF16:
+        return torch.from_numpy(a.view(np.uint16).copy()).view(torch.bfloat16).cuda()
+    return torch.from_numpy(a.copy()).cuda()
+
+
+def device_normal(shape, seed, std=1.0):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * std).to(torch.bfloat16)
+
+
+def big_weight(S, k, n, seed):
+    """W ~ N(0, 0.02) bf16 [K, N] -> per-output-channel int8 with the product's quantiser (itself pinned bit
+    for bit to the oracle's in test_weight_quantiser_*), packed for the device and mirrored on the host."""
+    w = device_normal((k, n), seed, 0.02)
+    gq = S.quantize_frozen_weight(w)
+    host = O.GroupQuantizedWeight(to_np(gq.codes), to_np(gq.scales), k, k, 8, gq.group_size)
+    packed = S.pack_weight(gq)
+    del w, gq
+    torch.cuda.empty_cache()
+    return host, packed
+
+
+def big_lora(S, na, k, rank, n, seed, alpha):
+    a = device_normal((na, k, rank), seed, 1.0 / np.sqrt(k))
+    b = device_normal((na, rank, n), seed + 1, 0.02)
+    s = np.full((na,), alpha / rank, dtype=np.float32)
+    packed = S.pack_lora(a, b, to_dev(s), in_features=k, padded_out_features=n)
+    return (to_np(a), to_np(b), s), packed
+
+
+def sample_rows(m, count, seed):
+    rng = np.random.default_rng(seed)
+    return np.sort(rng.choice(m, size=min(count, m), replace=False))
+
+
+def uniform_ids(m, na, seed):
+    return np.random.default_rng(seed).integers(0, na, size=m).astype(np.int32)
+
+
+def check_projection_chain(S, what, xin, w_host, w_packed, lora_host, lora_packed, ids, got, kind, residual=None):
+    """Pin one fused projection for a set of rows.
+
+    xin   bf16 [R, K]  exactly the rows the kernel's quantiser / LoRA-A stage saw
+    got   bf16         the fused kernel's output for those rows (taken from the full-size launch)
+    kind  "linear" | "swiglu" | "residual"
+    Returns the figures a report wants (max-abs, max-ulp, relative L2, tie counts)."""
+    a, b, s = lora_host
+    idd = to_dev(ids) if ids is not None else None
+    p32 = to_np(S.w8a8_lora_linear_f32(to_dev(xin), w_packed, lora_packed, adapter_ids=idd, enabled=True))
+    S.check_status()
+    y64, y32 = O.quantized_lora_linear_f64(xin, w_host, a, b, s, ids)
+    p_kernel, p_oracle = p32.astype(BF16), y32.astype(BF16)
+    ev = O.classify_bf16_mismatches(p_kernel, p_oracle, p32, y64)
+    assert ev["unexplained"] == 0, f"{what}: projection differs from the oracle beyond rounding ties: {ev}"
+    if kind == "swiglu":
+        from_kernel, want = O.swiglu_interleaved(p_kernel), O.swiglu_interleaved(p_oracle)
+    elif kind == "residual":
+        from_kernel, want = O.residual_add(p_kernel, residual), O.residual_add(p_oracle, residual)
+    else:
+        from_kernel, want = p_kernel, p_oracle
+    # (1) the fused kernel == its own epilogue applied to its own projection.  The residual add and the plain
+    # cast are exact; the SwiGLU product goes through exp, where the two libraries may differ in the last
+    # fp32 bit, which can move a bf16 rounding by one step on a few elements.
+    step = O.bf16_ulp_distance(got, from_kernel)
+    if kind == "swiglu":
+        assert step.max() <= 1 and (step > 0).mean() < 1e-3, f"{what}: fused epilogue {step.max()} ulp, {(step > 0).mean():.2e}"
+    else:
+        assert step.max() == 0, f"{what}: fused epilogue differs from cast + residual of the kernel's projection"
+    # (2) against the oracle end to end
+    g32, w32 = got.astype(np.float32), want.astype(np.float32)
+    assert np.all(np.isfinite(g32))
+    diff, ulp = np.abs(g32 - w32), O.bf16_ulp_distance(got, want)
+    rel = O.relative_l2(g32, w32)
+    assert rel < REL_L2, f"{what}: relative L2 {rel}"
+    # An output element may leave (max-abs AND one bf16 step) only DOWNSTREAM of a projection element on which
+    # kernel and oracle round to different neighbours (each of those is within the bar or a proven tie, see
+    # above): the SwiGLU product multiplies such a step by the other factor, the residual sum can land it on a
+    # result with a finer spacing.  Checked element by element, not by count.
+    flipped = O.bf16_ulp_distance(p_kernel, p_oracle) > 0
+    upstream = (flipped[:, 0::2] | flipped[:, 1::2]) if kind == "swiglu" else flipped
+    beyond = (diff > MAX_ABS) & (ulp > 1)
+    stray = int((beyond & ~upstream).sum())
+    assert stray == 0, f"{what}: {stray} elements beyond the bar that no rounding difference of the projection explains"
+    ev["beyond_downstream_of_a_flip"] = int(beyond.sum())
+    return dict(rel_l2=rel, max_abs=float(diff.max()), differing=float((ulp > 0).mean()), **ev)
+
+
+def small_batch_accumulator(S, codes_dev, scales_dev, packed):
+    """int32 accumulator of the small-batch GEMM plan (one wave of narrow tiles, or K split over int32 slabs
+    that the consumer adds) for m <= 128 rows of int8 codes, called through the C ABI's GEMM entry point with
+    the slab count the operators use.  Returns (accumulator int32 [m, n] on the host, number of K splits)."""
+    import ctypes as C
+
+    lib = S._lib.load()
+    m = codes_dev.shape[0]
+    n, k = packed.padded_out_features, packed.in_features
+    dev = codes_dev.device
+    st = torch.zeros(4, dtype=torch.int32, device=dev)
+    tiles = torch.tensor([[0, m, 0, 0]], dtype=torch.int32, device=dev)
+    num = torch.ones(4, dtype=torch.int32, device=dev)
+    splits = lib.skyrl_w8a8_gemm_k_splits(m, n, k, 16)
+    slabs = torch.full((splits, m, n), -7, dtype=torch.int32, device=dev)
+    g = S._lib.GemmArgs()
+    g.struct_size = C.sizeof(S._lib.GemmArgs)
+    g.epilogue, g.m, g.n, g.k, g.num_adapters, g.max_tiles = S.EPI_ACC_I32, m, n, k, 1, 1
+    g.xq, g.sx, g.wq, g.sw = codes_dev.data_ptr(), scales_dev.data_ptr(), packed.wq.data_ptr(), packed.sw.data_ptr()
+    g.tiles, g.num_tiles, g.out, g.out_row_stride = tiles.data_ptr(), num.data_ptr(), slabs.data_ptr(), n
+    g.status, g.split_k_slabs = st.data_ptr(), 16
+    S._lib.check(lib.skyrl_w8a8_gemm_sm100_v1(C.byref(g), torch.cuda.current_stream().cuda_stream), "w8a8_gemm")
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0, f"device status {int(st[0])}"
+    return to_np(slabs.sum(dim=0, dtype=torch.int32)), splits
+
+
+def check_mlp_layer(S, x, delta, ids, gate_up, down, *, rows=128, seed=0):
+    """Stage-pinned parity of ONE full-size MLP block on sampled token rows.
+
+    x bf16 [M, H] (device), delta bf16 [H] (device), ids int32 [M] (NumPy) or None;
+    gate_up / down = (host GroupQuantizedWeight, packed device weight, (A, B, s) host tables, packed tables).
+    Runs the block at its full shape (the configuration a benchmark times), then for `rows` sampled token
+    rows checks: RMSNorm within one bf16 step; int8 codes and scales of h bit-exact given the kernel's h;
+    the int32 accumulators of both projections at the full launch shape bit-exact; each fused projection
+    through `check_projection_chain`; the composed block against the oracle from x.
+    Returns a dict of figures; raises AssertionError where a bar is missed."""
+    wgu, pgu, lgu_h, lgu = gate_up
+    wd, pd, ld_h, ld = down
+    m, hidden = x.shape
+    inter = pd.in_features
+    na = lgu.num_adapters
+    idd = to_dev(ids) if ids is not None else None
+    out = S.w8a8_mlp_block(x, delta, pgu, lgu, pd, ld, idd, enabled=True, keep_normalized=True)
+    S.check_status()
+    perm, h, hq, sh, xn = [t.clone() for t in S.w8a8_mlp_stage_regions(m, hidden, inter, na, x.device)]
+    xq, sx, _ = [t.clone() for t in S.w8a8_mlp_workspace_regions(m, hidden, inter, na, x.device)]
+    sampled = sample_rows(m, rows, seed)
+    rt = torch.from_numpy(sampled).to(x.device)
+    if m > 128 and ids is not None:
+        inv = torch.empty(m, dtype=torch.int64, device=x.device)
+        inv[perm.long()] = torch.arange(m, device=x.device)
+        pos = inv[rt]
+    else:
+        pos = rt
+    ids_r = ids[sampled] if ids is not None else None
+    x_h, out_k = to_np(x[rt]), to_np(out[rt])
+    h_k, hq_k, sh_k, xn_k = to_np(h[pos]), to_np(hq[pos]), to_np(sh[pos]), to_np(xn[pos])
+    delta_h = to_np(delta) if delta is not None else None
+    if delta_h is not None:
+        step = O.bf16_ulp_distance(xn_k, O.rms_norm(x_h, delta_h))
+        assert step.max() <= 1 and (step > 0).mean() < 2e-3, "RMSNorm differs from the oracle by more than one bf16 step"
+    hcodes, hscales = O.dynamic_group_quantize(h_k, inter)
+    codes_ok = bool(np.array_equal(hq_k, hcodes[:, 0, :]) and np.array_equal(sh_k, hscales[:, 0]))
+    assert codes_ok, "int8 codes / scales of h are not bit-exact"
+    # int32 accumulators at the full launch shape (M rows), sampled rows compared
+    xcodes, _ = O.dynamic_group_quantize(xn_k, hidden)
+    acc_ok = True
+    if m > 128:
+        for src, rows_pos, packed, host, want_codes in ((xn, pos, pgu, wgu, xcodes), (h, pos, pd, wd, hcodes)):
+            acc = S.w8a8_int32_accumulator(src, packed, enabled=True)
+            S.check_status()
+            k, n = host.codes.shape
+            want = O.int8_group_gemm(want_codes, host.codes.reshape(1, k, n))[:, 0, :]
+            acc_ok = acc_ok and bool(np.array_equal(to_np(acc[rows_pos]), want))
+            del acc
+    else:
+        # small batches: the GEMM plans of the decode path, all rows
+        full_x, _ = O.dynamic_group_quantize(to_np(xn), hidden)
+        full_h, _ = O.dynamic_group_quantize(to_np(h), inter)
+        for codes_dev, scales_dev, packed, host, want_codes in ((xq, sx, pgu, wgu, full_x), (hq, sh, pd, wd, full_h)):
+            got_acc, _ = small_batch_accumulator(S, codes_dev, scales_dev, packed)
+            k, n = host.codes.shape
+            acc_ok = acc_ok and bool(np.array_equal(got_acc, O.int8_group_gemm(want_codes, host.codes.reshape(1, k, n))[:, 0, :]))
+    assert acc_ok, "int32 accumulator is not bit-exact"
+    front = check_projection_chain(S, "gate_up", xn_k, wgu, pgu, lgu_h, lgu, ids_r, h_k, "swiglu")
+    back = check_projection_chain(S, "down", h_k, wd, pd, ld_h, ld, ids_r, out_k, "residual", residual=x_h)
+    # The composed block.  (a) From the normalised rows the kernel produced: every boundary behind them is pinned
+    # by the reference's semantics, so this meets the bars (relative L2 1e-3; an element beyond max-abs 2e-2 AND
+    # one bf16 step only downstream of the rounding differences the stage pins account for: counted, bounded).
+    want = O.residual_add(O.quantized_lora_linear(
+        O.swiglu_interleaved(O.quantized_lora_linear(xn_k, wgu, *lgu_h, ids_r)), wd, *ld_h, ids_r), x_h)
+    diff = np.abs(out_k.astype(np.float32) - want.astype(np.float32))
+    ulp = O.bf16_ulp_distance(out_k, want)
+    rel = O.relative_l2(out_k, want)
+    assert rel < REL_L2, f"composed block: relative L2 {rel}"
+    beyond = int(((diff > MAX_ABS) & (ulp > 1)).sum())
+    assert beyond <= max(2, diff.size // 5000), f"composed block: {beyond} of {diff.size} elements beyond the bar"
+    # (b) From x through the oracle's own RMSNorm: no reference test pins how the sum of squares is rounded, a
+    # one-step difference of a normalised element re-draws the bf16 rounding of a whole row of the projection,
+    # and the relative L2 between two correct implementations is itself about 1e-3 at these sizes.  Reported.
+    from_x = O.mlp_block(x_h, delta_h, wgu, *lgu_h, wd, *ld_h, ids_r)
+    rel_from_x = O.relative_l2(out_k, from_x)
+    assert rel_from_x < 2e-3, f"composed block from x: relative L2 {rel_from_x}"
+    big = np.abs(want.astype(np.float32)) >= 1.0
+    return {"rows": int(len(sampled)), "codes_bit_exact": codes_ok, "acc_bit_exact": acc_ok,
+            "rel_l2": rel, "max_abs": float(diff.max()), "max_ulp_ge1": int(ulp[big].max()) if big.any() else 0,
+            "beyond_bar": beyond, "rel_l2_from_x_unpinned_rmsnorm": rel_from_x,
+            "gate_up": front, "down": back}

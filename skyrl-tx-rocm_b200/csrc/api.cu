@@ -181,15 +181,14 @@ static MlpWs carve_mlp(void* ws, int m, int hidden, int inter, int num_adapters)
   w.h = c.take<uint16_t>(static_cast<size_t>(m) * inter);
   w.hq = c.take<int8_t>(static_cast<size_t>(m) * inter);
   w.sh = c.take<float>(m);
+  w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
   if (m <= ROWS_PATH_MAX_M) {
-    w.xn = nullptr;
     const size_t gu = static_cast<size_t>(m) * 2 * inter *
                       plan_gemm(m, 2 * inter, hidden, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     const size_t dn = static_cast<size_t>(m) * hidden *
                       plan_gemm(m, hidden, inter, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     w.acc = c.take<int32_t>(gu > dn ? gu : dn);
   } else {
-    w.xn = c.take<uint16_t>(static_cast<size_t>(m) * hidden);
     w.acc = nullptr;
   }
   w.h_amax = c.take<float>(m);
@@ -290,7 +289,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   if (rows_path && lora && q.epilogue != SKYRL_EPI_ACC_I32) {
     float* z_rows = reinterpret_cast<float*>(q.z_parts);
     if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.na, q.a_packed, q.scaling, q.rank, q.m,
-                                    q.k, q.xq, q.sx, z_rows, q.status, stream, true)))
+                                    q.k, q.xq, q.sx, z_rows, q.status, stream, true, q.keep_xn ? q.xn : nullptr)))
       return rc;
     const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     g.struct_size = sizeof(g);
@@ -549,7 +548,8 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.rms_delta = a->rms_delta;
   q.eps = a->rms_eps;
   q.gather = pl.perm;
-  q.keep_xn = pl.routed || a->rms_delta != nullptr;
+  // small batches need no re-laid-out copy of x; they write one only when asked to (stage checks)
+  q.keep_xn = pl.rows_path ? (a->flags & SKYRL_MLP_KEEP_NORMALIZED) != 0 : (pl.routed || a->rms_delta != nullptr);
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;
@@ -686,6 +686,7 @@ extern "C" int skyrl_w8a8_mlp_workspace_stage_regions(int32_t m, int32_t hidden,
   offsets[1] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.h) - base);
   offsets[2] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.hq) - base);
   offsets[3] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.sh) - base);
+  offsets[4] = static_cast<size_t>(reinterpret_cast<unsigned char*>(w.xn) - base);
   return SKYRL_OK;
 }
 

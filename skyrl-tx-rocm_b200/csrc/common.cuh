@@ -86,7 +86,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
 // Adapter ids outside [0, num_adapters) are clamped and STATUS_BAD_ADAPTER_ID is recorded in `status`.
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                           int num_adapters, const void* a_packed, const float* scaling, int rank, int m, int k, void* xq,
-                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic = false);
+                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic = false,
+                          void* xn_out = nullptr);  // xn_out: optional bf16 [m, k] copy of the normalised rows
 int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const float* sx, const float* sw, const float* z_rows,
                          const int32_t* ids, int num_adapters, const void* b_table, int64_t b_adapter_stride,
                          int b_row_stride, int rank, int m, int n, const void* residual, int64_t res_stride, void* out,

@@ -50,7 +50,7 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
                       const __nv_bfloat16* __restrict__ delta, float eps, const int32_t* __restrict__ ids,
                       int num_adapters, const __nv_bfloat16* __restrict__ a_packed,
                       const float* __restrict__ scaling, int k, int8_t* __restrict__ xq, float* __restrict__ sx,
-                      float* __restrict__ z_rows, int32_t* status) {
+                      float* __restrict__ z_rows, int32_t* status, __nv_bfloat16* __restrict__ xn_out) {
   cg::cluster_group cluster = cg::this_cluster();
   __shared__ float red[ROWQ_THREADS / 32];
   __shared__ float zwarp[ROWQ_THREADS / 32][R];
@@ -146,10 +146,14 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
 #pragma unroll
   for (int j = 0; j < R; ++j) acc[j] = 0.f;
   uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k) + v0;
+  uint4* ndst = xn_out != nullptr ? reinterpret_cast<uint4*>(xn_out + static_cast<int64_t>(m) * k) + v0 : nullptr;
 #pragma unroll
   for (int i = 0; i < VMAX; ++i) {
     const int v = threadIdx.x + i * ROWQ_THREADS;
     if (v < cnt) {
+      if (ndst != nullptr)  // the (normalised) bf16 activations both the quantiser and the LoRA term saw, for stage checks
+        ndst[v] = make_uint4(pack_bf16x2(xv[i][0], xv[i][1]), pack_bf16x2(xv[i][2], xv[i][3]),
+                             pack_bf16x2(xv[i][4], xv[i][5]), pack_bf16x2(xv[i][6], xv[i][7]));
       int q[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) q[e] = quant_code(xv[i][e], scale, rcp);
@@ -273,12 +277,13 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
 template <int R, int VMAX, bool PREFETCH_A>
 static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                                int num_adapters, const void* a_packed, const float* scaling, int m, int k, void* xq,
-                               float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic) {
+                               float* sx, float* z_rows, int32_t* status, void* xn_out, cudaStream_t stream,
+                               bool programmatic) {
   cudaError_t e = launch_kernel(rms_quant_rows_kernel<R, VMAX, PREFETCH_A>, dim3(m * ROWQ_CLUSTER), dim3(ROWQ_THREADS), 0,
                                 stream, programmatic, static_cast<const __nv_bfloat16*>(x), x_row_stride,
                                 static_cast<const __nv_bfloat16*>(rms_delta), eps, ids, num_adapters,
                                 static_cast<const __nv_bfloat16*>(a_packed), scaling, k, static_cast<int8_t*>(xq), sx,
-                                z_rows, status);
+                                z_rows, status, static_cast<__nv_bfloat16*>(xn_out));
   if (e == cudaSuccess) e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "rms_quant_rows launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
@@ -286,7 +291,8 @@ static int launch_rows_variant(const void* x, int64_t x_row_stride, const void* 
 
 int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* ids,
                           int num_adapters, const void* a_packed, const float* scaling, int rank, int m, int k, void* xq,
-                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic) {
+                          float* sx, float* z_rows, int32_t* status, cudaStream_t stream, bool programmatic,
+                          void* xn_out) {
   if (x == nullptr || xq == nullptr || sx == nullptr || a_packed == nullptr || scaling == nullptr ||
       z_rows == nullptr || status == nullptr || m <= 0 || k <= 0 || num_adapters <= 0)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "rms_quant_rows: null buffer or non-positive shape");
@@ -302,7 +308,7 @@ int launch_rms_quant_rows(const void* x, int64_t x_row_stride, const void* rms_d
     return fail(SKYRL_ERR_UNSUPPORTED, "rms_quant_rows: rank must be in [1, %d], got %d", SKYRL_LORA_RANK_PAD, rank);
 #define SKYRL_ROWS(R, V, P) \
   return launch_rows_variant<R, V, P>(x, x_row_stride, rms_delta, eps, ids, num_adapters, a_packed, scaling, m, k, xq, sx, \
-                                      z_rows, status, stream, programmatic)
+                                      z_rows, status, xn_out, stream, programmatic)
   if (per_cta <= 2 * ROWQ_THREADS) {
     if (rank <= 16) SKYRL_ROWS(16, 2, false);
     if (rank <= 32) SKYRL_ROWS(32, 2, false);

@@ -29,7 +29,7 @@ from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_S
 __all__ = (
     "GroupQuantizedWeight", "PackedW8Weight", "PackedLoRA", "SkyrlKernelError",
     "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
-    "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator",
+    "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator", "w8a8_lora_linear_f32",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
     "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "w8a8_mlp_stage_regions",
     "chunk_rows",
@@ -132,7 +132,10 @@ def quantize_frozen_weight(weight: torch.Tensor, *, bits: int = 8, group_size: i
     w32[:k] = weight.to(torch.float32)
     grouped = w32.view(-1, group_size, n)
     amax = grouped.abs().amax(dim=1)
-    scales = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+    # a TENSOR divisor: dividing by a Python scalar is evaluated as a multiplication by the rounded reciprocal,
+    # which differs from the reference's fp32 quotient amax / 127 in the last bit for some values
+    qmax = torch.full((), 127.0, dtype=torch.float32, device=weight.device)
+    scales = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
     codes = torch.clamp(torch.round(grouped / scales[:, None, :]), -127, 127).to(torch.int8)
     return GroupQuantizedWeight(codes.view(kpad, n).contiguous(), scales.to(scale_dtype), k, kpad, 8, group_size)
 
@@ -522,6 +525,24 @@ def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
+def w8a8_lora_linear_f32(x, weight, lora_a=None, lora_b=None, lora_scaling=None, adapter_ids=None, *,
+                         enabled: bool = False):
+    """The fp32 value of `w8a8_lora_linear` BEFORE its single bf16 cast, (f32(acc) * sx) * sw + s (x A) B
+    (quantized_lora.py:248-252, 301-303), in token order.  Parity evidence: where a bf16 output differs from
+    the reference's by one unit in the last place, this value shows whether the exact result sat on a
+    rounding boundary.  `lora_a=None` gives the frozen base."""
+    _validate_exact_bool("enabled", enabled)
+    if not enabled:
+        raise RuntimeError("the W8A8 pre-cast probe is disabled by default")
+    w = _weight_of(weight)
+    k_logical = weight.original_in_features if isinstance(weight, GroupQuantizedWeight) else w.in_features
+    x2 = _check_x(x, k_logical)
+    lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
+    ids = _check_ids(adapter_ids, x2.shape[0], lora)
+    y = _run_linear(x2, w, lora, ids, EPI_PARTIAL_F32)
+    return y[:, : w.out_features]
+
+
 def w8a8_int32_accumulator(x, weight, *, enabled: bool = False):
     """Raw int32 accumulator xq @ wq^T and the activation codes' scales, for
     bit-exact parity checks (quantized_lora.py:242-247)."""
@@ -586,7 +607,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
                    gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
-                   row_amax_from_epilogue: bool = True):
+                   row_amax_from_epilogue: bool = True, keep_normalized: bool = False):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -667,6 +688,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         a.flags |= _lib.MLP_INPUT_PREPARED
     if not row_amax_from_epilogue:
         a.flags |= _lib.MLP_NO_ROW_AMAX
+    if keep_normalized:
+        a.flags |= _lib.MLP_KEEP_NORMALIZED
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)
@@ -756,19 +779,21 @@ def w8a8_mlp_workspace_regions(m: int, hidden: int, inter: int, num_adapters: in
 
 def w8a8_mlp_stage_regions(m: int, hidden: int, inter: int, num_adapters: int, device):
     """Views of what the last `w8a8_mlp_block` call of these sizes left in the workspace, for stage-by-stage
-    checks: (perm int32 [m], h bf16 [m, inter], codes of h int8 [m, inter], scales of h fp32 [m]).  h and its
-    codes are in the GEMM's row order: adapter-sorted (row i = token perm[i]) for m > 128 with adapter
-    ids, token order otherwise."""
+    checks: (perm int32 [m], h bf16 [m, inter], codes of h int8 [m, inter], scales of h fp32 [m],
+    rmsnorm(x) bf16 [m, hidden]).  h, its codes and the normalised rows are in the GEMM's row order:
+    adapter-sorted (row i = token perm[i]) for m > 128 with adapter ids, token order otherwise (small
+    batches store the normalised rows only when the block ran with `keep_normalized=True`)."""
     lib = _lib.load()
     na = max(int(num_adapters), 1)
     ws = _workspace(device, lib.skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na))
-    off = (C.c_size_t * 4)()
+    off = (C.c_size_t * 5)()
     _lib.check(lib.skyrl_w8a8_mlp_workspace_stage_regions(m, hidden, inter, na, off), "w8a8_mlp_workspace_stage_regions")
     perm = ws[off[0]: off[0] + 4 * m].view(torch.int32)
     h = ws[off[1]: off[1] + 2 * m * inter].view(torch.bfloat16).view(m, inter)
     hq = ws[off[2]: off[2] + m * inter].view(torch.int8).view(m, inter)
     sh = ws[off[3]: off[3] + 4 * m].view(torch.float32)
-    return perm, h, hq, sh
+    xn = ws[off[4]: off[4] + 2 * m * hidden].view(torch.bfloat16).view(m, hidden)
+    return perm, h, hq, sh, xn
 
 
 # --------------------------------------------------------------------------- #

@@ -97,3 +97,28 @@ def test_no_cpu_fallback():
     assert w.codes.dtype == torch.int8 and w.scales.shape == (1, 32) and w.group_size == 16
     with pytest.raises(S.SkyrlKernelError, match="CUDA"):
         S.pack_weight(w)
+
+
+def test_weight_quantiser_matches_oracle_bitwise():
+    # the product's offline quantiser (ops.quantize_frozen_weight, here on CPU tensors) against the oracle's
+    # restatement of quantized_lora.py:128-171: int8 codes from the fp32 scale, stored scale rounded to bf16
+    import ml_dtypes
+    import numpy as np
+    import torch
+
+    import skyrl_tx_rocm_b200 as S
+    from oracle import w8a8_oracle as O
+
+    rng = np.random.default_rng(0)
+    for k, n, group in ((256, 96, None), (130, 48, 64), (64, 17, 32)):
+        w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+        w[:, 2] = 0.0                       # zero column: scale 1.0, codes 0
+        w[1, 4] = 0.3                       # one element sets the column's absmax
+        wb = w.astype(ml_dtypes.bfloat16)
+        t = torch.from_numpy(wb.view(np.uint16).copy()).view(torch.bfloat16)
+        got = S.quantize_frozen_weight(t, group_size=group)
+        want = O.quantize_frozen_weight(wb, group_size=group if group is not None else k + (k % 2))
+        np.testing.assert_array_equal(got.codes.numpy(), want.codes)
+        np.testing.assert_array_equal(got.scales.view(torch.uint16).numpy(), want.scales.view(np.uint16))
+        assert (got.padded_in_features, got.group_size) == (want.padded_in_features, want.group_size)
+        assert int(np.abs(got.codes.numpy()[:, 2]).max()) == 0 and float(got.scales[0, 2]) == 1.0

@@ -4,14 +4,15 @@ Bars (from the task statement): integer and index work bit-exact (int8 codes,
 fp32 scales, int32 accumulator, routing); bf16 outputs within max-abs 2e-2 and
 relative-L2 1e-3 of the oracle.  One bf16 unit in the last place exceeds 2e-2
 once |y| >= 4, and the oracle's fp32 LoRA accumulation order is not pinned by
-the reference, so an element may instead differ by at most one bf16 ulp; the
-number of such elements is bounded as well.
+the reference, so where outputs reach that size the projection is checked with
+`check_projection_chain` (tests/parity_util.py): an element may differ by one
+unit in the last place only if the float64 statement of the formula shows a
+rounding tie.  `assert_bf16_close` is the plain form: max-abs 2e-2 everywhere.
 """
 
 from pathlib import Path
 
 import ml_dtypes
-import os
 
 import numpy as np
 import pytest
@@ -19,6 +20,7 @@ import pytest
 torch = pytest.importorskip("torch")
 
 from oracle import w8a8_oracle as O  # noqa: E402
+from parity_util import check_projection_chain  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 BF16 = ml_dtypes.bfloat16
@@ -48,10 +50,7 @@ def to_np(t):
     return t.numpy()
 
 
-def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what="", outliers=0):
-    """`outliers`: elements allowed beyond (max-abs AND one ulp).  Only outputs computed FROM the bf16
-    projection use it (SwiGLU product, residual sum): there a one-ulp flip of the projection, legitimate on
-    its own, can be amplified by the product or land on a result with a smaller ulp."""
+def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what=""):
     got, want = np.asarray(got), np.asarray(want)
     assert got.shape == want.shape, (got.shape, want.shape)
     g32, w32 = got.astype(np.float32), want.astype(np.float32)
@@ -59,9 +58,7 @@ def assert_bf16_close(got, want, *, max_ulp_frac=2e-3, what="", outliers=0):
     rel = O.relative_l2(g32, w32)
     diff = np.abs(g32 - w32)
     ulp = O.bf16_ulp_distance(got, want)
-    bad = (diff > MAX_ABS) & (ulp > 1)
-    assert int(bad.sum()) <= outliers, (
-        f"{what}: {int(bad.sum())} elements beyond max-abs {MAX_ABS} and 1 ulp; worst {diff.max()}")
+    assert diff.max() <= MAX_ABS, f"{what}: max-abs {diff.max()} > {MAX_ABS}"
     assert rel < REL_L2, f"{what}: relative L2 {rel} >= {REL_L2}"
     frac = float((ulp > 0).mean())
     assert frac <= max_ulp_frac, f"{what}: {frac:.2e} of the elements differ from the oracle"
@@ -275,10 +272,13 @@ def test_config1_single_linear(S):
 def test_multi_adapter_linear(S, m, k, n, rank, na, mode):
     x, w, a, b, s, ids = make_case(17 + m, m, k, n, rank, na, ids_mode=mode)
     q, packed = device_weight(S, w)
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=packed.in_features,
+                       padded_out_features=packed.padded_out_features)
     y = S.w8a8_lora_linear(to_dev(x), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(ids), enabled=True)
     S.check_status()
-    want = O.quantized_lora_linear(x, q, a, b, s, ids)
-    assert_bf16_close(to_np(y), want, what=f"multi-adapter m={m}")
+    # outputs reach |y| >= 4 at K = 4096: one-ulp differences must be proven rounding ties
+    stats = check_projection_chain(S, f"multi-adapter m={m}", x, q, packed, (a, b, s), lora, ids, to_np(y), "linear")
+    assert stats["differing"] <= 2e-3
 
 
 @pytest.mark.parametrize("m,k,n,g,rank,na", [(3, 128, 17, 64, 8, 1), (7, 128, 19, 64, 8, 1), (130, 256, 48, 128, 16, 3),
@@ -321,19 +321,19 @@ def test_large_problem_paired_tile_kernel(S, kind):
     q, packed = device_weight(S, w)
     xd, idd = to_dev(x), to_dev(ids)
     lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=k, padded_out_features=n)
+    res = None
     if kind == "linear":
         got = S.w8a8_lora_linear(xd, packed, lora, adapter_ids=idd, enabled=True)
-        want = O.quantized_lora_linear(x, q, a, b, s, ids)
     elif kind == "swiglu":
         got = S.w8a8_rms_gate_up_lora_swiglu(xd, None, packed, lora, adapter_ids=idd, enabled=True)
-        want = O.rms_gate_up_lora_swiglu(x, None, q, a, b, s, ids)
     else:
         res = np.random.default_rng(5).standard_normal((m, n)).astype(np.float32).astype(BF16)
         got = S.w8a8_down_lora_residual(xd, packed, lora, residual=to_dev(res), adapter_ids=idd, enabled=True)
-        want = O.down_lora_residual(x, q, a, b, s, res, ids)
     S.check_status()
-    assert_bf16_close(to_np(got), want, max_ulp_frac=5e-3, what=f"paired {kind}",
-                      outliers=want.size // 100000 + 10 if kind != "linear" else 0)
+    # pinned through the kernel's own fp32 projection: the fused epilogue reproduces it, and the projection
+    # differs from the oracle's only at proven rounding ties
+    stats = check_projection_chain(S, f"paired {kind}", x, q, packed, (a, b, s), lora, ids, to_np(got), kind, residual=res)
+    assert stats["differing"] <= 5e-3
     acc = S.w8a8_int32_accumulator(xd, packed, enabled=True)
     _, parts = O.quantized_lora_linear(x, q, return_parts=True)
     np.testing.assert_array_equal(to_np(acc), parts["acc"][:, 0, :])
@@ -359,12 +359,13 @@ def test_rms_gate_up_swiglu(S, m, hidden, inter, rank, na):
     h = S.w8a8_rms_gate_up_lora_swiglu(to_dev(x), to_dev(delta), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(ids),
                                        enabled=True)
     S.check_status()
-    want = O.rms_gate_up_lora_swiglu(to_np(xn), None, q, a, b, s, ids)
     assert h.shape == (m, inter)
-    assert_bf16_close(to_np(h), want, max_ulp_frac=5e-3, what="gate_up swiglu")
-    # and against the full oracle within the stated tolerance
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    stats = check_projection_chain(S, "gate_up swiglu", to_np(xn), q, packed, (a, b, s), lora, ids, to_np(h), "swiglu")
+    assert stats["differing"] <= 5e-3
+    # and against the full oracle (its own RMSNorm) within the stated tolerance
     full = O.rms_gate_up_lora_swiglu(x, delta, q, a, b, s, ids)
-    assert O.relative_l2(to_np(h), full) < 5e-3
+    assert O.relative_l2(to_np(h), full) < REL_L2
 
 
 @pytest.mark.parametrize("m,inter,hidden,rank,na", [(64, 384, 256, 16, 8), (300, 640, 512, 32, 4)])
@@ -378,8 +379,10 @@ def test_down_lora_residual(S, m, inter, hidden, rank, na):
     out = S.w8a8_down_lora_residual(to_dev(h), packed, to_dev(a), to_dev(b), to_dev(s), to_dev(res), to_dev(ids),
                                     enabled=True)
     S.check_status()
-    want = O.down_lora_residual(h, q, a, b, s, res, ids)
-    assert_bf16_close(to_np(out), want, what="down residual")
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=inter, padded_out_features=hidden)
+    stats = check_projection_chain(S, "down residual", h, q, packed, (a, b, s), lora, ids, to_np(out), "residual",
+                                   residual=res)
+    assert stats["differing"] <= 2e-3
 
 
 @pytest.mark.parametrize("m,hidden,inter,rank,na", [(64, 256, 512, 16, 32), (200, 512, 768, 8, 3)])
@@ -392,15 +395,26 @@ def test_mlp_block(S, m, hidden, inter, rank, na):
     qd, pd = device_weight(S, wd)
     lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
     ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
-    out = S.w8a8_mlp_block(to_dev(x), to_dev(delta), pgu, lgu, pd, ld, to_dev(ids), enabled=True)
+    out = S.w8a8_mlp_block(to_dev(x), to_dev(delta), pgu, lgu, pd, ld, to_dev(ids), enabled=True, keep_normalized=True)
     S.check_status()
-    want = O.mlp_block(x, delta, qgu, ga, gb, s, qd, da, db, s, ids)
     got = to_np(out)
     assert got.shape == (m, hidden)
-    # composed path: a one-ulp difference in h can move an int8 code of the down input, so the
-    # comparison is by tolerance only (relative L2 and max-abs), as for every unpinned boundary
-    assert O.relative_l2(got, want) < 2e-3
-    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
+    # stage by stage on what the kernels themselves produced: rows of h / xn are in the GEMM's row order
+    perm, h, hq, sh, xn = [to_np(t.clone()) for t in S.w8a8_mlp_stage_regions(m, hidden, inter, na, out.device)]
+    order = perm if m > 128 else np.arange(m)
+    step = O.bf16_ulp_distance(xn, O.rms_norm(x, delta)[order])
+    assert step.max() <= 1
+    check_projection_chain(S, "mlp front", xn, qgu, pgu, (ga, gb, s), lgu, ids[order], h, "swiglu")
+    hcodes, hscales = O.dynamic_group_quantize(h, inter)
+    np.testing.assert_array_equal(hq, hcodes[:, 0, :])
+    np.testing.assert_array_equal(sh, hscales[:, 0])
+    check_projection_chain(S, "mlp back", h, qd, pd, (da, db, s), ld, ids[order], got[order], "residual",
+                           residual=x[order])
+    # and the composed block from x within the stated bars (the RMSNorm boundary in between is not pinned)
+    want = O.mlp_block(x, delta, qgu, ga, gb, s, qd, da, db, s, ids)
+    diff = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert O.relative_l2(got, want) < REL_L2
+    assert int(((diff > MAX_ABS) & (O.bf16_ulp_distance(got, want) > 1)).sum()) <= max(2, diff.size // 5000)
 
 
 @pytest.mark.parametrize("m,hidden,inter,rank,na", [(300, 512, 640, 32, 4), (1000, 256, 400, 16, 9)])
@@ -476,8 +490,9 @@ def test_tensor_parallel_block_emulated_on_one_gpu(S, tp):
     S.check_status()
     want = O.tp_shard_mlp_reference(x, delta, qgu, ga, gb, s, wd, da, db, s, ids, tp)
     got = to_np(out)
-    assert O.relative_l2(got, want) < 2e-3
-    assert np.abs(got.astype(np.float32) - want.astype(np.float32)).max() < 0.1
+    diff = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert O.relative_l2(got, want) < REL_L2
+    assert int(((diff > MAX_ABS) & (O.bf16_ulp_distance(got, want) > 1)).sum()) <= max(2, diff.size // 5000)
 
 
 @pytest.mark.parametrize("tp", [2, 4])

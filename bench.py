@@ -335,7 +335,8 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                 return TensorParallelMLPStack([TensorParallelMLP(*b) for b in blks], num_chunks=args.tp_chunks,
                                               reserve_sms=args.tp_reserve_sms,
                                               sequence_parallel=bool(args.tp_sequence_parallel),
-                                              peer_scatter=False if args.tp_peer_scatter == "off" else args.tp_peer_scatter)
+                                              peer_scatter=False if args.tp_peer_scatter == "off" else args.tp_peer_scatter,
+                                              exchange_ctas=args.tp_exchange_ctas)
 
             tp_stack = make_stack(blocks)
         x_dev = x_host.to(device)
@@ -786,17 +787,22 @@ def main():
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
                     help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
                          "0: one fp32 all-reduce per chunk")
-    ap.add_argument("--tp-reserve-sms", type=int, default=8,
+    ap.add_argument("--tp-reserve-sms", type=int, default=-1,
                     help="SMs the GEMMs leave to the second stream's small kernels while chunks overlap (N > 1): the "
-                         "one-word all-reduce, the finalize / quantise kernels of the rank's own rows, the gathers")
-    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "epilogue", "copy", "off"],
+                         "fused exchange kernel (or the one-word all-reduce, finalize / quantise kernels and gathers of the "
+                         "other forms); -1 = 8 on two GPUs, 16 on more")
+    ap.add_argument("--tp-exchange-ctas", type=int, default=0, help="CTAs of the fused exchange kernel (0 = 4 per reserved SM)")
+    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "fused", "epilogue", "copy", "off"],
                     help="how the fp32 partial sums reach the rank that owns the rows: stores from the down GEMM's "
-                         "epilogue into the owner's memory, copy-engine pushes on the second stream, or (off) the "
-                         "NCCL reduce-scatter; auto = epilogue on 2 GPUs, copy on more")
+                         "epilogue into the owner's memory, copy-engine pushes on the second stream, the fused exchange "
+                         "kernel that pulls them (no collective between blocks), or (off) the NCCL reduce-scatter; "
+                         "auto = epilogue on 2 GPUs, fused on more")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="> 0: sets NCCL_MAX_CTAS (tuning aid)")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()
+    if args.tp_reserve_sms < 0:
+        args.tp_reserve_sms = 8 if args.gpus <= 2 else 16
     if args.impl == "reference":
         # before NumPy loads its BLAS: all host threads, whatever the launcher set for its per-GPU workers
         for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):

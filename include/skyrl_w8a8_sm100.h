@@ -423,6 +423,58 @@ SKYRL_API int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* args, i
  * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 6, 64]. */
 SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                      size_t* offsets);
+/* Fused exchange between two blocks of a sequence-parallel stack: ONE kernel per rank and row chunk in place
+ * of a reduce-scatter, the finalize kernel, the next block's quantiser stage and the gathers of its results.
+ * XLA inserts separate collectives around separately scheduled fusions here (the all-reduce behind the
+ * ("tp", "fsdp") sharded down_proj, skyrl/tx/models/qwen3_5.py:644).
+ *
+ * For this rank's sorted rows [row_begin, row_begin + row_count) of a chunk the kernel
+ *   - waits (bounded) until wait_flags[s] >= wait_value for every rank s: rank s raises its word in this
+ *     rank's memory with skyrl_w8a8_tp_signal_sm100_v1 once its down GEMM of the chunk has completed,
+ *   - reads the row's fp32 partial sums from partials[s] of EVERY rank (own buffer and peer mappings; plain
+ *     loads) and adds them in ascending s (skyrl/tx/kernels/quantized_lora.py:253),
+ *   - writes bf16(sum) + residual to `out` (row perm[i]; row i with SKYRL_MLP_FINALIZE_SORTED set in `block`),
+ *   - and, when `next` is given, runs the next block's RMSNorm + int8 quantiser on that row and stores the codes
+ *     and the scale into the workspace of EVERY rank (peer_workspaces[r], all of the layout of `next`; plain
+ *     stores), then projects the normalised rows onto LoRA-A and stores the parts into every workspace too.
+ * Finally signal_flags[r] (one word in each rank's memory, NULL entries skipped) are set to signal_value: the
+ * rows this rank owns have arrived everywhere.  A rank starts the next block's GEMMs on a chunk once the
+ * word of every rank has reached that value (skyrl_w8a8_tp_wait_sm100_v1 on the GEMM's stream).
+ *
+ * `block` is the argument block of the skyrl_w8a8_mlp_block_sm100_v1 call that produced the partial sums (its
+ * workspace holds the row permutation; x / residual give the residual), `next` that of the next block's call
+ * on the same chunk (NULL behind the last block: finalize only).  Flag values must only grow from call to call.
+ * No TMA and no multicast instruction touches peer memory; if a wait runs out, status 105 is recorded and the
+ * kernel returns. */
+typedef struct SkyrlW8A8TpExchangeArgs {
+  uint32_t struct_size;
+  int32_t tp;                  /* ranks of the group, 1 ... 8                                       */
+  int32_t row_begin, row_count;/* this rank's sorted rows                                           */
+  int32_t wait_value;
+  int32_t signal_value;
+  int32_t grid_ctas;           /* CTAs of the exchange kernel; 0 = 48                               */
+  int32_t reserved;
+  const float* partials[8];    /* rank s's fp32 [m, hidden] partial sums in sorted row order        */
+  const int32_t* wait_flags;   /* tp words in this rank's memory, or NULL (no wait)                 */
+  void* peer_workspaces[8];    /* rank r's workspace of the next block (used when next != NULL)     */
+  int32_t* signal_flags[8];
+  void* out;                   /* bf16 [m, hidden]                                                  */
+} SkyrlW8A8TpExchangeArgs;
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8TpExchangeArgs) == 240, "SkyrlW8A8TpExchangeArgs layout");
+SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8TpExchangeArgs, partials) == 32 && offsetof(SkyrlW8A8TpExchangeArgs, wait_flags) == 96 &&
+                     offsetof(SkyrlW8A8TpExchangeArgs, peer_workspaces) == 104 &&
+                     offsetof(SkyrlW8A8TpExchangeArgs, signal_flags) == 168 && offsetof(SkyrlW8A8TpExchangeArgs, out) == 232,
+                 "SkyrlW8A8TpExchangeArgs layout");
+SKYRL_API int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* block, const SkyrlW8A8MlpArgs* next,
+                                        const SkyrlW8A8TpExchangeArgs* exchange, skyrl_stream_t stream);
+/* After everything enqueued so far on `stream` has completed, set `count` (<= 8) flag words, each possibly in
+ * another rank's memory (NULL entries skipped), to `value` with release semantics at system scope. */
+SKYRL_API int skyrl_w8a8_tp_signal_sm100_v1(int32_t* const* flags, int32_t count, int32_t value, skyrl_stream_t stream);
+/* Hold `stream` until `count` flag words in this rank's memory have all reached `value` (bounded: after 2 s
+ * status 105 is recorded in *status and the stream continues). */
+SKYRL_API int skyrl_w8a8_tp_wait_sm100_v1(const int32_t* flags, int32_t count, int32_t value, int32_t* status,
+                                skyrl_stream_t stream);
+
 /* Byte offsets of the intermediate results a finished skyrl_w8a8_mlp_block_sm100_v1 call leaves in its
  * workspace, for stage-by-stage parity checks: offsets[0] row permutation int32 [m] (sorted position ->
  * token row; meaningful for m > 128 with adapter ids, otherwise rows keep token order), offsets[1]

@@ -33,6 +33,7 @@ ERROR_NAMES = {
 STATUS_NAMES = {
     101: "bounded wait ran out in the TMA producer", 102: "bounded wait ran out in the MMA issuer",
     103: "bounded wait ran out in the epilogue", 104: "bounded wait ran out in the LoRA step",
+    105: "bounded wait for another rank's flag ran out",
     190: "self-test wait ran out (expected)", 201: "adapter id outside [0, num_adapters)", 202: "tile list overflow", 203: "scattered partial-sum row without an owner",
 }
 
@@ -84,6 +85,15 @@ class MlpArgs(C.Structure):
     ]
 
 
+class TpExchangeArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("tp", C.c_int32), ("row_begin", C.c_int32), ("row_count", C.c_int32),
+        ("wait_value", C.c_int32), ("signal_value", C.c_int32), ("grid_ctas", C.c_int32), ("reserved", C.c_int32),
+        ("partials", C.c_void_p * 8), ("wait_flags", C.c_void_p), ("peer_workspaces", C.c_void_p * 8),
+        ("signal_flags", C.c_void_p * 8), ("out", C.c_void_p),
+    ]
+
+
 # name -> (restype, argtypes); every symbol the header declares
 SYMBOLS = {
     "skyrl_w8a8_abi_version": (C.c_int, []),
@@ -114,6 +124,10 @@ SYMBOLS = {
     "skyrl_w8a8_mlp_tp_prepare_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_int32, C.c_int32, C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_regions": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                    C.POINTER(C.c_size_t)]),
+    "skyrl_w8a8_mlp_tp_exchange_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.POINTER(MlpArgs), C.POINTER(TpExchangeArgs),
+                                                      C.c_void_p]),
+    "skyrl_w8a8_tp_signal_sm100_v1": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_void_p]),
+    "skyrl_w8a8_tp_wait_sm100_v1": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "skyrl_w8a8_mlp_workspace_stage_regions": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                                          C.POINTER(C.c_size_t)]),
     "skyrl_w8a8_mlp_tp_unsort_sm100_v1": (C.c_int, [C.POINTER(MlpArgs), C.c_void_p, C.c_void_p, C.c_void_p]),

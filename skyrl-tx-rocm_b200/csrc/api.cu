@@ -676,6 +676,92 @@ extern "C" int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32
   return SKYRL_OK;
 }
 
+extern "C" int skyrl_w8a8_tp_signal_sm100_v1(int32_t* const* flags, int32_t count, int32_t value, skyrl_stream_t stream) {
+  return launch_tp_signal(flags, count, value, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_w8a8_tp_wait_sm100_v1(const int32_t* flags, int32_t count, int32_t value, int32_t* status,
+                                            skyrl_stream_t stream) {
+  return launch_tp_wait(flags, count, value, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* blk, const SkyrlW8A8MlpArgs* next,
+                                                    const SkyrlW8A8TpExchangeArgs* x, skyrl_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (x == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: exchange args are null");
+  if (x->struct_size != sizeof(SkyrlW8A8TpExchangeArgs))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: struct_size %u does not match ABI v%d (%zu)", x->struct_size,
+                SKYRL_W8A8_ABI_VERSION, sizeof(SkyrlW8A8TpExchangeArgs));
+  if (x->tp < 1 || x->tp > 8) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: tp must be in [1, 8], got %d", x->tp);
+  if (x->out == nullptr) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: out is null");
+  MlpPlan pl;
+  int rc = plan_mlp(blk, "tp_exchange", &pl);
+  if (rc) return rc;
+  if (pl.rows_path) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: needs more than %d rows", ROWS_PATH_MAX_M);
+  if (x->row_count <= 0 || x->row_begin < 0 || x->row_begin + x->row_count > blk->m)
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: rows [%d, %d) are outside [0, %d)", x->row_begin,
+                x->row_begin + x->row_count, blk->m);
+  TpExchangeLaunch e = {};
+  e.tp = x->tp;
+  for (int s = 0; s < x->tp; ++s) e.partial[s] = x->partials[s];
+  e.row_begin = x->row_begin;
+  e.row_count = x->row_count;
+  e.hidden = blk->hidden;
+  e.perm = pl.perm;
+  e.residual = blk->residual != nullptr ? blk->residual : blk->x;
+  e.out = x->out;
+  e.out_sorted = (blk->flags & SKYRL_MLP_FINALIZE_SORTED) != 0;
+  e.wait_flags = x->wait_flags;
+  e.wait_value = x->wait_value;
+  e.status = blk->status;
+  e.grid_ctas = x->grid_ctas;
+  MlpPlan np;
+  const bool lora = next != nullptr && next->rank > 0;
+  if (next != nullptr) {
+    if ((rc = plan_mlp(next, "tp_exchange (next block)", &np))) return rc;
+    if (next->m != blk->m || next->hidden != blk->hidden)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: the next block has another shape");
+    if (x->row_begin < np.row0 || x->row_begin + x->row_count > np.row0 + np.rows)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: rows [%d, %d) are not inside the next block's chunk [%d, %d)",
+                  x->row_begin, x->row_begin + x->row_count, np.row0, np.row0 + np.rows);
+    unsigned char* const local = static_cast<unsigned char*>(next->workspace);
+    const size_t off_xq = reinterpret_cast<unsigned char*>(np.w.xq) - local;
+    const size_t off_sx = reinterpret_cast<unsigned char*>(np.w.sx) - local;
+    e.quantize = true;
+    e.delta = next->rms_delta;
+    e.eps = next->rms_eps;
+    e.xn = lora ? np.w.xn : nullptr;
+    for (int r = 0; r < x->tp; ++r) {
+      if (x->peer_workspaces[r] == nullptr || (reinterpret_cast<uintptr_t>(x->peer_workspaces[r]) & 1023u) != 0)
+        return fail(SKYRL_ERR_WORKSPACE, "tp_exchange: workspace of rank %d is null or not 1024-byte aligned", r);
+      unsigned char* const base = static_cast<unsigned char*>(x->peer_workspaces[r]);
+      e.xq_dst[r] = reinterpret_cast<int8_t*>(base + off_xq);
+      e.sx_dst[r] = reinterpret_cast<float*>(base + off_sx);
+    }
+  }
+  if ((rc = launch_tp_exchange(e, stream))) return rc;
+  if (lora) {
+    // LoRA-A projection of the rows just normalised, its parts stored into every rank's workspace
+    unsigned char* const local = static_cast<unsigned char*>(next->workspace);
+    const size_t off_z = reinterpret_cast<unsigned char*>(np.w.z_parts) - local;
+    void* extra[8];
+    int extra_count = 0;
+    for (int r = 0; r < x->tp; ++r) {
+      void* dst = static_cast<unsigned char*>(x->peer_workspaces[r]) + off_z;
+      if (dst != static_cast<void*>(np.w.z_parts)) extra[extra_count++] = dst;
+    }
+    if (extra_count > 7) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: this rank's workspace is not among peer_workspaces");
+    if ((rc = launch_lora_a_proj(np.w.xn, next->m, next->hidden, next->gu_a_packed, next->gu_scaling, np.na, next->rank,
+                                 np.tiles, np.num_tiles, np.mt, np.w.z_parts, next->status, stream, x->row_begin,
+                                 x->row_begin + x->row_count, extra, extra_count)))
+      return rc;
+  }
+  bool any = false;
+  for (int r = 0; r < x->tp; ++r) any = any || x->signal_flags[r] != nullptr;
+  if (any) return launch_tp_signal(x->signal_flags, x->tp, x->signal_value, stream);
+  return SKYRL_OK;
+}
+
 extern "C" int skyrl_w8a8_mlp_workspace_stage_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                                        size_t* offsets) {
   if (m <= 0 || hidden <= 0 || inter <= 0 || offsets == nullptr)

@@ -72,7 +72,8 @@ int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta,
 int launch_quant_stream(const void* x, const float* row_amax, int m, int k, void* xq, float* sx, cudaStream_t stream);
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
-                       int32_t* status, cudaStream_t stream, int row_lo = 0, int row_hi = -1);
+                       int32_t* status, cudaStream_t stream, int row_lo = 0, int row_hi = -1,
+                       void* const* extra_dests = nullptr, int extra_count = 0);  // extra copies of the rows written
 // Tile width and K split the GEMM launcher chooses for a shape (deterministic per device).
 struct GemmPlan {
   int bn_eff;
@@ -96,6 +97,29 @@ int launch_tp_finalize(const float* reduced, const int32_t* perm, const void* re
                        int row_begin, int row_count, cudaStream_t stream, bool out_sorted = false);
 int launch_tp_finalize_slabs(const float* const* slabs, int num_slabs, const int32_t* perm, const void* residual,
                              void* out, int hidden, int row_begin, int row_count, cudaStream_t stream, bool out_sorted);
+// Tensor-parallel exchange between two blocks (tp_exchange_sm100.cu).
+struct TpExchangeLaunch {
+  int tp;
+  const float* partial[8];
+  int row_begin, row_count, hidden;
+  const int32_t* perm;
+  const void* residual;
+  void* out;
+  bool out_sorted;
+  bool quantize;
+  const void* delta;
+  float eps;
+  int8_t* xq_dst[8];
+  float* sx_dst[8];
+  void* xn;
+  const int32_t* wait_flags;
+  int32_t wait_value;
+  int32_t* status;
+  int grid_ctas;
+};
+int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream);
+int launch_tp_signal(int32_t* const* flags, int count, int32_t value, cudaStream_t stream);
+int launch_tp_wait(const int32_t* flags, int count, int32_t value, int32_t* status, cudaStream_t stream);
 int launch_unsort_rows(const void* sorted_rows, const int32_t* perm, void* out, int m, int hidden, cudaStream_t stream);
 
 }  // namespace skyrl

@@ -38,7 +38,9 @@ struct ProjParams {
   const float* scaling;
   const int4* tiles;
   const int32_t* num_tiles;
-  __nv_bfloat16* z_parts;  // [m, 6, 64]: adapter slot 0 parts (hi, mid, lo), adapter slot 1 parts
+  __nv_bfloat16* z_parts[8];  // [m, 6, 64]: adapter slot 0 parts (hi, mid, lo), adapter slot 1 parts; the same rows
+  int z_count;                // are written to every one of the z_count destinations (a tensor-parallel rank hands
+                              // its rows to every peer's workspace with plain stores; one destination otherwise)
   int row_lo, row_hi;      // rows written
   int32_t* status;
   int k;
@@ -157,18 +159,22 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
             mid[i] = pack_bf16x2(m0, m1);
             lo[i] = pack_bf16x2(__fsub_rn(r0, m0), __fsub_rn(r1, m1));  // <= 8 bits left: exact in bf16
           }
-          __nv_bfloat16* base = p.z_parts + row * PROJ_Z_ROW + dslot * 3 * PROJ_N + (cc % (PROJ_N / 32)) * 32;
-          uint4* dh = reinterpret_cast<uint4*>(base);
-          uint4* dm = reinterpret_cast<uint4*>(base + PROJ_N);
-          uint4* dl = reinterpret_cast<uint4*>(base + 2 * PROJ_N);
+          const int64_t off = row * PROJ_Z_ROW + dslot * 3 * PROJ_N + (cc % (PROJ_N / 32)) * 32;
+          for (int d = 0; d < p.z_count; ++d) {
+            __nv_bfloat16* base = p.z_parts[d] + off;
+            uint4* dh = reinterpret_cast<uint4*>(base);
+            uint4* dm = reinterpret_cast<uint4*>(base + PROJ_N);
+            uint4* dl = reinterpret_cast<uint4*>(base + 2 * PROJ_N);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
-            dm[g] = make_uint4(mid[4 * g], mid[4 * g + 1], mid[4 * g + 2], mid[4 * g + 3]);
-            dl[g] = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+            for (int g = 0; g < 4; ++g) {
+              dh[g] = make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+              dm[g] = make_uint4(mid[4 * g], mid[4 * g + 1], mid[4 * g + 2], mid[4 * g + 3]);
+              dl[g] = make_uint4(lo[4 * g], lo[4 * g + 1], lo[4 * g + 2], lo[4 * g + 3]);
+            }
           }
         }
       }
+      if (p.z_count > 1) __threadfence_system();  // stores into other GPUs' memory are performed before the kernel ends
     }
   }
 
@@ -187,7 +193,8 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
 
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
-                       int32_t* status, cudaStream_t stream, int row_lo, int row_hi) {
+                       int32_t* status, cudaStream_t stream, int row_lo, int row_hi, void* const* extra_dests,
+                       int extra_count) {
   if (x == nullptr || a_packed == nullptr || scaling == nullptr || tiles == nullptr || num_tiles == nullptr ||
       z_parts == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: null buffer");
@@ -211,7 +218,15 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
   p.scaling = scaling;
   p.tiles = reinterpret_cast<const int4*>(tiles);
   p.num_tiles = num_tiles;
-  p.z_parts = static_cast<__nv_bfloat16*>(z_parts);
+  if (extra_count < 0 || extra_count > 7 || (extra_count > 0 && extra_dests == nullptr))
+    return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: at most 7 extra destinations");
+  p.z_parts[0] = static_cast<__nv_bfloat16*>(z_parts);
+  p.z_count = 1;
+  for (int d = 0; d < extra_count; ++d) {
+    if (extra_dests[d] == nullptr || !aligned16(extra_dests[d]))
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: extra destination %d is null or not 16-byte aligned", d);
+    p.z_parts[p.z_count++] = static_cast<__nv_bfloat16*>(extra_dests[d]);
+  }
   p.row_lo = row_lo;
   p.row_hi = row_hi < 0 ? m : row_hi;
   p.status = status;

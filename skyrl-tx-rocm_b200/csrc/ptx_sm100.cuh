@@ -20,6 +20,7 @@ enum : int {
   STATUS_TIMEOUT_MMA = 102,
   STATUS_TIMEOUT_EPILOGUE = 103,
   STATUS_TIMEOUT_LORA = 104,
+  STATUS_TIMEOUT_PEER = 105,  // a flag another rank raises did not arrive within the limit
   STATUS_BAD_ADAPTER_ID = 201,
   STATUS_TILE_OVERFLOW = 202,
   STATUS_SELFTEST_TIMEOUT = 190,  // the wait of the self-test kernel ran out, as it is meant to

@@ -5,6 +5,7 @@
 //   * pack kernels ....... one-time layout changes of weights and LoRA tables
 #include "common.cuh"
 #include "ptx_sm100.cuh"
+#include "quant_row.cuh"
 
 namespace skyrl {
 
@@ -159,24 +160,6 @@ int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int
 // bf16 (skyrl/tx/models/qwen3_5.py:274-278), then amax / 127 and
 // rint(x / scale) with IEEE division (skyrl/tx/kernels/quantized_lora.py:207-211).
 // ----------------------------------------------------------------------------
-constexpr int QUANT_THREADS = 256;
-
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = is_max ? fmaxf(v, other) : v + other;
-  }
-  __syncthreads();  // protects `red` against the previous use
-  if (lane == 0) red[warp] = v;
-  __syncthreads();
-  float r = red[0];
-#pragma unroll
-  for (int w = 1; w < QUANT_THREADS / 32; ++w) r = is_max ? fmaxf(r, red[w]) : r + red[w];
-  return r;
-}
-
 __global__ void __launch_bounds__(QUANT_THREADS)
 rms_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, const __nv_bfloat16* __restrict__ delta,
                  float eps, const int32_t* __restrict__ row_map, int k, int8_t* __restrict__ xq,
@@ -207,50 +190,12 @@ rms_quant_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride, cons
       }
     }
   }
-  if (norm) {
-    ss = block_reduce(ss, false, red);
-    const float var = __fdiv_rn(ss, static_cast<float>(k));
-    const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, eps)));
-    const uint4* dvec = reinterpret_cast<const uint4*>(delta);
-    uint4* xn_row = xn != nullptr ? reinterpret_cast<uint4*>(xn + static_cast<int64_t>(out_row) * k) : nullptr;
-    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-      const uint4 u = row[v];
-      const uint4 d = __ldg(dvec + v);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-      const uint32_t dw[4] = {d.x, d.y, d.z, d.w};
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = __fmul_rn(__fmul_rn(bf16_lo(w[j]), rinv), __fadd_rn(1.0f, bf16_lo(dw[j])));
-        const float b = __fmul_rn(__fmul_rn(bf16_hi(w[j]), rinv), __fadd_rn(1.0f, bf16_hi(dw[j])));
-        o[j] = pack_bf16x2(a, b);
-        amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
-      }
-      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-      row[v] = ov;
-      if (xn_row != nullptr) xn_row[v] = ov;
-    }
-  } else if (xn != nullptr) {
-    uint4* xn_row = reinterpret_cast<uint4*>(xn + static_cast<int64_t>(out_row) * k);
-    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) xn_row[v] = row[v];
-  }
-  amax = block_reduce(amax, true, red);
-  const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
-  const float rcp = quant_rcp(scale);
-  if (threadIdx.x == 0) sx[out_row] = scale;
-
-  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(out_row) * k);
-  for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-    const uint4 u = row[v];
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-    int q[8];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      q[2 * j] = quant_code(bf16_lo(w[j]), scale, rcp);
-      q[2 * j + 1] = quant_code(bf16_hi(w[j]), scale, rcp);
-    }
-    dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
-  }
+  QuantDests dst;
+  dst.count = 1;
+  dst.xq[0] = xq + static_cast<int64_t>(out_row) * k;
+  dst.sx[0] = sx + out_row;
+  quant_row_from_smem(row, k, delta, eps, ss, amax, red, dst,
+                      xn != nullptr ? reinterpret_cast<uint4*>(xn + static_cast<int64_t>(out_row) * k) : nullptr);
 }
 
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,

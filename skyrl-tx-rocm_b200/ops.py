@@ -32,6 +32,7 @@ __all__ = (
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator", "w8a8_lora_linear_f32",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
     "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "w8a8_mlp_stage_regions",
+    "w8a8_mlp_tp_exchange", "tp_signal", "tp_wait", "use_workspace",
     "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
     "check_status", "bounded_wait_selftest", "RMS_EPS",
@@ -249,6 +250,7 @@ def pack_lora(lora_a: torch.Tensor, lora_b: torch.Tensor, lora_scaling, *, in_fe
 # per-device scratch (torch owns the memory; the C ABI never allocates)
 # --------------------------------------------------------------------------- #
 _workspaces: dict[int, torch.Tensor] = {}
+_pinned_workspaces: set[int] = set()
 _status: dict[int, torch.Tensor] = {}
 
 
@@ -256,10 +258,32 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
     ws = _workspaces.get(idx)
     if ws is None or ws.numel() < nbytes + 1024:
+        if idx in _pinned_workspaces:
+            raise SkyrlKernelError(f"the workspace registered with use_workspace() has {ws.numel()} bytes, this call needs "
+                                   f"{nbytes + 1024}; register a larger one or release it with use_workspace(None)")
         ws = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
         _workspaces[idx] = ws
     off = (-ws.data_ptr()) % 1024
     return ws[off: off + nbytes]
+
+
+def use_workspace(buffer: torch.Tensor | None, device=None) -> None:
+    """Make the operators of `buffer`'s device carve their scratch from `buffer` (uint8, CUDA) instead of a
+    tensor of their own: a tensor-parallel stack registers a piece of peer-mapped (symmetric) memory here so
+    that other ranks can store the rows they prepared straight into this rank's workspace.  The operators
+    raise if a call needs more than the buffer holds.  `None` releases the registration."""
+    if buffer is None:
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        _pinned_workspaces.discard(idx)
+        _workspaces.pop(idx, None)
+        return
+    _require_cuda(buffer, "buffer")
+    if buffer.dtype != torch.uint8 or buffer.ndim != 1 or not buffer.is_contiguous():
+        raise TypeError("the workspace must be a contiguous one-dimensional uint8 tensor")
+    idx = buffer.device.index if buffer.device.index is not None else torch.cuda.current_device()
+    _workspaces[idx] = buffer
+    _pinned_workspaces.add(idx)
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -607,7 +631,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    enabled: bool = False, eps: float = RMS_EPS, out=None, down_epilogue: int = EPI_RESIDUAL,
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
                    gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
-                   row_amax_from_epilogue: bool = True, keep_normalized: bool = False):
+                   row_amax_from_epilogue: bool = True, keep_normalized: bool = False, build_only: bool = False):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -621,7 +645,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     GEMM store each owner's rows of the fp32 partial sums straight into that
     owner's slab (device addresses, possibly peer mappings) instead of `out`.
     `row_amax_from_epilogue=False` makes the quantiser of h find the row absmax itself (a cross-check:
-    both forms give identical bits)."""
+    both forms give identical bits).  `build_only=True` validates and returns the call handle without
+    enqueuing anything (the handle of the NEXT block is an argument of `w8a8_mlp_tp_exchange`)."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
         raise RuntimeError("the W8A8 MLP block is disabled by default")
@@ -699,6 +724,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
             raise ValueError("at most 8 scatter owners")
         for i, addr in enumerate(scatter[1]):
             a.tp_scatter_bases[i] = int(addr)
+    if build_only:
+        return out, (a, x2, delta, ids, r2)
     if prepare_rows is not None:
         _lib.check(lib.skyrl_w8a8_mlp_tp_prepare_sm100_v1(C.byref(a), int(prepare_rows[0]), int(prepare_rows[1]),
                                                         _stream()), "w8a8_mlp_tp_prepare")
@@ -754,6 +781,63 @@ def w8a8_mlp_tp_finalize_slabs(call, slab_addresses, out: torch.Tensor, row_begi
     finally:
         a.flags = flags
     return out
+
+
+def w8a8_mlp_tp_exchange(call, next_call, out: torch.Tensor, *, tp: int, row_begin: int, row_count: int, partials,
+                         wait_flags=None, wait_value: int = 0, peer_workspaces=None, signal_flags=None,
+                         signal_value: int = 0, sorted_out: bool = False, grid_ctas: int = 0):
+    """Fused exchange between two blocks of a sequence-parallel stack (one kernel per rank and row chunk).
+
+    `call` is the handle of the `w8a8_mlp_block(..., down_epilogue=EPI_PARTIAL_F32, return_call=True)` call that
+    produced this rank's partial sums, `next_call` the handle of the next block's call on the same chunk
+    (`build_only=True`; None behind the last block).  `partials` lists every rank's partial-sum buffer as a
+    device address (own buffer and peer mappings), `peer_workspaces` every rank's workspace base address,
+    `wait_flags` an int32 tensor of `tp` words in this rank's memory that the ranks raise to `wait_value` when
+    their partial sums are complete, `signal_flags` one flag address per rank that this call sets to
+    `signal_value` once the rows it prepared have been stored everywhere."""
+    a = call[0]
+    lib = _lib.load()
+    x = _lib.TpExchangeArgs()
+    x.struct_size = C.sizeof(_lib.TpExchangeArgs)
+    x.tp, x.row_begin, x.row_count = int(tp), int(row_begin), int(row_count)
+    x.wait_value, x.signal_value, x.grid_ctas = int(wait_value), int(signal_value), int(grid_ctas)
+    if len(partials) != tp:
+        raise ValueError(f"{tp} partial-sum buffers wanted, got {len(partials)}")
+    for s_, addr in enumerate(partials):
+        x.partials[s_] = int(addr)
+    x.wait_flags = wait_flags.data_ptr() if wait_flags is not None else None
+    if next_call is not None:
+        if peer_workspaces is None or len(peer_workspaces) != tp:
+            raise ValueError(f"{tp} workspace addresses wanted for the next block")
+        for r, addr in enumerate(peer_workspaces):
+            x.peer_workspaces[r] = int(addr)
+    if signal_flags is not None:
+        for r, addr in enumerate(signal_flags):
+            x.signal_flags[r] = int(addr) if addr else None
+    x.out = out.data_ptr()
+    flags = a.flags
+    a.flags = (flags | _lib.MLP_FINALIZE_SORTED) if sorted_out else (flags & ~_lib.MLP_FINALIZE_SORTED)
+    try:
+        _lib.check(lib.skyrl_w8a8_mlp_tp_exchange_sm100_v1(C.byref(a), C.byref(next_call[0]) if next_call is not None else None,
+                                                         C.byref(x), _stream()), "w8a8_mlp_tp_exchange")
+    finally:
+        a.flags = flags
+    return out
+
+
+def tp_signal(flag_addresses, value: int) -> None:
+    """After the work enqueued so far on the current stream: set the flag words at `flag_addresses` (device
+    addresses, possibly in other ranks' memory; None entries are skipped) to `value`."""
+    ptrs = (C.c_void_p * len(flag_addresses))(*[int(p) if p else None for p in flag_addresses])
+    _lib.check(_lib.load().skyrl_w8a8_tp_signal_sm100_v1(ptrs, len(flag_addresses), int(value), _stream()), "tp_signal")
+
+
+def tp_wait(flags: torch.Tensor, count: int, value: int) -> None:
+    """Hold the current stream until `count` int32 flag words of `flags` (this rank's memory) have reached
+    `value`; bounded (status 105 after 2 s, reported by `check_status`)."""
+    st = _status_word(flags.device)
+    _lib.check(_lib.load().skyrl_w8a8_tp_wait_sm100_v1(flags.data_ptr(), int(count), int(value), st.data_ptr(), _stream()),
+               "tp_wait")
 
 
 def w8a8_mlp_tp_unsort(call, sorted_rows: torch.Tensor, out: torch.Tensor):

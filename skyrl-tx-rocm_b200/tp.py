@@ -144,21 +144,32 @@ class TensorParallelMLPStack:
                   owner's rows on the second stream (no SM involved), so the transfer
                   also overlaps the other chunk's gate_up GEMM; best once the transfer
                   outlasts the down GEMM (4 and 8 ranks).
-    "auto" (default) picks by group size.  If symmetric memory cannot be set up the
-    NCCL reduce-scatter is used.
+      "fused"     no collective and no copy at all between two blocks: the down GEMM leaves its partial
+                  sums in this rank's symmetric buffer and raises a flag on every peer; ONE kernel per
+                  chunk then pulls the owned rows' partial sums from every rank over NVLink, adds them
+                  in rank order, finalizes, runs the next block's RMSNorm + quantiser and stores codes,
+                  scales and (after the LoRA-A projection) the projection parts straight into every
+                  rank's workspace, which lives in symmetric memory too; a second flag tells the peers
+                  that the rows have arrived (`ops.w8a8_mlp_tp_exchange`).  Block 0 is prepared by every
+                  rank for all rows (x is replicated), so the first exchange is the one behind block 0.
+    "auto" (default) = "fused" on more than 2 ranks, "epilogue" on 2.  If symmetric memory cannot be set up
+    the NCCL reduce-scatter is used.
 
     Blocks of fewer than 129 rows take the small-batch path and are not chunked.
     """
 
     def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 8, sm_count: int = 148,
-                 sequence_parallel: bool = True, peer_scatter="auto"):
+                 sequence_parallel: bool = True, peer_scatter="auto", exchange_ctas: int = 0):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self.sequence_parallel = sequence_parallel
         self.peer_scatter = peer_scatter
+        self.exchange_ctas = exchange_ctas if exchange_ctas > 0 else max(8, 4 * reserve_sms)
         self.scatter_mode = None
+        self._fused = None        # symmetric buffers of the fused exchange
+        self._seq = 0             # flag values only grow: one per block and forward pass
         self._slabs = None        # (shape key, local tensor, handle, per-rank base addresses, peer views)
         self._coalesce = True     # gathers of the three prepared regions go out as one NCCL group
         self._token = None
@@ -240,6 +251,11 @@ class TensorParallelMLPStack:
         spans = plan["spans"]
         self._buffers(x)
         if self.sequence_parallel and tp > 1 and m > ops.TILE_ROWS and self.blocks and plan["even"]:
+            mode = self.peer_scatter
+            if mode == "auto":
+                mode = "fused" if tp > 2 else "epilogue"
+            if mode == "fused" and self._fused_buffers(x, tp):
+                return self._forward_fused(x, adapter_ids, spans, chunks, tp, timing_events)
             return self._forward_sequence_parallel(x, adapter_ids, spans, chunks, tp, timing_events)
         main = torch.cuda.current_stream()
         prev_done = [None] * len(spans)
@@ -289,7 +305,7 @@ class TensorParallelMLPStack:
         lora = first.gate_up_lora is not None
         slab_ptrs = self._peer_slabs(x, tp) if self.peer_scatter else None
         mode = self.peer_scatter if slab_ptrs is not None else False
-        if mode in (True, "auto"):
+        if mode in (True, "auto", "fused"):   # "fused" lands here only when its buffers could not be set up
             mode = "epilogue" if tp <= 2 else "copy"
         peers = self._slabs[4] if slab_ptrs is not None else None
         self.scatter_mode = mode or "nccl"     # what actually delivers the partial sums, for reports
@@ -404,6 +420,140 @@ class TensorParallelMLPStack:
                         self._mark(f"L{l}c{c} finalize+prepare<", comm, "comm")
                         gathered[c] = gather_prepared(c)
                         self._mark(f"L{l}c{c} gather<", comm, "comm")
+            cur = dst
+        for fin, _ in final:
+            main.wait_event(fin)
+        return ops.w8a8_mlp_tp_unsort(final[-1][1], self._sorted, cur)
+
+    # ------------------------------------------------------------------ fused exchange (no collective between blocks)
+    MAX_CHUNK_SLOTS = 16
+
+    def _fused_buffers(self, x, tp):
+        """One symmetric allocation per rank: [fp32 partial sums m x hidden | MLP workspace | flag words].  Returns
+        False (decided together) when symmetric memory is unavailable."""
+        import torch
+        import torch.distributed as dist
+
+        from . import _lib, ops
+
+        m, hidden = x.shape
+        first = self.blocks[0]
+        inter = first.down_weight.in_features
+        na = first.gate_up_lora.num_adapters if first.gate_up_lora is not None else 1
+        key = (m, hidden, inter, na, tp, x.device)
+        if self._fused is not None and self._fused["key"] == key:
+            return True
+        ws_bytes = _lib.load().skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na)
+        up = lambda v: (v + 1023) // 1024 * 1024
+        off_ws = up(m * hidden * 4)
+        off_flags = off_ws + up(ws_bytes + 1024)
+        total = off_flags + 2 * self.MAX_CHUNK_SLOTS * 8 * 4
+        ok, local, ptrs = 1, None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            local = symm.empty((total,), dtype=torch.uint8, device=x.device)
+            handle = symm.rendezvous(local, self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in handle.buffer_ptrs]
+            if len(ptrs) != tp or ptrs[dist.get_rank(self.group)] != local.data_ptr() or any(p % 1024 for p in ptrs):
+                ok = 0
+        except Exception as exc:  # noqa: BLE001 - any failure means "use the collective"
+            import warnings
+
+            warnings.warn(f"symmetric memory unavailable ({exc}); using the NCCL reduce-scatter")
+            ok = 0
+        flag = torch.tensor([ok], device=x.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            self.peer_scatter = "copy"
+            return False
+        local[off_flags:].zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)       # every rank's flag words are zero before anyone raises one
+        self._fused = {
+            "key": key, "local": local, "handle": handle, "ptrs": ptrs, "off_ws": off_ws, "off_flags": off_flags,
+            "partial": local[: m * hidden * 4].view(torch.float32).view(m, hidden),
+            "workspace": local[off_ws: off_ws + ws_bytes + 1024],
+            "flags": local[off_flags:].view(torch.int32).view(2, self.MAX_CHUNK_SLOTS, 8),
+        }
+        ops.use_workspace(self._fused["workspace"])
+        self._seq = 0
+        return True
+
+    def _forward_fused(self, x, adapter_ids, spans, chunks, tp, timing_events):
+        import torch
+        import torch.distributed as dist
+
+        from . import ops
+
+        m, hidden = x.shape
+        rank = dist.get_rank(self.group)
+        main, comm = torch.cuda.current_stream(), self._comm
+        fb = self._fused
+        ptrs, off_ws, off_flags = fb["ptrs"], fb["off_ws"], fb["off_flags"]
+        partial, flags = fb["partial"], fb["flags"]
+        plan = exchange_plan(m, chunks, tp, rank, ops.TILE_ROWS)
+        own = plan["own"]
+        chunk_arg = lambda c: (c, chunks) if chunks > 1 else None
+        layers = len(self.blocks)
+        base = self._seq
+        self._seq += layers
+        self.scatter_mode = "fused"
+
+        def flag_addr(r, kind, c, src):
+            # word [kind][c][src] of rank r's flag block: raised by rank `src`
+            return ptrs[r] + off_flags + ((kind * self.MAX_CHUNK_SLOTS + c) * 8 + src) * 4
+
+        def block_call(blk, src, c, **kw):
+            return ops.w8a8_mlp_block(
+                src, blk.rms_delta, blk.gate_up_weight, blk.gate_up_lora, blk.down_weight, blk.down_lora, adapter_ids,
+                enabled=True, eps=blk.eps, out=partial, down_epilogue=ops.EPI_PARTIAL_F32, return_call=True,
+                chunk=chunk_arg(c), gemm_cta_limit=self.cta_limit if chunks > 1 else 0, **kw)[1]
+
+        # block 0: x is complete on every rank, so every rank prepares all rows itself (once per pass)
+        first = self.blocks[0]
+        self._mark("begin", main, "main")
+        for c, (r0, cnt) in enumerate(spans):
+            block_call(first, x, c, reuse_routing=c > 0, prepare_rows=(r0, cnt))
+        cur = x
+        final = []
+        for l, blk in enumerate(self.blocks):
+            dst = self._act[l & 1]
+            last = l + 1 == layers
+            value = base + l + 1
+            for c, (r0, cnt) in enumerate(spans):
+                o0, ocnt = own[c]
+                if l > 0:
+                    ops.tp_wait(flags[1, c], tp, value - 1)     # every rank's rows of this chunk have arrived
+                self._mark(f"L{l}c{c} gemms>", main, "main")
+                ev = timing_events[l] if (timing_events is not None and c == 0) else None
+                call = block_call(blk, cur, c, reuse_routing=True, input_prepared=True, timing_events=ev)
+                ops.tp_signal([flag_addr(r, 0, c, rank) for r in range(tp)], value)   # my partial sums are complete
+                self._mark(f"L{l}c{c} gemms<", main, "main")
+                computed = torch.cuda.Event()
+                computed.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(computed)
+                    self._mark(f"L{l}c{c} exchange>", comm, "comm")
+                    nxt = None
+                    if not last:
+                        nb = self.blocks[l + 1]
+                        nxt = ops.w8a8_mlp_block(
+                            dst, nb.rms_delta, nb.gate_up_weight, nb.gate_up_lora, nb.down_weight, nb.down_lora,
+                            adapter_ids, enabled=True, eps=nb.eps, out=partial, down_epilogue=ops.EPI_PARTIAL_F32,
+                            chunk=chunk_arg(c), reuse_routing=True, build_only=True)[1]
+                    ops.w8a8_mlp_tp_exchange(
+                        call, nxt, self._sorted if last else dst, tp=tp, row_begin=o0, row_count=ocnt,
+                        partials=[p for p in ptrs], wait_flags=flags[0, c], wait_value=value,
+                        peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
+                        signal_flags=[flag_addr(r, 1, c, rank) for r in range(tp)] if nxt is not None else None,
+                        signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas)
+                    self._mark(f"L{l}c{c} exchange<", comm, "comm")
+                    if last:
+                        dist.all_gather_into_tensor(self._sorted[r0:r0 + cnt], self._sorted[o0:o0 + ocnt], group=self.group)
+                        fin = torch.cuda.Event()
+                        fin.record(comm)
+                        final.append((fin, call))
             cur = dst
         for fin, _ in final:
             main.wait_event(fin)

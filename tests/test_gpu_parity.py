@@ -611,3 +611,121 @@ def test_config3_accumulator_sampled_tiles(S):
     # size-independent property: the accumulator is linear in the activation codes' sign
     acc_neg = S.w8a8_int32_accumulator(-x, packed, enabled=True)
     assert torch.equal(acc_neg, -acc)
+
+
+def _tp_shards(S, T, tp, seed, m, hidden, inter, rank, na):
+    """One seeded block cut into `tp` shards the way the ranks hold it (device side) plus the host-side pieces."""
+    rng = np.random.default_rng(seed)
+    x, wgu, ga, gb, s, ids = make_case(seed + 1, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(seed + 2, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    qgu = O.quantize_frozen_weight(wgu, group_size=hidden)
+    shards = []
+    for r in range(tp):
+        codes, scales, gb_r = T.shard_gate_up(qgu.codes, qgu.scales, gb, tp, r)
+        pgu = S.pack_weight(S.GroupQuantizedWeight(to_dev(codes), to_dev(scales), hidden, hidden, 8, hidden))
+        lo, hi = T.shard_bounds(inter, tp, r)
+        qd = O.quantize_frozen_weight(wd[lo:hi], group_size=hi - lo)
+        pd = S.pack_weight(S.GroupQuantizedWeight(to_dev(qd.codes), to_dev(qd.scales), hi - lo, hi - lo, 8, hi - lo))
+        _, da_r = T.shard_down(wd, da, tp, r)
+        lgu = S.pack_lora(to_dev(ga), to_dev(gb_r), to_dev(s), in_features=hidden, padded_out_features=2 * (hi - lo))
+        ld = S.pack_lora(to_dev(da_r), to_dev(db), to_dev(s), in_features=hi - lo, padded_out_features=hidden)
+        shards.append((to_dev(delta), pgu, lgu, pd, ld))
+    return x, ids, shards
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_fused_exchange_emulated_on_one_gpu(S, tp):
+    # The fused exchange of a two-block stack with every rank's work done in turn on this GPU: each "rank" has
+    # its own workspace, partial-sum buffer and flag words; the "peer mappings" are plain addresses of the other
+    # ranks' buffers.  All kernels run on one stream, every flag is raised before the kernel that waits for it
+    # is launched, so nothing ever waits on work that has not been enqueued.  Must equal, bit for bit, the
+    # all-reduce form of the same two blocks.
+    from skyrl_tx_rocm_b200 import _lib
+    from skyrl_tx_rocm_b200 import tp as T
+
+    m, hidden, inter, rank, na, chunks = 520, 256, 512, 16, 5, 2
+    x, ids, blk0 = _tp_shards(S, T, tp, 301, m, hidden, inter, rank, na)
+    _, _, blk1 = _tp_shards(S, T, tp, 401, m, hidden, inter, rank, na)
+    xd, idd = to_dev(x), to_dev(ids)
+    rows = S.chunk_rows(m, chunks)
+    spans = [(c * rows, min(rows, m - c * rows)) for c in range(chunks)]
+    assert all(cnt % tp == 0 for _, cnt in spans)
+
+    # all-reduce form, block after block
+    cur = xd
+    for shards in (blk0, blk1):
+        total = torch.zeros((m, hidden), dtype=torch.float32, device="cuda")
+        for delta, pgu, lgu, pd, ld in shards:
+            part, call = S.w8a8_mlp_block(cur, delta, pgu, lgu, pd, ld, idd, enabled=True,
+                                          down_epilogue=S.EPI_PARTIAL_F32, return_call=True)
+            total += part
+        nxt = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+        S.w8a8_mlp_tp_finalize(call, total, nxt)
+        cur = nxt
+    want = cur.clone()
+    S.check_status()
+
+    # fused exchange
+    ws_bytes = _lib.load().skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter // tp, na) + 2048
+    ws, partial, flags, act, srt = [], [], [], [], []
+    for r in range(tp):
+        buf = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        off = (-buf.data_ptr()) % 1024
+        ws.append(buf[off: off + ws_bytes - 1024])
+        partial.append(torch.full((m, hidden), float("nan"), dtype=torch.float32, device="cuda"))
+        flags.append(torch.zeros((2, 16, 8), dtype=torch.int32, device="cuda"))
+        act.append(torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda"))
+        srt.append(torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device="cuda"))
+    flag_addr = lambda q, kind, c, src: flags[q][kind, c, src].data_ptr()
+
+    def block(r, shards, src, c, **kw):
+        delta, pgu, lgu, pd, ld = shards[r]
+        return S.w8a8_mlp_block(src, delta, pgu, lgu, pd, ld, idd, enabled=True, out=partial[r],
+                                down_epilogue=S.EPI_PARTIAL_F32, chunk=(c, chunks), return_call=True, **kw)[1]
+
+    try:
+        for r in range(tp):                      # block 0: every rank prepares all rows itself
+            S.use_workspace(ws[r])
+            for c, (r0, cnt) in enumerate(spans):
+                block(r, blk0, xd, c, reuse_routing=c > 0, prepare_rows=(r0, cnt))
+        calls = {}
+        for c in range(chunks):                  # block 0 GEMMs, partial-sum flags
+            for r in range(tp):
+                S.use_workspace(ws[r])
+                calls[r, c] = block(r, blk0, xd, c, reuse_routing=True, input_prepared=True)
+                S.tp_signal([flag_addr(q, 0, c, r) for q in range(tp)], 1)
+        for c, (r0, cnt) in enumerate(spans):    # exchange behind block 0: feeds block 1 on every rank
+            for r in range(tp):
+                S.use_workspace(ws[r])
+                nxt = block(r, blk1, act[r], c, reuse_routing=True, build_only=True)
+                S.w8a8_mlp_tp_exchange(calls[r, c], nxt, act[r], tp=tp, row_begin=r0 + r * (cnt // tp), row_count=cnt // tp,
+                                       partials=[p.data_ptr() for p in partial], wait_flags=flags[r][0, c], wait_value=1,
+                                       peer_workspaces=[w.data_ptr() for w in ws],
+                                       signal_flags=[flag_addr(q, 1, c, r) for q in range(tp)], signal_value=1, grid_ctas=7)
+        for c in range(chunks):                  # block 1 GEMMs on the rows everyone delivered
+            for r in range(tp):
+                S.use_workspace(ws[r])
+                S.tp_wait(flags[r][1, c], tp, 1)
+                calls[r, c] = block(r, blk1, act[r], c, reuse_routing=True, input_prepared=True)
+                S.tp_signal([flag_addr(q, 0, c, r) for q in range(tp)], 2)
+        for c, (r0, cnt) in enumerate(spans):    # exchange behind the last block: finalize only, sorted rows
+            for r in range(tp):
+                S.use_workspace(ws[r])
+                S.w8a8_mlp_tp_exchange(calls[r, c], None, srt[r], tp=tp, row_begin=r0 + r * (cnt // tp), row_count=cnt // tp,
+                                       partials=[p.data_ptr() for p in partial], wait_flags=flags[r][0, c], wait_value=2,
+                                       sorted_out=True)
+        gathered = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+        for c, (r0, cnt) in enumerate(spans):
+            for r in range(tp):
+                lo = r0 + r * (cnt // tp)
+                gathered[lo: lo + cnt // tp] = srt[r][lo: lo + cnt // tp]
+        got = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
+        S.use_workspace(ws[0])
+        S.w8a8_mlp_tp_unsort(calls[0, 0], gathered, got)
+        S.check_status()
+    finally:
+        S.use_workspace(None)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    # a wait whose flag nobody raises runs into its limit and reports, without hanging the stream
+    # (not exercised here: it would hold the GPU for the 2 s limit; the bounded-wait self-test covers the mechanism)

@@ -1,8 +1,9 @@
 """Run under torchrun on 2+ GPUs: the sequence-parallel stack against the all-reduce stack and the oracle.
 
-Every rank builds the same seeded case, keeps its shard, runs a three-block stack four ways (all-reduce,
+Every rank builds the same seeded case, keeps its shard, runs a three-block stack five ways (all-reduce,
 sequence-parallel with the NCCL reduce-scatter, with the reduce-scatter folded into the down GEMM's epilogue
-over peer memory, and with copy-engine pushes into peer memory) and checks
+over peer memory, with copy-engine pushes into peer memory, and with the fused pull / finalize / prepare /
+push kernel that needs no collective between blocks) and checks
 (rank 0 prints one line, every rank exits non-zero on a mismatch):
   * sequence-parallel output == all-reduce output (bit-identical for 2 ranks, where the fp32 sum has one
     order; relative L2 below 1e-3 with under 1 % of elements differing for more ranks),
@@ -64,18 +65,21 @@ def main():
     xd, idd = to_dev(x), to_dev(ids)
     outs = {}
     for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False),
-                           ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy")):
+                           ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy"), ("fused", True, "fused")):
         stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
-        for _ in range(2):                      # the second pass reuses buffers and a warm workspace
+        for _ in range(3):                      # later passes reuse buffers, a warm workspace and growing flag values
             y = stack.forward(xd, idd)
         torch.cuda.synchronize()
         S.check_status()
         outs[name] = y.clone()
         if name == "peer_copy":
             used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
+        if name == "fused":
+            used_fused = stack.scatter_mode
+            S.use_workspace(None)               # the stack registered its symmetric workspace: release it
     a = outs["all_reduce"].float()
     ok, mismatched, between = True, 0, 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused"):
         b = outs[name].float()
         mism = int(((a - b).abs() > 0).sum())
         # more than two ranks: the collectives may add the fp32 partial sums in different orders, and a
@@ -83,11 +87,16 @@ def main():
         rel_b = float((a - b).norm() / a.norm())
         ok = ok and (mism == 0 if world == 2 else (mism <= a.numel() // 100 and rel_b < 1e-3))
         mismatched, between = max(mismatched, mism), max(between, rel_b)
+    # the three peer-memory forms add the partial sums in ascending rank order: identical bits at any group size
+    same_order = int(((outs["fused"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
+        int(((outs["peer_scatter"].float() - outs["peer_copy"].float()).abs() > 0).sum())
+    if used_peer and used_fused == "fused":
+        ok = ok and same_order == 0
     want = x
     for delta, qgu, ga, gb, wd, da, db in host:
         want = O.tp_shard_mlp_reference(want, delta, qgu, ga, gb, scal, wd, da, db, scal, ids, world)
     rel = 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused"):
         got = outs[name].cpu().view(torch.int16).numpy().view(BF16)
         rel = max(rel, O.relative_l2(got, want))
     ok = ok and rel < 2e-3
@@ -95,7 +104,8 @@ def main():
     dist.all_reduce(flag)
     if rank == 0:
         print(f"tp_multi_gpu_check world={world} mismatched={mismatched}/{a.numel()} rel_l2_between={between:.2e} "
-              f"rel_l2_vs_oracle={rel:.2e} peer_scatter_used={used_peer} "
+              f"rel_l2_vs_oracle={rel:.2e} peer_scatter_used={used_peer} fused_exchange={used_fused} "
+              f"rank_order_forms_differ_in={same_order} "
               f"{'OK' if int(flag) == 0 else 'FAILED'}", flush=True)
     dist.destroy_process_group()
     sys.exit(0 if int(flag) == 0 else 1)

@@ -204,10 +204,19 @@ typedef struct SkyrlW8A8GemmArgs {
                             /* NOT safe for a captured graph replayed next to eager launches on another       */
                             /* stream (the graph keeps its pairs).  The operator entry points below keep      */
                             /* their pairs in the caller's workspace and have no such constraint.             */
+  const float* z_rows;      /* Small batches (m <= SKYRL_TILE_ROWS rows in token order, every row with its    */
+  const int32_t* row_adapter_ids; /* own adapter): non-NULL z_rows selects the small-batch LoRA epilogue.    */
+  const void* lora_b_rows;  /* z_rows fp32 [m, 64] = s[a] * (x[i] A[a]) per row, row_adapter_ids int32 [m]    */
+  int32_t lora_b_rows_rank; /* (NULL: adapter 0), lora_b_rows the dense table bf16 [A, n, lora_b_rows_rank].  */
+  int32_t reserved;         /* The epilogue warps evaluate z B[a]^T per row on the CUDA cores while the main  */
+                            /* loop runs and add it before the single cast (skyrl/tx/layers/lora.py:142-157   */
+                            /* per token); z_parts / lora_b_packed / out_row_map are then unused, K is not    */
+                            /* split, and any epilogue but SKYRL_EPI_ACC_I32 is allowed.                      */
 } SkyrlW8A8GemmArgs;
-SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8GemmArgs) == 240, "SkyrlW8A8GemmArgs layout");
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8GemmArgs) == 272, "SkyrlW8A8GemmArgs layout");
 SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8GemmArgs, xq) == 32 && offsetof(SkyrlW8A8GemmArgs, out_row_stride) == 120 &&
-                     offsetof(SkyrlW8A8GemmArgs, scatter_bases) == 152 && offsetof(SkyrlW8A8GemmArgs, sched) == 232,
+                     offsetof(SkyrlW8A8GemmArgs, scatter_bases) == 152 && offsetof(SkyrlW8A8GemmArgs, sched) == 232 &&
+                     offsetof(SkyrlW8A8GemmArgs, z_rows) == 240 && offsetof(SkyrlW8A8GemmArgs, lora_b_rows_rank) == 264,
                  "SkyrlW8A8GemmArgs layout");
 
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
@@ -225,13 +234,16 @@ SKYRL_API int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t 
  * Fused front half: bf16_rms_gate_up_lora_swiglu_contiguous,
  * skyrl/tx/kernels/rocm/bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757.
  * Fused back half: bf16_lora_residual, skyrl/tx/kernels/rocm/bf16_lora_residual.py:507-566. */
+#define SKYRL_LINEAR_TWO_STEP_ROWS 1u /* batches of at most SKYRL_TILE_ROWS rows: leave the int32 accumulator in the
+                                         workspace and finish in a second, row-wise kernel instead of the GEMM's fused
+                                         epilogue; same bits, kept as a cross-check of the fused form */
 typedef struct SkyrlW8A8LinearArgs {
   uint32_t struct_size;
   int32_t epilogue;          /* SKYRL_EPI_LINEAR / _SWIGLU / _RESIDUAL / _ACC_I32 / _PARTIAL_F32 */
   int32_t m, n, k;
   int32_t rank;              /* 0 = frozen base only */
   int32_t num_adapters;
-  int32_t reserved0;
+  uint32_t flags;            /* SKYRL_LINEAR_* */
   const void* x;             /* bf16 [m, k] */
   int64_t x_row_stride;
   const void* rms_delta;     /* bf16 [k] or NULL: RMSNorm(1 + delta) in front of the quantiser */
@@ -329,6 +341,8 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
 #define SKYRL_MLP_KEEP_NORMALIZED 16u /* batches of at most SKYRL_TILE_ROWS rows: also store the normalised bf16
                                          activations rmsnorm(x) in the workspace (larger batches always do), so that
                                          a stage-by-stage check can feed the oracle what the kernels saw. */
+
+#define SKYRL_MLP_TWO_STEP_ROWS 32u /* as SKYRL_LINEAR_TWO_STEP_ROWS, for both projections of the block */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,

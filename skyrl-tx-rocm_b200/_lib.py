@@ -22,6 +22,8 @@ MLP_INPUT_PREPARED = 2
 MLP_FINALIZE_SORTED = 4
 MLP_NO_ROW_AMAX = 8
 MLP_KEEP_NORMALIZED = 16
+MLP_TWO_STEP_ROWS = 32
+LINEAR_TWO_STEP_ROWS = 1
 LORA_RANK_PAD = 64
 Z_PARTS = 6            # bf16 parts per row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo)
 TILE_ROWS = 128
@@ -50,13 +52,15 @@ class GemmArgs(C.Structure):
         ("split_k_slabs", C.c_int32), ("cta_limit", C.c_int32),
         ("scatter_bases", C.c_void_p * 8), ("scatter_row0", C.c_int32), ("scatter_rows", C.c_int32),
         ("row_amax", C.c_void_p), ("sched", C.c_void_p),
+        ("z_rows", C.c_void_p), ("row_adapter_ids", C.c_void_p), ("lora_b_rows", C.c_void_p),
+        ("lora_b_rows_rank", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
 class LinearArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("epilogue", C.c_int32), ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
-        ("rank", C.c_int32), ("num_adapters", C.c_int32), ("reserved0", C.c_int32),
+        ("rank", C.c_int32), ("num_adapters", C.c_int32), ("flags", C.c_uint32),
         ("x", C.c_void_p), ("x_row_stride", C.c_int64), ("rms_delta", C.c_void_p),
         ("rms_eps", C.c_float), ("reserved1", C.c_int32),
         ("wq", C.c_void_p), ("sw", C.c_void_p), ("lora_a_packed", C.c_void_p), ("lora_b_packed", C.c_void_p),

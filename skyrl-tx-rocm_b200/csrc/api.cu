@@ -218,6 +218,7 @@ struct Projection {
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
   bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
+  bool two_step_rows;     // row-wise route: GEMM to an int32 accumulator in memory + finalize kernel (cross-check)
   const float* known_amax;  // absmax of every source row, if the producer of x collected it (sorted route)
   float* row_amax;          // SwiGLU epilogue: collect the absmax of every output row here
   int cta_limit;
@@ -291,14 +292,14 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
     if ((rc = launch_rms_quant_rows(q.x, q.x_stride, q.rms_delta, q.eps, q.ids, q.na, q.a_packed, q.scaling, q.rank, q.m,
                                     q.k, q.xq, q.sx, z_rows, q.status, stream, true, q.keep_xn ? q.xn : nullptr)))
       return rc;
-    const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
+    const bool dense = q.b_rows != nullptr;
+    const int brow = dense ? q.b_rows_rank : SKYRL_LORA_RANK_PAD;
+    // timing events between the launches would cut the programmatic chain: use ordinary launches then
+    const bool chain = q.ev_begin == nullptr && q.ev_end == nullptr;
     g.struct_size = sizeof(g);
-    g.epilogue = SKYRL_EPI_ACC_I32;
-    g.split_k_slabs = MAX_SPLIT_K_SLABS;
     g.m = q.m;
     g.n = q.n;
     g.k = q.k;
-    g.rank = 0;
     g.num_adapters = q.na;
     g.max_tiles = q.mt;
     g.xq = q.xq;
@@ -307,18 +308,38 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
     g.sw = q.sw;
     g.tiles = q.tiles;
     g.num_tiles = q.num_tiles;
-    g.out = q.acc;
-    g.out_row_stride = q.n;
     g.status = q.status;
     g.sched = q.sched;
+    if (!q.two_step_rows) {
+      // one kernel: the GEMM's epilogue warps evaluate the per-row LoRA term while the weights stream and apply
+      // scales, LoRA, the cast and the SwiGLU / residual step from tensor memory
+      g.epilogue = q.epilogue;
+      g.rank = q.rank;
+      g.z_rows = z_rows;
+      g.row_adapter_ids = q.ids;
+      g.lora_b_rows = dense ? q.b_rows : q.b_packed;
+      g.lora_b_rows_rank = brow;
+      g.residual = q.residual;
+      g.residual_row_stride = q.residual_stride;
+      g.out = q.out;
+      g.out_row_stride = q.out_stride;
+      if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
+      rc = launch_gemm(g, stream, chain);
+      if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
+      return rc;
+    }
+    // two steps (kept as a cross-check of the fused epilogue): int32 accumulator to global memory, split over K
+    // when that fills the GPU better, then a row-wise kernel
+    const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
+    g.epilogue = SKYRL_EPI_ACC_I32;
+    g.split_k_slabs = MAX_SPLIT_K_SLABS;
+    g.rank = 0;
+    g.out = q.acc;
+    g.out_row_stride = q.n;
     if (q.ev_begin != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_begin), stream);
-    // timing events between the launches would cut the programmatic chain: use ordinary launches then
-    const bool chain = q.ev_begin == nullptr && q.ev_end == nullptr;
     rc = launch_gemm(g, stream, chain);
     if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
     if (rc) return rc;
-    const bool dense = q.b_rows != nullptr;
-    const int brow = dense ? q.b_rows_rank : SKYRL_LORA_RANK_PAD;
     return launch_finalize_rows(q.epilogue, q.acc, slabs, q.sx, q.sw, z_rows, q.ids, q.na,
                                 dense ? q.b_rows : q.b_packed, static_cast<int64_t>(q.n) * brow, brow, q.rank, q.m, q.n,
                                 q.residual, q.residual_stride, q.out, q.out_stride, q.status, stream, chain);
@@ -419,6 +440,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.eps = a->rms_eps;
   q.gather = routed ? w.perm : nullptr;
   q.keep_xn = routed || a->rms_delta != nullptr || a->x_row_stride != a->k;
+  q.two_step_rows = (a->flags & SKYRL_LINEAR_TWO_STEP_ROWS) != 0;
   q.m = a->m;
   q.n = a->n;
   q.k = a->k;
@@ -550,6 +572,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.gather = pl.perm;
   // small batches need no re-laid-out copy of x; they write one only when asked to (stage checks)
   q.keep_xn = pl.rows_path ? (a->flags & SKYRL_MLP_KEEP_NORMALIZED) != 0 : (pl.routed || a->rms_delta != nullptr);
+  q.two_step_rows = (a->flags & SKYRL_MLP_TWO_STEP_ROWS) != 0;
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;

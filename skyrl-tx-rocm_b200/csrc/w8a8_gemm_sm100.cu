@@ -97,6 +97,20 @@ struct GemmParams {
   // are >= 0) so that the quantiser of the next projection needs no pass of its own to find it.
   // Indexed by sorted row; the caller zeroes it before the launch.  NULL: not collected.
   float* row_amax;
+  // Small-batch LoRA (ROWS kernels, at most 128 rows in token order, every row with its own adapter): the
+  // epilogue warps evaluate l[m, n] = sum_j z[m, j] * B[a(m)][n, j] on the CUDA cores into a shared-memory
+  // tile WHILE the main loop streams the weights, and the epilogue proper adds it to the dequantised
+  // accumulator before the single cast.  z comes from rms_quant_rows_kernel (fp32 [m, 64], already scaled),
+  // B from the dense table [A, n, lora_rank_vecs * 8].
+  const float* z_rows;
+  const int32_t* row_ids;      // adapter id per row, NULL = adapter 0
+  const __nv_bfloat16* b_rows;
+  int64_t b_adapter_stride;    // elements between adapters of b_rows
+  int b_row_stride;            // elements between output channels of b_rows
+  int lora_rank_vecs;          // 8-element vectors of the rank that are used, 0 = no LoRA term
+  int num_adapters;
+  int lterm_off;               // byte offset of the l tile inside the stage area
+  int lterm_pitch;             // floats per row of the l tile (odd, so that a column is conflict-free)
 };
 
 // NULL (and status STATUS_BAD_SCATTER) for a row that has no owner: the caller skips the store.
@@ -236,7 +250,7 @@ template <int EPI, bool HAS_LORA>
 __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t taddr, int nc, int n_end, float sxr,
                                                 bool row_valid, int64_t orow, int64_t slab_off,
                                                 unsigned char* stage = nullptr, int lane = 0,
-                                                float* amax_acc = nullptr) {
+                                                float* amax_acc = nullptr, const float* lrow = nullptr) {
   uint32_t v[32];
   __syncwarp();
   tmem_ld32(taddr, v);
@@ -264,6 +278,10 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
       f[4 * g + 1] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 1])), sxr), w.y);
       f[4 * g + 2] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 2])), sxr), w.z);
       f[4 * g + 3] = __fmul_rn(__fmul_rn(__int2float_rn(static_cast<int>(v[4 * g + 3])), sxr), w.w);
+    }
+    if (lrow != nullptr) {  // small-batch LoRA term of this row (this chunk's 32 columns), added before the cast
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = __fadd_rn(f[i], lrow[i]);
     }
   }
   if (EPI == SKYRL_EPI_PARTIAL_F32) {
@@ -374,7 +392,51 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
   }
 }
 
-template <int BN, int EPI, bool HAS_LORA>
+// l tile of the small-batch LoRA path for one output tile: rows [0, rows) x columns [n0, n_end), written by the
+// eight epilogue warps (warp `ew` of 8 takes rows ew, ew + 8, ...; the lanes of a warp take consecutive columns,
+// so a warp reads whole 1 KB runs of one adapter's B table).  The fmaf order per element (rank vector q, then
+// the eight ranks of the vector) is the order of finalize_rows_kernel, so both give the same bits.
+__device__ __forceinline__ void rows_lora_tile(const GemmParams& p, float* lterm, int rows, int n0, int n_end, int ew,
+                                               int lane) {
+  const int cols = n_end - n0;
+  for (int r = ew; r < rows; r += EPI_THREADS / 32) {
+    int adapter = p.row_ids != nullptr ? __ldg(p.row_ids + r) : 0;
+    if (adapter < 0 || adapter >= p.num_adapters) {  // clamped and reported, never used as an index
+      if (lane == 0) atomicCAS(p.status, 0, STATUS_BAD_ADAPTER_ID);
+      adapter = min(max(adapter, 0), p.num_adapters - 1);
+    }
+    const __nv_bfloat16* btab = p.b_rows + adapter * p.b_adapter_stride + static_cast<int64_t>(n0) * p.b_row_stride;
+    const float* zr = p.z_rows + static_cast<int64_t>(r) * SKYRL_LORA_RANK_PAD;
+    float acc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+    for (int q = 0; q < p.lora_rank_vecs; ++q) {
+      const float4 z0 = *reinterpret_cast<const float4*>(zr + 8 * q);      // plain loads: written by the previous kernel
+      const float4 z1 = *reinterpret_cast<const float4*>(zr + 8 * q + 4);
+      const float z[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const int col = lane + 32 * c;
+        if (col < cols) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(btab + static_cast<int64_t>(col) * p.b_row_stride) + q);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[c] = fmaf(z[2 * j], bf16_lo(w[j]), acc[c]);
+            acc[c] = fmaf(z[2 * j + 1], bf16_hi(w[j]), acc[c]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int col = lane + 32 * c;
+      if (col < cols) lterm[r * p.lterm_pitch + col] = acc[c];
+    }
+  }
+}
+
+template <int BN, int EPI, bool HAS_LORA, bool ROWS = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -630,8 +692,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
     const int r = quad * 32 + lane;  // row of the tile == TMEM lane
     unsigned char* store_stage =
         p.direct_stores ? nullptr : smem + SINGLE_STAGE_AREA + (warp < 4 ? warp : warp - 2) * EPI_STAGE_BYTES;
+    float* lterm = reinterpret_cast<float*>(smem + p.lterm_off);
+    const bool rows_lora = ROWS && p.lora_rank_vecs > 0;
+    const int ew = warp < 4 ? warp : warp - 2;  // 0 ... 7 among the epilogue warps
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
+    if (ROWS) pdl_wait();  // scales, z and the residual may come from the kernel just before this one
     for (; ok; ++it) {
       const int t = sched_read(ring, it, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE, ok);
       ok = __all_sync(0xffffffffu, ok);
@@ -645,8 +711,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
       const bool row_valid = r < tile.y;
       const int srow = tile.x + r;
-      const float sxr = row_valid ? __ldg(p.sx + srow) : 0.f;
+      float sxr = 0.f;
+      if (row_valid) sxr = ROWS ? *(p.sx + srow) : __ldg(p.sx + srow);
       const int64_t orow = row_valid ? (p.out_row_map != nullptr ? __ldg(p.out_row_map + srow) : srow) : 0;
+      if (rows_lora) {
+        // the LoRA term of this tile, computed while the tensor cores still work on it
+        rows_lora_tile(p, lterm, tile.y, n0, n_end, ew, lane);
+        named_bar_sync(1, EPI_THREADS);
+      }
 
       ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[s], aphase, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
       if (!ok) break;
@@ -674,12 +746,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
 #pragma unroll 1
       for (int cc = c_begin; cc < c_end; ++cc)
         epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow,
-                                       (t % ksplits) * p.slab_stride, store_stage, lane, amax_acc);
+                                       (t % ksplits) * p.slab_stride, store_stage, lane, amax_acc,
+                                       (rows_lora && row_valid) ? lterm + r * p.lterm_pitch + cc * 32 : nullptr);
       // rounding to bf16 is monotonic, so the absmax of the stored values is the rounded absmax
       if (amax_acc != nullptr && row_valid && tile_amax > 0.f)
         atomicMax(reinterpret_cast<int*>(p.row_amax) + srow, __float_as_int(round_bf16(tile_amax)));
       tc_fence_before_sync();
       mbar_arrive(&tmem_empty[s]);
+      if (rows_lora) named_bar_sync(1, EPI_THREADS);  // the l tile is rewritten for the next tile
     }
   }
 
@@ -1015,10 +1089,10 @@ static int launch_pair(const GemmParams& p, int epi, bool lora, int grid, cudaSt
   }
 }
 
-template <int BN, int EPI, bool HAS_LORA>
+template <int BN, int EPI, bool HAS_LORA, bool ROWS = false>
 static int launch_variant(const GemmParams& p, int grid, cudaStream_t stream, bool programmatic) {
   using Cfg = GemmCfg<BN>;
-  auto kernel = w8a8_gemm_kernel<BN, EPI, HAS_LORA>;
+  auto kernel = w8a8_gemm_kernel<BN, EPI, HAS_LORA, ROWS>;
   static bool attr_set[MAX_DEVICES] = {};
   cudaError_t e = ensure_dynamic_smem(kernel, Cfg::SMEM_BYTES, attr_set);
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
@@ -1047,6 +1121,18 @@ static int launch_bn(const GemmParams& p, int epi, bool lora, int grid, cudaStre
       return launch_variant<BN, SKYRL_EPI_ACC_I32, false>(p, grid, stream, programmatic);
     default:
       return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
+  }
+}
+
+// small-batch variants: token order, per-row LoRA term on the CUDA cores (see GemmParams::z_rows)
+template <int BN>
+static int launch_rows_bn(const GemmParams& p, int epi, int grid, cudaStream_t stream, bool programmatic) {
+  switch (epi) {
+    case SKYRL_EPI_LINEAR: return launch_variant<BN, SKYRL_EPI_LINEAR, false, true>(p, grid, stream, programmatic);
+    case SKYRL_EPI_SWIGLU: return launch_variant<BN, SKYRL_EPI_SWIGLU, false, true>(p, grid, stream, programmatic);
+    case SKYRL_EPI_RESIDUAL: return launch_variant<BN, SKYRL_EPI_RESIDUAL, false, true>(p, grid, stream, programmatic);
+    case SKYRL_EPI_PARTIAL_F32: return launch_variant<BN, SKYRL_EPI_PARTIAL_F32, false, true>(p, grid, stream, programmatic);
+    default: return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the small-batch LoRA epilogue does not combine with epilogue %d", epi);
   }
 }
 
@@ -1121,7 +1207,17 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: buffers must be 16-byte aligned");
   if (a.rank < 0 || a.rank > SKYRL_LORA_RANK_PAD)
     return fail(SKYRL_ERR_UNSUPPORTED, "gemm: LoRA rank must be in [0, %d], got %d", SKYRL_LORA_RANK_PAD, a.rank);
-  const bool lora = a.rank > 0;
+  const bool rows = a.z_rows != nullptr;  // small-batch LoRA: token order, per-row adapter, CUDA-core LoRA term
+  if (rows) {
+    if (a.m > SKYRL_TILE_ROWS)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the small-batch LoRA epilogue takes at most %d rows, got %d", SKYRL_TILE_ROWS, a.m);
+    if (a.rank <= 0 || a.lora_b_rows == nullptr || !aligned16(a.lora_b_rows) || !aligned16(a.z_rows) ||
+        a.lora_b_rows_rank < a.rank || a.lora_b_rows_rank % 8 != 0 || a.num_adapters <= 0)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: small-batch LoRA operands missing, misaligned or of the wrong rank");
+    if (a.out_row_map != nullptr || a.split_k_slabs > 1 || a.scatter_rows > 0 || a.row_amax != nullptr)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the small-batch LoRA epilogue keeps token order and does not split K");
+  }
+  const bool lora = a.rank > 0 && !rows;
   if (lora && (a.z_parts == nullptr || !aligned16(a.z_parts) || a.lora_b_packed == nullptr || a.num_adapters <= 0))
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: LoRA buffers missing");
   if (lora && a.epilogue == SKYRL_EPI_ACC_I32)
@@ -1142,7 +1238,8 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   if (sms <= 0) return fail(SKYRL_ERR_LAUNCH, "gemm: no CUDA device");
   const GemmPlan pl = plan_gemm(a.m, a.n, a.k, a.epilogue, a.split_k_slabs);
   const int mt_est = (a.m + BM - 1) / BM;
-  const int bn_eff = pl.bn_eff;
+  int bn_eff = pl.bn_eff;
+  if (rows && a.m > 64 && bn_eff > 128) bn_eff = 128;  // the l tile (rows x columns fp32) must leave room for the pipeline
   const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
   const int bn = bn_eff > 128 ? 256 : 128;
 
@@ -1187,6 +1284,29 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   p.stage_bytes = p.a_rows * BK + (bn_eff * BK + 1023) / 1024 * 1024;
   if (lora && p.stage_bytes < 2 * Z_PLANE_BYTES) p.stage_bytes = 2 * Z_PLANE_BYTES;  // a slot also carries two z planes
   p.num_stages = SINGLE_STAGE_AREA / p.stage_bytes;
+  p.z_rows = nullptr;
+  p.row_ids = nullptr;
+  p.b_rows = nullptr;
+  p.b_adapter_stride = 0;
+  p.b_row_stride = 0;
+  p.lora_rank_vecs = 0;
+  p.num_adapters = a.num_adapters;
+  p.lterm_off = 0;
+  p.lterm_pitch = 0;
+  if (rows) {
+    p.z_rows = a.z_rows;
+    p.row_ids = a.row_adapter_ids;
+    p.b_rows = static_cast<const __nv_bfloat16*>(a.lora_b_rows);
+    p.b_row_stride = a.lora_b_rows_rank;
+    p.b_adapter_stride = static_cast<int64_t>(a.n) * a.lora_b_rows_rank;
+    p.lora_rank_vecs = (a.rank + 7) / 8;
+    p.lterm_pitch = (bn_eff + 31) / 32 * 32 + 1;
+    const int lterm_bytes = ((a.m <= 64 ? 64 : BM) * p.lterm_pitch * 4 + 1023) / 1024 * 1024;
+    p.num_stages = (SINGLE_STAGE_AREA - lterm_bytes) / p.stage_bytes;
+    if (p.num_stages < 2) return fail(SKYRL_ERR_UNSUPPORTED, "gemm: no room for the small-batch LoRA tile");
+    if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
+    p.lterm_off = p.num_stages * p.stage_bytes;
+  }
   p.scatter_rows = 0;
   p.scatter_row0 = 0;
   for (int o = 0; o < 8; ++o) p.scatter_base[o] = nullptr;
@@ -1223,7 +1343,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   // the next main loop, so this pays only when the K loop dwarfs it (measured: gain at K = 25600, loss at 5120).
   // Not with a row scatter: the pair's epilogue stores 16 bytes per row from registers, which NVLink carries
   // poorly; the single-tile kernel writes whole 128-byte lines through its staging tiles.
-  const bool paired = bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
+  const bool paired = !rows && bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
                 static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
   if (paired) {
     const int64_t pair_total = static_cast<int64_t>((a.max_tiles + 1) / 2) * ((a.n + 255) / 256);
@@ -1231,6 +1351,9 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
     if (a.cta_limit > 0 && pgrid > a.cta_limit) pgrid = a.cta_limit;
     return launch_pair(p, a.epilogue, lora, pgrid, stream);
   }
+  if (rows)
+    return bn == 256 ? launch_rows_bn<256>(p, a.epilogue, grid, stream, programmatic)
+                     : launch_rows_bn<128>(p, a.epilogue, grid, stream, programmatic);
   return bn == 256 ? launch_bn<256>(p, a.epilogue, lora, grid, stream, programmatic)
                    : launch_bn<128>(p, a.epilogue, lora, grid, stream, programmatic);
 }

@@ -729,3 +729,28 @@ def test_fused_exchange_emulated_on_one_gpu(S, tp):
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     # a wait whose flag nobody raises runs into its limit and reports, without hanging the stream
     # (not exercised here: it would hold the GPU for the 2 s limit; the bounded-wait self-test covers the mechanism)
+
+
+@pytest.mark.parametrize("m,hidden,inter,rank,na", [(64, 256, 512, 16, 32), (1, 128, 64, 8, 2), (128, 512, 768, 64, 5),
+                                                    (37, 384, 1040, 32, 7), (100, 2048, 4096, 16, 9)])
+def test_small_batch_fused_epilogue_equals_two_step_form(S, m, hidden, inter, rank, na):
+    # batches of at most 128 rows: the GEMM's fused epilogue (per-row LoRA term evaluated by the epilogue warps
+    # while the weights stream, scales + LoRA + cast + SwiGLU / residual from tensor memory) against the
+    # two-step form (int32 accumulator to memory, possibly split over K, then a row-wise kernel).  Same bits.
+    rng = np.random.default_rng(211 + m)
+    x, wgu, ga, gb, s, ids = make_case(213 + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+    _, wd, da, db, _, _ = make_case(217 + m, m, inter, hidden, rank, na, w_std=0.05)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    _, pgu = device_weight(S, wgu)
+    _, pd = device_weight(S, wd)
+    lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+    xd, dd, idd = to_dev(x), to_dev(delta), to_dev(ids)
+    want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, two_step_rows=True).clone()
+    got = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True)
+    S.check_status()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    lin_want = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True, two_step_rows=True).clone()
+    lin_got = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True)
+    S.check_status()
+    assert torch.equal(lin_got.view(torch.int16), lin_want.view(torch.int16))

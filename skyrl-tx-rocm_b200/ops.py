@@ -23,6 +23,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
+from ._cache import IdentityCache
 from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS, Z_PARTS,
                    WEIGHT_KBLOCK, SkyrlKernelError)
 
@@ -351,11 +352,18 @@ def _check_ids(adapter_ids, m: int, lora: PackedLoRA | None):
     return adapter_ids.contiguous()
 
 
+# Conversions of the reference's own argument types (GroupQuantizedWeight, [A, K, r] / [A, r, N] LoRA tables) to
+# the device format happen once per tensor version, not per call: the reference's design asks for a load-time
+# canonical weight (rocm/QUANTIZED_FFI.md:69-74), and a LoRA table changes only at an optimizer step.
+_pack_cache = IdentityCache()
+
+
 def _weight_of(weight) -> PackedW8Weight:
     if isinstance(weight, PackedW8Weight):
         return weight
     if isinstance(weight, GroupQuantizedWeight):
-        return pack_weight(weight)
+        return _pack_cache.get((weight.codes, weight.scales), (weight.group_size, weight.padded_in_features),
+                               lambda: pack_weight(weight))
     raise TypeError("weight must be a GroupQuantizedWeight or a PackedW8Weight")
 
 
@@ -368,8 +376,11 @@ def _lora_of(weight: PackedW8Weight, lora_a, lora_b, lora_scaling) -> PackedLoRA
             raise ValueError(f"lora_a K={a_k} does not match W8 K={weight.in_features}")
         if lora_b.shape[-1] != weight.out_features:
             raise ValueError(f"LoRA output N={lora_b.shape[-1]} does not match weight N={weight.out_features}")
-        lora = pack_lora(lora_a, lora_b, lora_scaling, in_features=weight.in_features,
-                         padded_out_features=weight.padded_out_features)
+        sources = (lora_a, lora_b) + ((lora_scaling,) if isinstance(lora_scaling, torch.Tensor) else ())
+        extra = (weight.in_features, weight.padded_out_features,
+                 None if isinstance(lora_scaling, torch.Tensor) else float(lora_scaling))
+        lora = _pack_cache.get(sources, extra, lambda: pack_lora(lora_a, lora_b, lora_scaling, in_features=weight.in_features,
+                                                                 padded_out_features=weight.padded_out_features))
     if lora.a.shape[2] != weight.in_features or lora.b.shape[1] != weight.padded_out_features:
         raise ValueError("packed LoRA tables do not match the packed weight")
     return lora

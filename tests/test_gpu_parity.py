@@ -754,3 +754,78 @@ def test_small_batch_fused_epilogue_equals_two_step_form(S, m, hidden, inter, ra
     lin_got = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True)
     S.check_status()
     assert torch.equal(lin_got.view(torch.int16), lin_want.view(torch.int16))
+
+
+# ----------------------------------------------------------------------------- model wiring + weight pipeline
+@pytest.mark.parametrize("batch,seq", [(2, 40), (3, 100)])
+def test_mlp_module_from_checkpoint_matrices(S, batch, seq, tmp_path):
+    # checkpoint-layout matrices ([out, in]) -> fuse gate/up -> quantise -> pack (through the on-disk cache) -> the
+    # Qwen3_5MLP-shaped module, against the oracle fed with the same fused, quantised weights
+    from skyrl_tx_rocm_b200 import mlp as M
+    from skyrl_tx_rocm_b200 import weights as W
+
+    rng = np.random.default_rng(71 + seq)
+    hidden, inter, rank, na = 256, 384, 16, 3
+    gate = (rng.standard_normal((inter, hidden)) * 0.05).astype(np.float32).astype(BF16)
+    up = (rng.standard_normal((inter, hidden)) * 0.05).astype(np.float32).astype(BF16)
+    down = (rng.standard_normal((hidden, inter)) * 0.05).astype(np.float32).astype(BF16)
+    cache = W.PackedWeightCache(tmp_path)
+    packed = cache.mlp(to_dev(gate), to_dev(up), to_dev(down))
+    again = cache.mlp(to_dev(gate), to_dev(up), to_dev(down))          # second build comes from the files
+    assert cache.misses == 2 and cache.hits == 2
+    assert torch.equal(again.gate_up.wq, packed.gate_up.wq) and torch.equal(again.down.sw, packed.down.sw)
+    fused = np.stack((gate.T.astype(np.float32), up.T.astype(np.float32)), axis=-1).reshape(hidden, 2 * inter).astype(BF16)
+    qgu = O.quantize_frozen_weight(fused, group_size=hidden)
+    qd = O.quantize_frozen_weight(np.ascontiguousarray(down.T), group_size=inter)
+    host_gu = W.unpack_weight(packed.gate_up)
+    np.testing.assert_array_equal(to_np(host_gu.codes), qgu.codes)
+    np.testing.assert_array_equal(to_np(W.unpack_weight(packed.down).codes), qd.codes)
+    # device pack kernel == host statement of the layout
+    assert torch.equal(packed.gate_up.wq.cpu(), W.pack_weight_host(host_gu.codes.cpu()))
+
+    _, _, ga, gb, s, _ = make_case(73, 4, hidden, 2 * inter, rank, na)
+    _, _, da, db, _, _ = make_case(79, 4, inter, hidden, rank, na)
+    lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+    ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+    module = M.Qwen3_5MLP(M.W8A8BackendConfig(w8a8_mlp=True, max_lora_adapters=na, max_lora_rank=rank), packed, lgu, ld)
+    x = rng.standard_normal((batch, seq, hidden)).astype(np.float32).astype(BF16)
+    delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+    seq_ids = rng.integers(0, na, size=batch).astype(np.int32)
+    ids = np.repeat(seq_ids, seq)
+    xd = to_dev(x)
+    norm = M.RMSNormWeights(to_dev(delta))
+    out = module.forward_with_post_attention_rms(xd, norm, to_dev(seq_ids), residual=xd)
+    S.check_status()
+    assert module.last_path == "w8a8_mlp_block" and out.shape == (batch, seq, hidden)
+    x2 = x.reshape(-1, hidden)
+    want = O.mlp_block(x2, delta, qgu, ga, gb, s, qd, da, db, s, ids)
+    assert O.relative_l2(to_np(out).reshape(-1, hidden), want) < 2e-3
+    # the same through the two fused halves (no residual given: the module adds none)
+    out2 = module.forward_with_post_attention_rms(xd, norm, to_dev(seq_ids))
+    S.check_status()
+    assert module.last_path == "w8a8_rms_gate_up_swiglu+down"
+    want2 = O.down_lora_residual(O.rms_gate_up_lora_swiglu(x2, delta, qgu, ga, gb, s, ids), qd, da, db, s, None, ids)
+    assert O.relative_l2(to_np(out2).reshape(-1, hidden), want2) < 2e-3
+
+
+def test_reference_argument_types_are_converted_once(S):
+    # the operators accept the reference's own types (GroupQuantizedWeight, [A, K, r] tables); they are packed on
+    # the first call and found again by identity afterwards
+    from skyrl_tx_rocm_b200 import ops
+
+    x, w, a, b, s, ids = make_case(301, 200, 256, 320, 16, 3)
+    q = O.quantize_frozen_weight(w, group_size=256)
+    gq = S.GroupQuantizedWeight(to_dev(q.codes), to_dev(q.scales), 256, 256, 8, 256)
+    ad, bd, sd, xd, idd = to_dev(a), to_dev(b), to_dev(s), to_dev(x), to_dev(ids)
+    ops._pack_cache.clear()
+    before = ops._pack_cache.misses
+    y0 = S.w8a8_lora_linear(xd, gq, ad, bd, sd, idd, enabled=True).clone()
+    first = ops._pack_cache.misses - before
+    y1 = S.w8a8_lora_linear(xd, gq, ad, bd, sd, idd, enabled=True)
+    S.check_status()
+    assert first == 2 and ops._pack_cache.misses - before == 2          # weight + tables, packed once
+    assert torch.equal(y0, y1)
+    bd.mul_(2)                                                          # an optimizer step: the tables are re-packed
+    y2 = S.w8a8_lora_linear(xd, gq, ad, bd, sd, idd, enabled=True)
+    S.check_status()
+    assert ops._pack_cache.misses - before == 3 and not torch.equal(y0, y2)

@@ -29,7 +29,8 @@ from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_S
 
 __all__ = (
     "GroupQuantizedWeight", "PackedW8Weight", "PackedLoRA", "SkyrlKernelError",
-    "quantize_frozen_weight", "pack_weight", "pack_weight_nk", "pack_lora", "prepare_routing", "rms_quant",
+    "quantize_frozen_weight", "pack_signed_int4", "unpack_signed_int4", "pack_weight", "pack_weight_nk", "pack_lora",
+    "prepare_routing", "rms_quant",
     "w8a8_lora_linear", "w8a8_frozen_linear", "w8a8_int32_accumulator", "w8a8_lora_linear_f32",
     "w8a8_rms_gate_up_lora_swiglu", "w8a8_down_lora_residual", "w8a8_mlp_block", "w8a8_mlp_tp_finalize",
     "w8a8_mlp_tp_finalize_slabs", "w8a8_mlp_tp_unsort", "w8a8_mlp_workspace_regions", "w8a8_mlp_stage_regions",
@@ -110,16 +111,42 @@ def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
 
 
+def pack_signed_int4(values: torch.Tensor) -> torch.Tensor:
+    """Pairs along axis zero -> low / high two's-complement nibbles of one byte (quantized_lora.py:94-107)."""
+    if values.ndim < 1 or values.shape[0] == 0 or values.shape[0] % 2:
+        raise ValueError("signed INT4 packing requires an even, nonempty axis zero")
+    if values.dtype not in (torch.int8, torch.int16, torch.int32, torch.int64):
+        raise TypeError(f"signed INT4 values must be integral, got {values.dtype}")
+    low = (values[0::2].to(torch.int16) & 0xF).to(torch.uint8)
+    high = (values[1::2].to(torch.int16) & 0xF).to(torch.uint8)
+    return low | (high << 4)
+
+
+def unpack_signed_int4(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of `pack_signed_int4` (quantized_lora.py:110-125): int8 values in [-8, 7]."""
+    if packed.ndim < 1 or packed.shape[0] == 0:
+        raise ValueError("signed INT4 input must have a nonempty axis zero")
+    if packed.dtype != torch.uint8:
+        raise TypeError(f"packed signed INT4 values must be uint8, got {packed.dtype}")
+    low = (packed & 0xF).to(torch.int16)
+    high = (packed >> 4).to(torch.int16)
+    low = torch.where(low >= 8, low - 16, low).to(torch.int8)
+    high = torch.where(high >= 8, high - 16, high).to(torch.int8)
+    return torch.stack((low, high), dim=1).reshape(packed.shape[0] * 2, *packed.shape[1:])
+
+
 def quantize_frozen_weight(weight: torch.Tensor, *, bits: int = 8, group_size: int | None = None,
                            scale_dtype: torch.dtype = torch.bfloat16) -> GroupQuantizedWeight:
-    """Offline symmetric quantiser of a [K, N] weight (quantized_lora.py:128-171).
+    """Offline symmetric quantiser of a [K, N] weight (quantized_lora.py:128-171), W8 or W4.
 
     `group_size=None` means one group over all of K (per-output-channel), the
     scheme every benchmark configuration uses.  Codes are computed with the
-    fp32 scale; the stored scale is cast to `scale_dtype` afterwards.
+    fp32 scale; the stored scale is cast to `scale_dtype` afterwards.  W4 codes
+    (range [-7, 7]) are packed two to a byte along K, as the reference stores them.
     """
-    if bits != 8:
-        raise ValueError(f"the B200 path stores W8 codes only, got bits={bits}")
+    if bits not in (4, 8):
+        raise ValueError(f"bits must be 4 or 8, got {bits}")
+    qmax_int = (1 << (bits - 1)) - 1
     if weight.ndim != 2:
         raise ValueError(f"weight must have shape [K, N], got {tuple(weight.shape)}")
     if not weight.is_floating_point():
@@ -136,16 +163,29 @@ def quantize_frozen_weight(weight: torch.Tensor, *, bits: int = 8, group_size: i
     amax = grouped.abs().amax(dim=1)
     # a TENSOR divisor: dividing by a Python scalar is evaluated as a multiplication by the rounded reciprocal,
     # which differs from the reference's fp32 quotient amax / 127 in the last bit for some values
-    qmax = torch.full((), 127.0, dtype=torch.float32, device=weight.device)
+    qmax = torch.full((), float(qmax_int), dtype=torch.float32, device=weight.device)
     scales = torch.where(amax > 0, amax / qmax, torch.ones_like(amax))
-    codes = torch.clamp(torch.round(grouped / scales[:, None, :]), -127, 127).to(torch.int8)
-    return GroupQuantizedWeight(codes.view(kpad, n).contiguous(), scales.to(scale_dtype), k, kpad, 8, group_size)
+    codes = torch.clamp(torch.round(grouped / scales[:, None, :]), -qmax_int, qmax_int).to(torch.int8)
+    codes = codes.view(kpad, n).contiguous()
+    if bits == 4:
+        codes = pack_signed_int4(codes)
+    return GroupQuantizedWeight(codes, scales.to(scale_dtype), k, kpad, bits, group_size)
 
 
 def pack_weight(weight: GroupQuantizedWeight) -> PackedW8Weight:
-    """[K, N] codes + [1, N] scales -> K-major int8 [Npad, K] + fp32 [Npad] on the device."""
+    """[K, N] codes + [groups, N] scales -> the packed device format.
+
+    W4 weights (quantized_lora.py:94-125: two codes per byte) are expanded to int8 codes here, once, at
+    load time: sm_100 has no int4 tensor-core kind, so the W4 arithmetic runs on the same int8 kernels
+    (exactly: the codes are the same integers), at W8 memory cost on the device."""
+    if weight.bits == 4:
+        if weight.codes.ndim != 2 or weight.codes.dtype != torch.uint8:
+            raise TypeError("W4 codes must be a rank-two UINT8 array of packed nibbles")
+        codes8 = unpack_signed_int4(weight.codes)[: weight.padded_in_features].contiguous()
+        weight = GroupQuantizedWeight(codes8, weight.scales, weight.original_in_features, weight.padded_in_features, 8,
+                                      weight.group_size)
     if weight.bits != 8:
-        raise ValueError(f"the B200 path requires W8 codes, got W{weight.bits}")
+        raise ValueError(f"the B200 path takes W8 or W4 codes, got W{weight.bits}")
     if weight.codes.ndim != 2 or weight.codes.dtype != torch.int8:
         raise TypeError("W8 codes must be a rank-two INT8 array")
     if weight.scales.ndim != 2 or not weight.scales.is_floating_point():

@@ -829,3 +829,56 @@ def test_reference_argument_types_are_converted_once(S):
     y2 = S.w8a8_lora_linear(xd, gq, ad, bd, sd, idd, enabled=True)
     S.check_status()
     assert ops._pack_cache.misses - before == 3 and not torch.equal(y0, y2)
+
+
+def test_attention_projections_qkv_and_o(S):
+    # the fused q/k/v projection (interleaved per key-value group) and the output projection of an attention block
+    # are the same W8A8 LoRA linear (skyrl/tx/models/qwen3_5.py:326-350): one call, split into its components
+    from skyrl_tx_rocm_b200 import projections as P
+
+    heads, kv_heads, head_dim, hidden, rank, na = 8, 2, 32, 256, 16, 3
+    q_per_kv = heads // kv_heads
+    groups = (q_per_kv * 2 * head_dim, head_dim, head_dim)
+    n = (heads * 2 + 2 * kv_heads) * head_dim
+    x, w, a, b, s, _ = make_case(501, 2 * 150, hidden, n, rank, na, w_std=0.05)
+    seq_ids = np.asarray([2, 0], dtype=np.int32)
+    ids = np.repeat(seq_ids, 150)
+    q, packed = device_weight(S, w)
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=hidden, padded_out_features=n)
+    qkv = P.FusedLoRALinearW8(packed, lora, components=("q_proj", "k_proj", "v_proj"), group_sizes=groups, enabled=True)
+    got = qkv(to_dev(x).reshape(2, 150, hidden), to_dev(seq_ids))
+    S.check_status()
+    want = O.quantized_lora_linear(x, q, a, b, s, ids)
+    fused = want.reshape(300, kv_heads, sum(groups))
+    off = 0
+    for part, g in zip(got, groups):
+        assert part.shape == (2, 150, kv_heads * g)
+        exp = fused[:, :, off:off + g].reshape(300, kv_heads * g)
+        assert_bf16_close(to_np(part).reshape(300, -1), exp, what="qkv component")
+        off += g
+    o_w = (np.random.default_rng(7).standard_normal((heads * head_dim, hidden)) * 0.05).astype(np.float32).astype(BF16)
+    qo, po = device_weight(S, o_w)
+    o_proj = P.LoRALinearW8(po, None, enabled=True)
+    attn = to_dev(x[:, : heads * head_dim])
+    np.testing.assert_array_equal(to_np(o_proj(attn)).view(np.uint16), O.quantized_lora_linear(x[:, : heads * head_dim], qo).view(np.uint16))
+    with pytest.raises(RuntimeError, match="disabled by default"):
+        P.LoRALinearW8(po)(attn)
+
+
+@pytest.mark.parametrize("m,k,n,g", [(40, 128, 48, 64), (200, 256, 96, 128), (64, 192, 32, 64)])
+def test_w4_weights_run_on_the_int8_kernels(S, m, k, n, g):
+    # W4 storage (two codes per byte, quantized_lora.py:94-125) expanded to int8 codes at load time: the same
+    # integers, so the frozen base is bit-exact against the oracle's W4A8 statement
+    x, w, a, b, s, ids = make_case(601 + m, m, k, n, 8, 2, w_std=0.05)
+    q4 = O.quantize_frozen_weight(w, group_size=g, bits=4)
+    gq = S.GroupQuantizedWeight(to_dev(q4.codes), to_dev(q4.scales), k, k, 4, g)
+    frozen = S.w8a8_frozen_linear(to_dev(x), gq, enabled=True)
+    S.check_status()
+    np.testing.assert_array_equal(to_np(frozen).view(np.uint16), O.quantized_lora_linear(x, q4).view(np.uint16))
+    y = S.w8a8_lora_linear(to_dev(x), gq, to_dev(a), to_dev(b), to_dev(s), to_dev(ids), enabled=True)
+    S.check_status()
+    assert_bf16_close(to_np(y), O.quantized_lora_linear(x, q4, a, b, s, ids), max_ulp_frac=0.02, what="W4 + LoRA")
+    # the device quantiser of W4 agrees with the oracle's, packed bytes included
+    dq = S.quantize_frozen_weight(to_dev(w), bits=4, group_size=g)
+    np.testing.assert_array_equal(to_np(dq.codes), q4.codes)
+    np.testing.assert_array_equal(to_np(dq.scales).view(np.uint16), q4.scales.view(np.uint16))

@@ -191,3 +191,37 @@ def test_identity_cache_converts_once_per_tensor_version():
     del c                                      # entries die with their source
     cache.get((a,), None, make)
     assert all(all(r() is not None for r in refs) for refs, _ in cache._items.values())
+
+
+# ----------------------------------------------------------------------------- other projections, W4
+def test_fuse_and_split_components_follow_the_group_interleave():
+    from skyrl_tx_rocm_b200 import projections as P
+
+    rng = np.random.default_rng(3)
+    q, k, v = (torch.from_numpy(rng.standard_normal((5, n))) for n in (24, 6, 6))    # 3 kv groups: 8 + 2 + 2 each
+    fused = P.fuse_components((q, k, v), (8, 2, 2))
+    assert fused.shape == (5, 36)
+    assert torch.equal(fused[:, :8], q[:, :8]) and torch.equal(fused[:, 8:10], k[:, :2]) and torch.equal(fused[:, 10:12], v[:, :2])
+    assert torch.equal(fused[:, 12:20], q[:, 8:16])
+    q2, k2, v2 = P.split_components(fused, (8, 2, 2))
+    assert torch.equal(q2, q) and torch.equal(k2, k) and torch.equal(v2, v)
+    gate, up = torch.from_numpy(rng.standard_normal((5, 7))), torch.from_numpy(rng.standard_normal((5, 7)))
+    assert torch.equal(P.fuse_components((gate, up), (1, 1)), W.fuse_gate_up(gate, up))
+    with pytest.raises(ValueError):
+        P.split_components(fused, (8, 2, 3))
+
+
+def test_w4_pack_bytes_and_quantiser_match_the_oracle():
+    from oracle import w8a8_oracle as O
+
+    values = torch.tensor([[-7, -1, 0], [-6, 1, 7], [-5, 2, 6], [-4, 3, 5]], dtype=torch.int8)
+    packed = S.pack_signed_int4(values)
+    np.testing.assert_array_equal(packed.numpy(), np.asarray([[0xA9, 0x1F, 0x70], [0xCB, 0x32, 0x56]], dtype=np.uint8))
+    assert torch.equal(S.unpack_signed_int4(packed), values)
+    rng = np.random.default_rng(5)
+    w = rng.standard_normal((70, 13)).astype(np.float32)
+    got = S.quantize_frozen_weight(torch.from_numpy(w), bits=4, group_size=14, scale_dtype=torch.float32)
+    want = O.quantize_frozen_weight(w, bits=4, group_size=14, scale_dtype=np.float32)
+    np.testing.assert_array_equal(got.codes.numpy(), want.codes)
+    np.testing.assert_array_equal(got.scales.numpy(), want.scales)
+    assert got.bits == 4 and got.codes.dtype == torch.uint8

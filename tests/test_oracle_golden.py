@@ -272,3 +272,29 @@ def test_composed_block_amplifies_one_step_differences():
     c1, _ = O.dynamic_group_quantize(moved, inter)
     assert 0 < (c0 != c1).mean() < 1e-3          # a few int8 codes moved, each by one
     assert np.abs(c0.astype(np.int32) - c1.astype(np.int32)).max() == 1
+
+
+def test_int4_pack_bytes_and_hand_coded_w4_vectors():
+    # the reference's own W4 known answers (tests/tx/kernels/test_quantized_lora.py:30-74): nibble order of the
+    # packing, independent dequantisation of hand-written codes / scales, and the W4A4 grouped linear
+    values = np.asarray([[-7, -1, 0], [-6, 1, 7], [-5, 2, 6], [-4, 3, 5]], dtype=np.int8)
+    packed = O.pack_signed_int4(values)
+    assert packed.dtype == np.uint8 and packed.shape == (2, 3)
+    np.testing.assert_array_equal(packed, np.asarray([[0xA9, 0x1F, 0x70], [0xCB, 0x32, 0x56]], dtype=np.uint8))
+    np.testing.assert_array_equal(O.unpack_signed_int4(packed), values)
+    weight = O.GroupQuantizedWeight(
+        codes=np.asarray([[0x31, 0x4E], [0x0B, 0x96]], dtype=np.uint8),
+        scales=np.asarray([[0.5, 2.0], [1.5, 0.25]], dtype=np.float32),
+        original_in_features=3, padded_in_features=4, bits=4, group_size=2)
+    np.testing.assert_array_equal(O.dequantize_frozen_weight(weight),
+                                  np.asarray([[0.5, -4.0], [1.5, 8.0], [-7.5, 1.5]], dtype=np.float32))
+    x = np.asarray([[7.0, -3.0, -7.0], [0.0, 0.0, 3.0]], dtype=np.float32)
+    np.testing.assert_allclose(O.quantized_frozen_linear_f32(x, weight, activation_bits=4),
+                               np.asarray([[51.5, -62.5], [-22.5, 4.5]], dtype=np.float32), rtol=1e-6, atol=1e-6)
+    # the quantiser: W4 codes stay within [-7, 7] and round-trip through the packing
+    rng = np.random.default_rng(4)
+    w = rng.standard_normal((70, 13)).astype(np.float32)
+    q4 = O.quantize_frozen_weight(w, group_size=14, bits=4, scale_dtype=np.float32)
+    codes = O.unpacked_codes(q4)
+    assert q4.codes.dtype == np.uint8 and codes.shape == (70, 13) and np.abs(codes).max() <= 7
+    assert O.relative_l2(O.dequantize_frozen_weight(q4), w) < 0.20      # the reference's W4 round-trip gate

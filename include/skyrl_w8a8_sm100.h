@@ -234,9 +234,13 @@ SKYRL_API int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t 
  * Fused front half: bf16_rms_gate_up_lora_swiglu_contiguous,
  * skyrl/tx/kernels/rocm/bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757.
  * Fused back half: bf16_lora_residual, skyrl/tx/kernels/rocm/bf16_lora_residual.py:507-566. */
-#define SKYRL_LINEAR_TWO_STEP_ROWS 1u /* batches of at most SKYRL_TILE_ROWS rows: leave the int32 accumulator in the
-                                         workspace and finish in a second, row-wise kernel instead of the GEMM's fused
-                                         epilogue; same bits, kept as a cross-check of the fused form */
+#define SKYRL_LINEAR_FUSED_ROWS 1u /* batches of at most SKYRL_TILE_ROWS rows: apply scales, the per-row LoRA term, the
+                                      cast and the SwiGLU / residual step in the GEMM's own epilogue (its eight epilogue
+                                      warps evaluate the LoRA term while the weights stream) instead of leaving the int32
+                                      accumulator in the workspace for a second, row-wise kernel.  Same bits.  One launch
+                                      fewer per projection, but on B200 the two-step form is faster at decode shapes (the
+                                      row-wise work is latency-bound and eight warps per SM hide less of it than a whole
+                                      grid does), so it stays the default */
 typedef struct SkyrlW8A8LinearArgs {
   uint32_t struct_size;
   int32_t epilogue;          /* SKYRL_EPI_LINEAR / _SWIGLU / _RESIDUAL / _ACC_I32 / _PARTIAL_F32 */
@@ -342,7 +346,7 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
                                          activations rmsnorm(x) in the workspace (larger batches always do), so that
                                          a stage-by-stage check can feed the oracle what the kernels saw. */
 
-#define SKYRL_MLP_TWO_STEP_ROWS 32u /* as SKYRL_LINEAR_TWO_STEP_ROWS, for both projections of the block */
+#define SKYRL_MLP_FUSED_ROWS 32u /* as SKYRL_LINEAR_FUSED_ROWS, for both projections of the block */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,

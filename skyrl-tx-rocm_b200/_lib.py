@@ -22,8 +22,8 @@ MLP_INPUT_PREPARED = 2
 MLP_FINALIZE_SORTED = 4
 MLP_NO_ROW_AMAX = 8
 MLP_KEEP_NORMALIZED = 16
-MLP_TWO_STEP_ROWS = 32
-LINEAR_TWO_STEP_ROWS = 1
+MLP_FUSED_ROWS = 32
+LINEAR_FUSED_ROWS = 1
 LORA_RANK_PAD = 64
 Z_PARTS = 6            # bf16 parts per row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo)
 TILE_ROWS = 128

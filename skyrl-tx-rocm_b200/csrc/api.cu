@@ -218,7 +218,7 @@ struct Projection {
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
   bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
-  bool two_step_rows;     // row-wise route: GEMM to an int32 accumulator in memory + finalize kernel (cross-check)
+  bool two_step_rows;     // row-wise route: GEMM to an int32 accumulator in memory + finalize kernel (default)
   const float* known_amax;  // absmax of every source row, if the producer of x collected it (sorted route)
   float* row_amax;          // SwiGLU epilogue: collect the absmax of every output row here
   int cta_limit;
@@ -328,8 +328,8 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
       if (q.ev_end != nullptr) cudaEventRecord(static_cast<cudaEvent_t>(q.ev_end), stream);
       return rc;
     }
-    // two steps (kept as a cross-check of the fused epilogue): int32 accumulator to global memory, split over K
-    // when that fills the GPU better, then a row-wise kernel
+    // two steps (the default: faster at decode shapes): int32 accumulator to global memory, split over K when
+    // that fills the GPU better, then a row-wise kernel run by a whole grid
     const int slabs = plan_gemm(q.m, q.n, q.k, SKYRL_EPI_ACC_I32, MAX_SPLIT_K_SLABS).k_splits;
     g.epilogue = SKYRL_EPI_ACC_I32;
     g.split_k_slabs = MAX_SPLIT_K_SLABS;
@@ -440,7 +440,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.eps = a->rms_eps;
   q.gather = routed ? w.perm : nullptr;
   q.keep_xn = routed || a->rms_delta != nullptr || a->x_row_stride != a->k;
-  q.two_step_rows = (a->flags & SKYRL_LINEAR_TWO_STEP_ROWS) != 0;
+  q.two_step_rows = (a->flags & SKYRL_LINEAR_FUSED_ROWS) == 0;
   q.m = a->m;
   q.n = a->n;
   q.k = a->k;
@@ -572,7 +572,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.gather = pl.perm;
   // small batches need no re-laid-out copy of x; they write one only when asked to (stage checks)
   q.keep_xn = pl.rows_path ? (a->flags & SKYRL_MLP_KEEP_NORMALIZED) != 0 : (pl.routed || a->rms_delta != nullptr);
-  q.two_step_rows = (a->flags & SKYRL_MLP_TWO_STEP_ROWS) != 0;
+  q.two_step_rows = (a->flags & SKYRL_MLP_FUSED_ROWS) == 0;
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;

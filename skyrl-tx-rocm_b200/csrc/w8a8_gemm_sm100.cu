@@ -392,46 +392,83 @@ __device__ __forceinline__ void epi_store_chunk(const GemmParams& p, uint32_t ta
   }
 }
 
-// l tile of the small-batch LoRA path for one output tile: rows [0, rows) x columns [n0, n_end), written by the
-// eight epilogue warps (warp `ew` of 8 takes rows ew, ew + 8, ...; the lanes of a warp take consecutive columns,
-// so a warp reads whole 1 KB runs of one adapter's B table).  The fmaf order per element (rank vector q, then
-// the eight ranks of the vector) is the order of finalize_rows_kernel, so both give the same bits.
+// l tile of the small-batch LoRA path for one output tile: l[r, c] = sum_j z[r, j] * B[a(r)][n0 + c, j] for
+// rows [0, rows) x columns [n0, n_end), written by the eight epilogue warps while the main loop runs.
+//
+// Everything here is bound by memory latency (every row reads its own adapter's table), so the work is laid
+// out for loads in flight, not for arithmetic: first the tile's adapter ids and z rows are staged in shared
+// memory with one round of loads; then warp `ew` takes rows ew, ew + 8, ..., its lanes take consecutive
+// columns (a warp-wide load is one contiguous run of one adapter's table), and the (rank vector q, row,
+// column) items of a warp are processed in batches of ROWS_LORA_BATCH independent 16-byte loads per lane
+// before any of them is used.  Per element the fmaf order is rank vector q ascending, then the eight ranks of
+// the vector: the order of finalize_rows_kernel, so both give the same bits.
+constexpr int ROWS_LORA_BATCH = 24;
+
 __device__ __forceinline__ void rows_lora_tile(const GemmParams& p, float* lterm, int rows, int n0, int n_end, int ew,
-                                               int lane) {
+                                               int lane, int epi_tid) {
   const int cols = n_end - n0;
-  for (int r = ew; r < rows; r += EPI_THREADS / 32) {
+  const int rank_floats = p.lora_rank_vecs * 8;
+  const int rows_pad = p.a_rows;                                    // rows of the l tile (64 or 128)
+  float* zs = lterm + rows_pad * p.lterm_pitch;                     // [rows_pad][rank_floats]
+  int* ids_s = reinterpret_cast<int*>(zs + rows_pad * rank_floats);  // [rows_pad]
+  // stage ids (clamped, reported) and z
+  for (int r = epi_tid; r < rows; r += EPI_THREADS) {
     int adapter = p.row_ids != nullptr ? __ldg(p.row_ids + r) : 0;
-    if (adapter < 0 || adapter >= p.num_adapters) {  // clamped and reported, never used as an index
-      if (lane == 0) atomicCAS(p.status, 0, STATUS_BAD_ADAPTER_ID);
+    if (adapter < 0 || adapter >= p.num_adapters) {  // never used as an index
+      atomicCAS(p.status, 0, STATUS_BAD_ADAPTER_ID);
       adapter = min(max(adapter, 0), p.num_adapters - 1);
     }
-    const __nv_bfloat16* btab = p.b_rows + adapter * p.b_adapter_stride + static_cast<int64_t>(n0) * p.b_row_stride;
-    const float* zr = p.z_rows + static_cast<int64_t>(r) * SKYRL_LORA_RANK_PAD;
-    float acc[8];
+    ids_s[r] = adapter;
+  }
+  const int zvecs = rows * (rank_floats >> 2);
+  for (int v = epi_tid; v < zvecs; v += EPI_THREADS) {
+    const int r = v / (rank_floats >> 2), j = v - r * (rank_floats >> 2);
+    // plain loads: z was written by the kernel just before this one
+    reinterpret_cast<float4*>(zs)[v] = *reinterpret_cast<const float4*>(p.z_rows + static_cast<int64_t>(r) * SKYRL_LORA_RANK_PAD + 4 * j);
+  }
+  named_bar_sync(1, EPI_THREADS);
+
+  const int nr = rows > ew ? (rows - ew + EPI_THREADS / 32 - 1) / (EPI_THREADS / 32) : 0;  // rows of this warp
+  const int cpl = (cols + 31) / 32;                                                        // columns per lane
+  const int items = p.lora_rank_vecs * nr * cpl;                                           // (q, row, column) per lane
+  // item -> (q, row, column) without integer division (cpl <= 8, nr <= 16, items <= 1024: the float quotients of
+  // (i + 0.5) are never within 0.03 of an integer, so truncation is exact)
+  const float inv_cpl = 1.0f / static_cast<float>(max(cpl, 1)), inv_nr = 1.0f / static_cast<float>(max(nr, 1));
+  for (int base = 0; base < items; base += ROWS_LORA_BATCH) {
+    uint4 u[ROWS_LORA_BATCH];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-    for (int q = 0; q < p.lora_rank_vecs; ++q) {
-      const float4 z0 = *reinterpret_cast<const float4*>(zr + 8 * q);      // plain loads: written by the previous kernel
-      const float4 z1 = *reinterpret_cast<const float4*>(zr + 8 * q + 4);
-      const float z[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int col = lane + 32 * c;
-        if (col < cols) {
-          const uint4 u = __ldg(reinterpret_cast<const uint4*>(btab + static_cast<int64_t>(col) * p.b_row_stride) + q);
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[c] = fmaf(z[2 * j], bf16_lo(w[j]), acc[c]);
-            acc[c] = fmaf(z[2 * j + 1], bf16_hi(w[j]), acc[c]);
-          }
-        }
+    for (int i = 0; i < ROWS_LORA_BATCH; ++i) {
+      const int item = base + i;
+      u[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (item < items) {
+        const int qr = __float2int_rz((item + 0.5f) * inv_cpl), c = item - qr * cpl;
+        const int q = __float2int_rz((qr + 0.5f) * inv_nr), ri = qr - q * nr;
+        const int r = ew + ri * (EPI_THREADS / 32), col = lane + 32 * c;
+        if (col < cols)
+          u[i] = __ldg(reinterpret_cast<const uint4*>(p.b_rows + ids_s[r] * p.b_adapter_stride +
+                                                       static_cast<int64_t>(n0 + col) * p.b_row_stride) + q);
       }
     }
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const int col = lane + 32 * c;
-      if (col < cols) lterm[r * p.lterm_pitch + col] = acc[c];
+    for (int i = 0; i < ROWS_LORA_BATCH; ++i) {
+      const int item = base + i;
+      if (item < items) {
+        const int qr = __float2int_rz((item + 0.5f) * inv_cpl), c = item - qr * cpl;
+        const int q = __float2int_rz((qr + 0.5f) * inv_nr), ri = qr - q * nr;
+        const int r = ew + ri * (EPI_THREADS / 32), col = lane + 32 * c;
+        if (col < cols) {
+          const float* z = zs + r * rank_floats + 8 * q;
+          float* dst = lterm + r * p.lterm_pitch + col;
+          float acc = q == 0 ? 0.f : *dst;
+          const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc = fmaf(z[2 * j], bf16_lo(w[j]), acc);
+            acc = fmaf(z[2 * j + 1], bf16_hi(w[j]), acc);
+          }
+          *dst = acc;
+        }
+      }
     }
   }
 }
@@ -716,7 +753,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       const int64_t orow = row_valid ? (p.out_row_map != nullptr ? __ldg(p.out_row_map + srow) : srow) : 0;
       if (rows_lora) {
         // the LoRA term of this tile, computed while the tensor cores still work on it
-        rows_lora_tile(p, lterm, tile.y, n0, n_end, ew, lane);
+        rows_lora_tile(p, lterm, tile.y, n0, n_end, ew, lane, ew * 32 + lane);
         named_bar_sync(1, EPI_THREADS);
       }
 
@@ -1301,7 +1338,9 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
     p.b_adapter_stride = static_cast<int64_t>(a.n) * a.lora_b_rows_rank;
     p.lora_rank_vecs = (a.rank + 7) / 8;
     p.lterm_pitch = (bn_eff + 31) / 32 * 32 + 1;
-    const int lterm_bytes = ((a.m <= 64 ? 64 : BM) * p.lterm_pitch * 4 + 1023) / 1024 * 1024;
+    // l tile [rows][pitch] fp32 + staged z [rows][rank] fp32 + adapter ids [rows]
+    const int lrows = a.m <= 64 ? 64 : BM;
+    const int lterm_bytes = (lrows * (p.lterm_pitch + p.lora_rank_vecs * 8 + 1) * 4 + 1023) / 1024 * 1024;
     p.num_stages = (SINGLE_STAGE_AREA - lterm_bytes) / p.stage_bytes;
     if (p.num_stages < 2) return fail(SKYRL_ERR_UNSUPPORTED, "gemm: no room for the small-batch LoRA tile");
     if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;

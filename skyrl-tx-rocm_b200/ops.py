@@ -487,7 +487,7 @@ def _run_linear_grouped(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids
 
 
 def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilogue, *, rms_delta=None, eps=RMS_EPS,
-                residual=None, out=None, timing_events=None, two_step_rows=False):
+                residual=None, out=None, timing_events=None, fused_rows=False):
     if weight.group_size:
         if epilogue != EPI_LINEAR or rms_delta is not None or residual is not None:
             raise SkyrlKernelError("grouped weights (group_size < K) are served by w8a8_lora_linear and "
@@ -518,7 +518,7 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
     a.m, a.n, a.k = m, npad, k
     a.rank = lora.rank if lora is not None else 0
     a.num_adapters = na
-    a.flags = _lib.LINEAR_TWO_STEP_ROWS if two_step_rows else 0
+    a.flags = _lib.LINEAR_FUSED_ROWS if fused_rows else 0
     a.x = x2.data_ptr()
     a.x_row_stride = x2.stride(0)
     a.rms_delta = rms_delta.data_ptr() if rms_delta is not None else None
@@ -581,7 +581,7 @@ def w8a8_frozen_linear(x, weight, *, enabled: bool = False, interpret: bool = Fa
 
 def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_ids=None, *, enabled: bool = False,
                      interpret: bool = False, block_m: int = 128, block_n: int = 256, row_superblock: int = 0,
-                     timing_events=None, two_step_rows: bool = False):
+                     timing_events=None, fused_rows: bool = False):
     """y = bf16(dequant(xq wq^T) + s (x A) B) (w8a8_lora.py:870-920).
 
     `lora_a` [K, r] / `lora_b` [r, N] / scalar scaling select one adapter as in
@@ -597,7 +597,7 @@ def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_
     x2 = _check_x(x, k_logical)
     lora = _lora_of(w, lora_a, lora_b, lora_scaling)
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
-    y = _run_linear(x2, w, lora, ids, EPI_LINEAR, timing_events=timing_events, two_step_rows=two_step_rows)
+    y = _run_linear(x2, w, lora, ids, EPI_LINEAR, timing_events=timing_events, fused_rows=fused_rows)
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
@@ -684,7 +684,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
                    gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
                    row_amax_from_epilogue: bool = True, keep_normalized: bool = False, build_only: bool = False,
-                   two_step_rows: bool = False):
+                   fused_rows: bool = False):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -698,8 +698,9 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     GEMM store each owner's rows of the fp32 partial sums straight into that
     owner's slab (device addresses, possibly peer mappings) instead of `out`.
     `row_amax_from_epilogue=False` makes the quantiser of h find the row absmax itself (a cross-check:
-    both forms give identical bits); `two_step_rows=True` makes small batches (at most 128 rows) finish each
-    projection in a second row-wise kernel instead of the GEMM's fused epilogue (same bits, cross-check).  `build_only=True` validates and returns the call handle without
+    both forms give identical bits); `fused_rows=True` makes small batches (at most 128 rows) finish each
+    projection in the GEMM's own epilogue instead of a second row-wise kernel (same bits, one launch fewer;
+    slower on B200 at decode shapes, so not the default).  `build_only=True` validates and returns the call handle without
     enqueuing anything (the handle of the NEXT block is an argument of `w8a8_mlp_tp_exchange`)."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
@@ -769,8 +770,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         a.flags |= _lib.MLP_NO_ROW_AMAX
     if keep_normalized:
         a.flags |= _lib.MLP_KEEP_NORMALIZED
-    if two_step_rows:
-        a.flags |= _lib.MLP_TWO_STEP_ROWS
+    if fused_rows:
+        a.flags |= _lib.MLP_FUSED_ROWS
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)

@@ -746,12 +746,12 @@ def test_small_batch_fused_epilogue_equals_two_step_form(S, m, hidden, inter, ra
     lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
     ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
     xd, dd, idd = to_dev(x), to_dev(delta), to_dev(ids)
-    want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, two_step_rows=True).clone()
-    got = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True)
+    want = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True).clone()
+    got = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, fused_rows=True)
     S.check_status()
     assert torch.equal(got.view(torch.int16), want.view(torch.int16))
-    lin_want = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True, two_step_rows=True).clone()
-    lin_got = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True)
+    lin_want = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True).clone()
+    lin_got = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True, fused_rows=True)
     S.check_status()
     assert torch.equal(lin_got.view(torch.int16), lin_want.view(torch.int16))
 

@@ -208,7 +208,8 @@ typedef struct SkyrlW8A8GemmArgs {
   const int32_t* row_adapter_ids; /* own adapter): non-NULL z_rows selects the small-batch LoRA epilogue.    */
   const void* lora_b_rows;  /* z_rows fp32 [m, 64] = s[a] * (x[i] A[a]) per row, row_adapter_ids int32 [m]    */
   int32_t lora_b_rows_rank; /* (NULL: adapter 0), lora_b_rows the dense table bf16 [A, n, lora_b_rows_rank].  */
-  int32_t reserved;         /* The epilogue warps evaluate z B[a]^T per row on the CUDA cores while the main  */
+  int32_t variant;          /* SKYRL_GEMM_VARIANT_* (0: the library chooses).                                 */
+                            /* The epilogue warps evaluate z B[a]^T per row on the CUDA cores while the main  */
                             /* loop runs and add it before the single cast (skyrl/tx/layers/lora.py:142-157   */
                             /* per token); z_parts / lora_b_packed / out_row_map are then unused, K is not    */
                             /* split, and any epilogue but SKYRL_EPI_ACC_I32 is allowed.                      */
@@ -219,6 +220,13 @@ SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8GemmArgs, xq) == 32 && offsetof(SkyrlW8A8Gemm
                      offsetof(SkyrlW8A8GemmArgs, z_rows) == 240 && offsetof(SkyrlW8A8GemmArgs, lora_b_rows_rank) == 264,
                  "SkyrlW8A8GemmArgs layout");
 
+/* Kernel variants of the GEMM for large problems (all give the same bits; the choice is a matter of speed):
+ * one 128 x 256 tile per CTA; two M tiles per CTA against one weight tile; a CTA pair per 256 x 256 tile
+ * (tcgen05 cta_group::2).  A forced variant that does not apply to the shape falls back to the single tile. */
+#define SKYRL_GEMM_VARIANT_AUTO 0
+#define SKYRL_GEMM_VARIANT_SINGLE 1
+#define SKYRL_GEMM_VARIANT_TWO_TILES 2
+#define SKYRL_GEMM_VARIANT_CTA_PAIR 3
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
 /* Number of K splits (slabs written) the GEMM uses for this shape when given `split_k_slabs` slabs. */
 SKYRL_API int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t split_k_slabs);
@@ -347,6 +355,8 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
                                          a stage-by-stage check can feed the oracle what the kernels saw. */
 
 #define SKYRL_MLP_FUSED_ROWS 32u /* as SKYRL_LINEAR_FUSED_ROWS, for both projections of the block */
+#define SKYRL_FLAGS_GEMM_VARIANT_SHIFT 8 /* bits 8-9 of SkyrlW8A8LinearArgs.flags / SkyrlW8A8MlpArgs.flags: a
+                                            SKYRL_GEMM_VARIANT_* forced on the call's GEMMs (0: the library chooses) */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the
  * per-token adapter routing done once (Qwen3_5MLP.forward_with_post_attention_rms,

@@ -24,6 +24,8 @@ MLP_NO_ROW_AMAX = 8
 MLP_KEEP_NORMALIZED = 16
 MLP_FUSED_ROWS = 32
 LINEAR_FUSED_ROWS = 1
+GEMM_VARIANT_AUTO, GEMM_VARIANT_SINGLE, GEMM_VARIANT_TWO_TILES, GEMM_VARIANT_CTA_PAIR = 0, 1, 2, 3
+FLAGS_GEMM_VARIANT_SHIFT = 8
 LORA_RANK_PAD = 64
 Z_PARTS = 6            # bf16 parts per row of the LoRA-A projection: 2 adapter slots x (hi, mid, lo)
 TILE_ROWS = 128
@@ -53,7 +55,7 @@ class GemmArgs(C.Structure):
         ("scatter_bases", C.c_void_p * 8), ("scatter_row0", C.c_int32), ("scatter_rows", C.c_int32),
         ("row_amax", C.c_void_p), ("sched", C.c_void_p),
         ("z_rows", C.c_void_p), ("row_adapter_ids", C.c_void_p), ("lora_b_rows", C.c_void_p),
-        ("lora_b_rows_rank", C.c_int32), ("reserved", C.c_int32),
+        ("lora_b_rows_rank", C.c_int32), ("variant", C.c_int32),
     ]
 
 

@@ -218,6 +218,7 @@ struct Projection {
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
   bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
+  int gemm_variant;       // SKYRL_GEMM_VARIANT_* forced on the GEMM (0: the library chooses)
   bool two_step_rows;     // row-wise route: GEMM to an int32 accumulator in memory + finalize kernel (default)
   const float* known_amax;  // absmax of every source row, if the producer of x collected it (sorted route)
   float* row_amax;          // SwiGLU epilogue: collect the absmax of every output row here
@@ -370,6 +371,7 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
   g.residual_row_stride = q.residual_stride;
   g.status = q.status;
   g.sched = q.sched;
+  g.variant = q.gemm_variant;
   g.cta_limit = q.cta_limit;
   if (q.row_amax != nullptr && q.epilogue == SKYRL_EPI_SWIGLU) {
     const int r0 = q.q_row0, rows = q.q_rows > 0 ? q.q_rows : q.m;
@@ -441,6 +443,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.gather = routed ? w.perm : nullptr;
   q.keep_xn = routed || a->rms_delta != nullptr || a->x_row_stride != a->k;
   q.two_step_rows = (a->flags & SKYRL_LINEAR_FUSED_ROWS) == 0;
+  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 3u);
   q.m = a->m;
   q.n = a->n;
   q.k = a->k;
@@ -573,6 +576,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   // small batches need no re-laid-out copy of x; they write one only when asked to (stage checks)
   q.keep_xn = pl.rows_path ? (a->flags & SKYRL_MLP_KEEP_NORMALIZED) != 0 : (pl.routed || a->rms_delta != nullptr);
   q.two_step_rows = (a->flags & SKYRL_MLP_FUSED_ROWS) == 0;
+  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 3u);
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;

@@ -1093,6 +1093,373 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
   if (threadIdx.x == 0) sched_finish(p.sched);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 cta_group::2) for large problems with a short K loop.  Two CTAs of a cluster
+// compute a 256-row x 256-column output tile: each stages ITS 128-row activation tile and ITS 128 output
+// channels of the weight tile (32 KB per K stage and CTA instead of 48 KB), the leader issues one 256-row MMA
+// per K step that reads both CTAs' shared memory, and each CTA receives its 128 rows of the accumulator in
+// its own tensor memory (256 columns, two stages: the epilogue of a pair's tile overlaps the next main loop).
+// Per unit of tensor-core work a CTA pulls a third fewer bytes from L2, which is what bounds the single-tile
+// kernel (bytes in flight per SM).  The two M tiles of a pair are neighbours in the tile list.
+//
+// LoRA: one MMA spans both tiles and has ONE B operand, while the two tiles may hold rows of up to four
+// adapters.  For every distinct adapter of the pair the leader issues the rank-r MMAs once, with each CTA
+// staging, at the same offset, the z planes of the slot that adapter has in ITS tile or, if it has none, a
+// box that lies outside the tensor and is therefore filled with zeros; every row receives exactly its own
+// adapter's term.
+//
+// Static schedule (pair i takes tiles i, i + pairs, ...).  Barriers: TMA loads of both CTAs report to the
+// leader's full barrier; commits arrive on both CTAs' barriers; the epilogue warps of both CTAs release an
+// accumulator stage (and announce the rewritten accumulator) on the leader's barriers.  All waits bounded.
+// ---------------------------------------------------------------------------------------------------
+constexpr int PAIR2_STAGE_BYTES = BM * BK + 128 * BK;                      // 32 KB: A tile + half of the weight tile
+constexpr int PAIR2_STAGES = SINGLE_STAGE_AREA / PAIR2_STAGE_BYTES;        // 6
+constexpr int PAIR2_BN = 256;
+constexpr int PAIR2_EPI_WARPS = EPI_THREADS / 32;
+
+struct PairAdapters {
+  int count;       // distinct adapters of the pair, <= 4
+  int adapter[4];
+  int slot[4];     // z slot of that adapter in THIS CTA's tile (0 / 1) or -1 (none: zero planes)
+};
+// `first` / `second` of the two tiles of a pair (second == 0: none); `mine` selects this CTA's tile
+__device__ __forceinline__ PairAdapters pair_adapters(const int4& t0, bool has1, const int4& t1, int mine) {
+  PairAdapters pa;
+  pa.count = 0;
+  const int cand[4] = {t0.z, t0.w != 0 ? (t0.w & 0xffff) - 1 : -1, has1 ? t1.z : -1, (has1 && t1.w != 0) ? (t1.w & 0xffff) - 1 : -1};
+  const int4& me = mine == 0 ? t0 : t1;
+  const bool have_me = mine == 0 || has1;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (cand[i] < 0) continue;
+    bool seen = false;
+    for (int j = 0; j < pa.count; ++j) seen = seen || pa.adapter[j] == cand[i];
+    if (seen) continue;
+    int slot = -1;
+    if (have_me && me.z == cand[i]) slot = 0;
+    else if (have_me && me.w != 0 && (me.w & 0xffff) - 1 == cand[i]) slot = 1;
+    pa.adapter[pa.count] = cand[i];
+    pa.slot[pa.count] = slot;
+    ++pa.count;
+  }
+  return pa;
+}
+
+template <int EPI, bool HAS_LORA>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = GemmCfg<PAIR2_BN>;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
+  uint64_t* full_bar = bars;                          // the leader's are used
+  uint64_t* empty_bar = bars + MAX_STAGES;            // each CTA's own, released by the leader's commits
+  uint64_t* tmem_full = bars + 2 * MAX_STAGES;        // [2], each CTA's own
+  uint64_t* tmem_empty = tmem_full + 2;               // [2], the leader's: one arrival per epilogue warp of both CTAs
+  uint64_t* conv_done = tmem_empty + 2;               // the leader's: accumulators of both CTAs rewritten
+  uint64_t* lora_done = conv_done + 1;                // each CTA's own
+  uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full[s], 1);
+      mbar_init(&tmem_empty[s], 2 * PAIR2_EPI_WARPS);
+    }
+    mbar_init(conv_done, 2 * PAIR2_EPI_WARPS);
+    mbar_init(lora_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc_pair(tmem_ptr_smem, 512);
+    tmem_relinquish_pair();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&p.tm_xq);
+    tma_prefetch_desc(&p.tm_w);
+    if (HAS_LORA) {
+      tma_prefetch_desc(&p.tm_z);
+      tma_prefetch_desc(&p.tm_b);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer's barriers exist before anything of this CTA signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int tm = *p.num_tiles;
+  const int tpairs = (tm + 1) / 2;
+  const int tn = (p.n + PAIR2_BN - 1) / PAIR2_BN;
+  const int total = tpairs * tn;
+  const int kblocks = (p.k + BK - 1) / BK;
+  const int band = min(max(p.band / 2, 1), max(tpairs, 1));
+  const int pair_id = static_cast<int>(blockIdx.x >> 1), num_pairs = static_cast<int>(gridDim.x >> 1);
+  const int oob_row = p.m;   // a box that starts here lies outside the tensor: filled with zeros
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true, have_prev = false;
+      int4 prev0 = make_int4(0, 0, 0, 0), prev1 = prev0;
+      bool prev_has1 = false;
+      int prev_n0 = 0;
+      auto next_stage = [&]() {
+        if (++stage == PAIR2_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      };
+      // LoRA operands of the pair's previous tile: per distinct adapter two pipeline slots
+      // (slot A: z parts lo and mid; slot B: z part hi and this CTA's half of the adapter's B tile)
+      auto lora_slots = [&]() -> bool {
+        const PairAdapters pa = pair_adapters(prev0, prev_has1, prev1, static_cast<int>(rank));
+        const int4& me = rank == 0 ? prev0 : prev1;
+        for (int g = 0; g < pa.count; ++g) {
+          const int zrow = pa.slot[g] >= 0 ? me.x : oob_row;
+          const int zs = pa.slot[g] >= 0 ? pa.slot[g] : 0;
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+          unsigned char* sa = smem + stage * PAIR2_STAGE_BYTES;
+          uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * 2 * Z_PLANE_BYTES);
+          tma_load_3d_pair(sa, &p.tm_z, 0, 3 * zs + 2, zrow, fb);
+          tma_load_3d_pair(sa + Z_PLANE_BYTES, &p.tm_z, 0, 3 * zs + 1, zrow, fb);
+          next_stage();
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER)) return false;
+          sa = smem + stage * PAIR2_STAGE_BYTES;
+          fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * (Z_PLANE_BYTES + 128 * LORA_ROW_BYTES));
+          tma_load_3d_pair(sa, &p.tm_z, 0, 3 * zs, zrow, fb);
+          tma_load_3d_pair(sa + Z_PLANE_BYTES, &p.tm_b, 0, prev_n0 + static_cast<int>(rank) * 128, pa.adapter[g], fb);
+          next_stage();
+        }
+        return true;
+      };
+      for (int t = pair_id; t < total && ok; t += num_pairs) {
+        const TileCoord c = tile_coord(t, tpairs, tn, band);
+        const int4 t0 = __ldg(p.tiles + 2 * c.m_idx);
+        const bool has1 = 2 * c.m_idx + 1 < tm;
+        const int4 t1 = has1 ? __ldg(p.tiles + 2 * c.m_idx + 1) : make_int4(oob_row, 0, 0, 0);
+        const int row0 = rank == 0 ? t0.x : (has1 ? t1.x : oob_row);
+        const int n0 = c.n_idx * PAIR2_BN;
+        const int inject_at = min(LORA_INJECT_AFTER, kblocks);
+        int issued = 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_PRODUCER);
+          if (!ok) break;
+          unsigned char* sa = smem + stage * PAIR2_STAGE_BYTES;
+          const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * PAIR2_STAGE_BYTES);
+          tma_load_2d_pair(sa, &p.tm_xq, kb * BK, row0, fb);
+          tma_load_3d_pair(sa + BM * BK, &p.tm_w, 0, n0 + static_cast<int>(rank) * 128, kb, fb);
+          next_stage();
+          if (HAS_LORA && have_prev && ++issued == inject_at) {
+            ok = lora_slots();
+            if (!ok) break;
+          }
+        }
+        prev0 = t0;
+        prev1 = t1;
+        prev_has1 = has1;
+        prev_n0 = n0;
+        have_prev = true;
+      }
+      if (HAS_LORA && have_prev && ok) lora_slots();
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer (the leader only) ---------------------------
+    if (lane == 0 && leader) {
+      const uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, 2 * BM, PAIR2_BN);
+      const uint32_t idesc_lora = make_idesc(IDESC_D_F32, IDESC_BF16, IDESC_BF16, 2 * BM, PAIR2_BN);
+      int stage = 0;
+      uint32_t phase = 0, it = 0, lora_rounds = 0;
+      bool ok = true, have_prev = false;
+      uint32_t prev_s = 0;
+      int prev_groups = 0;
+      auto next_stage = [&]() {
+        if (++stage == PAIR2_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      };
+      auto lora_mma = [&](uint32_t acc_stage, int groups) -> bool {
+        for (int g = 0; g < groups; ++g) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+          const int st1 = stage;
+          next_stage();
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+          const int st2 = stage;
+          next_stage();
+          if (g == 0 && !mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+          tc_fence_after_sync();
+          const uint32_t e1 = smem_u32(smem + st1 * PAIR2_STAGE_BYTES), e2 = smem_u32(smem + st2 * PAIR2_STAGE_BYTES);
+          const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
+          const uint64_t zd[3] = {make_desc_sw128(e1), make_desc_sw128(e1 + Z_PLANE_BYTES), make_desc_sw128(e2)};
+          const uint32_t d = tmem_base + acc_stage * PAIR2_BN;
+          for (int plane = 0; plane < 3; ++plane)   // smallest plane first
+            for (int kk = 0; kk < p.rank_blocks; ++kk) mma_bf16_pair(d, zd[plane] + 2 * kk, bd + 2 * kk, idesc_lora, 1u);
+          mma_commit_pair(&empty_bar[st1]);
+          mma_commit_pair(&empty_bar[st2]);
+        }
+        mma_commit_pair(lora_done);
+        ++lora_rounds;
+        return true;
+      };
+      for (int t = pair_id; t < total && ok; t += num_pairs, ++it) {
+        const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
+        ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d = tmem_base + s * PAIR2_BN;
+        int groups = 0;
+        if (HAS_LORA) {
+          const TileCoord c = tile_coord(t, tpairs, tn, band);
+          const int4 t0 = __ldg(p.tiles + 2 * c.m_idx);
+          const bool has1 = 2 * c.m_idx + 1 < tm;
+          const int4 t1 = has1 ? __ldg(p.tiles + 2 * c.m_idx + 1) : make_int4(0, 0, 0, 0);
+          groups = pair_adapters(t0, has1, t1, 0).count;
+        }
+        const int inject_at = min(LORA_INJECT_AFTER, kblocks);
+        int issued = 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * PAIR2_STAGE_BYTES);
+          const uint64_t adesc = make_desc_sw128(sa);
+          const uint64_t bdesc = make_desc_sw128(sa + BM * BK);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K_I8; ++j)
+            mma_i8_pair(d, adesc + 2 * j, bdesc + 2 * j, idesc, (kb != 0 || j != 0) ? 1u : 0u);
+          mma_commit_pair(&empty_bar[stage]);
+          next_stage();
+          if (HAS_LORA && have_prev && ++issued == inject_at) {
+            ok = lora_mma(prev_s, prev_groups);
+            if (!ok) break;
+          }
+        }
+        if (ok) mma_commit_pair(&tmem_full[s]);
+        prev_s = s;
+        prev_groups = groups;
+        have_prev = true;
+      }
+      if (HAS_LORA && have_prev && ok) lora_mma(prev_s, prev_groups);
+    }
+  } else {
+    // ------------------------------ epilogue warps 0-3, 6-9 (both CTAs, own tile) ----------
+    const int quad = warp & 3;
+    const int c_begin = warp < 4 ? 0 : 4, c_end = warp < 4 ? 4 : 8;   // 32-column chunks of the 256 columns
+    const int r = quad * 32 + lane;
+    unsigned char* store_stage = smem + SINGLE_STAGE_AREA + (warp < 4 ? warp : warp - 2) * EPI_STAGE_BYTES;
+    const uint32_t conv_remote = map_to_cta(smem_u32(conv_done), 0);
+    uint32_t it = 0, lora_it = 0;
+    bool ok = true;
+    for (int t = pair_id; t < total && ok; t += num_pairs, ++it) {
+      const TileCoord c = tile_coord(t, tpairs, tn, band);
+      const int tidx = 2 * c.m_idx + static_cast<int>(rank);
+      const bool present = tidx < tm;
+      const int4 tile = present ? __ldg(p.tiles + tidx) : make_int4(0, 0, 0, 0);
+      const int n0 = c.n_idx * PAIR2_BN;
+      const int n_end = min(p.n, n0 + PAIR2_BN);
+      const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
+      const bool row_valid = r < tile.y;
+      const int srow = tile.x + r;
+      const float sxr = row_valid ? __ldg(p.sx + srow) : 0.f;
+      const int64_t orow = row_valid ? (p.out_row_map != nullptr ? __ldg(p.out_row_map + srow) : srow) : 0;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(&tmem_full[s], aphase, abort_flag, p.status, STATUS_TIMEOUT_EPILOGUE));
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t tbase = tmem_base + s * PAIR2_BN + (static_cast<uint32_t>(quad * 32) << 16);
+      if (HAS_LORA) {
+#pragma unroll 1
+        for (int cc = c_begin; cc < c_end; ++cc)
+          epi_convert_chunk(tbase + cc * 32, n0 + cc * 32, n_end, sxr, p.sw);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(conv_remote);
+        ok = __all_sync(0xffffffffu, mbar_wait(lora_done, lora_it & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA));
+        if (!ok) break;
+        tc_fence_after_sync();
+        ++lora_it;
+      }
+      float tile_amax = 0.f;
+      float* amax_acc = (EPI == SKYRL_EPI_SWIGLU && p.row_amax != nullptr) ? &tile_amax : nullptr;
+#pragma unroll 1
+      for (int cc = c_begin; cc < c_end; ++cc)
+        epi_store_chunk<EPI, HAS_LORA>(p, tbase + cc * 32, n0 + cc * 32, n_end, sxr, row_valid, orow, 0, store_stage, lane,
+                                       amax_acc);
+      if (amax_acc != nullptr && row_valid && tile_amax > 0.f)
+        atomicMax(reinterpret_cast<int*>(p.row_amax) + srow, __float_as_int(round_bf16(tile_amax)));
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[s]), 0));
+    }
+  }
+
+  // ------------------------------ teardown -------------------------------------
+  __syncwarp();
+  if (*abort_flag) {
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers or read its shared memory
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int EPI, bool HAS_LORA>
+static int launch_pair2_variant(const GemmParams& p, int grid, cudaStream_t stream) {
+  using Cfg = GemmCfg<PAIR2_BN>;
+  auto kernel = w8a8_gemm_pair2_kernel<EPI, HAS_LORA>;
+  static bool attr_set[MAX_DEVICES] = {};
+  cudaError_t e = ensure_dynamic_smem(kernel, Cfg::SMEM_BYTES, attr_set);
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
+  kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
+  return SKYRL_OK;
+}
+
+static int launch_pair2(const GemmParams& p, int epi, bool lora, int grid, cudaStream_t stream) {
+  switch (epi) {
+    case SKYRL_EPI_LINEAR:
+      return lora ? launch_pair2_variant<SKYRL_EPI_LINEAR, true>(p, grid, stream)
+                  : launch_pair2_variant<SKYRL_EPI_LINEAR, false>(p, grid, stream);
+    case SKYRL_EPI_SWIGLU:
+      return lora ? launch_pair2_variant<SKYRL_EPI_SWIGLU, true>(p, grid, stream)
+                  : launch_pair2_variant<SKYRL_EPI_SWIGLU, false>(p, grid, stream);
+    case SKYRL_EPI_RESIDUAL:
+      return lora ? launch_pair2_variant<SKYRL_EPI_RESIDUAL, true>(p, grid, stream)
+                  : launch_pair2_variant<SKYRL_EPI_RESIDUAL, false>(p, grid, stream);
+    case SKYRL_EPI_PARTIAL_F32:
+      return lora ? launch_pair2_variant<SKYRL_EPI_PARTIAL_F32, true>(p, grid, stream)
+                  : launch_pair2_variant<SKYRL_EPI_PARTIAL_F32, false>(p, grid, stream);
+    case SKYRL_EPI_ACC_I32:
+      return launch_pair2_variant<SKYRL_EPI_ACC_I32, false>(p, grid, stream);
+    default:
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: unknown epilogue %d", epi);
+  }
+}
+
 template <int EPI, bool HAS_LORA>
 static int launch_pair_variant(const GemmParams& p, int grid, cudaStream_t stream) {
   auto kernel = w8a8_gemm_pair_kernel<EPI, HAS_LORA>;
@@ -1279,6 +1646,20 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   if (rows && a.m > 64 && bn_eff > 128) bn_eff = 128;  // the l tile (rows x columns fp32) must leave room for the pipeline
   const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
   const int bn = bn_eff > 128 ? 256 : 128;
+  // Kernel variant.  Large problems with a long K loop: two M tiles per CTA (the pair's epilogue is not overlapped
+  // with the next main loop, so this pays only when the K loop dwarfs it: gain at K = 25600, loss at 5120).  Large
+  // problems with a shorter K loop: a CTA pair per 256 x 256 tile (cta_group::2), which cuts the bytes a CTA pulls
+  // per unit of tensor-core work by a third and keeps two accumulator stages.  Neither with a row scatter (their
+  // tile order is static and a pair's epilogue of the two-tile kernel stores 16 bytes per row from registers,
+  // which NVLink carries poorly), nor with a CTA cap (a concurrent stream wants SMs: dynamic tile claims).
+  const bool big = !rows && bn_eff == 256 && k_splits == 1 && a.scatter_rows == 0 &&
+                   static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
+  bool paired = big && kblocks_of(a.k) >= 64;
+  bool pair2 = false;   // not chosen automatically
+  if (a.variant == SKYRL_GEMM_VARIANT_SINGLE) paired = pair2 = false;
+  if (a.variant == SKYRL_GEMM_VARIANT_TWO_TILES) paired = big, pair2 = false;
+  if (a.variant == SKYRL_GEMM_VARIANT_CTA_PAIR) pair2 = big && a.cta_limit <= 0, paired = paired && !pair2;
+  const int w_box_rows = pair2 ? 128 : bn_eff;   // a CTA of a pair stages half of the weight (and LoRA-B) tile
 
   GemmParams p;
   int rc;
@@ -1286,7 +1667,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
                            (!lora && a.m <= 64) ? 64 : BM)))
     return rc;
   if ((rc = encode_tmap_3d(&p.tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.wq, BK, a.n, (a.k + BK - 1) / BK, BK,
-                           static_cast<uint64_t>(a.n) * BK, BK, bn_eff)))
+                           static_cast<uint64_t>(a.n) * BK, BK, w_box_rows)))
     return rc;
   if (lora) {
     if ((rc = encode_tmap_3d(&p.tm_z, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.z_parts, SKYRL_LORA_RANK_PAD, SKYRL_Z_PARTS,
@@ -1294,7 +1675,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
       return rc;
     if ((rc = encode_tmap_3d(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a.lora_b_packed, SKYRL_LORA_RANK_PAD, a.n,
                              a.num_adapters, LORA_ROW_BYTES, static_cast<uint64_t>(a.n) * LORA_ROW_BYTES,
-                             SKYRL_LORA_RANK_PAD, bn_eff)))
+                             SKYRL_LORA_RANK_PAD, w_box_rows)))
       return rc;
   } else {
     p.tm_z = p.tm_xq;
@@ -1378,12 +1759,11 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   const int64_t max_total = static_cast<int64_t>(a.max_tiles) * ((a.n + bn_eff - 1) / bn_eff) * k_splits;
   int grid = static_cast<int>(max_total < sms ? max_total : sms);
   if (a.cta_limit > 0 && grid > a.cta_limit) grid = a.cta_limit;  // leave SMs to a concurrent collective
-  // Large problems with a long K loop: two M tiles per CTA.  The pair's epilogue is not overlapped with
-  // the next main loop, so this pays only when the K loop dwarfs it (measured: gain at K = 25600, loss at 5120).
-  // Not with a row scatter: the pair's epilogue stores 16 bytes per row from registers, which NVLink carries
-  // poorly; the single-tile kernel writes whole 128-byte lines through its staging tiles.
-  const bool paired = !rows && bn_eff == 256 && k_splits == 1 && kblocks_of(a.k) >= 64 && p.scatter_rows == 0 &&
-                static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
+  if (pair2) {
+    const int64_t pair_total = static_cast<int64_t>((a.max_tiles + 1) / 2) * ((a.n + 255) / 256);
+    const int pairs = static_cast<int>(pair_total < sms / 2 ? pair_total : sms / 2);
+    return launch_pair2(p, a.epilogue, lora, 2 * pairs, stream);
+  }
   if (paired) {
     const int64_t pair_total = static_cast<int64_t>((a.max_tiles + 1) / 2) * ((a.n + 255) / 256);
     int pgrid = static_cast<int>(pair_total < sms ? pair_total : sms);

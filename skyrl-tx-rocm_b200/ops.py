@@ -24,7 +24,8 @@ import torch
 
 from . import _lib
 from ._cache import IdentityCache
-from ._lib import (EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS, Z_PARTS,
+from ._lib import (GEMM_VARIANT_AUTO, GEMM_VARIANT_CTA_PAIR, GEMM_VARIANT_SINGLE, GEMM_VARIANT_TWO_TILES,  # noqa: F401
+                   EPI_ACC_I32, EPI_LINEAR, EPI_PARTIAL_F32, EPI_RESIDUAL, EPI_SWIGLU, LORA_RANK_PAD, TILE_ROWS, Z_PARTS,
                    WEIGHT_KBLOCK, SkyrlKernelError)
 
 __all__ = (
@@ -37,6 +38,7 @@ __all__ = (
     "w8a8_mlp_tp_exchange", "tp_signal", "tp_wait", "use_workspace",
     "chunk_rows",
     "EPI_LINEAR", "EPI_SWIGLU", "EPI_RESIDUAL", "EPI_ACC_I32", "EPI_PARTIAL_F32",
+    "GEMM_VARIANT_AUTO", "GEMM_VARIANT_SINGLE", "GEMM_VARIANT_TWO_TILES", "GEMM_VARIANT_CTA_PAIR",
     "check_status", "bounded_wait_selftest", "RMS_EPS",
 )
 
@@ -487,7 +489,7 @@ def _run_linear_grouped(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids
 
 
 def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilogue, *, rms_delta=None, eps=RMS_EPS,
-                residual=None, out=None, timing_events=None, fused_rows=False):
+                residual=None, out=None, timing_events=None, fused_rows=False, gemm_variant=0):
     if weight.group_size:
         if epilogue != EPI_LINEAR or rms_delta is not None or residual is not None:
             raise SkyrlKernelError("grouped weights (group_size < K) are served by w8a8_lora_linear and "
@@ -518,7 +520,7 @@ def _run_linear(x2, weight: PackedW8Weight, lora: PackedLoRA | None, ids, epilog
     a.m, a.n, a.k = m, npad, k
     a.rank = lora.rank if lora is not None else 0
     a.num_adapters = na
-    a.flags = _lib.LINEAR_FUSED_ROWS if fused_rows else 0
+    a.flags = (_lib.LINEAR_FUSED_ROWS if fused_rows else 0) | (int(gemm_variant) << _lib.FLAGS_GEMM_VARIANT_SHIFT)
     a.x = x2.data_ptr()
     a.x_row_stride = x2.stride(0)
     a.rms_delta = rms_delta.data_ptr() if rms_delta is not None else None
@@ -581,7 +583,7 @@ def w8a8_frozen_linear(x, weight, *, enabled: bool = False, interpret: bool = Fa
 
 def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_ids=None, *, enabled: bool = False,
                      interpret: bool = False, block_m: int = 128, block_n: int = 256, row_superblock: int = 0,
-                     timing_events=None, fused_rows: bool = False):
+                     timing_events=None, fused_rows: bool = False, gemm_variant: int = 0):
     """y = bf16(dequant(xq wq^T) + s (x A) B) (w8a8_lora.py:870-920).
 
     `lora_a` [K, r] / `lora_b` [r, N] / scalar scaling select one adapter as in
@@ -597,12 +599,12 @@ def w8a8_lora_linear(x, weight, lora_a, lora_b=None, lora_scaling=None, adapter_
     x2 = _check_x(x, k_logical)
     lora = _lora_of(w, lora_a, lora_b, lora_scaling)
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
-    y = _run_linear(x2, w, lora, ids, EPI_LINEAR, timing_events=timing_events, fused_rows=fused_rows)
+    y = _run_linear(x2, w, lora, ids, EPI_LINEAR, timing_events=timing_events, fused_rows=fused_rows, gemm_variant=gemm_variant)
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
 def w8a8_lora_linear_f32(x, weight, lora_a=None, lora_b=None, lora_scaling=None, adapter_ids=None, *,
-                         enabled: bool = False):
+                         enabled: bool = False, gemm_variant: int = 0):
     """The fp32 value of `w8a8_lora_linear` BEFORE its single bf16 cast, (f32(acc) * sx) * sw + s (x A) B
     (quantized_lora.py:248-252, 301-303), in token order.  Parity evidence: where a bf16 output differs from
     the reference's by one unit in the last place, this value shows whether the exact result sat on a
@@ -615,11 +617,11 @@ def w8a8_lora_linear_f32(x, weight, lora_a=None, lora_b=None, lora_scaling=None,
     x2 = _check_x(x, k_logical)
     lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
-    y = _run_linear(x2, w, lora, ids, EPI_PARTIAL_F32)
+    y = _run_linear(x2, w, lora, ids, EPI_PARTIAL_F32, gemm_variant=gemm_variant)
     return y[:, : w.out_features]
 
 
-def w8a8_int32_accumulator(x, weight, *, enabled: bool = False):
+def w8a8_int32_accumulator(x, weight, *, enabled: bool = False, gemm_variant: int = 0):
     """Raw int32 accumulator xq @ wq^T and the activation codes' scales, for
     bit-exact parity checks (quantized_lora.py:242-247)."""
     _validate_exact_bool("enabled", enabled)
@@ -627,12 +629,13 @@ def w8a8_int32_accumulator(x, weight, *, enabled: bool = False):
         raise RuntimeError("the W8A8 accumulator probe is disabled by default")
     w = _weight_of(weight)
     x2 = _check_x(x, w.in_features if not isinstance(weight, GroupQuantizedWeight) else weight.original_in_features)
-    acc = _run_linear(x2, w, None, None, EPI_ACC_I32)
+    acc = _run_linear(x2, w, None, None, EPI_ACC_I32, gemm_variant=gemm_variant)
     return acc[:, : w.out_features]
 
 
 def w8a8_rms_gate_up_lora_swiglu(x, rms_delta, frozen_weight, lora_a, lora_b=None, lora_scaling=None,
-                                 adapter_ids=None, *, enabled: bool = False, eps: float = RMS_EPS, timing_events=None):
+                                 adapter_ids=None, *, enabled: bool = False, eps: float = RMS_EPS, timing_events=None,
+                                 gemm_variant: int = 0):
     """h = swiglu(W8A8-LoRA gate_up(rmsnorm(x))) with interleaved (gate, up)
     columns; never materialises the [M, 2I] projection
     (bf16_rms_gate_up_lora_swiglu_contiguous.py:698-757).  `rms_delta=None`
@@ -648,13 +651,14 @@ def w8a8_rms_gate_up_lora_swiglu(x, rms_delta, frozen_weight, lora_a, lora_b=Non
     lora = _lora_of(w, lora_a, lora_b, lora_scaling) if lora_a is not None else None
     ids = _check_ids(adapter_ids, x2.shape[0], lora)
     delta = _pad_delta(rms_delta, k_logical, w.in_features) if rms_delta is not None else None
-    h = _run_linear(x2, w, lora, ids, EPI_SWIGLU, rms_delta=delta, eps=eps, timing_events=timing_events)
+    h = _run_linear(x2, w, lora, ids, EPI_SWIGLU, rms_delta=delta, eps=eps, timing_events=timing_events,
+                    gemm_variant=gemm_variant)
     inter = w.out_features // 2
     return h[:, :inter].reshape(*x.shape[:-1], inter)
 
 
 def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=None, residual=None,
-                            adapter_ids=None, *, enabled: bool = False, timing_events=None):
+                            adapter_ids=None, *, enabled: bool = False, timing_events=None, gemm_variant: int = 0):
     """out = residual + W8A8-LoRA down(x) (bf16_lora_residual.py:507-566)."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
@@ -674,7 +678,8 @@ def w8a8_down_lora_residual(x, frozen_weight, lora_a, lora_b=None, lora_scaling=
         if r2.shape != (x2.shape[0], w.out_features):
             raise ValueError(f"residual must have shape ({x2.shape[0]}, {w.out_features}), got {tuple(r2.shape)}")
         r2 = _pad_cols(r2, w.padded_out_features)
-        y = _run_linear(x2, w, lora, ids, EPI_RESIDUAL, residual=r2, timing_events=timing_events)
+        y = _run_linear(x2, w, lora, ids, EPI_RESIDUAL, residual=r2, timing_events=timing_events,
+                        gemm_variant=gemm_variant)
     return y[:, : w.out_features].reshape(*x.shape[:-1], w.out_features)
 
 
@@ -684,7 +689,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
                    gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
                    row_amax_from_epilogue: bool = True, keep_normalized: bool = False, build_only: bool = False,
-                   fused_rows: bool = False):
+                   fused_rows: bool = False, gemm_variant: int = 0):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -772,6 +777,7 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
         a.flags |= _lib.MLP_KEEP_NORMALIZED
     if fused_rows:
         a.flags |= _lib.MLP_FUSED_ROWS
+    a.flags |= int(gemm_variant) << _lib.FLAGS_GEMM_VARIANT_SHIFT
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)

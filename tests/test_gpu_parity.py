@@ -882,3 +882,33 @@ def test_w4_weights_run_on_the_int8_kernels(S, m, k, n, g):
     dq = S.quantize_frozen_weight(to_dev(w), bits=4, group_size=g)
     np.testing.assert_array_equal(to_np(dq.codes), q4.codes)
     np.testing.assert_array_equal(to_np(dq.scales).view(np.uint16), q4.scales.view(np.uint16))
+
+
+@pytest.mark.parametrize("kind", ["acc", "linear", "swiglu", "residual"])
+def test_cta_pair_kernel_equals_single_tile_kernel(S, kind):
+    # the CTA-pair variant (tcgen05 cta_group::2: two CTAs per 256 x 256 tile) against the single-tile kernel on a
+    # problem with an odd number of M tiles, seven adapters (pairs with one to four distinct adapters), K and N
+    # tails: identical bits for every epilogue
+    m, k, n, rank, na = 2200, 1024, 9728 + 64, 32, 7
+    x, w, a, b, s, ids = make_case(191, m, k, n, rank, na, w_std=0.012)
+    q, packed = device_weight(S, w)
+    xd, idd = to_dev(x), to_dev(ids)
+    lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=k, padded_out_features=packed.padded_out_features)
+    res = to_dev(np.random.default_rng(5).standard_normal((m, n)).astype(np.float32).astype(BF16))
+
+    def run(variant):
+        if kind == "acc":
+            return S.w8a8_int32_accumulator(xd, packed, enabled=True, gemm_variant=variant)
+        if kind == "linear":
+            return S.w8a8_lora_linear(xd, packed, lora, adapter_ids=idd, enabled=True, gemm_variant=variant)
+        if kind == "swiglu":
+            return S.w8a8_rms_gate_up_lora_swiglu(xd, None, packed, lora, adapter_ids=idd, enabled=True, gemm_variant=variant)
+        return S.w8a8_down_lora_residual(xd, packed, lora, residual=res, adapter_ids=idd, enabled=True, gemm_variant=variant)
+
+    want = run(S.GEMM_VARIANT_SINGLE).clone()
+    got = run(S.GEMM_VARIANT_CTA_PAIR)
+    S.check_status()
+    assert torch.equal(got, want)
+    if kind == "acc":
+        _, parts = O.quantized_lora_linear(x, q, return_parts=True)
+        np.testing.assert_array_equal(to_np(got), parts["acc"][:, 0, :])

@@ -43,6 +43,7 @@ WORKLOADS = {
     "c2": dict(kind="mlp", m=64, hidden=4096, inter=12288, rank=16, adapters=32, layers=36, ids="uniform", bound="hbm"),
     "c3": dict(kind="gate_up", m=8192, k=4096, n=24576, rank=32, adapters=4, layers=1, ids="runs512", bound="tensor"),
     "c4": dict(kind="down", m=16384, k=12288, n=4096, rank=32, adapters=8, layers=1, ids="uniform", bound="tensor"),
+    "c5_gate_up": dict(kind="gate_up", m=16384, k=5120, n=51200, rank=64, adapters=16, layers=1, ids="uniform", bound="tensor"),
     "c5": dict(kind="mlp", m=16384, hidden=5120, inter=25600, rank=64, adapters=16, layers=8, ids="uniform", bound="tensor"),
 }
 
@@ -376,7 +377,7 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                 dst = act[l & 1]
                 # adapter ids are the same for every layer of a step: route once, then reuse
                 S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev,
-                                 reuse_routing=l > 0)
+                                 reuse_routing=l > 0, gemm_variant=args.gemm_variant)
                 cur = dst
             return cur
     else:
@@ -408,11 +409,13 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
         def step(x_in, ids_in, events=None):
             ev = events[0][:2] if events is not None else None
             if kind == "linear":
-                return S.w8a8_lora_linear(x_in, w, lora, adapter_ids=ids_in, enabled=True, timing_events=ev)
+                return S.w8a8_lora_linear(x_in, w, lora, adapter_ids=ids_in, enabled=True, timing_events=ev,
+                                          gemm_variant=args.gemm_variant)
             if kind == "gate_up":
-                return S.w8a8_rms_gate_up_lora_swiglu(x_in, delta, w, lora, adapter_ids=ids_in, enabled=True, timing_events=ev)
+                return S.w8a8_rms_gate_up_lora_swiglu(x_in, delta, w, lora, adapter_ids=ids_in, enabled=True, timing_events=ev,
+                                                      gemm_variant=args.gemm_variant)
             return S.w8a8_down_lora_residual(x_in, w, lora, residual=res_holder[0], adapter_ids=ids_in, enabled=True,
-                                             timing_events=ev)
+                                             timing_events=ev, gemm_variant=args.gemm_variant)
 
     def barrier():
         if dist is not None:
@@ -481,6 +484,10 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
     clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = t_begin.elapsed_time(t_end)
     S.check_status(device)
+    if args.gemm_variant & 4 and rank == 0:
+        prof = S.ops._status_word(device).tolist()
+        print(f"issuer profile of CTA 0 (x1024 cycles, summed over all profiled launches): operands {prof[1]}, "
+              f"accumulator {prof[2]}, total {prof[3]}", file=sys.stderr, flush=True)
     if graph is not None:
         # per-kernel durations cannot be read from events inside a graph: take them from an eager pass
         for i in range(event_steps):
@@ -800,6 +807,9 @@ def main():
                          "kernel that pulls them (no collective between blocks), or (off) the NCCL reduce-scatter; "
                          "auto = epilogue on 2 GPUs, fused on more")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="> 0: sets NCCL_MAX_CTAS (tuning aid)")
+    ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6, 7],
+                    help="force a kernel variant of the large GEMMs (0: the library chooses; 1 single tile per CTA, "
+                         "2 two M tiles per CTA, 3 CTA pair per 256 x 256 tile); all give the same bits")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()

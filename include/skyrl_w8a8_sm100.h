@@ -227,6 +227,11 @@ SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8GemmArgs, xq) == 32 && offsetof(SkyrlW8A8Gemm
 #define SKYRL_GEMM_VARIANT_SINGLE 1
 #define SKYRL_GEMM_VARIANT_TWO_TILES 2
 #define SKYRL_GEMM_VARIANT_CTA_PAIR 3
+#define SKYRL_GEMM_VARIANT_PROFILE 4 /* or-ed in: the MMA-issuing thread of CTA 0 adds, in units of 1024 cycles, to the
+                                        three int32 words BEHIND the status word (status[1..3], which must then exist):
+                                        cycles waiting for operands in shared memory; cycles waiting for a free or a
+                                        rewritten accumulator; total cycles of its loop.  A diagnostic of what bounds a
+                                        launch (operand feed, epilogue, or neither: the tensor pipe itself). */
 SKYRL_API int skyrl_w8a8_gemm_sm100_v1(const SkyrlW8A8GemmArgs* args, skyrl_stream_t stream);
 /* Number of K splits (slabs written) the GEMM uses for this shape when given `split_k_slabs` slabs. */
 SKYRL_API int skyrl_w8a8_gemm_k_splits(int32_t m, int32_t n, int32_t k, int32_t split_k_slabs);
@@ -355,7 +360,7 @@ SKYRL_API int skyrl_w8a8_lora_forward_noalloc_sm100_v1(const SkyrlW8A8LinearArgs
                                          a stage-by-stage check can feed the oracle what the kernels saw. */
 
 #define SKYRL_MLP_FUSED_ROWS 32u /* as SKYRL_LINEAR_FUSED_ROWS, for both projections of the block */
-#define SKYRL_FLAGS_GEMM_VARIANT_SHIFT 8 /* bits 8-9 of SkyrlW8A8LinearArgs.flags / SkyrlW8A8MlpArgs.flags: a
+#define SKYRL_FLAGS_GEMM_VARIANT_SHIFT 8 /* bits 8-10 of SkyrlW8A8LinearArgs.flags / SkyrlW8A8MlpArgs.flags: a
                                             SKYRL_GEMM_VARIANT_* forced on the call's GEMMs (0: the library chooses) */
 
 /* Whole MLP block: out = residual + down(swiglu(gate_up(rmsnorm(x)))) with the

@@ -443,7 +443,7 @@ extern "C" int skyrl_w8a8_lora_forward_sm100_v1(const SkyrlW8A8LinearArgs* a, sk
   q.gather = routed ? w.perm : nullptr;
   q.keep_xn = routed || a->rms_delta != nullptr || a->x_row_stride != a->k;
   q.two_step_rows = (a->flags & SKYRL_LINEAR_FUSED_ROWS) == 0;
-  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 3u);
+  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 7u);
   q.m = a->m;
   q.n = a->n;
   q.k = a->k;
@@ -576,7 +576,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   // small batches need no re-laid-out copy of x; they write one only when asked to (stage checks)
   q.keep_xn = pl.rows_path ? (a->flags & SKYRL_MLP_KEEP_NORMALIZED) != 0 : (pl.routed || a->rms_delta != nullptr);
   q.two_step_rows = (a->flags & SKYRL_MLP_FUSED_ROWS) == 0;
-  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 3u);
+  q.gemm_variant = static_cast<int>((a->flags >> SKYRL_FLAGS_GEMM_VARIANT_SHIFT) & 7u);
   q.m = a->m;
   q.n = 2 * a->inter;
   q.k = a->hidden;

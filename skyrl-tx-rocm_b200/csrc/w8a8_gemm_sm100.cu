@@ -109,6 +109,7 @@ struct GemmParams {
   int b_row_stride;            // elements between output channels of b_rows
   int lora_rank_vecs;          // 8-element vectors of the rank that are used, 0 = no LoRA term
   int num_adapters;
+  int profile;                 // 1: the MMA issuer of CTA 0 adds the cycles it spent waiting to status[1..3]
   int lterm_off;               // byte offset of the l tile inside the stage area
   int lterm_pitch;             // floats per row of the l tile (odd, so that a column is conflict-free)
 };
@@ -165,6 +166,26 @@ __device__ __forceinline__ void sched_finish(int* sched) {
     sched[1] = 0;
     __threadfence();
   }
+}
+
+// Where the MMA issuer's time goes (diagnostic, CTA 0 only): cycles waiting for operands in shared memory,
+// for a free accumulator stage, and for the epilogue's rewrite of the accumulator in front of the LoRA MMAs.
+struct IssuerProfile {
+  long long operands = 0, accumulator = 0, rewrite = 0;
+};
+__device__ __forceinline__ bool timed_wait(bool on, long long& acc, uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                           int* status, int code) {
+  if (!on) return mbar_wait(bar, parity, abort_flag, status, code);
+  const long long t0 = clock64();
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  acc += clock64() - t0;
+  return ok;
+}
+__device__ __forceinline__ void store_profile(const IssuerProfile& pr, int* status, long long total) {
+  // in units of 1024 cycles, so that a long launch fits an int32 word; the caller's status word [0] is untouched
+  atomicAdd(status + 1, static_cast<int>(pr.operands >> 10));
+  atomicAdd(status + 2, static_cast<int>((pr.accumulator + pr.rewrite) >> 10));
+  atomicAdd(status + 3, static_cast<int>(total >> 10));
 }
 
 struct TileCoord {
@@ -642,6 +663,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
       bool ok = true, have_prev = false;
       uint32_t prev_s = 0;
       int prev_second = 0;
+      const bool prof = p.profile != 0 && blockIdx.x == 0;
+      IssuerProfile pr;
+      const long long prof_t0 = clock64();
       // rank-r bf16 MMAs of one adapter slot of one tile, accumulated onto the accumulator the epilogue
       // rewrote as fp32; `first` waits for that rewrite, `last` hands the accumulator back to the epilogue
       auto lora_mma_of = [&](uint32_t acc_stage, bool first, bool last) -> bool {
@@ -657,7 +681,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
           stage = 0;
           phase ^= 1u;
         }
-        if (first && !mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+        if (first && !timed_wait(prof, pr.rewrite, conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
         tc_fence_after_sync();
         const uint32_t e1 = smem_u32(smem + st1 * stage_bytes), e2 = smem_u32(smem + st2 * stage_bytes);
         const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
@@ -683,7 +707,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         if (ok) sched_release(ring, it);
         if (t < 0) break;
         const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
-        ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        ok = timed_wait(prof, pr.accumulator, &tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d = tmem_base + s * BN;
@@ -693,7 +717,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         const int second = HAS_LORA ? __ldg(p.tiles + tile_coord(t / ksplits, tm, tn, band).m_idx).w : 0;
         int issued = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+          ok = timed_wait(prof, pr.operands, &full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * stage_bytes);
@@ -719,6 +743,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         have_prev = true;
       }
       if (HAS_LORA && have_prev && ok) lora_mma(prev_s, prev_second);
+      if (prof) store_profile(pr, p.status, clock64() - prof_t0);
     }
   } else {
     // ------------------------------ epilogue warps 0-3, 6-9 --------------------
@@ -1113,9 +1138,14 @@ __global__ void __launch_bounds__(PAIR_THREADS, 1) w8a8_gemm_pair_kernel(const _
 // accumulator stage (and announce the rewritten accumulator) on the leader's barriers.  All waits bounded.
 // ---------------------------------------------------------------------------------------------------
 constexpr int PAIR2_STAGE_BYTES = BM * BK + 128 * BK;                      // 32 KB: A tile + half of the weight tile
-constexpr int PAIR2_STAGES = SINGLE_STAGE_AREA / PAIR2_STAGE_BYTES;        // 6
 constexpr int PAIR2_BN = 256;
-constexpr int PAIR2_EPI_WARPS = EPI_THREADS / 32;
+// Sixteen epilogue warps per CTA (four per tensor-memory lane quadrant, 64 columns each): with eight the
+// epilogue of a 128 x 256 tile (two passes over tensor memory with LoRA, SwiGLU math, staged stores) takes
+// longer than the tile's main loop and bounds the kernel; warp 16 is the TMA producer, warp 17 issues the MMAs.
+constexpr int PAIR2_EPI_WARPS = 16;
+constexpr int PAIR2_THREADS = (PAIR2_EPI_WARPS + 2) * 32;
+constexpr int PAIR2_STAGE_AREA = STAGE_AREA_BYTES - PAIR2_EPI_WARPS * EPI_STAGE_BYTES;   // store-staging tiles on top
+constexpr int PAIR2_STAGES = PAIR2_STAGE_AREA / PAIR2_STAGE_BYTES;                        // 5
 
 struct PairAdapters {
   int count;       // distinct adapters of the pair, <= 4
@@ -1146,7 +1176,7 @@ __device__ __forceinline__ PairAdapters pair_adapters(const int4& t0, bool has1,
 }
 
 template <int EPI, bool HAS_LORA>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR2_THREADS, 1)
 w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<PAIR2_BN>;
   extern __shared__ unsigned char smem_unaligned[];
@@ -1181,11 +1211,11 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == PAIR2_EPI_WARPS + 1) {
     tmem_alloc_pair(tmem_ptr_smem, 512);
     tmem_relinquish_pair();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == PAIR2_EPI_WARPS && lane == 0) {
     tma_prefetch_desc(&p.tm_xq);
     tma_prefetch_desc(&p.tm_w);
     if (HAS_LORA) {
@@ -1208,7 +1238,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
   const int pair_id = static_cast<int>(blockIdx.x >> 1), num_pairs = static_cast<int>(gridDim.x >> 1);
   const int oob_row = p.m;   // a box that starts here lies outside the tensor: filled with zeros
 
-  if (warp == 4) {
+  if (warp == PAIR2_EPI_WARPS) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     if (lane == 0) {
       int stage = 0;
@@ -1279,7 +1309,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
       }
       if (HAS_LORA && have_prev && ok) lora_slots();
     }
-  } else if (warp == 5) {
+  } else if (warp == PAIR2_EPI_WARPS + 1) {
     // ------------------------------ MMA issuer (the leader only) ---------------------------
     if (lane == 0 && leader) {
       const uint32_t idesc = make_idesc(IDESC_D_S32, IDESC_S8, IDESC_S8, 2 * BM, PAIR2_BN);
@@ -1289,6 +1319,9 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
       bool ok = true, have_prev = false;
       uint32_t prev_s = 0;
       int prev_groups = 0;
+      const bool prof = p.profile != 0 && blockIdx.x == 0;
+      IssuerProfile pr;
+      const long long prof_t0 = clock64();
       auto next_stage = [&]() {
         if (++stage == PAIR2_STAGES) {
           stage = 0;
@@ -1303,7 +1336,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
           const int st2 = stage;
           next_stage();
-          if (g == 0 && !mbar_wait(conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
+          if (g == 0 && !timed_wait(prof, pr.rewrite, conv_done, lora_rounds & 1u, abort_flag, p.status, STATUS_TIMEOUT_LORA)) return false;
           tc_fence_after_sync();
           const uint32_t e1 = smem_u32(smem + st1 * PAIR2_STAGE_BYTES), e2 = smem_u32(smem + st2 * PAIR2_STAGE_BYTES);
           const uint64_t bd = make_desc_sw128(e2 + Z_PLANE_BYTES);
@@ -1320,7 +1353,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
       };
       for (int t = pair_id; t < total && ok; t += num_pairs, ++it) {
         const uint32_t s = it & 1u, aphase = (it >> 1) & 1u;
-        ok = mbar_wait(&tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+        ok = timed_wait(prof, pr.accumulator, &tmem_empty[s], aphase ^ 1u, abort_flag, p.status, STATUS_TIMEOUT_MMA);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d = tmem_base + s * PAIR2_BN;
@@ -1335,7 +1368,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
         const int inject_at = min(LORA_INJECT_AFTER, kblocks);
         int issued = 0;
         for (int kb = 0; kb < kblocks; ++kb) {
-          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
+          ok = timed_wait(prof, pr.operands, &full_bar[stage], phase, abort_flag, p.status, STATUS_TIMEOUT_MMA);
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * PAIR2_STAGE_BYTES);
@@ -1357,13 +1390,14 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
         have_prev = true;
       }
       if (HAS_LORA && have_prev && ok) lora_mma(prev_s, prev_groups);
+      if (prof) store_profile(pr, p.status, clock64() - prof_t0);
     }
   } else {
-    // ------------------------------ epilogue warps 0-3, 6-9 (both CTAs, own tile) ----------
-    const int quad = warp & 3;
-    const int c_begin = warp < 4 ? 0 : 4, c_end = warp < 4 ? 4 : 8;   // 32-column chunks of the 256 columns
+    // ------------------------------ epilogue warps 0-15 (both CTAs, own tile) ---------------
+    const int quad = warp & 3;                                          // tensor-memory lane quadrant of this warp
+    const int c_begin = (warp >> 2) * 2, c_end = c_begin + 2;           // two 32-column chunks of the 256 columns
     const int r = quad * 32 + lane;
-    unsigned char* store_stage = smem + SINGLE_STAGE_AREA + (warp < 4 ? warp : warp - 2) * EPI_STAGE_BYTES;
+    unsigned char* store_stage = smem + PAIR2_STAGE_AREA + warp * EPI_STAGE_BYTES;
     const uint32_t conv_remote = map_to_cta(smem_u32(conv_done), 0);
     uint32_t it = 0, lora_it = 0;
     bool ok = true;
@@ -1420,7 +1454,7 @@ w8a8_gemm_pair2_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();   // neither CTA leaves while the other may still signal its barriers or read its shared memory
-  if (warp == 5) {
+  if (warp == PAIR2_EPI_WARPS + 1) {
     tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, 512);
   }
@@ -1433,7 +1467,7 @@ static int launch_pair2_variant(const GemmParams& p, int grid, cudaStream_t stre
   static bool attr_set[MAX_DEVICES] = {};
   cudaError_t e = ensure_dynamic_smem(kernel, Cfg::SMEM_BYTES, attr_set);
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm attribute: %s", cudaGetErrorString(e));
-  kernel<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
+  kernel<<<grid, PAIR2_THREADS, Cfg::SMEM_BYTES, stream>>>(p);
   e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "gemm launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;
@@ -1646,19 +1680,25 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   if (rows && a.m > 64 && bn_eff > 128) bn_eff = 128;  // the l tile (rows x columns fp32) must leave room for the pipeline
   const int k_splits = pl.k_splits, kb_per_split = pl.kb_per_split;
   const int bn = bn_eff > 128 ? 256 : 128;
-  // Kernel variant.  Large problems with a long K loop: two M tiles per CTA (the pair's epilogue is not overlapped
-  // with the next main loop, so this pays only when the K loop dwarfs it: gain at K = 25600, loss at 5120).  Large
-  // problems with a shorter K loop: a CTA pair per 256 x 256 tile (cta_group::2), which cuts the bytes a CTA pulls
-  // per unit of tensor-core work by a third and keeps two accumulator stages.  Neither with a row scatter (their
-  // tile order is static and a pair's epilogue of the two-tile kernel stores 16 bytes per row from registers,
-  // which NVLink carries poorly), nor with a CTA cap (a concurrent stream wants SMs: dynamic tile claims).
+  // Kernel variant for large problems (all give the same bits).
+  //   long K loop (>= 64 blocks of 128): a CTA pair per 256 x 256 tile (tcgen05 cta_group::2): each CTA stages its
+  //     128 rows and half of the weight tile, a third fewer bytes per unit of tensor-core work, two accumulator
+  //     stages, sixteen epilogue warps.  Measured on B200: down projection of the Qwen3-32B-shaped block (K = 25600)
+  //     1.57 ms against 1.61 ms for the two-tiles-per-CTA kernel, the Qwen3-8B-shaped one (K = 12288) 0.555 against
+  //     0.607 ms.  With a CTA cap (a concurrent stream wants SMs) the two-tile kernel, whose tile claims are dynamic.
+  //   shorter K loop: one 128 x 256 tile per CTA.  There the MMA-issuing thread is blocked on the tensor pipe ~89 %
+  //     of the time whatever the variant (SKYRL_GEMM_VARIANT_PROFILE), the CTA pair brings nothing (K = 5120:
+  //     3.61 ms against 3.50 ms), and the single tile keeps dynamic tile claims.
+  // Neither pair form with a row scatter (their epilogues' tile order is static / their stores are 16 bytes per
+  // row from registers, which NVLink carries poorly).
   const bool big = !rows && bn_eff == 256 && k_splits == 1 && a.scatter_rows == 0 &&
                    static_cast<int64_t>(mt_est) * ((a.n + 255) / 256) >= 4 * sms;
-  bool paired = big && kblocks_of(a.k) >= 64;
-  bool pair2 = false;   // not chosen automatically
-  if (a.variant == SKYRL_GEMM_VARIANT_SINGLE) paired = pair2 = false;
-  if (a.variant == SKYRL_GEMM_VARIANT_TWO_TILES) paired = big, pair2 = false;
-  if (a.variant == SKYRL_GEMM_VARIANT_CTA_PAIR) pair2 = big && a.cta_limit <= 0, paired = paired && !pair2;
+  bool pair2 = big && kblocks_of(a.k) >= 64 && a.cta_limit <= 0;
+  bool paired = big && kblocks_of(a.k) >= 64 && !pair2;
+  const int forced = a.variant & 3;
+  if (forced == SKYRL_GEMM_VARIANT_SINGLE) paired = pair2 = false;
+  if (forced == SKYRL_GEMM_VARIANT_TWO_TILES) paired = big, pair2 = false;
+  if (forced == SKYRL_GEMM_VARIANT_CTA_PAIR) pair2 = big && a.cta_limit <= 0, paired = paired && !pair2;
   const int w_box_rows = pair2 ? 128 : bn_eff;   // a CTA of a pair stages half of the weight (and LoRA-B) tile
 
   GemmParams p;
@@ -1711,6 +1751,7 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   p.num_adapters = a.num_adapters;
   p.lterm_off = 0;
   p.lterm_pitch = 0;
+  p.profile = (a.variant & SKYRL_GEMM_VARIANT_PROFILE) != 0;
   if (rows) {
     p.z_rows = a.z_rows;
     p.row_ids = a.row_adapter_ids;

@@ -801,11 +801,12 @@ def main():
                          "fused exchange kernel (or the one-word all-reduce, finalize / quantise kernels and gathers of the "
                          "other forms); -1 = 8 on two GPUs, 16 on more")
     ap.add_argument("--tp-exchange-ctas", type=int, default=0, help="CTAs of the fused exchange kernel (0 = 4 per reserved SM)")
-    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "fused", "epilogue", "copy", "off"],
+    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "fused", "fused_copy", "epilogue", "copy", "off"],
                     help="how the fp32 partial sums reach the rank that owns the rows: stores from the down GEMM's "
                          "epilogue into the owner's memory, copy-engine pushes on the second stream, the fused exchange "
-                         "kernel that pulls them (no collective between blocks), or (off) the NCCL reduce-scatter; "
-                         "auto = epilogue on 2 GPUs, fused on more")
+                         "kernel (fused: it pulls them over NVLink; fused_copy: the copy engines push them and it adds "
+                         "local slabs; no collective between blocks either way), or (off) the NCCL reduce-scatter; "
+                         "auto = epilogue on 2 GPUs, fused_copy on more")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="> 0: sets NCCL_MAX_CTAS (tuning aid)")
     ap.add_argument("--gemm-variant", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6, 7],
                     help="force a kernel variant of the large GEMMs (0: the library chooses; 1 single tile per CTA, "

@@ -59,10 +59,11 @@ __device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
 // the owning GPU's L2, never by a line an earlier pass left in this SM's L1.
 __device__ __forceinline__ float4 ld_peer16(const float4* p) {
   float4 v;
+  // volatile (never hoisted above the flag wait and the barrier behind it) but no memory clobber: the loads of
+  // one vector are independent and should all be in flight together
   asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p)
-               : "memory");
+               : "l"(p));
   return v;
 }
 

@@ -152,8 +152,13 @@ class TensorParallelMLPStack:
                   rank's workspace, which lives in symmetric memory too; a second flag tells the peers
                   that the rows have arrived (`ops.w8a8_mlp_tp_exchange`).  Block 0 is prepared by every
                   rank for all rows (x is replicated), so the first exchange is the one behind block 0.
-    "auto" (default) = "fused" on more than 2 ranks, "epilogue" on 2.  If symmetric memory cannot be set up
-    the NCCL reduce-scatter is used.
+      "fused_copy" the same kernel fed by the copy engines: every rank pushes each owner's rows of its partial
+                  sums into a slab in the owner's memory (no SM involved, the transfer overlaps the other
+                  chunk's GEMMs), raises the flag, and the owner's kernel adds LOCAL slabs.  Pulling over
+                  NVLink inside the kernel ("fused") keeps every CTA waiting on peer-load latency one row at
+                  a time; with local slabs the kernel is short and needs few SMs.
+    "auto" (default) = "fused_copy" on more than 2 ranks, "epilogue" on 2.  If symmetric memory cannot be set
+    up the NCCL reduce-scatter is used.
 
     Blocks of fewer than 129 rows take the small-batch path and are not chunked.
     """
@@ -253,9 +258,9 @@ class TensorParallelMLPStack:
         if self.sequence_parallel and tp > 1 and m > ops.TILE_ROWS and self.blocks and plan["even"]:
             mode = self.peer_scatter
             if mode == "auto":
-                mode = "fused" if tp > 2 else "epilogue"
-            if mode == "fused" and self._fused_buffers(x, tp):
-                return self._forward_fused(x, adapter_ids, spans, chunks, tp, timing_events)
+                mode = "fused_copy" if tp > 2 else "epilogue"
+            if mode in ("fused", "fused_copy") and self._fused_buffers(x, tp):
+                return self._forward_fused(x, adapter_ids, spans, chunks, tp, timing_events, pull=(mode == "fused"))
             return self._forward_sequence_parallel(x, adapter_ids, spans, chunks, tp, timing_events)
         main = torch.cuda.current_stream()
         prev_done = [None] * len(spans)
@@ -305,7 +310,7 @@ class TensorParallelMLPStack:
         lora = first.gate_up_lora is not None
         slab_ptrs = self._peer_slabs(x, tp) if self.peer_scatter else None
         mode = self.peer_scatter if slab_ptrs is not None else False
-        if mode in (True, "auto", "fused"):   # "fused" lands here only when its buffers could not be set up
+        if mode in (True, "auto", "fused", "fused_copy"):   # the fused forms land here only when their buffers could not be set up
             mode = "epilogue" if tp <= 2 else "copy"
         peers = self._slabs[4] if slab_ptrs is not None else None
         self.scatter_mode = mode or "nccl"     # what actually delivers the partial sums, for reports
@@ -429,8 +434,9 @@ class TensorParallelMLPStack:
     MAX_CHUNK_SLOTS = 16
 
     def _fused_buffers(self, x, tp):
-        """One symmetric allocation per rank: [fp32 partial sums m x hidden | MLP workspace | flag words].  Returns
-        False (decided together) when symmetric memory is unavailable."""
+        """One symmetric allocation per rank: [fp32 partial sums m x hidden | slabs tp x m/tp x hidden fp32 (the other
+        ranks' partial sums of this rank's rows, when the copy engines deliver them) | MLP workspace | flag words].
+        Returns False (decided together) when symmetric memory is unavailable."""
         import torch
         import torch.distributed as dist
 
@@ -445,7 +451,8 @@ class TensorParallelMLPStack:
             return True
         ws_bytes = _lib.load().skyrl_w8a8_mlp_workspace_bytes(m, hidden, inter, na)
         up = lambda v: (v + 1023) // 1024 * 1024
-        off_ws = up(m * hidden * 4)
+        off_slabs = up(m * hidden * 4)
+        off_ws = off_slabs + up(tp * (m // tp) * hidden * 4)
         off_flags = off_ws + up(ws_bytes + 1024)
         total = off_flags + 2 * self.MAX_CHUNK_SLOTS * 8 * 4
         ok, local, ptrs = 1, None, None
@@ -472,6 +479,8 @@ class TensorParallelMLPStack:
         dist.barrier(group=self.group)       # every rank's flag words are zero before anyone raises one
         self._fused = {
             "key": key, "local": local, "handle": handle, "ptrs": ptrs, "off_ws": off_ws, "off_flags": off_flags,
+            "off_slabs": off_slabs,
+            "peer_slabs": [handle.get_buffer(r, (tp, m // tp, hidden), torch.float32, off_slabs // 4) for r in range(tp)],
             "partial": local[: m * hidden * 4].view(torch.float32).view(m, hidden),
             "workspace": local[off_ws: off_ws + ws_bytes + 1024],
             "flags": local[off_flags:].view(torch.int32).view(2, self.MAX_CHUNK_SLOTS, 8),
@@ -480,7 +489,7 @@ class TensorParallelMLPStack:
         self._seq = 0
         return True
 
-    def _forward_fused(self, x, adapter_ids, spans, chunks, tp, timing_events):
+    def _forward_fused(self, x, adapter_ids, spans, chunks, tp, timing_events, pull=False):
         import torch
         import torch.distributed as dist
 
@@ -493,12 +502,32 @@ class TensorParallelMLPStack:
         ptrs, off_ws, off_flags = fb["ptrs"], fb["off_ws"], fb["off_flags"]
         partial, flags = fb["partial"], fb["flags"]
         plan = exchange_plan(m, chunks, tp, rank, ops.TILE_ROWS)
-        own = plan["own"]
+        own, own_off, own_rows = plan["own"], plan["own_off"], plan["own_rows"]
         chunk_arg = lambda c: (c, chunks) if chunks > 1 else None
         layers = len(self.blocks)
         base = self._seq
         self._seq += layers
-        self.scatter_mode = "fused"
+        self.scatter_mode = "fused" if pull else "fused_copy"
+        row_bytes = hidden * 4
+        peer_slabs, slab_base = fb["peer_slabs"], ptrs[rank] + fb["off_slabs"]
+
+        def partial_sources(c):
+            """Address of every rank's partial sums such that `address + sorted_row * row_bytes` is the row: the
+            ranks' own buffers (pull over NVLink), or this rank's slabs (rank s's rows sit at slab s, chunk after
+            chunk) with its own buffer for its own share."""
+            if pull:
+                return [p for p in ptrs]
+            o0 = own[c][0]
+            return [ptrs[rank] if s == rank else slab_base + ((s * own_rows + own_off[c]) - o0) * row_bytes
+                    for s in range(tp)]
+
+        def push_partial(c):
+            # copy engines: this rank's partial sums of owner o's rows -> o's slab for this rank
+            (r0, cnt), ocnt = spans[c], own[c][1]
+            for step in range(1, tp):
+                o = (rank + step) % tp       # every rank starts with a different owner
+                peer_slabs[o][rank, own_off[c]:own_off[c] + ocnt].copy_(
+                    partial[r0 + o * ocnt:r0 + (o + 1) * ocnt], non_blocking=True)
 
         def flag_addr(r, kind, c, src):
             # word [kind][c][src] of rank r's flag block: raised by rank `src`
@@ -528,13 +557,18 @@ class TensorParallelMLPStack:
                 self._mark(f"L{l}c{c} gemms>", main, "main")
                 ev = timing_events[l] if (timing_events is not None and c == 0) else None
                 call = block_call(blk, cur, c, reuse_routing=True, input_prepared=True, timing_events=ev)
-                ops.tp_signal([flag_addr(r, 0, c, rank) for r in range(tp)], value)   # my partial sums are complete
+                if pull:
+                    ops.tp_signal([flag_addr(r, 0, c, rank) for r in range(tp)], value)   # my partial sums are complete
                 self._mark(f"L{l}c{c} gemms<", main, "main")
                 computed = torch.cuda.Event()
                 computed.record(main)
                 with torch.cuda.stream(comm):
                     comm.wait_event(computed)
                     self._mark(f"L{l}c{c} exchange>", comm, "comm")
+                    if not pull:
+                        push_partial(c)
+                        ops.tp_signal([flag_addr(r, 0, c, rank) for r in range(tp)], value)   # my rows have arrived
+                        self._mark(f"L{l}c{c} pushed", comm, "comm")
                     nxt = None
                     if not last:
                         nb = self.blocks[l + 1]
@@ -544,7 +578,7 @@ class TensorParallelMLPStack:
                             chunk=chunk_arg(c), reuse_routing=True, build_only=True)[1]
                     ops.w8a8_mlp_tp_exchange(
                         call, nxt, self._sorted if last else dst, tp=tp, row_begin=o0, row_count=ocnt,
-                        partials=[p for p in ptrs], wait_flags=flags[0, c], wait_value=value,
+                        partials=partial_sources(c), wait_flags=flags[0, c], wait_value=value,
                         peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
                         signal_flags=[flag_addr(r, 1, c, rank) for r in range(tp)] if nxt is not None else None,
                         signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas)

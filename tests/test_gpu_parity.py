@@ -311,11 +311,13 @@ def test_reference_group64_fixture(S):
     assert_bf16_close(to_np(y), z[f"{name}.expected_bf16"].view(BF16), max_ulp_frac=0.05, what=name)
 
 
+@pytest.mark.parametrize("variant", [0, 2], ids=["default_cta_pair", "two_tiles_per_cta"])
 @pytest.mark.parametrize("kind", ["linear", "swiglu", "residual"])
-def test_large_problem_paired_tile_kernel(S, kind):
+def test_large_problem_paired_tile_kernel(S, kind, variant):
     # enough 128x256 tiles (>= 4 per SM) and a long enough K loop (>= 64 blocks of 128) for the launcher to
-    # pick the two-tiles-per-CTA kernel; an odd number of M tiles and five adapters exercise the half-empty
-    # pair and per-tile LoRA operands
+    # pick a pair kernel: by default a CTA pair per 256 x 256 tile, forced here also to the two-tiles-per-CTA
+    # kernel (what a launch with a CTA cap takes); an odd number of M tiles and five adapters exercise the
+    # half-empty pair and per-tile LoRA operands
     m, k, n, rank, na = 2200, 8192, 9728, 32, 5
     x, w, a, b, s, ids = make_case(91, m, k, n, rank, na, w_std=0.012)
     q, packed = device_weight(S, w)
@@ -323,18 +325,19 @@ def test_large_problem_paired_tile_kernel(S, kind):
     lora = S.pack_lora(to_dev(a), to_dev(b), to_dev(s), in_features=k, padded_out_features=n)
     res = None
     if kind == "linear":
-        got = S.w8a8_lora_linear(xd, packed, lora, adapter_ids=idd, enabled=True)
+        got = S.w8a8_lora_linear(xd, packed, lora, adapter_ids=idd, enabled=True, gemm_variant=variant)
     elif kind == "swiglu":
-        got = S.w8a8_rms_gate_up_lora_swiglu(xd, None, packed, lora, adapter_ids=idd, enabled=True)
+        got = S.w8a8_rms_gate_up_lora_swiglu(xd, None, packed, lora, adapter_ids=idd, enabled=True, gemm_variant=variant)
     else:
         res = np.random.default_rng(5).standard_normal((m, n)).astype(np.float32).astype(BF16)
-        got = S.w8a8_down_lora_residual(xd, packed, lora, residual=to_dev(res), adapter_ids=idd, enabled=True)
+        got = S.w8a8_down_lora_residual(xd, packed, lora, residual=to_dev(res), adapter_ids=idd, enabled=True,
+                                        gemm_variant=variant)
     S.check_status()
     # pinned through the kernel's own fp32 projection: the fused epilogue reproduces it, and the projection
     # differs from the oracle's only at proven rounding ties
     stats = check_projection_chain(S, f"paired {kind}", x, q, packed, (a, b, s), lora, ids, to_np(got), kind, residual=res)
     assert stats["differing"] <= 5e-3
-    acc = S.w8a8_int32_accumulator(xd, packed, enabled=True)
+    acc = S.w8a8_int32_accumulator(xd, packed, enabled=True, gemm_variant=variant)
     _, parts = O.quantized_lora_linear(x, q, return_parts=True)
     np.testing.assert_array_equal(to_np(acc), parts["acc"][:, 0, :])
 

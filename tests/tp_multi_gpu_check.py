@@ -65,7 +65,8 @@ def main():
     xd, idd = to_dev(x), to_dev(ids)
     outs = {}
     for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False),
-                           ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy"), ("fused", True, "fused")):
+                           ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy"), ("fused", True, "fused"),
+                           ("fused_copy", True, "fused_copy")):
         stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
         for _ in range(3):                      # later passes reuse buffers, a warm workspace and growing flag values
             y = stack.forward(xd, idd)
@@ -74,12 +75,12 @@ def main():
         outs[name] = y.clone()
         if name == "peer_copy":
             used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
-        if name == "fused":
-            used_fused = stack.scatter_mode
+        if name in ("fused", "fused_copy"):
+            used_fused = stack.scatter_mode if name == "fused" else used_fused
             S.use_workspace(None)               # the stack registered its symmetric workspace: release it
     a = outs["all_reduce"].float()
     ok, mismatched, between = True, 0, 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy"):
         b = outs[name].float()
         mism = int(((a - b).abs() > 0).sum())
         # more than two ranks: the collectives may add the fp32 partial sums in different orders, and a
@@ -89,6 +90,7 @@ def main():
         mismatched, between = max(mismatched, mism), max(between, rel_b)
     # the three peer-memory forms add the partial sums in ascending rank order: identical bits at any group size
     same_order = int(((outs["fused"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
+        int(((outs["fused_copy"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
         int(((outs["peer_scatter"].float() - outs["peer_copy"].float()).abs() > 0).sum())
     if used_peer and used_fused == "fused":
         ok = ok and same_order == 0
@@ -96,7 +98,7 @@ def main():
     for delta, qgu, ga, gb, wd, da, db in host:
         want = O.tp_shard_mlp_reference(want, delta, qgu, ga, gb, scal, wd, da, db, scal, ids, world)
     rel = 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy"):
         got = outs[name].cpu().view(torch.int16).numpy().view(BF16)
         rel = max(rel, O.relative_l2(got, want))
     ok = ok and rel < 2e-3

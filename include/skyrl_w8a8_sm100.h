@@ -128,6 +128,21 @@ SKYRL_API int skyrl_rms_quant_sm100_v1(const void* x, int64_t x_row_stride, cons
                              const int32_t* row_map, int32_t m, int32_t k, void* xq, float* sx, void* xn,
                              skyrl_stream_t stream);
 
+/* Output-cotangent quantiser of the backward pass (input gradient).  The straight-through
+ * backward of the W8A8 linear, _quantized_lora_linear_bwd
+ * (skyrl/tx/kernels/quantized_lora.py:337-394), needs dx = dy deq(W)^T + R A^T.  This call
+ * moves the weight's per-output-channel scale to the cotangent, g = dy * col_scale, and
+ * splits each row of g into int8 planes g ~= s1 q1 + s2 q2 (per-row absmax / 127 scales;
+ * the second plane quantises the residual of the first), so that the int8 GEMM entry point
+ * over the TRANSPOSED packed weight (unit weight scales) computes g wq^T.
+ *   dy         bf16 [*, n], row pitch dy_row_stride elements
+ *   col_scale  fp32 [n] (the forward weight's sw)
+ *   row_map    int32 [m] source row of each output row, or NULL
+ *   q1, q2     int8 [m, n];  s1, s2 fp32 [m];  q2 = s2 = NULL gives one plane          */
+SKYRL_API int skyrl_w8a8_grad_quant_sm100_v1(const void* dy, int64_t dy_row_stride, const float* col_scale,
+                             const int32_t* row_map, int32_t m, int32_t n, void* q1, float* s1, void* q2,
+                             float* s2, skyrl_stream_t stream);
+
 /* LoRA-A projection on the tensor cores: z[i, :] = s[a] * (x[i, :] @ A[a]) for
  * the adapter a of row i's tile, written as three bf16 planes
  * (hi, mid, lo) whose sum is the fp32 value of z exactly.  Replaces the first ragged_dot of

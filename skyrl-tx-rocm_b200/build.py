@@ -19,7 +19,7 @@ CSRC = PKG / "csrc"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libskyrl_w8a8_sm100.so"
 SOURCES = ["api.cu", "quant_route_sm100.cu", "lora_a_proj_sm100.cu", "lora_rows_sm100.cu",
-           "w8a8_gemm_sm100.cu", "tp_exchange_sm100.cu"]
+           "w8a8_gemm_sm100.cu", "tp_exchange_sm100.cu", "grad_quant_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

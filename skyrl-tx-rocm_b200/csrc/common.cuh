@@ -66,6 +66,8 @@ inline cudaError_t ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[MA
 int launch_route(const int32_t* ids, int m, int num_adapters, int32_t* perm, int32_t* tiles, int32_t* num_tiles,
                  int max_tiles, int32_t* status, cudaStream_t stream, int chunk_rows = 0, int chunk_cap = 0,
                  int32_t* zero_words = nullptr, int zero_count = 0);
+int launch_grad_quant(const void* dy, int64_t dy_row_stride, const float* col_scale, const int32_t* row_map, int m, int n,
+                      void* q1, float* s1, void* q2, float* s2, cudaStream_t stream);
 int launch_rms_quant(const void* x, int64_t x_row_stride, const void* rms_delta, float eps, const int32_t* row_map,
                      int m, int k, void* xq, float* sx, void* xn, cudaStream_t stream);
 // rows [m, k] contiguous (row pitch k) with their absmax known: codes and scales in one streaming pass

@@ -225,3 +225,27 @@ def test_w4_pack_bytes_and_quantiser_match_the_oracle():
     np.testing.assert_array_equal(got.codes.numpy(), want.codes)
     np.testing.assert_array_equal(got.scales.numpy(), want.scales)
     assert got.bits == 4 and got.codes.dtype == torch.uint8
+
+
+def test_lora_parameter_grads_match_the_oracle_vjp_on_cpu():
+    # the rank-r gradient reductions are host-orchestrated library matmuls: checked here without a GPU
+    from oracle import w8a8_oracle as O
+    from skyrl_tx_rocm_b200 import backward as B
+
+    rng = np.random.default_rng(3)
+    m, k, n, r, na = 40, 24, 20, 4, 3
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    dy = rng.standard_normal((m, n)).astype(np.float32)
+    a = rng.standard_normal((na, k, r)).astype(np.float32) * 0.2
+    b = rng.standard_normal((na, r, n)).astype(np.float32) * 0.2
+    s = np.asarray([0.5, 1.0, 2.0], dtype=np.float32)
+    ids = rng.integers(0, na, size=m).astype(np.int32)
+    ids[ids == 1] = 0                                             # an adapter with no rows keeps zero gradients
+    q = O.quantize_frozen_weight(rng.standard_normal((k, n)).astype(np.float32), scale_dtype=np.float32)
+    _, want_da, want_db, want_ds = O.quantized_lora_linear_vjp(x, q, a, b, s, dy, ids)
+    d_a, d_b, d_s = B.lora_parameter_grads(torch.from_numpy(x), torch.from_numpy(dy), torch.from_numpy(a),
+                                           torch.from_numpy(b), torch.from_numpy(s), torch.from_numpy(ids))
+    np.testing.assert_allclose(d_a.numpy(), want_da, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(d_b.numpy(), want_db, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(d_s.numpy(), want_ds, rtol=1e-5, atol=1e-5)
+    assert not d_a[1].any() and not d_b[1].any() and d_s[1] == 0

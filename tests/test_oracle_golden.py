@@ -298,3 +298,54 @@ def test_int4_pack_bytes_and_hand_coded_w4_vectors():
     codes = O.unpacked_codes(q4)
     assert q4.codes.dtype == np.uint8 and codes.shape == (70, 13) and np.abs(codes).max() <= 7
     assert O.relative_l2(O.dequantize_frozen_weight(q4), w) < 0.20      # the reference's W4 round-trip gate
+
+
+def test_vjp_matches_finite_differences_of_the_dequantised_model():
+    # the reference pins its backward to these equations (tests/tx/kernels/test_quantized_lora.py:116-159:
+    # jax.grad of the custom VJP == the documented closed form).  Here the closed form is checked against
+    # central differences of the straight-through model y = x deq(W) + s (x A) B it is the gradient of.
+    rng = np.random.default_rng(31)
+    m, k, n, r, na = 6, 10, 7, 3, 2
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = rng.standard_normal((k, n)).astype(np.float32)
+    a = (rng.standard_normal((na, k, r)) * 0.1).astype(np.float32)
+    b = (rng.standard_normal((na, r, n)) * 0.1).astype(np.float32)
+    s = np.asarray([0.75, 1.5], dtype=np.float32)
+    ids = rng.integers(0, na, size=m).astype(np.int32)
+    dy = rng.standard_normal((m, n)).astype(np.float32)
+    q = O.quantize_frozen_weight(w, group_size=10, scale_dtype=np.float32)
+    deq = O.dequantize_frozen_weight(q).astype(np.float64)
+
+    def loss(x_, a_, b_, s_):
+        y = x_.astype(np.float64) @ deq
+        for i in range(m):
+            y[i] += s_[ids[i]] * ((x_[i].astype(np.float64) @ a_[ids[i]].astype(np.float64)) @ b_[ids[i]].astype(np.float64))
+        return float(np.sum(y * dy))
+
+    dx, d_a, d_b, d_s = O.quantized_lora_linear_vjp(x, q, a, b, s, dy, ids)
+
+    def numeric(arr, which):
+        g = np.zeros(arr.shape, dtype=np.float64)
+        it = np.nditer(arr, flags=["multi_index"])
+        for _ in it:
+            i = it.multi_index
+            hi, lo = arr.astype(np.float64).copy(), arr.astype(np.float64).copy()
+            hi[i] += 1e-3
+            lo[i] -= 1e-3
+            args_hi = [x, a, b, s]
+            args_lo = [x, a, b, s]
+            args_hi[which], args_lo[which] = hi, lo
+            g[i] = (loss(*args_hi) - loss(*args_lo)) / 2e-3
+        return g
+
+    np.testing.assert_allclose(dx, numeric(x, 0), rtol=2e-4, atol=2e-4)
+    np.testing.assert_allclose(d_a, numeric(a, 1), rtol=2e-4, atol=2e-4)
+    np.testing.assert_allclose(d_b, numeric(b, 2), rtol=2e-4, atol=2e-4)
+    np.testing.assert_allclose(d_s, numeric(s, 3), rtol=2e-4, atol=2e-4)
+    # single-adapter form equals the reference's documented closed form
+    dx1, da1, db1, ds1 = O.quantized_lora_linear_vjp(x, q, a[0], b[0], 0.75, dy)
+    low = (dy @ b[0].T) * np.float32(0.75)
+    np.testing.assert_allclose(dx1, dy @ O.dequantize_frozen_weight(q).T + low @ a[0].T, rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(da1[0], x.T @ low, rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(db1[0], ((x @ a[0]).T @ dy) * np.float32(0.75), rtol=2e-6, atol=2e-6)
+    np.testing.assert_allclose(ds1[0], np.sum(dy * ((x @ a[0]) @ b[0])), rtol=2e-6, atol=2e-6)

@@ -368,6 +368,8 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
             # per layer: two quantiser launches, two LoRA-A (or LoRA-B row) launches, two GEMMs; one routing launch
             launches_per_step = layers * 6 + 1
 
+        prefetch_bytes = (args.prefetch_mb << 20) if (m <= 128 and tp == 1) else 0
+
         def step(x_in, ids_in, events=None):
             if tp > 1:
                 return tp_stack.forward(x_in, ids_in, timing_events=events)
@@ -376,8 +378,12 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                 ev = events[l] if events is not None else None
                 dst = act[l & 1]
                 # adapter ids are the same for every layer of a step: route once, then reuse
+                # decode: every GEMM asks the leading bytes of the next GEMM's weights into L2 (the next layer's
+                # gate_up behind down; the step's first layer behind the last, for the next step)
                 S.w8a8_mlp_block(cur, delta, gu_w, gu_l, dn_w, dn_l, ids_in, enabled=True, out=dst, timing_events=ev,
-                                 reuse_routing=l > 0, gemm_variant=args.gemm_variant)
+                                 reuse_routing=l > 0, gemm_variant=args.gemm_variant,
+                                 prefetch_next=blocks[(l + 1) % len(blocks)][1] if prefetch_bytes else None,
+                                 prefetch_bytes=prefetch_bytes)
                 cur = dst
             return cur
     else:
@@ -584,7 +590,8 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                    "adapter_ids": wl["ids"], "parallelism": f"tp{tp}", "cuda_graph": graph is not None,
                    **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
                        "tp_peer_scatter": (tp_stack.scatter_mode or "all_reduce") if tp_stack is not None else "off",
-                       "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer"},
+                       "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer",
+                   **({"l2_prefetch_mb": args.prefetch_mb} if (kind == "mlp" and m <= 128 and tp == 1) else {})},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -796,6 +803,9 @@ def main():
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
                     help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
                          "0: one fp32 all-reduce per chunk")
+    ap.add_argument("--prefetch-mb", type=int, default=0,
+                    help="decode shapes (at most 128 rows, one GPU): MiB of the next GEMM's weights every GEMM asks into L2 "
+                         "after its own loads (0 = off, the default: measured slower on B200, 2.62 -> 2.70 ms per c2 step at 48 MiB)")
     ap.add_argument("--tp-reserve-sms", type=int, default=-1,
                     help="SMs the GEMMs leave to the second stream's small kernels while chunks overlap (N > 1): the "
                          "fused exchange kernel (or the one-word all-reduce, finalize / quantise kernels and gathers of the "

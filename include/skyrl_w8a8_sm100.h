@@ -228,8 +228,13 @@ typedef struct SkyrlW8A8GemmArgs {
                             /* loop runs and add it before the single cast (skyrl/tx/layers/lora.py:142-157   */
                             /* per token); z_parts / lora_b_packed / out_row_map are then unused, K is not    */
                             /* split, and any epilogue but SKYRL_EPI_ACC_I32 is allowed.                      */
+  const void* prefetch;     /* Optional: once a CTA has requested its last weight tile it asks the memory     */
+  int64_t prefetch_bytes;   /* system to bring its share of [prefetch, prefetch + prefetch_bytes) into L2     */
+                            /* (cp.async.bulk.prefetch.L2; 16-byte aligned address and size): the weights of  */
+                            /* the NEXT GEMM of a decode step, which HBM can deliver while the short row-wise */
+                            /* kernels between two GEMMs run.  No effect on any result.  0 bytes: nothing.    */
 } SkyrlW8A8GemmArgs;
-SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8GemmArgs) == 272, "SkyrlW8A8GemmArgs layout");
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8GemmArgs) == 288, "SkyrlW8A8GemmArgs layout");
 SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8GemmArgs, xq) == 32 && offsetof(SkyrlW8A8GemmArgs, out_row_stride) == 120 &&
                      offsetof(SkyrlW8A8GemmArgs, scatter_bases) == 152 && offsetof(SkyrlW8A8GemmArgs, sched) == 232 &&
                      offsetof(SkyrlW8A8GemmArgs, z_rows) == 240 && offsetof(SkyrlW8A8GemmArgs, lora_b_rows_rank) == 264,
@@ -423,8 +428,12 @@ typedef struct SkyrlW8A8MlpArgs {
   void* tp_scatter_bases[8]; /* their owners, tp_scatter_rows consecutive sorted rows each starting at the    */
                              /* first row of the call's chunk (see SkyrlW8A8GemmArgs.scatter_bases); `out` is  */
                              /* then not written.                                                             */
+  const void* prefetch_next; /* Batches of at most SKYRL_TILE_ROWS rows: packed weight codes of the projection  */
+  int64_t prefetch_next_bytes; /* that runs after this block (the next block's gate_up) and how many of their  */
+                             /* leading bytes the down GEMM should bring into L2 (SkyrlW8A8GemmArgs.prefetch); */
+  int64_t prefetch_down_bytes; /* leading bytes of dn_wq the gate_up GEMM brings into L2.  0: no prefetch.      */
 } SkyrlW8A8MlpArgs;
-SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8MlpArgs) == 312, "SkyrlW8A8MlpArgs layout");
+SKYRL_ABI_ASSERT(sizeof(SkyrlW8A8MlpArgs) == 336, "SkyrlW8A8MlpArgs layout");
 SKYRL_ABI_ASSERT(offsetof(SkyrlW8A8MlpArgs, x) == 32 && offsetof(SkyrlW8A8MlpArgs, gu_wq) == 56 &&
                      offsetof(SkyrlW8A8MlpArgs, out) == 144 && offsetof(SkyrlW8A8MlpArgs, timing_events) == 176 &&
                      offsetof(SkyrlW8A8MlpArgs, flags) == 208 && offsetof(SkyrlW8A8MlpArgs, num_chunks) == 232 &&

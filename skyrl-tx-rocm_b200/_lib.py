@@ -56,6 +56,8 @@ class GemmArgs(C.Structure):
         ("row_amax", C.c_void_p), ("sched", C.c_void_p),
         ("z_rows", C.c_void_p), ("row_adapter_ids", C.c_void_p), ("lora_b_rows", C.c_void_p),
         ("lora_b_rows_rank", C.c_int32), ("variant", C.c_int32),
+        ("prefetch", C.c_void_p),
+        ("prefetch_bytes", C.c_int64),
     ]
 
 
@@ -88,6 +90,9 @@ class MlpArgs(C.Structure):
         ("flags", C.c_uint32), ("b_rows_rank", C.c_int32), ("gu_b_rows", C.c_void_p), ("dn_b_rows", C.c_void_p),
         ("num_chunks", C.c_int32), ("chunk_index", C.c_int32), ("gemm_cta_limit", C.c_int32), ("tp_scatter_rows", C.c_int32),
         ("tp_scatter_bases", C.c_void_p * 8),
+        ("prefetch_next", C.c_void_p),
+        ("prefetch_next_bytes", C.c_int64),
+        ("prefetch_down_bytes", C.c_int64),
     ]
 
 

@@ -249,6 +249,8 @@ struct Projection {
   int64_t out_stride;
   int32_t* status;
   int32_t* sched;         // {claimed, finished} words of the GEMM launch inside the caller's workspace
+  const void* prefetch;   // row-wise route: bytes the GEMM asks into L2 after its own loads (the next GEMM's weights)
+  int64_t prefetch_bytes;
   void* ev_begin;
   void* ev_end;
 };
@@ -311,6 +313,8 @@ static int run_projection(const Projection& q, cudaStream_t stream) {
     g.num_tiles = q.num_tiles;
     g.status = q.status;
     g.sched = q.sched;
+    g.prefetch = q.prefetch;
+    g.prefetch_bytes = q.prefetch_bytes;
     if (!q.two_step_rows) {
       // one kernel: the GEMM's epilogue warps evaluate the per-row LoRA term while the weights stream and apply
       // scales, LoRA, the cast and the SwiGLU / residual step from tensor memory
@@ -632,6 +636,12 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   // streaming pass (SKYRL_MLP_NO_ROW_AMAX keeps the two-pass quantiser; the two must agree bit for bit)
   const bool collect = !pl.rows_path && (a->flags & SKYRL_MLP_NO_ROW_AMAX) == 0;
   q.row_amax = collect ? w.h_amax : nullptr;
+  if (pl.rows_path && a->prefetch_down_bytes > 0) {
+    // the down weights travel to L2 while the row-wise kernels behind gate_up run
+    const int64_t dn_bytes = static_cast<int64_t>((a->inter + SKYRL_WEIGHT_KBLOCK - 1) / SKYRL_WEIGHT_KBLOCK) * a->hidden * SKYRL_WEIGHT_KBLOCK;
+    q.prefetch = a->dn_wq;
+    q.prefetch_bytes = (a->prefetch_down_bytes < dn_bytes ? a->prefetch_down_bytes : dn_bytes) / 16 * 16;
+  }
   if ((rc = run_projection(q, stream))) return rc;
 
   // back half: quant(h) -> down W8A8 LoRA -> + residual, rows scattered back to token order
@@ -654,6 +664,12 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.xq = w.hq;
   q.sx = w.sh;
   q.sched = w.sched + 2;
+  q.prefetch = nullptr;
+  q.prefetch_bytes = 0;
+  if (pl.rows_path && a->prefetch_next != nullptr && a->prefetch_next_bytes > 0) {
+    q.prefetch = a->prefetch_next;
+    q.prefetch_bytes = a->prefetch_next_bytes;
+  }
   q.epilogue = a->down_epilogue;
   q.out_row_map = a->down_epilogue == SKYRL_EPI_PARTIAL_F32 ? nullptr : pl.perm;
   q.residual = a->residual != nullptr ? a->residual : a->x;

@@ -112,7 +112,21 @@ struct GemmParams {
   int profile;                 // 1: the MMA issuer of CTA 0 adds the cycles it spent waiting to status[1..3]
   int lterm_off;               // byte offset of the l tile inside the stage area
   int lterm_pitch;             // floats per row of the l tile (odd, so that a column is conflict-free)
+  const unsigned char* prefetch;  // bytes another kernel will stream soon: requested into L2 once the own loads are out
+  long long prefetch_bytes;
 };
+
+// The producer's last act: this CTA's share of the prefetch range, in pieces interleaved over the grid so
+// that the range arrives roughly front to back (the order its consumer reads it in).
+__device__ __forceinline__ void prefetch_share_to_l2(const GemmParams& p) {
+  constexpr long long PIECE = 16384;
+  const long long pieces = (p.prefetch_bytes + PIECE - 1) / PIECE;
+  for (long long i = blockIdx.x; i < pieces; i += gridDim.x) {
+    const long long off = i * PIECE;
+    const uint32_t bytes = static_cast<uint32_t>(min(PIECE, p.prefetch_bytes - off));
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.prefetch + off), "r"(bytes) : "memory");
+  }
+}
 
 // NULL (and status STATUS_BAD_SCATTER) for a row that has no owner: the caller skips the store.
 __device__ __forceinline__ float* partial_row_ptr(const GemmParams& p, int64_t orow) {
@@ -652,6 +666,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) w8a8_gemm_kernel(const __grid
         have_prev = true;
       }
       if (HAS_LORA && have_prev && ok) lora_slots(prev_row0, prev_n0, prev_adapter, prev_second);
+      if (ok && p.prefetch_bytes > 0) prefetch_share_to_l2(p);
     }
   } else if (warp == 5) {
     // ------------------------------ MMA issuer --------------------------------
@@ -1794,6 +1809,14 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   if (p.num_stages > MAX_STAGES) p.num_stages = MAX_STAGES;
   p.sched = a.sched != nullptr ? a.sched : next_sched_counter();
   if (p.sched == nullptr) return fail(SKYRL_ERR_LAUNCH, "gemm: scheduler counters unavailable");
+  p.prefetch = nullptr;
+  p.prefetch_bytes = 0;
+  if (a.prefetch != nullptr && a.prefetch_bytes > 0) {
+    if (!aligned16(a.prefetch) || a.prefetch_bytes % 16 != 0)
+      return fail(SKYRL_ERR_INVALID_ARGUMENT, "gemm: the prefetch range must be 16-byte aligned in address and size");
+    p.prefetch = static_cast<const unsigned char*>(a.prefetch);
+    p.prefetch_bytes = a.prefetch_bytes;
+  }
   p.k_splits = k_splits;
   p.kb_per_split = kb_per_split;
   p.slab_stride = static_cast<int64_t>(a.m) * a.out_row_stride;

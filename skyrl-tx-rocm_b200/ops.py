@@ -689,7 +689,8 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
                    timing_events=None, return_call: bool = False, reuse_routing: bool = False, chunk=None,
                    gemm_cta_limit: int = 0, input_prepared: bool = False, prepare_rows=None, scatter=None,
                    row_amax_from_epilogue: bool = True, keep_normalized: bool = False, build_only: bool = False,
-                   fused_rows: bool = False, gemm_variant: int = 0):
+                   fused_rows: bool = False, gemm_variant: int = 0, prefetch_next: PackedW8Weight | None = None,
+                   prefetch_bytes: int = 0):
     """One MLP block, out = residual + down(swiglu(gate_up(rmsnorm(x)))), with
     the adapter routing computed once and h kept on the device in sorted row
     order (qwen3_5.py:786-826).  Takes packed weights and tables only.
@@ -706,7 +707,11 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     both forms give identical bits); `fused_rows=True` makes small batches (at most 128 rows) finish each
     projection in the GEMM's own epilogue instead of a second row-wise kernel (same bits, one launch fewer;
     slower on B200 at decode shapes, so not the default).  `build_only=True` validates and returns the call handle without
-    enqueuing anything (the handle of the NEXT block is an argument of `w8a8_mlp_tp_exchange`)."""
+    enqueuing anything (the handle of the NEXT block is an argument of `w8a8_mlp_tp_exchange`).
+    `prefetch_bytes > 0` (small batches only) makes each GEMM ask up to that many leading bytes of the NEXT
+    GEMM's weights into L2 once its own loads are out — the down weights behind gate_up, and behind down the
+    gate_up weights of `prefetch_next` (the following block) — so that HBM keeps delivering during the
+    row-wise kernels between two GEMMs; it changes no value."""
     _validate_exact_bool("enabled", enabled)
     if not enabled:
         raise RuntimeError("the W8A8 MLP block is disabled by default")
@@ -781,6 +786,11 @@ def w8a8_mlp_block(x, rms_delta, gate_up_weight: PackedW8Weight, gate_up_lora: P
     if chunk is not None:
         a.chunk_index, a.num_chunks = int(chunk[0]), int(chunk[1])
     a.gemm_cta_limit = int(gemm_cta_limit)
+    if prefetch_bytes > 0:
+        a.prefetch_down_bytes = int(prefetch_bytes) // 16 * 16
+        if prefetch_next is not None:
+            a.prefetch_next = prefetch_next.wq.data_ptr()
+            a.prefetch_next_bytes = min(int(prefetch_bytes), prefetch_next.wq.numel()) // 16 * 16
     if scatter is not None:
         a.tp_scatter_rows = int(scatter[0])
         if len(scatter[1]) > 8:

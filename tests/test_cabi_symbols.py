@@ -69,9 +69,9 @@ def test_struct_sizes_are_stable():
 
     # Natural alignment, no packing: these sizes are part of ABI v1 and are
     # checked against struct_size by every entry point.
-    assert ctypes.sizeof(_lib.GemmArgs) == 32 + 11 * 8 + 2 * 8 + 8 + 8 + 8 * 8 + 8 + 8 + 8 + 4 * 8 == 272
+    assert ctypes.sizeof(_lib.GemmArgs) == 32 + 11 * 8 + 2 * 8 + 8 + 8 + 8 * 8 + 8 + 8 + 8 + 4 * 8 + 2 * 8 == 288
     assert ctypes.sizeof(_lib.LinearArgs) == 32 + 3 * 8 + 8 + 7 * 8 + 8 + 8 + 8 + 8 + 8 + 8 + 2 * 8 + 16 == 200
-    assert ctypes.sizeof(_lib.MlpArgs) == 32 + 18 * 8 + 4 * 8 + 8 + 16 + 16 + 8 * 8 == 312
+    assert ctypes.sizeof(_lib.MlpArgs) == 32 + 18 * 8 + 4 * 8 + 8 + 16 + 16 + 8 * 8 + 3 * 8 == 336
 
 
 def test_disabled_by_default_and_exact_bool():

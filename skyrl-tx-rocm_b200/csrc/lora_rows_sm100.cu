@@ -22,6 +22,10 @@ namespace cg = cooperative_groups;
 
 namespace skyrl {
 
+#ifndef SKYRL_FINALIZE_PAIRS
+#define SKYRL_FINALIZE_PAIRS 1  // column pairs per thread of the finalize kernel on wide projections (1, 2 or 4; measured on the c2 step: 2.58, 2.68, 2.79 ms)
+#endif
+
 constexpr int ROWQ_THREADS = 128;
 constexpr int ROWQ_CLUSTER = 8;
 
@@ -198,7 +202,12 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
   cluster.sync();  // no CTA may leave while another still reads its shared memory
 }
 
-template <int EPI>
+// P column pairs per thread (pairs j * 256 + threadIdx.x of the CTA's run of 256 * P pairs), rank <= 8 * RV.
+// Every load is issued before the first value is used: the scales, the residual and the RAW LoRA-B rows
+// before the wait for the GEMM in front of this kernel (CTAs that are resident while that GEMM still runs
+// hide them completely), the accumulator right after it, and only then is the LoRA term evaluated.  A CTA
+// that starts after the GEMM has finished therefore pays one memory latency, not two in a row.
+template <int EPI, int P, int RV>
 __global__ void __launch_bounds__(256)
 finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_stride, const float* __restrict__ sx,
                      const float* __restrict__ sw,
@@ -211,66 +220,100 @@ finalize_rows_kernel(const int32_t* __restrict__ acc, int slabs, int64_t slab_st
   if (rank_vecs > 0 && threadIdx.x < SKYRL_LORA_RANK_PAD)
     zs[threadIdx.x] = z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x];
   __syncthreads();
-  const int n0 = 2 * (blockIdx.x * 256 + threadIdx.x);  // this thread owns columns n0 and n0 + 1
-  if (n0 >= n) return;  // (a thread that leaves counts as having passed pdl_wait / pdl_trigger)
-  // everything that does not come from the GEMM just before this kernel is fetched and the LoRA term
-  // computed while that GEMM may still be running; only the accumulator is read after the wait
+  const int base = 2 * (blockIdx.x * 256 * P + threadIdx.x);  // pair j of this thread: columns base + 512 j, + 1
   const float sxm = __ldg(sx + m);
-  const float2 w2 = __ldg(reinterpret_cast<const float2*>(sw + n0));
-  float l0 = 0.f, l1 = 0.f;
+  int adapter = 0;
   if (rank_vecs > 0) {
-    int adapter = ids != nullptr ? ids[m] : 0;
+    adapter = ids != nullptr ? ids[m] : 0;
     if (adapter < 0 || adapter >= num_adapters) {  // clamped and reported, never used as an index
       if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(status, 0, STATUS_BAD_ADAPTER_ID);
       adapter = min(max(adapter, 0), num_adapters - 1);
     }
-    const __nv_bfloat16* b0 = b_table + static_cast<int64_t>(adapter) * b_adapter_stride +
-                              static_cast<int64_t>(n0) * b_row_stride;
-    const uint4* r0 = reinterpret_cast<const uint4*>(b0);
-    const uint4* r1 = reinterpret_cast<const uint4*>(b0 + b_row_stride);
-    for (int q = 0; q < rank_vecs; ++q) {
-      const uint4 u0 = __ldg(r0 + q), u1 = __ldg(r1 + q);
-      const uint32_t c0[4] = {u0.x, u0.y, u0.z, u0.w};
-      const uint32_t c1[4] = {u1.x, u1.y, u1.z, u1.w};
+  }
+  float2 w2[P];
+  uint32_t rv[P];
+  uint4 braw[P][2][RV];
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        l0 = fmaf(zs[8 * q + 2 * j], bf16_lo(c0[j]), l0);
-        l0 = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(c0[j]), l0);
-        l1 = fmaf(zs[8 * q + 2 * j], bf16_lo(c1[j]), l1);
-        l1 = fmaf(zs[8 * q + 2 * j + 1], bf16_hi(c1[j]), l1);
+  for (int j = 0; j < P; ++j) {
+    const int n0 = base + 512 * j;
+    const bool live = n0 < n;
+    w2[j] = live ? __ldg(reinterpret_cast<const float2*>(sw + n0)) : make_float2(0.f, 0.f);
+    rv[j] = (EPI == SKYRL_EPI_RESIDUAL && live)
+                ? __ldg(reinterpret_cast<const uint32_t*>(residual + static_cast<int64_t>(m) * res_stride + n0))
+                : 0u;
+    const __nv_bfloat16* b0 = b_table + static_cast<int64_t>(adapter) * b_adapter_stride +
+                              static_cast<int64_t>(live ? n0 : 0) * b_row_stride;
+#pragma unroll
+    for (int q = 0; q < RV; ++q) {
+      const bool use = live && q < rank_vecs;
+      braw[j][0][q] = use ? __ldg(reinterpret_cast<const uint4*>(b0) + q) : zero4;
+      braw[j][1][q] = use ? __ldg(reinterpret_cast<const uint4*>(b0 + b_row_stride) + q) : zero4;
+    }
+  }
+  pdl_wait();
+  pdl_trigger();
+  int2 a2[P];
+#pragma unroll
+  for (int j = 0; j < P; ++j) {
+    const int n0 = base + 512 * j;
+    a2[j] = n0 < n ? ld_stream_int2(acc + static_cast<int64_t>(m) * n + n0) : make_int2(0, 0);
+  }
+  float l0[P], l1[P];
+#pragma unroll
+  for (int j = 0; j < P; ++j) {
+    l0[j] = 0.f;
+    l1[j] = 0.f;
+#pragma unroll
+    for (int q = 0; q < RV; ++q) {
+      if (q < rank_vecs) {  // same order of additions as a loop over q = 0 .. rank_vecs - 1
+        const uint32_t c0[4] = {braw[j][0][q].x, braw[j][0][q].y, braw[j][0][q].z, braw[j][0][q].w};
+        const uint32_t c1[4] = {braw[j][1][q].x, braw[j][1][q].y, braw[j][1][q].z, braw[j][1][q].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          l0[j] = fmaf(zs[8 * q + 2 * e], bf16_lo(c0[e]), l0[j]);
+          l0[j] = fmaf(zs[8 * q + 2 * e + 1], bf16_hi(c0[e]), l0[j]);
+          l1[j] = fmaf(zs[8 * q + 2 * e], bf16_lo(c1[e]), l1[j]);
+          l1[j] = fmaf(zs[8 * q + 2 * e + 1], bf16_hi(c1[e]), l1[j]);
+        }
       }
     }
   }
-  uint32_t rv = 0u;
-  if (EPI == SKYRL_EPI_RESIDUAL)
-    rv = __ldg(reinterpret_cast<const uint32_t*>(residual + static_cast<int64_t>(m) * res_stride + n0));
-  pdl_wait();
-  pdl_trigger();
-  int2 a2 = ld_stream_int2(acc + static_cast<int64_t>(m) * n + n0);
   for (int sl = 1; sl < slabs; ++sl) {  // split-K partial sums: int32 addition is exact
-    const int2 t2 = ld_stream_int2(acc + sl * slab_stride + static_cast<int64_t>(m) * n + n0);
-    a2.x += t2.x;
-    a2.y += t2.y;
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+      const int n0 = base + 512 * j;
+      if (n0 < n) {
+        const int2 t2 = ld_stream_int2(acc + sl * slab_stride + static_cast<int64_t>(m) * n + n0);
+        a2[j].x += t2.x;
+        a2[j].y += t2.y;
+      }
+    }
   }
-  float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a2.x), sxm), w2.x);
-  float f1 = __fmul_rn(__fmul_rn(__int2float_rn(a2.y), sxm), w2.y);
-  if (rank_vecs > 0) {
-    f0 = __fadd_rn(f0, l0);
-    f1 = __fadd_rn(f1, l1);
-  }
-  if (EPI == SKYRL_EPI_PARTIAL_F32) {
-    *reinterpret_cast<float2*>(static_cast<float*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
-        make_float2(f0, f1);
-  } else if (EPI == SKYRL_EPI_SWIGLU) {
-    const float g = round_bf16(f0), u = round_bf16(f1);
-    const float h = __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u);
-    static_cast<__nv_bfloat16*>(out)[static_cast<int64_t>(m) * out_stride + (n0 >> 1)] = __float2bfloat16_rn(h);
-  } else if (EPI == SKYRL_EPI_RESIDUAL) {
-    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
-        pack_bf16x2(__fadd_rn(round_bf16(f0), bf16_lo(rv)), __fadd_rn(round_bf16(f1), bf16_hi(rv)));
-  } else {
-    *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
-        pack_bf16x2(f0, f1);
+#pragma unroll
+  for (int j = 0; j < P; ++j) {
+    const int n0 = base + 512 * j;
+    if (n0 >= n) continue;
+    float f0 = __fmul_rn(__fmul_rn(__int2float_rn(a2[j].x), sxm), w2[j].x);
+    float f1 = __fmul_rn(__fmul_rn(__int2float_rn(a2[j].y), sxm), w2[j].y);
+    if (rank_vecs > 0) {
+      f0 = __fadd_rn(f0, l0[j]);
+      f1 = __fadd_rn(f1, l1[j]);
+    }
+    if (EPI == SKYRL_EPI_PARTIAL_F32) {
+      *reinterpret_cast<float2*>(static_cast<float*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+          make_float2(f0, f1);
+    } else if (EPI == SKYRL_EPI_SWIGLU) {
+      const float g = round_bf16(f0), u = round_bf16(f1);
+      const float h = __fmul_rn(__fdiv_rn(g, 1.0f + expf(-g)), u);
+      static_cast<__nv_bfloat16*>(out)[static_cast<int64_t>(m) * out_stride + (n0 >> 1)] = __float2bfloat16_rn(h);
+    } else if (EPI == SKYRL_EPI_RESIDUAL) {
+      *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+          pack_bf16x2(__fadd_rn(round_bf16(f0), bf16_lo(rv[j])), __fadd_rn(round_bf16(f1), bf16_hi(rv[j])));
+    } else {
+      *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(out) + static_cast<int64_t>(m) * out_stride + n0) =
+          pack_bf16x2(f0, f1);
+    }
   }
 }
 
@@ -332,15 +375,29 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: LoRA operands missing or misaligned");
   if (epilogue == SKYRL_EPI_RESIDUAL && residual == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: residual missing");
-  dim3 grid((n / 2 + 255) / 256, m);
+  // pairs per thread: 4 (16 or 20 independent 16-byte loads in flight per thread) for wide projections with rank <= 16,
+  // else 1 (rank up to 64: the raw LoRA-B rows of one pair are already 64 registers)
   const int rank_vecs = (rank + 7) / 8;
+  const bool wide_rank = rank_vecs > 2;
+  const int pairs = (!wide_rank && static_cast<int64_t>(n / 2) * m >= 4 * 256 * sm_count()) ? SKYRL_FINALIZE_PAIRS : 1;
+  dim3 grid((n / 2 + 256 * pairs - 1) / (256 * pairs), m);
   const __nv_bfloat16* bt = static_cast<const __nv_bfloat16*>(b_table);
   const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(residual);
   cudaError_t le = cudaSuccess;
-#define SKYRL_FINALIZE(E)                                                                                            \
-  le = launch_kernel(finalize_rows_kernel<E>, grid, dim3(256), 0, stream, programmatic, acc, slabs,                  \
+#define SKYRL_FINALIZE_P(E, PP, RR)                                                                                  \
+  le = launch_kernel(finalize_rows_kernel<E, PP, RR>, grid, dim3(256), 0, stream, programmatic, acc, slabs,          \
                      static_cast<int64_t>(m) * n, sx, sw, z_rows, ids, num_adapters, bt, b_adapter_stride, b_row_stride, \
                      rank_vecs, n, res, res_stride, out, out_stride, status)
+#define SKYRL_FINALIZE(E)                                \
+  if (wide_rank) {                                       \
+    SKYRL_FINALIZE_P(E, 1, 8);                           \
+  } else if (pairs == 4) {                               \
+    SKYRL_FINALIZE_P(E, 4, 2);                           \
+  } else if (pairs == 2) {                               \
+    SKYRL_FINALIZE_P(E, 2, 2);                           \
+  } else {                                               \
+    SKYRL_FINALIZE_P(E, 1, 2);                           \
+  }
   switch (epilogue) {
     case SKYRL_EPI_LINEAR: SKYRL_FINALIZE(SKYRL_EPI_LINEAR); break;
     case SKYRL_EPI_SWIGLU: SKYRL_FINALIZE(SKYRL_EPI_SWIGLU); break;
@@ -348,6 +405,7 @@ int launch_finalize_rows(int epilogue, const int32_t* acc, int slabs, const floa
     case SKYRL_EPI_PARTIAL_F32: SKYRL_FINALIZE(SKYRL_EPI_PARTIAL_F32); break;
     default: return fail(SKYRL_ERR_INVALID_ARGUMENT, "finalize_rows: unsupported epilogue %d", epilogue);
   }
+#undef SKYRL_FINALIZE_P
 #undef SKYRL_FINALIZE
   cudaError_t e = le != cudaSuccess ? le : cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "finalize_rows launch: %s", cudaGetErrorString(e));

@@ -503,14 +503,20 @@ SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_
  * on the same chunk (NULL behind the last block: finalize only).  Flag values must only grow from call to call.
  * No TMA and no multicast instruction touches peer memory; if a wait runs out, status 105 is recorded and the
  * kernel returns. */
+#define SKYRL_TP_EXCHANGE_SINGLE_KERNEL 1u /* sum, finalize and quantise row by row in ONE kernel.  The default is
+                                            * two launches on the stream: a streaming kernel that waits, sums the
+                                            * slabs and finalizes (every thread keeps loads in flight all the time),
+                                            * then the row-wise quantiser over the bf16 rows it wrote.  Same bits;
+                                            * on the few SMs the GEMMs spare the two launches are about twice as
+                                            * fast as the single kernel. */
 typedef struct SkyrlW8A8TpExchangeArgs {
   uint32_t struct_size;
   int32_t tp;                  /* ranks of the group, 1 ... 8                                       */
   int32_t row_begin, row_count;/* this rank's sorted rows                                           */
   int32_t wait_value;
   int32_t signal_value;
-  int32_t grid_ctas;           /* CTAs of the exchange kernel; 0 = 48                               */
-  int32_t reserved;
+  int32_t grid_ctas;           /* CTAs of each exchange kernel; 0 = 48                              */
+  uint32_t flags;              /* SKYRL_TP_EXCHANGE_*                                               */
   const float* partials[8];    /* rank s's fp32 [m, hidden] partial sums in sorted row order        */
   const int32_t* wait_flags;   /* tp words in this rank's memory, or NULL (no wait)                 */
   void* peer_workspaces[8];    /* rank r's workspace of the next block (used when next != NULL)     */

@@ -22,6 +22,7 @@ MLP_INPUT_PREPARED = 2
 MLP_FINALIZE_SORTED = 4
 MLP_NO_ROW_AMAX = 8
 MLP_KEEP_NORMALIZED = 16
+TP_EXCHANGE_SINGLE_KERNEL = 1
 MLP_FUSED_ROWS = 32
 LINEAR_FUSED_ROWS = 1
 GEMM_VARIANT_AUTO, GEMM_VARIANT_SINGLE, GEMM_VARIANT_TWO_TILES, GEMM_VARIANT_CTA_PAIR = 0, 1, 2, 3
@@ -99,7 +100,7 @@ class MlpArgs(C.Structure):
 class TpExchangeArgs(C.Structure):
     _fields_ = [
         ("struct_size", C.c_uint32), ("tp", C.c_int32), ("row_begin", C.c_int32), ("row_count", C.c_int32),
-        ("wait_value", C.c_int32), ("signal_value", C.c_int32), ("grid_ctas", C.c_int32), ("reserved", C.c_int32),
+        ("wait_value", C.c_int32), ("signal_value", C.c_int32), ("grid_ctas", C.c_int32), ("flags", C.c_uint32),
         ("partials", C.c_void_p * 8), ("wait_flags", C.c_void_p), ("peer_workspaces", C.c_void_p * 8),
         ("signal_flags", C.c_void_p * 8), ("out", C.c_void_p),
     ]

@@ -758,6 +758,7 @@ extern "C" int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* blk, 
   e.wait_value = x->wait_value;
   e.status = blk->status;
   e.grid_ctas = x->grid_ctas;
+  e.single_kernel = (x->flags & SKYRL_TP_EXCHANGE_SINGLE_KERNEL) != 0;
   MlpPlan np;
   const bool lora = next != nullptr && next->rank > 0;
   if (next != nullptr) {

@@ -118,6 +118,7 @@ struct TpExchangeLaunch {
   int32_t wait_value;
   int32_t* status;
   int grid_ctas;
+  bool single_kernel;  // true: one kernel sums, finalizes and quantises row by row; false: a streaming sum kernel, then the row-wise one
 };
 int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream);
 int launch_tp_signal(int32_t* const* flags, int count, int32_t value, cudaStream_t stream);

@@ -36,6 +36,7 @@ struct ExchangeParams {
   const __nv_bfloat16* residual;        // bf16 [m, hidden], token order
   __nv_bfloat16* out;                   // bf16 [m, hidden]: row perm[i], or row i when out_sorted
   int out_sorted;
+  int from_out;                         // 1: the finalized row is already in `out` (tp_sum_kernel ran): no partial sums are read
   int quantize;                         // 1: run the next block's quantiser stage on the finalized row
   const __nv_bfloat16* delta;           // next block's RMSNorm weights (NULL: no normalisation)
   float eps;
@@ -106,41 +107,61 @@ __global__ void __launch_bounds__(QUANT_THREADS) tp_exchange_kernel(const __grid
     uint4* dst = reinterpret_cast<uint4*>(p.out + (p.out_sorted ? srow : trow) * p.hidden);
     const bool norm = p.delta != nullptr;
     float ss = 0.f, amax = 0.f;
-    // Every rank's two float4 of this vector are requested before the first is used: TP x 32 bytes in
-    // flight per thread, which is what keeps the NVLink loads streaming.
-    for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
-      float4 lo[TP], hi[TP];
+    if (p.from_out) {
+      // second phase of the two-kernel form: the streaming kernel wrote the finalized row, this pass only stages it
+      // and accumulates what the quantiser needs, with the same values in the same order as the fused pass below
+      for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+        const uint4 ov = ld_stream16(dst + v);
+        const uint32_t o[4] = {ov.x, ov.y, ov.z, ov.w};
 #pragma unroll
-      for (int s = 0; s < TP; ++s) {
-        const float4* src = reinterpret_cast<const float4*>(p.partial[s] + srow * p.hidden) + 2 * v;
-        lo[s] = ld_peer16(src);
-        hi[s] = ld_peer16(src + 1);
-      }
-      const uint4 rv = __ldg(res + v);
-      float4 a = lo[0], b = hi[0];
-#pragma unroll
-      for (int s = 1; s < TP; ++s) {  // ascending rank order, one fp32 addition per rank
-        a.x = __fadd_rn(a.x, lo[s].x); a.y = __fadd_rn(a.y, lo[s].y); a.z = __fadd_rn(a.z, lo[s].z); a.w = __fadd_rn(a.w, lo[s].w);
-        b.x = __fadd_rn(b.x, hi[s].x); b.y = __fadd_rn(b.y, hi[s].y); b.z = __fadd_rn(b.z, hi[s].z); b.w = __fadd_rn(b.w, hi[s].w);
-      }
-      const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-      uint32_t o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])),
-                           __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
-        const float x0 = bf16_lo(o[j]), x1 = bf16_hi(o[j]);
-        if (norm) {
-          ss = fmaf(x0, x0, ss);
-          ss = fmaf(x1, x1, ss);
-        } else {
-          amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+        for (int j = 0; j < 4; ++j) {
+          const float x0 = bf16_lo(o[j]), x1 = bf16_hi(o[j]);
+          if (norm) {
+            ss = fmaf(x0, x0, ss);
+            ss = fmaf(x1, x1, ss);
+          } else {
+            amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+          }
         }
+        row[v] = ov;
       }
-      const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
-      dst[v] = ov;
-      row[v] = ov;
+    } else {
+      // Every rank's two float4 of this vector are requested before the first is used: TP x 32 bytes in
+      // flight per thread, which is what keeps the NVLink loads streaming.
+      for (int v = threadIdx.x; v < nvec; v += QUANT_THREADS) {
+        float4 lo[TP], hi[TP];
+  #pragma unroll
+        for (int s = 0; s < TP; ++s) {
+          const float4* src = reinterpret_cast<const float4*>(p.partial[s] + srow * p.hidden) + 2 * v;
+          lo[s] = ld_peer16(src);
+          hi[s] = ld_peer16(src + 1);
+        }
+        const uint4 rv = __ldg(res + v);
+        float4 a = lo[0], b = hi[0];
+  #pragma unroll
+        for (int s = 1; s < TP; ++s) {  // ascending rank order, one fp32 addition per rank
+          a.x = __fadd_rn(a.x, lo[s].x); a.y = __fadd_rn(a.y, lo[s].y); a.z = __fadd_rn(a.z, lo[s].z); a.w = __fadd_rn(a.w, lo[s].w);
+          b.x = __fadd_rn(b.x, hi[s].x); b.y = __fadd_rn(b.y, hi[s].y); b.z = __fadd_rn(b.z, hi[s].z); b.w = __fadd_rn(b.w, hi[s].w);
+        }
+        const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+        uint32_t o[4];
+  #pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])),
+                             __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
+          const float x0 = bf16_lo(o[j]), x1 = bf16_hi(o[j]);
+          if (norm) {
+            ss = fmaf(x0, x0, ss);
+            ss = fmaf(x1, x1, ss);
+          } else {
+            amax = fmaxf(amax, fmaxf(fabsf(x0), fabsf(x1)));
+          }
+        }
+        const uint4 ov = make_uint4(o[0], o[1], o[2], o[3]);
+        dst[v] = ov;
+        row[v] = ov;
+      }
     }
     if (p.quantize) {
       QuantDests qd;
@@ -159,6 +180,46 @@ __global__ void __launch_bounds__(QUANT_THREADS) tp_exchange_kernel(const __grid
     __syncthreads();  // the staged row is reused by the next iteration
   }
   __threadfence_system();  // this thread's peer stores are performed before the kernel counts as finished
+}
+
+// First phase of the two-kernel form: out = bf16(sum over ranks, ascending) + residual for this rank's rows,
+// as a pure streaming pass.  Nothing here is row-wide, so every thread keeps TP x 32 bytes of loads in flight
+// all the time (the fused kernel above alternates between a load phase and the quantiser's reductions, which
+// leaves the few SMs the GEMMs spare idle half of the time); the quantiser then runs as a second pass over the
+// bf16 rows, an eighth to a sixteenth of the bytes.
+template <int TP>
+__global__ void __launch_bounds__(256) tp_sum_kernel(const __grid_constant__ ExchangeParams p) {
+  if (threadIdx.x == 0 && p.wait_flags != nullptr) wait_flags_reach(p.wait_flags, TP, p.wait_value, p.status);
+  __syncthreads();
+  const int nvec = p.hidden >> 3;
+  const int64_t total = static_cast<int64_t>(p.row_count) * nvec;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int r = static_cast<int>(i / nvec);
+    const int v = static_cast<int>(i - static_cast<int64_t>(r) * nvec);
+    const int64_t srow = p.row_begin + r;
+    const int64_t trow = p.perm != nullptr ? p.perm[srow] : srow;
+    float4 lo[TP], hi[TP];
+#pragma unroll
+    for (int s = 0; s < TP; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(p.partial[s] + srow * p.hidden) + 2 * v;
+      lo[s] = ld_peer16(src);
+      hi[s] = ld_peer16(src + 1);
+    }
+    const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + trow * p.hidden) + v);
+    float4 a = lo[0], b = hi[0];
+#pragma unroll
+    for (int s = 1; s < TP; ++s) {  // ascending rank order, one fp32 addition per rank
+      a.x = __fadd_rn(a.x, lo[s].x); a.y = __fadd_rn(a.y, lo[s].y); a.z = __fadd_rn(a.z, lo[s].z); a.w = __fadd_rn(a.w, lo[s].w);
+      b.x = __fadd_rn(b.x, hi[s].x); b.y = __fadd_rn(b.y, hi[s].y); b.z = __fadd_rn(b.z, hi[s].z); b.w = __fadd_rn(b.w, hi[s].w);
+    }
+    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])), __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
+    reinterpret_cast<uint4*>(p.out + (p.out_sorted ? srow : trow) * p.hidden)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
 }
 
 // One warp: after everything enqueued before it on the stream has completed, raise `value` in up to eight
@@ -205,10 +266,19 @@ int launch_tp_wait(const int32_t* flags, int count, int32_t value, int32_t* stat
 }
 
 template <int TP>
-static int launch_exchange_variant(const ExchangeParams& p, int grid, size_t smem, cudaStream_t stream) {
+static int launch_exchange_variant(ExchangeParams p, int grid, int sum_grid, bool single_kernel, size_t smem,
+                                   cudaStream_t stream) {
   static bool attr_set[MAX_DEVICES] = {};
   cudaError_t e = ensure_dynamic_smem(tp_exchange_kernel<TP>, 200 * 1024, attr_set);
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_exchange attribute: %s", cudaGetErrorString(e));
+  if (!single_kernel) {
+    tp_sum_kernel<TP><<<sum_grid, 256, 0, stream>>>(p);
+    e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_sum launch: %s", cudaGetErrorString(e));
+    if (!p.quantize) return SKYRL_OK;
+    p.from_out = 1;          // the same stream orders the two phases
+    p.wait_flags = nullptr;  // the first phase has waited
+  }
   tp_exchange_kernel<TP><<<grid, QUANT_THREADS, smem, stream>>>(p);
   e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_exchange launch: %s", cudaGetErrorString(e));
@@ -248,17 +318,24 @@ int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream) {
   p.wait_flags = a.wait_flags;
   p.wait_value = a.wait_value;
   p.status = a.status;
+  p.from_out = 0;
   int grid = a.grid_ctas > 0 ? a.grid_ctas : 48;
+  // The row-wise kernel keeps up to eight CTAs per SM busy; the streaming kernel wants every thread slot of the SMs
+  // it gets (eight 256-thread CTAs per SM as well), so both use the same grid unless rows are few.
+  int sum_grid = grid;
+  const int64_t vec_ctas = (static_cast<int64_t>(a.row_count) * (a.hidden >> 3) + 255) / 256;
+  if (sum_grid > vec_ctas) sum_grid = static_cast<int>(vec_ctas);
   if (grid > a.row_count) grid = a.row_count;
+  const bool single = a.single_kernel;
   switch (a.tp) {
-    case 1: return launch_exchange_variant<1>(p, grid, smem, stream);
-    case 2: return launch_exchange_variant<2>(p, grid, smem, stream);
-    case 3: return launch_exchange_variant<3>(p, grid, smem, stream);
-    case 4: return launch_exchange_variant<4>(p, grid, smem, stream);
-    case 5: return launch_exchange_variant<5>(p, grid, smem, stream);
-    case 6: return launch_exchange_variant<6>(p, grid, smem, stream);
-    case 7: return launch_exchange_variant<7>(p, grid, smem, stream);
-    default: return launch_exchange_variant<8>(p, grid, smem, stream);
+    case 1: return launch_exchange_variant<1>(p, grid, sum_grid, single, smem, stream);
+    case 2: return launch_exchange_variant<2>(p, grid, sum_grid, single, smem, stream);
+    case 3: return launch_exchange_variant<3>(p, grid, sum_grid, single, smem, stream);
+    case 4: return launch_exchange_variant<4>(p, grid, sum_grid, single, smem, stream);
+    case 5: return launch_exchange_variant<5>(p, grid, sum_grid, single, smem, stream);
+    case 6: return launch_exchange_variant<6>(p, grid, sum_grid, single, smem, stream);
+    case 7: return launch_exchange_variant<7>(p, grid, sum_grid, single, smem, stream);
+    default: return launch_exchange_variant<8>(p, grid, sum_grid, single, smem, stream);
   }
 }
 

@@ -164,14 +164,16 @@ class TensorParallelMLPStack:
     """
 
     def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 8, sm_count: int = 148,
-                 sequence_parallel: bool = True, peer_scatter="auto", exchange_ctas: int = 0):
+                 sequence_parallel: bool = True, peer_scatter="auto", exchange_ctas: int = 0,
+                 exchange_single_kernel: bool = False):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self.sequence_parallel = sequence_parallel
         self.peer_scatter = peer_scatter
-        self.exchange_ctas = exchange_ctas if exchange_ctas > 0 else max(8, 4 * reserve_sms)
+        self.exchange_ctas = exchange_ctas if exchange_ctas > 0 else max(8, 6 * reserve_sms)
+        self.exchange_single_kernel = bool(exchange_single_kernel)
         self.scatter_mode = None
         self._fused = None        # symmetric buffers of the fused exchange
         self._seq = 0             # flag values only grow: one per block and forward pass
@@ -581,7 +583,8 @@ class TensorParallelMLPStack:
                         partials=partial_sources(c), wait_flags=flags[0, c], wait_value=value,
                         peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
                         signal_flags=[flag_addr(r, 1, c, rank) for r in range(tp)] if nxt is not None else None,
-                        signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas)
+                        signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas,
+                        single_kernel=self.exchange_single_kernel)
                     self._mark(f"L{l}c{c} exchange<", comm, "comm")
                     if last:
                         dist.all_gather_into_tensor(self._sorted[r0:r0 + cnt], self._sorted[o0:o0 + ocnt], group=self.group)

@@ -809,9 +809,9 @@ def main():
     ap.add_argument("--tp-reserve-sms", type=int, default=-1,
                     help="SMs the GEMMs leave to the second stream's small kernels while chunks overlap (N > 1): the "
                          "fused exchange kernel (or the one-word all-reduce, finalize / quantise kernels and gathers of the "
-                         "other forms); -1 = 8 on two GPUs, 16 on more")
+                         "other forms); -1 = 8 on two GPUs, 4 on more (the exchange kernels there run on all SMs beside the GEMM)")
     ap.add_argument("--tp-exchange-ctas", type=int, default=0, help="CTAs of the fused exchange kernel (0 = 4 per reserved SM)")
-    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "fused", "fused_copy", "epilogue", "copy", "off"],
+    ap.add_argument("--tp-peer-scatter", default="auto", choices=["auto", "fused", "fused_copy", "fused_mc", "epilogue", "copy", "off"],
                     help="how the fp32 partial sums reach the rank that owns the rows: stores from the down GEMM's "
                          "epilogue into the owner's memory, copy-engine pushes on the second stream, the fused exchange "
                          "kernel (fused: it pulls them over NVLink; fused_copy: the copy engines push them and it adds "
@@ -825,7 +825,7 @@ def main():
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()
     if args.tp_reserve_sms < 0:
-        args.tp_reserve_sms = 8 if args.gpus <= 2 else 16
+        args.tp_reserve_sms = 8 if args.gpus <= 2 else 4
     if args.impl == "reference":
         # before NumPy loads its BLAS: all host threads, whatever the launcher set for its per-GPU workers
         for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):

@@ -509,6 +509,21 @@ SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_
                                             * then the row-wise quantiser over the bf16 rows it wrote.  Same bits;
                                             * on the few SMs the GEMMs spare the two launches are about twice as
                                             * fast as the single kernel. */
+#define SKYRL_TP_EXCHANGE_MULTIMEM 2u /* partials[0] is the MULTICAST address of a symmetric buffer that holds every
+                                       * rank's partial sums at the same offset (an NVSwitch multicast object, e.g.
+                                       * torch symmetric memory's multicast_ptr): the sum over ranks is formed in the
+                                       * switch by one multimem.ld_reduce per 16 bytes instead of tp peer loads, so
+                                       * each row crosses this GPU's links once.  fp32 additions in an order the
+                                       * switch chooses: results agree with the rank-ordered forms to fp32 rounding,
+                                       * not bit for bit.  partials[1..] are ignored.  Two-launch form only. */
+#define SKYRL_TP_EXCHANGE_PROFILE 4u /* diagnostic: CTA 0 of the two-launch kernels adds, in units of 1.024 us, to the
+                                      * words status[1], status[2], status[3] of `block` the time it spent waiting for
+                                      * the flags, in the streaming sum and in the row-wise quantiser */
+#define SKYRL_TP_EXCHANGE_WIDE 8u /* two-launch form: grid_ctas CTAs of 256 threads and no shared memory, which the
+                                   * hardware places on every SM, also beside the persistent CTAs of a GEMM that runs
+                                   * at the same time (shorter exchange, slightly slower GEMM).  Default: grid_ctas fat
+                                   * CTAs (1024 threads and a shared-memory request of more than half an SM's), one
+                                   * per SM and never beside a GEMM CTA: they stay on the SMs the GEMM leaves free. */
 typedef struct SkyrlW8A8TpExchangeArgs {
   uint32_t struct_size;
   int32_t tp;                  /* ranks of the group, 1 ... 8                                       */

@@ -23,6 +23,9 @@ MLP_FINALIZE_SORTED = 4
 MLP_NO_ROW_AMAX = 8
 MLP_KEEP_NORMALIZED = 16
 TP_EXCHANGE_SINGLE_KERNEL = 1
+TP_EXCHANGE_MULTIMEM = 2
+TP_EXCHANGE_PROFILE = 4
+TP_EXCHANGE_WIDE = 8
 MLP_FUSED_ROWS = 32
 LINEAR_FUSED_ROWS = 1
 GEMM_VARIANT_AUTO, GEMM_VARIANT_SINGLE, GEMM_VARIANT_TWO_TILES, GEMM_VARIANT_CTA_PAIR = 0, 1, 2, 3

@@ -757,8 +757,13 @@ extern "C" int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* blk, 
   e.wait_flags = x->wait_flags;
   e.wait_value = x->wait_value;
   e.status = blk->status;
+  if (static_cast<int64_t>(blk->m) * (blk->hidden >> 3) > 0x7fffffffLL)
+    return fail(SKYRL_ERR_UNSUPPORTED, "tp_exchange: m * hidden / 8 must fit 31 bits");
   e.grid_ctas = x->grid_ctas;
   e.single_kernel = (x->flags & SKYRL_TP_EXCHANGE_SINGLE_KERNEL) != 0;
+  e.multimem = (x->flags & SKYRL_TP_EXCHANGE_MULTIMEM) != 0;
+  e.profile = (x->flags & SKYRL_TP_EXCHANGE_PROFILE) != 0;
+  e.wide = (x->flags & SKYRL_TP_EXCHANGE_WIDE) != 0;
   MlpPlan np;
   const bool lora = next != nullptr && next->rank > 0;
   if (next != nullptr) {
@@ -774,7 +779,7 @@ extern "C" int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* blk, 
     e.quantize = true;
     e.delta = next->rms_delta;
     e.eps = next->rms_eps;
-    e.xn = lora ? np.w.xn : nullptr;
+    e.xn = np.w.xn;  // the LoRA-A projection reads it; without LoRA it is still the scratch of the warp-per-row quantiser
     for (int r = 0; r < x->tp; ++r) {
       if (x->peer_workspaces[r] == nullptr || (reinterpret_cast<uintptr_t>(x->peer_workspaces[r]) & 1023u) != 0)
         return fail(SKYRL_ERR_WORKSPACE, "tp_exchange: workspace of rank %d is null or not 1024-byte aligned", r);

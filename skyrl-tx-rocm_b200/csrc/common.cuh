@@ -118,6 +118,9 @@ struct TpExchangeLaunch {
   int32_t wait_value;
   int32_t* status;
   int grid_ctas;
+  bool profile;        // CTA 0 of the two-launch kernels adds its wait / sum / quantiser times to status[1..3]
+  bool wide;           // two-launch form as many small CTAs on all SMs instead of fat CTAs on the spare ones
+  bool multimem;       // partial[0] is a multicast address: the sum over ranks is one multimem.ld_reduce per vector
   bool single_kernel;  // true: one kernel sums, finalizes and quantises row by row; false: a streaming sum kernel, then the row-wise one
 };
 int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream);

@@ -46,6 +46,8 @@ struct ExchangeParams {
   const int32_t* wait_flags;            // tp words in this rank's memory, word s raised by rank s
   int32_t wait_value;
   int32_t* status;
+  int profile;                          // 1: CTA 0 adds to status[1..3] what it spent, in units of 1.024 us: waiting for
+                                        // the flags, in the streaming sum, in the row-wise quantiser
 };
 
 __device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
@@ -182,44 +184,236 @@ __global__ void __launch_bounds__(QUANT_THREADS) tp_exchange_kernel(const __grid
   __threadfence_system();  // this thread's peer stores are performed before the kernel counts as finished
 }
 
+// Sum over all ranks formed inside NVSwitch: one load from the multicast address of a symmetric buffer returns
+// the fp32 sum of every rank's copy (order of the additions not specified), so a row crosses this GPU's links
+// once instead of tp - 1 times and no rank pushes anything.
+__device__ __forceinline__ float4 ld_reduce_mc16(const float4* p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Where the exchange kernels run.  They share the GPU with the GEMMs of the other row chunk, whose persistent
+// CTAs leave `reserve` SMs free.  A kernel of small CTAs does not stay on those SMs: a CTA without shared memory
+// fits BESIDE a GEMM CTA and fights it for issue slots, and small CTAs that start before the GEMM spread one per
+// SM and keep GEMM CTAs out.  Both exchange kernels are therefore launched as `grid` FAT CTAs (512 or 1024
+// threads and a shared-memory request above half an SM's): exactly one per SM, never beside a GEMM CTA, `grid`
+// SMs in all whichever kernel arrives first.
+constexpr int XCH_FAT_SMEM = 120 * 1024;
+
 // First phase of the two-kernel form: out = bf16(sum over ranks, ascending) + residual for this rank's rows,
-// as a pure streaming pass.  Nothing here is row-wide, so every thread keeps TP x 32 bytes of loads in flight
-// all the time (the fused kernel above alternates between a load phase and the quantiser's reductions, which
-// leaves the few SMs the GEMMs spare idle half of the time); the quantiser then runs as a second pass over the
-// bf16 rows, an eighth to a sixteenth of the bytes.
-template <int TP>
-__global__ void __launch_bounds__(256) tp_sum_kernel(const __grid_constant__ ExchangeParams p) {
+// as a pure streaming pass.  Nothing here is row-wide, so every thread keeps its loads in flight all the time
+// (the fused kernel above alternates between a load phase and the quantiser's reductions); the quantiser then
+// runs as a second pass over the bf16 rows, an eighth to a sixteenth of the bytes.
+template <int TP, bool MC>
+__global__ void __launch_bounds__((MC || TP <= 4) ? 1024 : 512) tp_sum_kernel(const __grid_constant__ ExchangeParams p) {
+  const bool prof = p.profile != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+  const unsigned long long t_begin = prof ? global_timer_ns() : 0ull;
   if (threadIdx.x == 0 && p.wait_flags != nullptr) wait_flags_reach(p.wait_flags, TP, p.wait_value, p.status);
   __syncthreads();
+  const unsigned long long t_ready = prof ? global_timer_ns() : 0ull;
   const int nvec = p.hidden >> 3;
   const int64_t total = static_cast<int64_t>(p.row_count) * nvec;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
-    const int r = static_cast<int>(i / nvec);
-    const int v = static_cast<int>(i - static_cast<int64_t>(r) * nvec);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  constexpr int U = MC ? 4 : 1;  // vectors per thread and pass: 8 (in-switch sum) or 2 TP (peer loads) 16-byte loads in flight
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += U * stride) {
+    float4 a[U], b[U];
+    uint4 rv[U];
+    int ovec[U];  // 16-byte vector of `out` this result goes to (-1: past the end)
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      const bool live = i < total;
+      const int r = live ? static_cast<int>(i / nvec) : 0;
+      const int v = live ? static_cast<int>(i - static_cast<int64_t>(r) * nvec) : 0;
+      const int64_t srow = p.row_begin + r;
+      const int64_t trow = p.perm != nullptr ? p.perm[srow] : srow;
+      ovec[u] = live ? static_cast<int>((p.out_sorted ? srow : trow) * nvec + v) : -1;
+      if (MC) {
+        const float4* src = reinterpret_cast<const float4*>(p.partial[0] + srow * p.hidden) + 2 * v;  // multicast address
+        a[u] = ld_reduce_mc16(src);
+        b[u] = ld_reduce_mc16(src + 1);
+      } else {
+        float4 lo[TP], hi[TP];
+#pragma unroll
+        for (int s = 0; s < TP; ++s) {
+          const float4* src = reinterpret_cast<const float4*>(p.partial[s] + srow * p.hidden) + 2 * v;
+          lo[s] = ld_peer16(src);
+          hi[s] = ld_peer16(src + 1);
+        }
+        a[u] = lo[0];
+        b[u] = hi[0];
+#pragma unroll
+        for (int s = 1; s < TP; ++s) {  // ascending rank order, one fp32 addition per rank
+          a[u].x = __fadd_rn(a[u].x, lo[s].x); a[u].y = __fadd_rn(a[u].y, lo[s].y);
+          a[u].z = __fadd_rn(a[u].z, lo[s].z); a[u].w = __fadd_rn(a[u].w, lo[s].w);
+          b[u].x = __fadd_rn(b[u].x, hi[s].x); b[u].y = __fadd_rn(b[u].y, hi[s].y);
+          b[u].z = __fadd_rn(b[u].z, hi[s].z); b[u].w = __fadd_rn(b[u].w, hi[s].w);
+        }
+      }
+      rv[u] = __ldg(reinterpret_cast<const uint4*>(p.residual + trow * p.hidden) + v);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ovec[u] < 0) continue;
+      const float f[8] = {a[u].x, a[u].y, a[u].z, a[u].w, b[u].x, b[u].y, b[u].z, b[u].w};
+      const uint32_t rw[4] = {rv[u].x, rv[u].y, rv[u].z, rv[u].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])), __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
+      reinterpret_cast<uint4*>(p.out)[ovec[u]] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (prof) {
+    atomicAdd(p.status + 1, static_cast<int>((t_ready - t_begin) >> 10));
+    atomicAdd(p.status + 2, static_cast<int>((global_timer_ns() - t_ready) >> 10));
+  }
+}
+
+// Second phase: the next block's RMSNorm + int8 quantiser over the finalized bf16 rows, ONE WARP PER ROW.
+// A row-per-CTA kernel spends most of its time in block-wide barriers with a single row in flight; a fat CTA of
+// 32 warps keeps 32 rows in flight per SM and needs no barrier and no shared memory at all: the three passes
+// re-read the row from L2 (it was written a moment ago) and the normalised row makes its round trip through
+// the `xn` buffer the LoRA-A projection wants anyway (each lane reads back only what it wrote itself).
+// Arithmetic and ORDER are those of quant_row_from_smem with 256 threads, so the bits are the same: lane l plays
+// the threads l, l + 32, ..., l + 224 (one per warp w of that kernel), keeps their eight partial sums of squares
+// apart, reduces each across the lanes with the same xor butterfly and adds the eight results in ascending w.
+constexpr int XQ_VIRTUAL_WARPS = QUANT_THREADS / 32;
+__global__ void __launch_bounds__(1024) tp_quant_rows_kernel(const __grid_constant__ ExchangeParams p) {
+  const bool prof = p.profile != 0 && blockIdx.x == 0 && threadIdx.x == 0;
+  const unsigned long long t_begin = prof ? global_timer_ns() : 0ull;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_cta = blockDim.x >> 5;
+  const int nvec = p.hidden >> 3;
+  const bool norm = p.delta != nullptr;
+  const uint4* dvec = reinterpret_cast<const uint4*>(p.delta);
+  for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < p.row_count; r += gridDim.x * warps_per_cta) {
     const int64_t srow = p.row_begin + r;
     const int64_t trow = p.perm != nullptr ? p.perm[srow] : srow;
-    float4 lo[TP], hi[TP];
+    const uint4* src = reinterpret_cast<const uint4*>(p.out + (p.out_sorted ? srow : trow) * p.hidden);
+    uint4* xn_row = reinterpret_cast<uint4*>(p.xn + srow * p.hidden);
+    float amax = 0.f;
+    constexpr int B = 4;  // vectors a lane requests before it uses the first: the passes are bound by load latency
+    if (norm) {
+      // pass 1: sums of squares, one per thread of the 256-thread kernel this lane plays; thread l + 32 w owns
+      // vectors l + 32 w + 256 i and adds them in ascending i
+      float ssw[XQ_VIRTUAL_WARPS];
 #pragma unroll
-    for (int s = 0; s < TP; ++s) {
-      const float4* src = reinterpret_cast<const float4*>(p.partial[s] + srow * p.hidden) + 2 * v;
-      lo[s] = ld_peer16(src);
-      hi[s] = ld_peer16(src + 1);
+      for (int w = 0; w < XQ_VIRTUAL_WARPS; ++w) ssw[w] = 0.f;
+      for (int i = 0; i * QUANT_THREADS < nvec; ++i) {
+        uint4 u[XQ_VIRTUAL_WARPS];
+#pragma unroll
+        for (int w = 0; w < XQ_VIRTUAL_WARPS; ++w) {
+          const int v = lane + 32 * w + QUANT_THREADS * i;
+          u[w] = v < nvec ? ld_stream16(src + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int w = 0; w < XQ_VIRTUAL_WARPS; ++w) {
+          if (lane + 32 * w + QUANT_THREADS * i < nvec) {  // (a zero vector would add +0 and change nothing, but keep the order explicit)
+            const uint32_t o[4] = {u[w].x, u[w].y, u[w].z, u[w].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float x0 = bf16_lo(o[j]), x1 = bf16_hi(o[j]);
+              ssw[w] = fmaf(x0, x0, ssw[w]);
+              ssw[w] = fmaf(x1, x1, ssw[w]);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int w = 0; w < XQ_VIRTUAL_WARPS; ++w)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ssw[w] = ssw[w] + __shfl_xor_sync(0xffffffffu, ssw[w], o);
+      float total = ssw[0];
+#pragma unroll
+      for (int w = 1; w < XQ_VIRTUAL_WARPS; ++w) total = total + ssw[w];
+      const float var = __fdiv_rn(total, static_cast<float>(p.hidden));
+      const float rinv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(var, p.eps)));
+      // pass 2: normalise, round to bf16, absmax; the normalised row goes to xn
+      for (int v0 = lane; v0 < nvec; v0 += 32 * B) {
+        uint4 u[B], d[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const int v = v0 + 32 * b;
+          u[b] = v < nvec ? ld_stream16(src + v) : make_uint4(0u, 0u, 0u, 0u);
+          d[b] = v < nvec ? __ldg(dvec + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const int v = v0 + 32 * b;
+          if (v >= nvec) continue;
+          const uint32_t w4[4] = {u[b].x, u[b].y, u[b].z, u[b].w};
+          const uint32_t dw[4] = {d[b].x, d[b].y, d[b].z, d[b].w};
+          uint32_t o[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a = __fmul_rn(__fmul_rn(bf16_lo(w4[j]), rinv), __fadd_rn(1.0f, bf16_lo(dw[j])));
+            const float c = __fmul_rn(__fmul_rn(bf16_hi(w4[j]), rinv), __fadd_rn(1.0f, bf16_hi(dw[j])));
+            o[j] = pack_bf16x2(a, c);
+            amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+          }
+          xn_row[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    } else {
+      for (int v0 = lane; v0 < nvec; v0 += 32 * B) {
+        uint4 u[B];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const int v = v0 + 32 * b;
+          u[b] = v < nvec ? ld_stream16(src + v) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+          const int v = v0 + 32 * b;
+          if (v >= nvec) continue;
+          const uint32_t o[4] = {u[b].x, u[b].y, u[b].z, u[b].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+          xn_row[v] = u[b];
+        }
+      }
     }
-    const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + trow * p.hidden) + v);
-    float4 a = lo[0], b = hi[0];
 #pragma unroll
-    for (int s = 1; s < TP; ++s) {  // ascending rank order, one fp32 addition per rank
-      a.x = __fadd_rn(a.x, lo[s].x); a.y = __fadd_rn(a.y, lo[s].y); a.z = __fadd_rn(a.z, lo[s].z); a.w = __fadd_rn(a.w, lo[s].w);
-      b.x = __fadd_rn(b.x, hi[s].x); b.y = __fadd_rn(b.y, hi[s].y); b.z = __fadd_rn(b.z, hi[s].z); b.w = __fadd_rn(b.w, hi[s].w);
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const float rcp = quant_rcp(scale);
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < XCH_MAX_RANKS; ++s)
+        if (s < p.tp && p.sx_dst[s] != nullptr) p.sx_dst[s][srow] = scale;
     }
-    const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-    const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-    uint32_t o[4];
+    // pass 3: codes of the normalised row (each lane reads back its own stores, in program order)
+    for (int v0 = lane; v0 < nvec; v0 += 32 * B) {
+      uint4 u[B];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      o[j] = pack_bf16x2(__fadd_rn(round_bf16(f[2 * j]), bf16_lo(rw[j])), __fadd_rn(round_bf16(f[2 * j + 1]), bf16_hi(rw[j])));
-    reinterpret_cast<uint4*>(p.out + (p.out_sorted ? srow : trow) * p.hidden)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      for (int b = 0; b < B; ++b) {
+        const int v = v0 + 32 * b;
+        u[b] = v < nvec ? ld_stream16(xn_row + v) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int b = 0; b < B; ++b) {
+        const int v = v0 + 32 * b;
+        if (v >= nvec) continue;
+        const uint32_t w4[4] = {u[b].x, u[b].y, u[b].z, u[b].w};
+        int q[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          q[2 * j] = quant_code(bf16_lo(w4[j]), scale, rcp);
+          q[2 * j + 1] = quant_code(bf16_hi(w4[j]), scale, rcp);
+        }
+        const uint2 packed = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+#pragma unroll
+        for (int s = 0; s < XCH_MAX_RANKS; ++s)
+          if (s < p.tp && p.xq_dst[s] != nullptr) reinterpret_cast<uint2*>(p.xq_dst[s] + srow * p.hidden)[v] = packed;
+      }
+    }
   }
+  __threadfence_system();  // this thread's peer stores are performed before the kernel counts as finished
+  if (prof) atomicAdd(p.status + 3, static_cast<int>((global_timer_ns() - t_begin) >> 10));
 }
 
 // One warp: after everything enqueued before it on the stream has completed, raise `value` in up to eight
@@ -266,18 +460,36 @@ int launch_tp_wait(const int32_t* flags, int count, int32_t value, int32_t* stat
 }
 
 template <int TP>
-static int launch_exchange_variant(ExchangeParams p, int grid, int sum_grid, bool single_kernel, size_t smem,
-                                   cudaStream_t stream) {
+static int launch_exchange_variant(ExchangeParams p, int grid, int fat_grid, bool single_kernel, bool multimem, bool wide,
+                                   size_t smem, cudaStream_t stream) {
   static bool attr_set[MAX_DEVICES] = {};
   cudaError_t e = ensure_dynamic_smem(tp_exchange_kernel<TP>, 200 * 1024, attr_set);
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_exchange attribute: %s", cudaGetErrorString(e));
   if (!single_kernel) {
-    tp_sum_kernel<TP><<<sum_grid, 256, 0, stream>>>(p);
-    e = cudaPeekAtLastError();
+    static bool sum_attr[MAX_DEVICES] = {}, sum_mc_attr[MAX_DEVICES] = {}, quant_attr[MAX_DEVICES] = {};
+    // wide: many 256-thread CTAs without shared memory, which run on every SM beside the GEMM CTAs (they finish
+    // sooner and slow the GEMM a little); otherwise fat CTAs confined to the SMs the GEMM leaves free
+    const size_t fat_smem = wide ? 0 : XCH_FAT_SMEM;
+    const int sum_threads = wide ? 256 : ((multimem || TP <= 4) ? 1024 : 512);
+    if (multimem) {
+      e = ensure_dynamic_smem(tp_sum_kernel<TP, true>, XCH_FAT_SMEM, sum_mc_attr);
+      if (e == cudaSuccess) tp_sum_kernel<TP, true><<<fat_grid, sum_threads, fat_smem, stream>>>(p);
+    } else {
+      e = ensure_dynamic_smem(tp_sum_kernel<TP, false>, XCH_FAT_SMEM, sum_attr);
+      if (e == cudaSuccess) tp_sum_kernel<TP, false><<<fat_grid, sum_threads, fat_smem, stream>>>(p);
+    }
+    if (e == cudaSuccess) e = cudaPeekAtLastError();
     if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_sum launch: %s", cudaGetErrorString(e));
     if (!p.quantize) return SKYRL_OK;
-    p.from_out = 1;          // the same stream orders the two phases
-    p.wait_flags = nullptr;  // the first phase has waited
+    p.wait_flags = nullptr;  // the first phase has waited; the stream orders the two phases
+    if (p.xn != nullptr) {
+      e = ensure_dynamic_smem(tp_quant_rows_kernel, XCH_FAT_SMEM, quant_attr);
+      if (e == cudaSuccess) tp_quant_rows_kernel<<<fat_grid, wide ? 256 : 1024, fat_smem, stream>>>(p);
+      if (e == cudaSuccess) e = cudaPeekAtLastError();
+      if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "tp_quant_rows launch: %s", cudaGetErrorString(e));
+      return SKYRL_OK;
+    }
+    p.from_out = 1;  // no buffer for the normalised rows: the row-per-CTA kernel stages them in shared memory
   }
   tp_exchange_kernel<TP><<<grid, QUANT_THREADS, smem, stream>>>(p);
   e = cudaPeekAtLastError();
@@ -296,7 +508,7 @@ int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream) {
   ExchangeParams p = {};
   p.tp = a.tp;
   for (int s = 0; s < a.tp; ++s) {
-    if (a.partial[s] == nullptr || !aligned16(a.partial[s]))
+    if ((s == 0 || !a.multimem) && (a.partial[s] == nullptr || !aligned16(a.partial[s])))
       return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: partial-sum buffer %d is null or not 16-byte aligned", s);
     p.partial[s] = a.partial[s];
     p.xq_dst[s] = a.xq_dst[s];
@@ -318,24 +530,27 @@ int launch_tp_exchange(const TpExchangeLaunch& a, cudaStream_t stream) {
   p.wait_flags = a.wait_flags;
   p.wait_value = a.wait_value;
   p.status = a.status;
+  p.profile = a.profile ? 1 : 0;
   p.from_out = 0;
   int grid = a.grid_ctas > 0 ? a.grid_ctas : 48;
-  // The row-wise kernel keeps up to eight CTAs per SM busy; the streaming kernel wants every thread slot of the SMs
-  // it gets (eight 256-thread CTAs per SM as well), so both use the same grid unless rows are few.
-  int sum_grid = grid;
-  const int64_t vec_ctas = (static_cast<int64_t>(a.row_count) * (a.hidden >> 3) + 255) / 256;
-  if (sum_grid > vec_ctas) sum_grid = static_cast<int>(vec_ctas);
+  // two-launch form: grid_ctas fat CTAs, one per SM (see XCH_FAT_SMEM)
+  int fat_grid = grid;
+  const int64_t fat_need = (static_cast<int64_t>(a.row_count) * (a.hidden >> 3) + 1023) / 1024;
+  if (fat_grid > fat_need) fat_grid = static_cast<int>(fat_need);
+  if (!a.wide && fat_grid > sm_count()) fat_grid = sm_count();
   if (grid > a.row_count) grid = a.row_count;
   const bool single = a.single_kernel;
+  const bool mc = a.multimem;
+  if (mc && single) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: the in-switch sum needs the two-launch form");
   switch (a.tp) {
-    case 1: return launch_exchange_variant<1>(p, grid, sum_grid, single, smem, stream);
-    case 2: return launch_exchange_variant<2>(p, grid, sum_grid, single, smem, stream);
-    case 3: return launch_exchange_variant<3>(p, grid, sum_grid, single, smem, stream);
-    case 4: return launch_exchange_variant<4>(p, grid, sum_grid, single, smem, stream);
-    case 5: return launch_exchange_variant<5>(p, grid, sum_grid, single, smem, stream);
-    case 6: return launch_exchange_variant<6>(p, grid, sum_grid, single, smem, stream);
-    case 7: return launch_exchange_variant<7>(p, grid, sum_grid, single, smem, stream);
-    default: return launch_exchange_variant<8>(p, grid, sum_grid, single, smem, stream);
+    case 1: return launch_exchange_variant<1>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 2: return launch_exchange_variant<2>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 3: return launch_exchange_variant<3>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 4: return launch_exchange_variant<4>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 5: return launch_exchange_variant<5>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 6: return launch_exchange_variant<6>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    case 7: return launch_exchange_variant<7>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
+    default: return launch_exchange_variant<8>(p, grid, fat_grid, single, mc, a.wide, smem, stream);
   }
 }
 

@@ -858,7 +858,8 @@ def w8a8_mlp_tp_finalize_slabs(call, slab_addresses, out: torch.Tensor, row_begi
 
 def w8a8_mlp_tp_exchange(call, next_call, out: torch.Tensor, *, tp: int, row_begin: int, row_count: int, partials,
                          wait_flags=None, wait_value: int = 0, peer_workspaces=None, signal_flags=None,
-                         signal_value: int = 0, sorted_out: bool = False, grid_ctas: int = 0, single_kernel: bool = False):
+                         signal_value: int = 0, sorted_out: bool = False, grid_ctas: int = 0, single_kernel: bool = False,
+                         multimem: bool = False, profile: bool = False, wide: bool = False):
     """Fused exchange between two blocks of a sequence-parallel stack (one kernel per rank and row chunk).
 
     `call` is the handle of the `w8a8_mlp_block(..., down_epilogue=EPI_PARTIAL_F32, return_call=True)` call that
@@ -868,16 +869,18 @@ def w8a8_mlp_tp_exchange(call, next_call, out: torch.Tensor, *, tp: int, row_beg
     `wait_flags` an int32 tensor of `tp` words in this rank's memory that the ranks raise to `wait_value` when
     their partial sums are complete, `signal_flags` one flag address per rank that this call sets to
     `signal_value` once the rows it prepared have been stored everywhere.  `single_kernel=True` selects the
-    one-kernel form (same bits; the default is a streaming sum kernel followed by the row-wise quantiser)."""
+    one-kernel form (same bits; the default is a streaming sum kernel followed by the row-wise quantiser).
+    `multimem=True`: `partials[0]` is the multicast address of a symmetric buffer holding every rank's partial
+    sums; the sum is then formed inside NVSwitch (agrees with the other forms to fp32 rounding)."""
     a = call[0]
     lib = _lib.load()
     x = _lib.TpExchangeArgs()
     x.struct_size = C.sizeof(_lib.TpExchangeArgs)
     x.tp, x.row_begin, x.row_count = int(tp), int(row_begin), int(row_count)
     x.wait_value, x.signal_value, x.grid_ctas = int(wait_value), int(signal_value), int(grid_ctas)
-    x.flags = _lib.TP_EXCHANGE_SINGLE_KERNEL if single_kernel else 0
-    if len(partials) != tp:
-        raise ValueError(f"{tp} partial-sum buffers wanted, got {len(partials)}")
+    x.flags = (_lib.TP_EXCHANGE_SINGLE_KERNEL if single_kernel else 0) | (_lib.TP_EXCHANGE_MULTIMEM if multimem else 0) | (_lib.TP_EXCHANGE_PROFILE if profile else 0) | (_lib.TP_EXCHANGE_WIDE if wide else 0)
+    if len(partials) != (1 if multimem else tp):
+        raise ValueError(f"{1 if multimem else tp} partial-sum buffers wanted, got {len(partials)}")
     for s_, addr in enumerate(partials):
         x.partials[s_] = int(addr)
     x.wait_flags = wait_flags.data_ptr() if wait_flags is not None else None

@@ -152,12 +152,20 @@ class TensorParallelMLPStack:
                   rank's workspace, which lives in symmetric memory too; a second flag tells the peers
                   that the rows have arrived (`ops.w8a8_mlp_tp_exchange`).  Block 0 is prepared by every
                   rank for all rows (x is replicated), so the first exchange is the one behind block 0.
-      "fused_copy" the same kernel fed by the copy engines: every rank pushes each owner's rows of its partial
+      "fused_copy" the same exchange fed by the copy engines: every rank pushes each owner's rows of its partial
                   sums into a slab in the owner's memory (no SM involved, the transfer overlaps the other
-                  chunk's GEMMs), raises the flag, and the owner's kernel adds LOCAL slabs.  Pulling over
-                  NVLink inside the kernel ("fused") keeps every CTA waiting on peer-load latency one row at
-                  a time; with local slabs the kernel is short and needs few SMs.
-    "auto" (default) = "fused_copy" on more than 2 ranks, "epilogue" on 2.  If symmetric memory cannot be set
+                  chunk's GEMMs), raises the flag, and the owner's kernels add LOCAL slabs.  SM-issued loads over
+                  NVLink ("fused", "fused_mc") move the same bytes at half the copy engines' rate and slow the
+                  GEMM that runs beside them; with local slabs the exchange kernels take under 0.1 ms.
+      "fused_mc"  as "fused", but the sum over ranks is formed inside NVSwitch: the exchange's streaming kernel
+                  reads the MULTICAST address of the symmetric buffer with multimem.ld_reduce, so each owned row
+                  crosses this GPU's links once (not tp - 1 times) and nobody pushes anything.  fp32 additions
+                  in the switch's order: equal to the rank-ordered forms to fp32 rounding, not bit for bit.
+                  Falls back to "fused_copy" when the fabric offers no multicast object.
+    "auto" (default) = "fused_copy" on more than 2 ranks, "epilogue" on 2.
+    The exchange itself is two launches (a streaming sum + finalize kernel, then a warp-per-row quantiser that
+    stores codes and scales into every rank's workspace) followed by the LoRA-A projection and the flag signal;
+    `exchange_wide` / `exchange_single_kernel` / `exchange_ctas` choose its launch form.  If symmetric memory cannot be set
     up the NCCL reduce-scatter is used.
 
     Blocks of fewer than 129 rows take the small-batch path and are not chunked.
@@ -165,15 +173,25 @@ class TensorParallelMLPStack:
 
     def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 8, sm_count: int = 148,
                  sequence_parallel: bool = True, peer_scatter="auto", exchange_ctas: int = 0,
-                 exchange_single_kernel: bool = False):
+                 exchange_single_kernel: bool = False, exchange_wide: bool = True):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
         self.cta_limit = max(1, sm_count - reserve_sms) if reserve_sms > 0 else 0
         self.sequence_parallel = sequence_parallel
         self.peer_scatter = peer_scatter
-        self.exchange_ctas = exchange_ctas if exchange_ctas > 0 else max(8, 6 * reserve_sms)
+        # Grid of the exchange kernels.  Wide form (default): four 256-thread CTAs per SM on ALL SMs, beside the GEMM's CTAs
+        # (measured on 4 GPUs with the copy engines delivering the slabs: 7.26 ms per 4 layers against 8.46 for fat
+        # CTAs on 8 spare SMs and 7.55 for the chain of separate kernels + NCCL gathers); fat form: one CTA per spare
+        # SM; one-kernel form: six small CTAs on each spare SM.
+        if exchange_ctas > 0:
+            self.exchange_ctas = exchange_ctas
+        elif exchange_single_kernel:
+            self.exchange_ctas = max(8, 6 * reserve_sms)
+        else:
+            self.exchange_ctas = 4 * sm_count if exchange_wide else max(4, reserve_sms)
         self.exchange_single_kernel = bool(exchange_single_kernel)
+        self.exchange_wide = bool(exchange_wide)
         self.scatter_mode = None
         self._fused = None        # symmetric buffers of the fused exchange
         self._seq = 0             # flag values only grow: one per block and forward pass
@@ -261,8 +279,10 @@ class TensorParallelMLPStack:
             mode = self.peer_scatter
             if mode == "auto":
                 mode = "fused_copy" if tp > 2 else "epilogue"
-            if mode in ("fused", "fused_copy") and self._fused_buffers(x, tp):
-                return self._forward_fused(x, adapter_ids, spans, chunks, tp, timing_events, pull=(mode == "fused"))
+            if mode in ("fused", "fused_copy", "fused_mc") and self._fused_buffers(x, tp):
+                if mode == "fused_mc" and not self._fused["multicast"]:
+                    mode = "fused_copy"         # no multicast object on this fabric (decided together)
+                return self._forward_fused(x, adapter_ids, spans, chunks, tp, timing_events, form=mode)
             return self._forward_sequence_parallel(x, adapter_ids, spans, chunks, tp, timing_events)
         main = torch.cuda.current_stream()
         prev_done = [None] * len(spans)
@@ -312,7 +332,7 @@ class TensorParallelMLPStack:
         lora = first.gate_up_lora is not None
         slab_ptrs = self._peer_slabs(x, tp) if self.peer_scatter else None
         mode = self.peer_scatter if slab_ptrs is not None else False
-        if mode in (True, "auto", "fused", "fused_copy"):   # the fused forms land here only when their buffers could not be set up
+        if mode in (True, "auto", "fused", "fused_copy", "fused_mc"):   # the fused forms land here only when their buffers could not be set up
             mode = "epilogue" if tp <= 2 else "copy"
         peers = self._slabs[4] if slab_ptrs is not None else None
         self.scatter_mode = mode or "nccl"     # what actually delivers the partial sums, for reports
@@ -457,7 +477,7 @@ class TensorParallelMLPStack:
         off_ws = off_slabs + up(tp * (m // tp) * hidden * 4)
         off_flags = off_ws + up(ws_bytes + 1024)
         total = off_flags + 2 * self.MAX_CHUNK_SLOTS * 8 * 4
-        ok, local, ptrs = 1, None, None
+        ok, local, ptrs, mc_ptr = 1, None, None, 0
         try:
             import torch.distributed._symmetric_memory as symm
 
@@ -466,14 +486,15 @@ class TensorParallelMLPStack:
             ptrs = [int(p) for p in handle.buffer_ptrs]
             if len(ptrs) != tp or ptrs[dist.get_rank(self.group)] != local.data_ptr() or any(p % 1024 for p in ptrs):
                 ok = 0
+            mc_ptr = int(getattr(handle, "multicast_ptr", 0) or 0)
         except Exception as exc:  # noqa: BLE001 - any failure means "use the collective"
             import warnings
 
             warnings.warn(f"symmetric memory unavailable ({exc}); using the NCCL reduce-scatter")
             ok = 0
-        flag = torch.tensor([ok], device=x.device, dtype=torch.int32)
+        flag = torch.tensor([ok, 1 if (ok and mc_ptr and mc_ptr % 1024 == 0) else 0], device=x.device, dtype=torch.int32)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
-        if int(flag.item()) == 0:
+        if int(flag[0].item()) == 0:
             self.peer_scatter = "copy"
             return False
         local[off_flags:].zero_()
@@ -481,6 +502,7 @@ class TensorParallelMLPStack:
         dist.barrier(group=self.group)       # every rank's flag words are zero before anyone raises one
         self._fused = {
             "key": key, "local": local, "handle": handle, "ptrs": ptrs, "off_ws": off_ws, "off_flags": off_flags,
+            "multicast": mc_ptr if int(flag[1].item()) else 0,
             "off_slabs": off_slabs,
             "peer_slabs": [handle.get_buffer(r, (tp, m // tp, hidden), torch.float32, off_slabs // 4) for r in range(tp)],
             "partial": local[: m * hidden * 4].view(torch.float32).view(m, hidden),
@@ -491,7 +513,7 @@ class TensorParallelMLPStack:
         self._seq = 0
         return True
 
-    def _forward_fused(self, x, adapter_ids, spans, chunks, tp, timing_events, pull=False):
+    def _forward_fused(self, x, adapter_ids, spans, chunks, tp, timing_events, form="fused_copy"):
         import torch
         import torch.distributed as dist
 
@@ -509,7 +531,9 @@ class TensorParallelMLPStack:
         layers = len(self.blocks)
         base = self._seq
         self._seq += layers
-        self.scatter_mode = "fused" if pull else "fused_copy"
+        pull = form in ("fused", "fused_mc")   # partial sums stay where the GEMM wrote them; the exchange reads across NVLink
+        multimem = form == "fused_mc"
+        self.scatter_mode = form
         row_bytes = hidden * 4
         peer_slabs, slab_base = fb["peer_slabs"], ptrs[rank] + fb["off_slabs"]
 
@@ -517,6 +541,8 @@ class TensorParallelMLPStack:
             """Address of every rank's partial sums such that `address + sorted_row * row_bytes` is the row: the
             ranks' own buffers (pull over NVLink), or this rank's slabs (rank s's rows sit at slab s, chunk after
             chunk) with its own buffer for its own share."""
+            if multimem:
+                return [fb["multicast"]]      # one address: the switch adds every rank's copy
             if pull:
                 return [p for p in ptrs]
             o0 = own[c][0]
@@ -584,7 +610,8 @@ class TensorParallelMLPStack:
                         peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
                         signal_flags=[flag_addr(r, 1, c, rank) for r in range(tp)] if nxt is not None else None,
                         signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas,
-                        single_kernel=self.exchange_single_kernel)
+                        single_kernel=self.exchange_single_kernel and not multimem, multimem=multimem,
+                        profile=self.trace is not None, wide=self.exchange_wide)
                     self._mark(f"L{l}c{c} exchange<", comm, "comm")
                     if last:
                         dist.all_gather_into_tensor(self._sorted[r0:r0 + cnt], self._sorted[o0:o0 + ocnt], group=self.group)

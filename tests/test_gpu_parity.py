@@ -637,9 +637,9 @@ def _tp_shards(S, T, tp, seed, m, hidden, inter, rank, na):
     return x, ids, shards
 
 
-@pytest.mark.parametrize("single_kernel", [False, True])
+@pytest.mark.parametrize("form", ["fat", "wide", "single"])
 @pytest.mark.parametrize("tp", [2, 4])
-def test_fused_exchange_emulated_on_one_gpu(S, tp, single_kernel):
+def test_fused_exchange_emulated_on_one_gpu(S, tp, form):
     # The fused exchange of a two-block stack with every rank's work done in turn on this GPU: each "rank" has
     # its own workspace, partial-sum buffer and flag words; the "peer mappings" are plain addresses of the other
     # ranks' buffers.  All kernels run on one stream, every flag is raised before the kernel that waits for it
@@ -707,7 +707,7 @@ def test_fused_exchange_emulated_on_one_gpu(S, tp, single_kernel):
                                        partials=[p.data_ptr() for p in partial], wait_flags=flags[r][0, c], wait_value=1,
                                        peer_workspaces=[w.data_ptr() for w in ws],
                                        signal_flags=[flag_addr(q, 1, c, r) for q in range(tp)], signal_value=1, grid_ctas=7,
-                                       single_kernel=single_kernel)
+                                       single_kernel=form == "single", wide=form == "wide")
         for c in range(chunks):                  # block 1 GEMMs on the rows everyone delivered
             for r in range(tp):
                 S.use_workspace(ws[r])
@@ -719,7 +719,7 @@ def test_fused_exchange_emulated_on_one_gpu(S, tp, single_kernel):
                 S.use_workspace(ws[r])
                 S.w8a8_mlp_tp_exchange(calls[r, c], None, srt[r], tp=tp, row_begin=r0 + r * (cnt // tp), row_count=cnt // tp,
                                        partials=[p.data_ptr() for p in partial], wait_flags=flags[r][0, c], wait_value=2,
-                                       sorted_out=True, single_kernel=single_kernel)
+                                       sorted_out=True, single_kernel=form == "single", wide=form == "wide")
         gathered = torch.empty((m, hidden), dtype=torch.bfloat16, device="cuda")
         for c, (r0, cnt) in enumerate(spans):
             for r in range(tp):

@@ -64,9 +64,10 @@ def main():
         blocks.append(T.TensorParallelMLP(to_dev(delta), pgu, lgu, pd, ld))
     xd, idd = to_dev(x), to_dev(ids)
     outs = {}
+    used_peer = used_fused = used_mc = None
     for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False),
                            ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy"), ("fused", True, "fused"),
-                           ("fused_copy", True, "fused_copy")):
+                           ("fused_copy", True, "fused_copy"), ("fused_mc", True, "fused_mc")):
         stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
         for _ in range(3):                      # later passes reuse buffers, a warm workspace and growing flag values
             y = stack.forward(xd, idd)
@@ -75,12 +76,13 @@ def main():
         outs[name] = y.clone()
         if name == "peer_copy":
             used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
-        if name in ("fused", "fused_copy"):
+        if name in ("fused", "fused_copy", "fused_mc"):
             used_fused = stack.scatter_mode if name == "fused" else used_fused
+            used_mc = stack.scatter_mode if name == "fused_mc" else used_mc
             S.use_workspace(None)               # the stack registered its symmetric workspace: release it
     a = outs["all_reduce"].float()
     ok, mismatched, between = True, 0, 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy", "fused_mc"):
         b = outs[name].float()
         mism = int(((a - b).abs() > 0).sum())
         # more than two ranks: the collectives may add the fp32 partial sums in different orders, and a
@@ -98,7 +100,7 @@ def main():
     for delta, qgu, ga, gb, wd, da, db in host:
         want = O.tp_shard_mlp_reference(want, delta, qgu, ga, gb, scal, wd, da, db, scal, ids, world)
     rel = 0.0
-    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy"):
+    for name in ("sequence_parallel", "peer_scatter", "peer_copy", "fused", "fused_copy", "fused_mc"):
         got = outs[name].cpu().view(torch.int16).numpy().view(BF16)
         rel = max(rel, O.relative_l2(got, want))
     ok = ok and rel < 2e-3
@@ -106,7 +108,7 @@ def main():
     dist.all_reduce(flag)
     if rank == 0:
         print(f"tp_multi_gpu_check world={world} mismatched={mismatched}/{a.numel()} rel_l2_between={between:.2e} "
-              f"rel_l2_vs_oracle={rel:.2e} peer_scatter_used={used_peer} fused_exchange={used_fused} "
+              f"rel_l2_vs_oracle={rel:.2e} peer_scatter_used={used_peer} fused_exchange={used_fused} in_switch_sum={used_mc} "
               f"rank_order_forms_differ_in={same_order} "
               f"{'OK' if int(flag) == 0 else 'FAILED'}", flush=True)
     dist.destroy_process_group()

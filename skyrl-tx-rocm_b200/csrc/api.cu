@@ -217,6 +217,7 @@ struct Projection {
   bool keep_xn;           // sorted route: x must be re-laid out (gathered / normalised) for the projection MMA
   int m, n, k, rank, na, mt;
   int q_row0, q_rows;     // sorted rows the quantiser stage covers (a chunk of the block, or all m rows)
+  int list_row0;          // first sorted row of the tile list `tiles` (0, or the first row of the call's chunk)
   bool skip_quant;        // the quantiser stage of these rows already ran (its outputs are in xq / sx / z_parts)
   int gemm_variant;       // SKYRL_GEMM_VARIANT_* forced on the GEMM (0: the library chooses)
   bool two_step_rows;     // row-wise route: GEMM to an int32 accumulator in memory + finalize kernel (default)
@@ -279,7 +280,7 @@ static int run_quant_stage(const Projection& q, cudaStream_t stream) {
   if (lora) {
     const void* xa = need_xn ? static_cast<const void*>(q.xn) : q.x;
     if ((rc = launch_lora_a_proj(xa, q.m, q.k, q.a_packed, q.scaling, q.na, q.rank, q.tiles, q.num_tiles, q.mt,
-                                 q.z_parts, q.status, stream, r0, r0 + rows)))
+                                 q.z_parts, q.status, stream, r0, r0 + rows, nullptr, 0, q.list_row0)))
       return rc;
   }
   return SKYRL_OK;
@@ -589,6 +590,7 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.mt = pl.mt;
   q.q_row0 = pl.row0;
   q.q_rows = pl.rows;
+  q.list_row0 = pl.row0;
   q.cta_limit = a->gemm_cta_limit;
   q.wq = a->gu_wq;
   q.sw = a->gu_sw;
@@ -802,7 +804,7 @@ extern "C" int skyrl_w8a8_mlp_tp_exchange_sm100_v1(const SkyrlW8A8MlpArgs* blk, 
     if (extra_count > 7) return fail(SKYRL_ERR_INVALID_ARGUMENT, "tp_exchange: this rank's workspace is not among peer_workspaces");
     if ((rc = launch_lora_a_proj(np.w.xn, next->m, next->hidden, next->gu_a_packed, next->gu_scaling, np.na, next->rank,
                                  np.tiles, np.num_tiles, np.mt, np.w.z_parts, next->status, stream, x->row_begin,
-                                 x->row_begin + x->row_count, extra, extra_count)))
+                                 x->row_begin + x->row_count, extra, extra_count, np.row0)))
       return rc;
   }
   bool any = false;

@@ -75,7 +75,7 @@ int launch_quant_stream(const void* x, const float* row_amax, int m, int k, void
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream, int row_lo = 0, int row_hi = -1,
-                       void* const* extra_dests = nullptr, int extra_count = 0);  // extra copies of the rows written
+                       void* const* extra_dests = nullptr, int extra_count = 0, int list_row0 = -1);  // extra copies of the rows written
 // Tile width and K split the GEMM launcher chooses for a shape (deterministic per device).
 struct GemmPlan {
   int bn_eff;

@@ -42,6 +42,7 @@ struct ProjParams {
   int z_count;                // are written to every one of the z_count destinations (a tensor-parallel rank hands
                               // its rows to every peer's workspace with plain stores; one destination otherwise)
   int row_lo, row_hi;      // rows written
+  int tile_base;           // CTA b looks at tile tile_base + b (a row window needs only the tiles that can overlap it)
   int32_t* status;
   int k;
 };
@@ -58,8 +59,9 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  if (static_cast<int>(blockIdx.x) >= *p.num_tiles) return;  // uniform for the CTA
-  const int4 tile = __ldg(p.tiles + blockIdx.x);
+  const int tile_index = static_cast<int>(blockIdx.x) + p.tile_base;
+  if (tile_index >= *p.num_tiles) return;  // uniform for the CTA
+  const int4 tile = __ldg(p.tiles + tile_index);
   if (tile.x >= p.row_hi || tile.x + tile.y <= p.row_lo) return;  // outside the row window, also uniform
 
   if (threadIdx.x == 0) {
@@ -194,7 +196,7 @@ __global__ void __launch_bounds__(PROJ_THREADS, 1) lora_a_proj_kernel(const __gr
 int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const float* scaling, int num_adapters,
                        int rank, const int32_t* tiles, const int32_t* num_tiles, int max_tiles, void* z_parts,
                        int32_t* status, cudaStream_t stream, int row_lo, int row_hi, void* const* extra_dests,
-                       int extra_count) {
+                       int extra_count, int list_row0) {
   if (x == nullptr || a_packed == nullptr || scaling == nullptr || tiles == nullptr || num_tiles == nullptr ||
       z_parts == nullptr || status == nullptr)
     return fail(SKYRL_ERR_INVALID_ARGUMENT, "lora_a_proj: null buffer");
@@ -234,7 +236,21 @@ int launch_lora_a_proj(const void* x, int m, int k, const void* a_packed, const 
   static bool attr_set[MAX_DEVICES] = {};
   cudaError_t e = ensure_dynamic_smem(lora_a_proj_kernel, PROJ_SMEM_BYTES, attr_set);
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj attribute: %s", cudaGetErrorString(e));
-  lora_a_proj_kernel<<<max_tiles, PROJ_THREADS, PROJ_SMEM_BYTES, stream>>>(p);
+  // `tiles` lists the tiles of the sorted rows from list_row0 on (a whole block, or one row chunk of it).  A tile
+  // holds at most 128 rows and is short only where an adapter's run ends, so the tile that holds row r has an
+  // index in [(r - list_row0) / 128, (r - list_row0) / 128 + adapters + 1]: a row window launches only those.
+  // (Every CTA asks for most of an SM's shared memory, so CTAs that would only find out that they have nothing to
+  // do still queue for an SM; beside a running GEMM that queue is what the projection of a small window costs.)
+  int grid = max_tiles;
+  p.tile_base = 0;
+  if ((p.row_lo > list_row0 || p.row_hi < m) && list_row0 >= 0 && p.row_lo >= list_row0 && p.row_hi > p.row_lo) {
+    p.tile_base = (p.row_lo - list_row0) / PROJ_BM;
+    const int last = (p.row_hi - 1 - list_row0) / PROJ_BM + num_adapters + 1;
+    grid = last - p.tile_base + 1;
+    if (grid > max_tiles - p.tile_base) grid = max_tiles - p.tile_base;
+    if (grid <= 0) return SKYRL_OK;
+  }
+  lora_a_proj_kernel<<<grid, PROJ_THREADS, PROJ_SMEM_BYTES, stream>>>(p);
   e = cudaPeekAtLastError();
   if (e != cudaSuccess) return fail(SKYRL_ERR_LAUNCH, "lora_a_proj launch: %s", cudaGetErrorString(e));
   return SKYRL_OK;

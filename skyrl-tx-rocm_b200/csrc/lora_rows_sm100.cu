@@ -136,32 +136,16 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
   for (int i = 0; i < VMAX; ++i)
 #pragma unroll
     for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(xv[i][e]));
-  amax = rowq_block_reduce(amax, true, red);
-  if (threadIdx.x == 0) part_amax = amax;
-  cluster.sync();
-  float row_amax = 0.f;
-#pragma unroll
-  for (int r = 0; r < ROWQ_CLUSTER; ++r) row_amax = fmaxf(row_amax, *cluster.map_shared_rank(&part_amax, r));
-  const float scale = row_amax > 0.f ? __fdiv_rn(row_amax, 127.0f) : 1.0f;
-  const float rcp = quant_rcp(scale);
-  if (crank == 0 && threadIdx.x == 0) sx[m] = scale;
-
+  // The projection z = n A[a] needs the normalised row but not its absmax, so it is evaluated HERE, before the
+  // absmax is exchanged: its LoRA-A loads are in flight during the block reductions, and the partial absmax and
+  // the partial z of every CTA cross the cluster behind ONE barrier instead of two.
   float acc[R];
 #pragma unroll
   for (int j = 0; j < R; ++j) acc[j] = 0.f;
-  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k) + v0;
-  uint4* ndst = xn_out != nullptr ? reinterpret_cast<uint4*>(xn_out + static_cast<int64_t>(m) * k) + v0 : nullptr;
 #pragma unroll
   for (int i = 0; i < VMAX; ++i) {
     const int v = threadIdx.x + i * ROWQ_THREADS;
     if (v < cnt) {
-      if (ndst != nullptr)  // the (normalised) bf16 activations both the quantiser and the LoRA term saw, for stage checks
-        ndst[v] = make_uint4(pack_bf16x2(xv[i][0], xv[i][1]), pack_bf16x2(xv[i][2], xv[i][3]),
-                             pack_bf16x2(xv[i][4], xv[i][5]), pack_bf16x2(xv[i][6], xv[i][7]));
-      int q[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) q[e] = quant_code(xv[i][e], scale, rcp);
-      dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
 #pragma unroll
       for (int j = 0; j < R; ++j) {
         const uint4 aw = PREFETCH_A ? ar[i][j] : __ldg(a_base + static_cast<int64_t>(j) * nvec + v);
@@ -182,7 +166,8 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     if (lane == 0) zwarp[warp][j] = v;
   }
-  __syncthreads();
+  amax = rowq_block_reduce(amax, true, red);   // (its barriers also publish zwarp)
+  if (threadIdx.x == 0) part_amax = amax;
   if (threadIdx.x < R) {
     float z = 0.f;
 #pragma unroll
@@ -190,6 +175,9 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
     part_z[threadIdx.x] = z;
   }
   cluster.sync();
+  float row_amax = 0.f;
+#pragma unroll
+  for (int r = 0; r < ROWQ_CLUSTER; ++r) row_amax = fmaxf(row_amax, *cluster.map_shared_rank(&part_amax, r));
   if (crank == 0 && threadIdx.x < SKYRL_LORA_RANK_PAD) {
     float z = 0.f;
     if (threadIdx.x < R) {
@@ -198,6 +186,24 @@ rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,
       z = __fmul_rn(z, __ldg(scaling + adapter));
     }
     z_rows[static_cast<int64_t>(m) * SKYRL_LORA_RANK_PAD + threadIdx.x] = z;
+  }
+  const float scale = row_amax > 0.f ? __fdiv_rn(row_amax, 127.0f) : 1.0f;
+  const float rcp = quant_rcp(scale);
+  if (crank == 0 && threadIdx.x == 0) sx[m] = scale;
+  uint2* dst = reinterpret_cast<uint2*>(xq + static_cast<int64_t>(m) * k) + v0;
+  uint4* ndst = xn_out != nullptr ? reinterpret_cast<uint4*>(xn_out + static_cast<int64_t>(m) * k) + v0 : nullptr;
+#pragma unroll
+  for (int i = 0; i < VMAX; ++i) {
+    const int v = threadIdx.x + i * ROWQ_THREADS;
+    if (v < cnt) {
+      if (ndst != nullptr)  // the (normalised) bf16 activations both the quantiser and the LoRA term saw, for stage checks
+        ndst[v] = make_uint4(pack_bf16x2(xv[i][0], xv[i][1]), pack_bf16x2(xv[i][2], xv[i][3]),
+                             pack_bf16x2(xv[i][4], xv[i][5]), pack_bf16x2(xv[i][6], xv[i][7]));
+      int q[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) q[e] = quant_code(xv[i][e], scale, rcp);
+      dst[v] = make_uint2(pack_codes4(q[0], q[1], q[2], q[3]), pack_codes4(q[4], q[5], q[6], q[7]));
+    }
   }
   cluster.sync();  // no CTA may leave while another still reads its shared memory
 }

@@ -759,6 +759,11 @@ def test_small_batch_fused_epilogue_equals_two_step_form(S, m, hidden, inter, ra
     lin_got = S.w8a8_lora_linear(xd, pgu, lgu, adapter_ids=idd, enabled=True, fused_rows=True)
     S.check_status()
     assert torch.equal(lin_got.view(torch.int16), lin_want.view(torch.int16))
+    # asking the next GEMM's weights into L2 is a hint to the memory system: no value may change, whatever the size
+    for nbytes in (1 << 12, 1 << 30):
+        pre = S.w8a8_mlp_block(xd, dd, pgu, lgu, pd, ld, idd, enabled=True, prefetch_next=pgu, prefetch_bytes=nbytes)
+        S.check_status()
+        assert torch.equal(pre.view(torch.int16), want.view(torch.int16))
 
 
 # ----------------------------------------------------------------------------- model wiring + weight pipeline

@@ -537,7 +537,49 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
     # and download of step i - 1 on streams of their own, double-buffered on both sides).  Every step still uploads
     # its inputs from pinned host memory and downloads its result inside the timed region.
     pipelined = graph is None and tp == 1 and kind != "down"
-    if pipelined:
+    pipelined_tp = graph is None and tp > 1 and kind == "mlp" and m % tp == 0
+    if pipelined_tp:
+        # N GPUs: the same pipeline; every rank uploads its share of the rows and the shares are all-gathered over NVLink
+        # on the upload stream (a process group of its own, so that this collective never interleaves with the stack's)
+        main_s, up_s, down_s = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        up_group = dist.new_group(list(range(world)))
+        r0, r1 = rank * (m // tp), (rank + 1) * (m // tp)
+        xbuf = [torch.empty_like(x_dev) for _ in range(2)]
+        idbuf = [torch.empty_like(ids) for _ in range(2)] if ids is not None else [None, None]
+        ostage = [torch.empty((r1 - r0, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
+        ohost = [torch.empty((r1 - r0, hidden), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+
+        def e2e_run(n):
+            consumed, downloaded = [None, None], [None, None]
+            for i in range(n):
+                b = i & 1
+                with torch.cuda.stream(up_s):
+                    if consumed[b] is not None:
+                        up_s.wait_event(consumed[b])
+                    xbuf[b][r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                    dist.all_gather_into_tensor(xbuf[b], xbuf[b][r0:r1], group=up_group)
+                    if ids is not None:
+                        idbuf[b].copy_(ids_host, non_blocking=True)
+                    uploaded = torch.cuda.Event()
+                    uploaded.record(up_s)
+                main_s.wait_event(uploaded)
+                y = step(xbuf[b], idbuf[b])
+                consumed[b] = torch.cuda.Event()
+                consumed[b].record(main_s)
+                if downloaded[b] is not None:
+                    main_s.wait_event(downloaded[b])
+                ostage[b].copy_(y[r0:r1])        # the stack's output buffer is reused by the next step
+                staged = torch.cuda.Event()
+                staged.record(main_s)
+                with torch.cuda.stream(down_s):
+                    down_s.wait_event(staged)
+                    ohost[b].copy_(ostage[b], non_blocking=True)
+                    downloaded[b] = torch.cuda.Event()
+                    downloaded[b].record(down_s)
+            for ev in downloaded:
+                if ev is not None:
+                    main_s.wait_event(ev)
+    elif pipelined:
         main_s, up_s, down_s = torch.cuda.current_stream(), torch.cuda.Stream(), torch.cuda.Stream()
         xbuf = [torch.empty((m, x_host.shape[1]), dtype=torch.bfloat16, device=device) for _ in range(2)]
         idbuf = [torch.empty_like(ids) for _ in range(2)] if ids is not None else [None, None]
@@ -643,7 +685,7 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms,
                 "copies": "every step uploads its inputs and downloads its result; consecutive steps' copies overlap the "
-                          "compute (double-buffered, streams of their own)" if pipelined else "in line with the compute"},
+                          "compute (double-buffered, streams of their own)" if (pipelined or pipelined_tp) else "in line with the compute"},
         "gpu_launches": launches_per_step * steps,
         "clocks": clocks,
         # time x clock: what a comparison across runs at different SM clocks (a power-capped 1-GPU run against an

@@ -480,16 +480,18 @@ SKYRL_API int skyrl_w8a8_mlp_tp_prepare_sm100_v1(const SkyrlW8A8MlpArgs* args, i
  * offsets[0] int8 codes [m, hidden], offsets[1] fp32 scales [m], offsets[2] bf16 LoRA-A parts [m, 6, 64]. */
 SKYRL_API int skyrl_w8a8_mlp_workspace_regions(int32_t m, int32_t hidden, int32_t inter, int32_t num_adapters,
                                      size_t* offsets);
-/* Fused exchange between two blocks of a sequence-parallel stack: ONE kernel per rank and row chunk in place
- * of a reduce-scatter, the finalize kernel, the next block's quantiser stage and the gathers of its results.
+/* Fused exchange between two blocks of a sequence-parallel stack: flag words and this library's own kernels
+ * (two launches per rank and row chunk, or one with SKYRL_TP_EXCHANGE_SINGLE_KERNEL) in place of a
+ * reduce-scatter, the finalize kernel, the next block's quantiser stage and the gathers of its results.
  * XLA inserts separate collectives around separately scheduled fusions here (the all-reduce behind the
  * ("tp", "fsdp") sharded down_proj, skyrl/tx/models/qwen3_5.py:644).
  *
- * For this rank's sorted rows [row_begin, row_begin + row_count) of a chunk the kernel
+ * For this rank's sorted rows [row_begin, row_begin + row_count) of a chunk the call
  *   - waits (bounded) until wait_flags[s] >= wait_value for every rank s: rank s raises its word in this
  *     rank's memory with skyrl_w8a8_tp_signal_sm100_v1 once its down GEMM of the chunk has completed,
- *   - reads the row's fp32 partial sums from partials[s] of EVERY rank (own buffer and peer mappings; plain
- *     loads) and adds them in ascending s (skyrl/tx/kernels/quantized_lora.py:253),
+ *   - reads the row's fp32 partial sums from partials[s] of EVERY rank (own buffer and peer mappings, or slabs in
+ *     this rank's memory that the ranks filled; plain loads) and adds them in ascending s
+ *     (skyrl/tx/kernels/quantized_lora.py:253),
  *   - writes bf16(sum) + residual to `out` (row perm[i]; row i with SKYRL_MLP_FINALIZE_SORTED set in `block`),
  *   - and, when `next` is given, runs the next block's RMSNorm + int8 quantiser on that row and stores the codes
  *     and the scale into the workspace of EVERY rank (peer_workspaces[r], all of the layout of `next`; plain

@@ -1,24 +1,27 @@
-// Tensor-parallel exchange between two MLP blocks, fused into one kernel per rank and row chunk.
+// Tensor-parallel exchange between two MLP blocks: flag words and three kernels per rank and row chunk.
 //
 // The reference shards gate_up by output features and down by input features and lets GSPMD add one
 // all-reduce behind down_proj (skyrl/tx/models/qwen3_5.py:633,644).  Every stage between the down GEMM of
 // block l and the gate_up GEMM of block l + 1 is row-wise, so a rank owns 1/tp of a chunk's adapter-sorted
-// rows there, and this kernel does for those rows, in one pass over NVLink:
+// rows there, and for those rows this file does:
 //
-//   pull     the fp32 partial sums of the row from EVERY rank's buffer (plain peer loads, no collective),
-//            added in ascending rank order: the fp32 group sum of skyrl/tx/kernels/quantized_lora.py:253
+//   sum      the fp32 partial sums of the row from EVERY rank, added in ascending rank order (the fp32 group sum of
+//            skyrl/tx/kernels/quantized_lora.py:253): from slabs in this rank's memory that the ranks' copy engines
+//            filled, from the ranks' own buffers with plain peer loads, or as one multimem.ld_reduce per 16 bytes
+//            from the multicast address of a symmetric buffer (the sum formed inside NVSwitch, in its order)
 //   finalize bf16(sum) + residual in bf16 (quantized_lora.py:304, qwen3_5.py:784) -> the block's output row
 //   prepare  the next block's RMSNorm(1 + delta), per-token absmax, int8 codes (qwen3_5.py:274-278,
-//            quantized_lora.py:199-212), same code as rms_quant_kernel
+//            quantized_lora.py:199-212), bit for bit what rms_quant_kernel produces
 //   push     the codes and the scale of the row into EVERY rank's workspace (plain peer stores), the
 //            normalised bf16 row into this rank's, for the LoRA-A projection that follows
 //
-// Ordering between ranks is by flag words in each rank's memory, never by a collective: a rank raises
-// "partial sums of (block, chunk) complete" on every peer after its down GEMM, and "prepared rows of
-// (block + 1, chunk) delivered" after its pushes.  Flag values only grow (one sequence number per block and
-// chunk), so nothing is ever reset.  Every wait is bounded: when the limit runs out the kernel records
-// STATUS_TIMEOUT_PEER in the caller's status word and carries on (its rows are then wrong, the context is
-// intact, and no GPU is left waiting).  No TMA and no multicast touches peer memory anywhere.
+// as two launches (tp_sum_kernel: sum + finalize, a streaming pass; tp_quant_rows_kernel: prepare + push, one warp
+// per row) or as one row-per-CTA kernel (tp_exchange_kernel).  Ordering between ranks is by flag words in each
+// rank's memory, never by a collective: a rank raises "partial sums of (block, chunk) in place" on every peer, and
+// "prepared rows of (block + 1, chunk) delivered" after its pushes.  Flag values only grow (one sequence number
+// per block and chunk), so nothing is ever reset.  Every wait is bounded: when the limit runs out the kernel
+// records STATUS_TIMEOUT_PEER in the caller's status word and carries on (its rows are then wrong, the context is
+// intact, and no GPU is left waiting).  No TMA touches peer memory anywhere.
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 #include "quant_row.cuh"

@@ -114,3 +114,26 @@ def test_autograd_function_matches_oracle_vjp(S, B):
     assert O.relative_l2(to_np(ta.grad).astype(np.float32), want_da) < 4e-3   # gradients are cast to the parameter dtype
     assert O.relative_l2(to_np(tb.grad).astype(np.float32), want_db) < 4e-3
     assert O.relative_l2(to_np(ts.grad), want_ds) < 1e-4
+
+
+def test_input_gradient_at_the_c5_down_shape_sampled_rows(S, B):
+    # full launch size of the Qwen3-32B-shaped down projection (M 16384, K 25600, N 5120, 16 adapters of rank 64);
+    # every row of dx depends on its own row of dy only, so a seeded sample of rows goes through the oracle
+    from parity_util import sample_rows
+
+    m, k, n, rank, na = 16384, 25600, 5120, 64, 16
+    w_host, w_packed = big_weight(S, k, n, 61)
+    (a, b, s), _ = big_lora(S, na, k, rank, n, 67, 128.0)
+    ids = uniform_ids(m, na, 71)
+    dy = device_normal((m, n), 73, 0.02)
+    wb = B.pack_weight_backward(w_packed)
+    lb = B.pack_lora_backward(to_dev(a), to_dev(b), to_dev(s), wb)
+    dx = B.w8a8_lora_linear_input_grad(dy, wb, lb, to_dev(ids), enabled=True)
+    S.check_status()
+    rows = sample_rows(m, 96, 79)
+    dy_rows = to_np(dy[torch.from_numpy(rows).cuda()])
+    x_dummy = np.zeros((len(rows), k), dtype=dy_rows.dtype)          # dx does not depend on x
+    want, _, _, _ = O.quantized_lora_linear_vjp(x_dummy, w_host, a, b, s, dy_rows, ids[rows])
+    got = to_np(dx[torch.from_numpy(rows).cuda()]).astype(np.float32)
+    rel = O.relative_l2(got, want.astype(np.float32))
+    assert rel < 4e-3, rel

@@ -14,7 +14,8 @@ per-output-channel scale moves to the cotangent, g = dy * sw, each row of g is s
 codes (unit weight scales) into fp32 slabs.  dx therefore equals the fp32 product to about 2^-15 relative
 (two planes) — far inside bf16's own rounding — at the cost of one bf16 GEMM, and `R @ A^T` rides the LoRA
 slice of the last plane's launch exactly as `s (x A) B` does in the forward.  The rank-r reductions dA, dB and
-ds are two orders of magnitude smaller and use library matmuls over the adapter-sorted rows.
+ds are two orders of magnitude smaller and use library matmuls over the adapter-sorted rows (bf16 tensor-core
+products with fp32 results; the small fp32 factors are split into two bf16 terms).
 
 `W8A8LoRALinearFunction` ties forward and backward together for `torch.autograd`, the counterpart of the
 reference's `quantized_lora_linear.defvjp(...)` (quantized_lora.py:397).
@@ -129,41 +130,68 @@ def w8a8_lora_linear_input_grad(dy: torch.Tensor, weight_bwd: PackedW8Backward, 
     return dx.reshape(*dy.shape[:-1], k)
 
 
+def _mm_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 result of a @ b.  bf16 operands on a CUDA device multiply on the tensor cores (products of bf16 pairs are
+    exact in the fp32 accumulator) without an fp32 copy of either operand; anything else takes the plain fp32 path."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16:
+        return torch.mm(a, b, out_dtype=torch.float32)
+    return a.float() @ b.float()
+
+
+def _split_bf16(t: torch.Tensor):
+    """fp32 -> (hi, lo) bf16 with hi + lo == t to 2^-17 relative: keeps a small fp32 factor exact enough for a bf16
+    tensor-core matmul against a large bf16 operand."""
+    hi = t.to(torch.bfloat16)
+    return hi, (t - hi.float()).to(torch.bfloat16)
+
+
 def lora_parameter_grads(x: torch.Tensor, dy: torch.Tensor, lora_a: torch.Tensor, lora_b: torch.Tensor, lora_scaling,
                          adapter_ids=None):
     """(dA [A, K, r], dB [A, r, N], ds [A]) in fp32 (quantized_lora.py:374-389), rows grouped by adapter.
-    Library matmuls: each is a rank-r reduction over the rows, ~r / N of the input-gradient work."""
+
+    Library matmuls.  Each gradient is a rank-r reduction over the rows: U = x A and R' = dy B^T are [M, r]; then
+    dA = x^T (s R'), dB = s U^T dy and ds = sum(U * R') (the reference's sum(dy * (U B)) with the contraction over N
+    done first).  On a CUDA device the large operands x and dy stay bf16: the small fp32 factors are split into two
+    bf16 terms, so every product runs on the tensor cores with fp32 accumulation."""
     squeeze = lora_a.ndim == 2
     if squeeze:
         lora_a, lora_b = lora_a[None], lora_b[None]
     na, k, r = lora_a.shape
     n = lora_b.shape[2]
-    x2 = x.reshape(-1, k).float()
-    dy2 = dy.reshape(-1, n).float()
+    x2 = x.reshape(-1, k)
+    dy2 = dy.reshape(-1, n)
     m = x2.shape[0]
     scaling = torch.as_tensor(lora_scaling, dtype=torch.float32, device=x.device).reshape(-1)
     d_a = torch.zeros((na, k, r), dtype=torch.float32, device=x.device)
     d_b = torch.zeros((na, r, n), dtype=torch.float32, device=x.device)
     d_s = torch.zeros((na,), dtype=torch.float32, device=x.device)
     if adapter_ids is None:
-        order, counts = torch.arange(m, device=x.device), [m] + [0] * (na - 1)
+        xs, gs, counts = x2, dy2, [m] + [0] * (na - 1)
     else:
         ids = adapter_ids.reshape(-1).to(torch.int64)
         order = torch.argsort(ids, stable=True)
         counts = torch.bincount(ids, minlength=na).tolist()
+        xs, gs = x2[order], dy2[order]            # one gather; the adapters' rows are then contiguous slices
+    fast = xs.is_cuda and xs.dtype == torch.bfloat16 and gs.dtype == torch.bfloat16
     start = 0
     for a, count in enumerate(counts):
         if count == 0:
             continue
-        rows = order[start:start + count]
+        xa, ga = xs[start:start + count], gs[start:start + count]
         start += count
-        xa, ga = x2[rows], dy2[rows]
-        a32, b32 = lora_a[a].float(), lora_b[a].float()
-        inter = xa @ a32
-        low = (ga @ b32.t()) * scaling[a]
-        d_a[a] = xa.t() @ low
-        d_b[a] = (inter.t() @ ga) * scaling[a]
-        d_s[a] = (ga * (inter @ b32)).sum()
+        inter = _mm_f32(xa, lora_a[a])                       # U  [Ma, r]
+        low_unscaled = _mm_f32(ga, lora_b[a].t())            # R' [Ma, r]
+        low = low_unscaled * scaling[a]
+        if fast:
+            low_hi, low_lo = _split_bf16(low)
+            int_hi, int_lo = _split_bf16(inter)
+            xat, gat = xa.t(), ga
+            d_a[a] = _mm_f32(xat, low_hi) + _mm_f32(xat, low_lo)
+            d_b[a] = (_mm_f32(int_hi.t(), gat) + _mm_f32(int_lo.t(), gat)) * scaling[a]
+        else:
+            d_a[a] = xa.float().t() @ low
+            d_b[a] = (inter.t() @ ga.float()) * scaling[a]
+        d_s[a] = (inter * low_unscaled).sum()
     if squeeze:
         return d_a[0], d_b[0], d_s[0]
     return d_a, d_b, d_s

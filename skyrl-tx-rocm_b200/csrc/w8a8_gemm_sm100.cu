@@ -1750,7 +1750,10 @@ int launch_gemm(const SkyrlW8A8GemmArgs& a, cudaStream_t stream, bool programmat
   p.n = a.n;
   p.k = a.k;
   p.rank_blocks = (a.rank + 15) / 16;
-  p.band = 16;
+#ifndef SKYRL_RASTER_BAND
+#define SKYRL_RASTER_BAND 32  // M tiles per raster band; c5 step on one B200: 51.1 / 49.4 / 48.7 / 49.9 ms for 8 / 16 / 32 / 64
+#endif
+  p.band = SKYRL_RASTER_BAND;
   p.bn_eff = bn_eff;
   // The whole stage area is pipeline depth: the main loop is bound by bytes in flight per SM.
   p.a_rows = (!lora && a.m <= 64) ? 64 : BM;

@@ -364,6 +364,11 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
             # per layer and row chunk: quantiser of h, LoRA-A of h, two GEMMs, finalize, next layer's quantiser and
             # LoRA-A projection of the own rows; one routing launch and one row un-sort per step
             launches_per_step = layers * args.tp_chunks * 7 + 2
+            if args.tp_peer_scatter in ("auto", "fused", "fused_copy", "fused_mc") and (tp > 2 or args.tp_peer_scatter != "auto"):
+                # fused exchange, per layer and chunk: flag wait, quantiser of h, LoRA-A of h, two GEMMs, flag signal, sum
+                # kernel, row quantiser, LoRA-A projection, flag signal (the last layer has no next block: three fewer);
+                # per step: routing, the first block's quantiser + LoRA-A per chunk, un-sort
+                launches_per_step = layers * args.tp_chunks * 10 - 3 * args.tp_chunks + 2 * args.tp_chunks + 2
         else:
             # per layer: two quantiser launches, two LoRA-A (or LoRA-B row) launches, two GEMMs; one routing launch
             launches_per_step = layers * 6 + 1

@@ -145,9 +145,9 @@ class TensorParallelMLPStack:
                   also overlaps the other chunk's gate_up GEMM; best once the transfer
                   outlasts the down GEMM (4 and 8 ranks).
       "fused"     no collective and no copy at all between two blocks: the down GEMM leaves its partial
-                  sums in this rank's symmetric buffer and raises a flag on every peer; ONE kernel per
-                  chunk then pulls the owned rows' partial sums from every rank over NVLink, adds them
-                  in rank order, finalizes, runs the next block's RMSNorm + quantiser and stores codes,
+                  sums in this rank's symmetric buffer and raises a flag on every peer; this rank's exchange
+                  kernels then pull the owned rows' partial sums from every rank over NVLink, add them
+                  in rank order, finalize, run the next block's RMSNorm + quantiser and store codes,
                   scales and (after the LoRA-A projection) the projection parts straight into every
                   rank's workspace, which lives in symmetric memory too; a second flag tells the peers
                   that the rows have arrived (`ops.w8a8_mlp_tp_exchange`).  Block 0 is prepared by every

@@ -239,6 +239,10 @@ def init_distributed(args):
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The collectives left on this path are small (flags, the last block's gather, the upload gather); every
+        # multi-GPU number of this repository was taken with NCCL's in-switch (NVLS) algorithms off, which also keeps
+        # NCCL from binding multicast objects beside the symmetric-memory buffers.  Export NCCL_NVLS_ENABLE=1 to override.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         if args.nccl_max_ctas > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_max_ctas))
         if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":

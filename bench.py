@@ -834,9 +834,12 @@ def cpu_sample(workload: str, wl: dict, rows: int):
     return time.perf_counter() - t0
 
 
+CPU_SAMPLE_ROWS = 1024   # token rows of one layer the CPU arms time per sample (about 4 s on 16 cores at the c5 shape)
+
+
 def cpu_baseline(workload: str, wl: dict, rows: int | None = None, reps: int = 2):
     cores = host_threads()
-    rows = rows or min(wl["m"], 256)
+    rows = rows or min(wl["m"], CPU_SAMPLE_ROWS)
     cpu_sample(workload, wl, min(rows, 16))  # warm BLAS threads
     secs = min(cpu_sample(workload, wl, rows) for _ in range(reps))
     per_layer_rows_per_s = rows / secs
@@ -860,7 +863,7 @@ def run_reference(args):
     if rank != 0:
         return
     wl = dict(WORKLOADS[args.workload])
-    rows = min(wl["m"], 256)
+    rows = min(wl["m"], CPU_SAMPLE_ROWS)
     for _ in range(max(args.warmup, 1)):
         cpu_sample(args.workload, wl, min(rows, 16))
     times = [cpu_sample(args.workload, wl, rows) for _ in range(max(1, min(args.steps, 30)))]

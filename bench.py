@@ -834,7 +834,7 @@ def cpu_sample(workload: str, wl: dict, rows: int):
     return time.perf_counter() - t0
 
 
-CPU_SAMPLE_ROWS = 1024   # token rows of one layer the CPU arms time per sample (about 4 s on 16 cores at the c5 shape)
+CPU_SAMPLE_ROWS = 2048   # token rows of one layer the CPU arms time per sample (about 4.7 s on 16 cores at the c5 shape)
 
 
 def cpu_baseline(workload: str, wl: dict, rows: int | None = None, reps: int = 2):

@@ -900,9 +900,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-row oracle check in front of the timed region")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode (c2) sub-benchmark of the default c5 line")
-    ap.add_argument("--tp-chunks", type=int, default=-1,
-                    help="row chunks per block whose exchange overlaps the next chunk's kernels (N > 1); -1 = 2, and 3 on 8 "
-                         "GPUs, where a chunk's exchange no longer fits into one GEMM phase (11.05 against 11.30 ms per step)")
+    ap.add_argument("--tp-chunks", type=int, default=2,
+                    help="row chunks per block whose exchange overlaps the next chunk's kernels (N > 1).  On 8 GPUs two and "
+                         "three chunks measure the same within the box-to-box spread (11.05-11.3 ms per step); two keep the "
+                         "host's enqueue time at a third of the step")
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
                     help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
                          "0: one fp32 all-reduce per chunk")
@@ -927,8 +928,6 @@ def main():
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the step from a CUDA graph (auto: small-batch workloads on one GPU)")
     args = ap.parse_args()
-    if args.tp_chunks < 0:
-        args.tp_chunks = 3 if args.gpus >= 8 else 2
     if args.tp_reserve_sms < 0:
         args.tp_reserve_sms = 8 if args.gpus <= 2 else 4
     if args.impl == "reference":

@@ -173,7 +173,7 @@ class TensorParallelMLPStack:
 
     def __init__(self, blocks, *, group=None, num_chunks: int = 2, reserve_sms: int = 8, sm_count: int = 148,
                  sequence_parallel: bool = True, peer_scatter="auto", exchange_ctas: int = 0,
-                 exchange_single_kernel: bool = False, exchange_wide: bool = True):
+                 exchange_single_kernel: bool = False, exchange_wide: bool = True, exchange_splits: int = 1):
         self.blocks = list(blocks)
         self.group = group
         self.num_chunks = num_chunks
@@ -192,6 +192,7 @@ class TensorParallelMLPStack:
             self.exchange_ctas = 4 * sm_count if exchange_wide else max(4, reserve_sms)
         self.exchange_single_kernel = bool(exchange_single_kernel)
         self.exchange_wide = bool(exchange_wide)
+        self.exchange_splits = max(1, int(exchange_splits))
         self.scatter_mode = None
         self._fused = None        # symmetric buffers of the fused exchange
         self._seq = 0             # flag values only grow: one per block and forward pass
@@ -561,13 +562,23 @@ class TensorParallelMLPStack:
                 caches.clear()
             cache = caches[ckey] = {"push": {}, "next": {}}
 
-        def push_partial(c):
-            # copy engines: this rank's partial sums of owner o's rows -> o's slab for this rank
-            pairs = cache["push"].get(c)
+        # A chunk's delivery and exchange may be cut into `splits` runs of the own rows: the copy engines push run j + 1
+        # while the exchange kernels work on run j, so what follows a chunk's GEMMs is one run's push plus the runs'
+        # exchanges instead of the whole push plus the whole exchange.  The GEMMs stay one launch per chunk.
+        splits = self.exchange_splits if not pull else 1
+        if any(cnt_own % splits for _, cnt_own in own) or len(spans) * splits > self.MAX_CHUNK_SLOTS:
+            splits = 1
+        slot = lambda c, j: c * splits + j
+
+        def push_partial(c, j):
+            # copy engines: this rank's partial sums of run j of owner o's rows -> o's slab for this rank
+            pairs = cache["push"].get((c, j))
             if pairs is None:
                 (r0, cnt), ocnt = spans[c], own[c][1]
-                pairs = cache["push"][c] = [
-                    (peer_slabs[o][rank, own_off[c]:own_off[c] + ocnt], partial[r0 + o * ocnt:r0 + (o + 1) * ocnt])
+                sub = ocnt // splits
+                pairs = cache["push"][c, j] = [
+                    (peer_slabs[o][rank, own_off[c] + j * sub:own_off[c] + (j + 1) * sub],
+                     partial[r0 + o * ocnt + j * sub:r0 + o * ocnt + (j + 1) * sub])
                     for o in ((rank + step) % tp for step in range(1, tp))]   # every rank starts with a different owner
             for dst_view, src_view in pairs:
                 dst_view.copy_(src_view, non_blocking=True)
@@ -596,9 +607,11 @@ class TensorParallelMLPStack:
             value = base + l + 1
             for c, (r0, cnt) in enumerate(spans):
                 o0, ocnt = own[c]
+                sub = ocnt // splits
                 if l > 0:
                     main.wait_event(exchanged[c])               # this rank's own exchange first (an event, not a spin) ...
-                    ops.tp_wait(flags[1, c], tp, value - 1)     # ... then every other rank's rows of this chunk
+                    for j in range(splits):                     # ... then every other rank's rows of this chunk
+                        ops.tp_wait(flags[1, slot(c, j)], tp, value - 1)
                 self._mark(f"L{l}c{c} gemms>", main, "main")
                 ev = timing_events[l] if (timing_events is not None and c == 0) else None
                 call = block_call(blk, cur, c, reuse_routing=True, input_prepared=True, timing_events=ev)
@@ -607,23 +620,26 @@ class TensorParallelMLPStack:
                 self._mark(f"L{l}c{c} gemms<", main, "main")
                 computed = torch.cuda.Event()
                 computed.record(main)
+                pushed = []
                 if not pull:
                     # Copy engines on a stream of their own: the pushes of this chunk overlap the exchange kernels of
-                    # the chunk before it (one stream for both made every exchange wait for the previous one's
+                    # the chunk (or run) before it (one stream for both made every exchange wait for the previous one's
                     # kernels: 0.33 ms of pushes + 0.35 ms of kernels per chunk in series on 8 GPUs, more than a
                     # chunk's GEMMs).  The exchange kernels are ordered behind this rank's OWN signal by an event, so
                     # that they only ever spin on flags other GPUs raise.
                     with torch.cuda.stream(self._copy):
                         self._copy.wait_event(computed)
                         self._mark(f"L{l}c{c} push>", self._copy, "copy")
-                        push_partial(c)
-                        ops.tp_signal([flag_addr(r, 0, c, rank) for r in range(tp)], value)   # my rows have arrived
+                        for j in range(splits):
+                            push_partial(c, j)
+                            ops.tp_signal([flag_addr(r, 0, slot(c, j), rank) for r in range(tp)], value)   # my rows have arrived
+                            ev_pushed = torch.cuda.Event()
+                            ev_pushed.record(self._copy)
+                            pushed.append(ev_pushed)
                         self._mark(f"L{l}c{c} pushed", self._copy, "copy")
-                        pushed = torch.cuda.Event()
-                        pushed.record(self._copy)
                 with torch.cuda.stream(comm):
-                    comm.wait_event(computed if pull else pushed)
-                    self._mark(f"L{l}c{c} exchange>", comm, "comm")
+                    if pull:
+                        comm.wait_event(computed)
                     nxt = None
                     if not last:
                         nxt = cache["next"].get((l, c))
@@ -633,14 +649,19 @@ class TensorParallelMLPStack:
                                 dst, nb.rms_delta, nb.gate_up_weight, nb.gate_up_lora, nb.down_weight, nb.down_lora,
                                 adapter_ids, enabled=True, eps=nb.eps, out=partial, down_epilogue=ops.EPI_PARTIAL_F32,
                                 chunk=chunk_arg(c), reuse_routing=True, build_only=True)[1]
-                    ops.w8a8_mlp_tp_exchange(
-                        call, nxt, self._sorted if last else dst, tp=tp, row_begin=o0, row_count=ocnt,
-                        partials=partial_sources(c), wait_flags=flags[0, c], wait_value=value,
-                        peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
-                        signal_flags=[flag_addr(r, 1, c, rank) for r in range(tp)] if nxt is not None else None,
-                        signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas,
-                        single_kernel=self.exchange_single_kernel and not multimem, multimem=multimem,
-                        profile=self.trace is not None, wide=self.exchange_wide)
+                    for j in range(splits):
+                        if not pull:
+                            comm.wait_event(pushed[j])
+                        if j == 0:
+                            self._mark(f"L{l}c{c} exchange>", comm, "comm")
+                        ops.w8a8_mlp_tp_exchange(
+                            call, nxt, self._sorted if last else dst, tp=tp, row_begin=o0 + j * sub, row_count=sub,
+                            partials=partial_sources(c), wait_flags=flags[0, slot(c, j)], wait_value=value,
+                            peer_workspaces=[p + off_ws for p in ptrs] if nxt is not None else None,
+                            signal_flags=[flag_addr(r, 1, slot(c, j), rank) for r in range(tp)] if nxt is not None else None,
+                            signal_value=value, sorted_out=last, grid_ctas=self.exchange_ctas,
+                            single_kernel=self.exchange_single_kernel and not multimem, multimem=multimem,
+                            profile=self.trace is not None, wide=self.exchange_wide)
                     self._mark(f"L{l}c{c} exchange<", comm, "comm")
                     exchanged[c] = torch.cuda.Event()
                     exchanged[c].record(comm)

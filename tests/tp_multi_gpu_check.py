@@ -67,8 +67,10 @@ def main():
     used_peer = used_fused = used_mc = None
     for name, sp, peer in (("all_reduce", False, False), ("sequence_parallel", True, False),
                            ("peer_scatter", True, "epilogue"), ("peer_copy", True, "copy"), ("fused", True, "fused"),
-                           ("fused_copy", True, "fused_copy"), ("fused_mc", True, "fused_mc")):
-        stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer)
+                           ("fused_copy", True, "fused_copy"), ("fused_mc", True, "fused_mc"),
+                           ("fused_copy_split", True, "fused_copy")):
+        stack = T.TensorParallelMLPStack(blocks, num_chunks=2, sequence_parallel=sp, peer_scatter=peer,
+                                         exchange_splits=2 if name == "fused_copy_split" else 1)
         for _ in range(3):                      # later passes reuse buffers, a warm workspace and growing flag values
             y = stack.forward(xd, idd)
         torch.cuda.synchronize()
@@ -76,7 +78,7 @@ def main():
         outs[name] = y.clone()
         if name == "peer_copy":
             used_peer = stack.peer_scatter      # False: symmetric memory was unavailable and the collective ran
-        if name in ("fused", "fused_copy", "fused_mc"):
+        if name in ("fused", "fused_copy", "fused_mc", "fused_copy_split"):
             used_fused = stack.scatter_mode if name == "fused" else used_fused
             used_mc = stack.scatter_mode if name == "fused_mc" else used_mc
             S.use_workspace(None)               # the stack registered its symmetric workspace: release it
@@ -93,6 +95,7 @@ def main():
     # the three peer-memory forms add the partial sums in ascending rank order: identical bits at any group size
     same_order = int(((outs["fused"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
         int(((outs["fused_copy"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
+        int(((outs["fused_copy_split"].float() - outs["peer_copy"].float()).abs() > 0).sum()) + \
         int(((outs["peer_scatter"].float() - outs["peer_copy"].float()).abs() > 0).sum())
     if used_peer and used_fused == "fused":
         ok = ok and same_order == 0

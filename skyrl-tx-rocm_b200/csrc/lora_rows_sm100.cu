@@ -5,7 +5,7 @@
 //
 //   rms_quant_rows_kernel<R> ... a cluster of 8 CTAs per token row: RMSNorm, absmax, int8 codes and
 //                                z[m, :] = s[a] * (n[m, :] @ A[a]); every CTA owns one eighth of K and
-//                                the three row-wide reductions go through distributed shared memory
+//                                the row-wide reductions go through distributed shared memory (two exchanges)
 //   finalize_rows_kernel<EPI> .. v = (f32(acc) * sx[m]) * sw[n] + sum_j z[m, j] * B[a(m)][n, j], then the
 //                                single bf16 cast and SwiGLU / residual, from the int32 accumulator the
 //                                GEMM left in global memory
@@ -47,7 +47,8 @@ __device__ __forceinline__ float rowq_block_reduce(float v, bool is_max, float* 
 
 // Each thread owns up to VMAX 8-element vectors of its CTA's K slice and keeps them in registers; every
 // global load (activations, RMSNorm weights, and with PREFETCH_A the LoRA-A slice) is issued before the
-// first reduction, so the kernel pays one memory latency plus three cluster barriers.
+// first reduction, so the kernel pays one memory latency plus the cluster barriers (sum of squares; then absmax and
+// projection together; one more so that no CTA leaves while its shared memory is read).
 template <int R, int VMAX, bool PREFETCH_A>
 __global__ void __cluster_dims__(ROWQ_CLUSTER, 1, 1) __launch_bounds__(ROWQ_THREADS)
 rms_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_row_stride,

@@ -347,8 +347,18 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
         x_dev = x_host.to(device)
         act = [torch.empty((m, hidden), dtype=torch.bfloat16, device=device) for _ in range(2)]
         ops_per_step = 2.0 * m * (hidden * 2 * inter + inter * hidden) * layers  # whole job, all ranks
-        # the timed GEMM launches are those of chunk 0 when the tensor-parallel stack cuts the rows into chunks
+        # one GPU, many rows: the rows run as chunks on two streams (skyrl_tx_rocm_b200.stack.MLPStack)
+        row_stack, row_chunks = None, 1
+        if tp == 1 and m > 128:
+            from skyrl_tx_rocm_b200.stack import MLPStack
+
+            row_stack = MLPStack(blocks, num_chunks=args.row_chunks, gemm_variant=args.gemm_variant,
+                                 gemm_cta_limit=args.row_chunk_cta_limit)
+            row_chunks = row_stack.chunks_for(m)
+        # the timed GEMM launches are those of chunk 0 when the rows are cut into chunks
         m_launch = min(m, S.chunk_rows(m, args.tp_chunks)) if (tp > 1 and m > 128) else m
+        if row_chunks > 1:
+            m_launch = min(m, S.chunk_rows(m, row_chunks))
         gu_ops_launch = 2.0 * m_launch * hidden * 2 * ish
         dn_ops_launch = 2.0 * m_launch * ish * hidden
         gu_bytes_launch = 2 * ish * hidden + m * hidden + 4 * (2 * ish) + 4 * m + 3 * m * 64 * 2 \
@@ -375,13 +385,15 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                 launches_per_step = layers * args.tp_chunks * 10 - 3 * args.tp_chunks + 2 * args.tp_chunks + 2
         else:
             # per layer: two quantiser launches, two LoRA-A (or LoRA-B row) launches, two GEMMs; one routing launch
-            launches_per_step = layers * 6 + 1
+            launches_per_step = layers * 6 * row_chunks + 1
 
         prefetch_bytes = (args.prefetch_mb << 20) if (m <= 128 and tp == 1) else 0
 
         def step(x_in, ids_in, events=None):
             if tp > 1:
                 return tp_stack.forward(x_in, ids_in, timing_events=events)
+            if row_stack is not None:
+                return row_stack.forward(x_in, ids_in, timing_events=events)
             cur = x_in
             for l, (delta, gu_w, gu_l, dn_w, dn_l) in enumerate(blocks):
                 ev = events[l] if events is not None else None
@@ -688,7 +700,8 @@ def measure(args, workload, steps, rank, local_rank, world, device, dist, sub=Fa
                    **({"tp_chunks": args.tp_chunks, "tp_sequence_parallel": bool(args.tp_sequence_parallel),
                        "tp_peer_scatter": (tp_stack.scatter_mode or "all_reduce") if tp_stack is not None else "off",
                        "tp_reserve_sms": args.tp_reserve_sms} if tp > 1 else {}), "l2": "inputs_exceed_l2" if ops_per_step > 1e11 else "weights_stream_once_per_layer",
-                   **({"l2_prefetch_mb": args.prefetch_mb} if (kind == "mlp" and m <= 128 and tp == 1) else {})},
+                   **({"l2_prefetch_mb": args.prefetch_mb} if (kind == "mlp" and m <= 128 and tp == 1) else {}),
+                   **({"row_chunks": row_chunks} if (kind == "mlp" and tp == 1 and m > 128) else {})},
         "int8_tops": ops_per_step / (ms_per_step * 1e-3) / 1e12,
         "int8_tops_frac_of_peak": ops_per_step / (ms_per_step * 1e-3) / 1e12 / (i8_peak * world),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -907,6 +920,12 @@ def main():
     ap.add_argument("--tp-sequence-parallel", type=int, default=1,
                     help="1: ranks own row slices between blocks (reduce-scatter + gather of int8 codes); "
                          "0: one fp32 all-reduce per chunk")
+    ap.add_argument("--row-chunks", type=int, default=1,
+                    help="one GPU, more than 128 rows: chunks of the sorted rows that run on two streams, so that "
+                         "one chunk's quantisers and LoRA-A projections run beside the other chunk's GEMM (1 = off)")
+    ap.add_argument("--row-chunk-cta-limit", type=int, default=0,
+                    help="with --row-chunks > 1: CTAs a GEMM may use (0 = one per SM); the SMs left over run the other "
+                         "stream's LoRA-A projection, which cannot share an SM with a GEMM CTA")
     ap.add_argument("--prefetch-mb", type=int, default=0,
                     help="decode shapes (at most 128 rows, one GPU): MiB of the next GEMM's weights every GEMM asks into L2 "
                          "after its own loads (0 = off, the default: measured slower on B200, 2.62 -> 2.70 ms per c2 step at 48 MiB)")

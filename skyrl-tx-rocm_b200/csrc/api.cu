@@ -162,7 +162,7 @@ struct MlpWs {
   float* sh;
   int32_t* acc;  // int32 [m, max(2I, H)] accumulator, row-wise path only
   float* h_amax; // fp32 [m]: absmax of every row of h, collected by the gate_up epilogue
-  int32_t* sched; // tile-claim counters: words 0-1 gate_up GEMM, 2-3 down GEMM (zeroed by the routing kernel)
+  int32_t* sched; // tile-claim counters: words 0-1 gate_up GEMM, 2-3 down GEMM, 4-7 the same for odd chunks (zeroed by the routing kernel)
   size_t bytes;
 };
 
@@ -612,7 +612,9 @@ static Projection front_projection(const SkyrlW8A8MlpArgs* a, const MlpPlan& pl)
   q.out = w.h;
   q.out_stride = a->inter;
   q.status = a->status;
-  q.sched = w.sched;
+  // odd and even chunks claim tiles through counter pairs of their own, so that two chunks of one block may run
+  // on two streams at the same time
+  q.sched = w.sched + (pl.chunked ? (a->chunk_index & 1) * 4 : 0);
   q.ev_begin = a->timing_events[0];
   q.ev_end = a->timing_events[1];
   return q;
@@ -665,7 +667,7 @@ extern "C" int skyrl_w8a8_mlp_block_sm100_v1(const SkyrlW8A8MlpArgs* a, skyrl_st
   q.scaling = a->dn_scaling;
   q.xq = w.hq;
   q.sx = w.sh;
-  q.sched = w.sched + 2;
+  q.sched += 2;
   q.prefetch = nullptr;
   q.prefetch_bytes = 0;
   if (pl.rows_path && a->prefetch_next != nullptr && a->prefetch_next_bytes > 0) {

@@ -461,6 +461,47 @@ def test_chunked_block_equals_whole_block(S, m, chunks):
     assert torch.equal(out.view(torch.int16), whole.view(torch.int16))
 
 
+@pytest.mark.parametrize("m,chunks", [(2304, 2), (3100, 3)])
+def test_row_chunk_stack_on_two_streams_equals_the_plain_loop(S, m, chunks):
+    # chunks of the sorted rows run through the whole stack on two streams; every stage is row-wise, so the bits
+    # are those of the block-by-block loop
+    from skyrl_tx_rocm_b200.stack import MLPStack
+
+    rng = np.random.default_rng(83)
+    hidden, inter, rank, na, layers = 256, 384, 16, 5, 3
+    blocks = []
+    x = ids = None
+    for l in range(layers):
+        x_l, wgu, ga, gb, s, ids_l = make_case(89 + 7 * l + m, m, hidden, 2 * inter, rank, na, w_std=0.05)
+        _, wd, da, db, _, _ = make_case(97 + 7 * l + m, m, inter, hidden, rank, na, w_std=0.05)
+        if l == 0:
+            x, ids = x_l, ids_l
+        delta = (rng.standard_normal(hidden) * 0.02).astype(np.float32).astype(BF16)
+        _, pgu = device_weight(S, wgu)
+        _, pd = device_weight(S, wd)
+        lgu = S.pack_lora(to_dev(ga), to_dev(gb), to_dev(s), in_features=hidden, padded_out_features=2 * inter)
+        ld = S.pack_lora(to_dev(da), to_dev(db), to_dev(s), in_features=inter, padded_out_features=hidden)
+        blocks.append((to_dev(delta), pgu, lgu, pd, ld))
+    xd, idd = to_dev(x), to_dev(ids)
+    plain = MLPStack(blocks, num_chunks=1)
+    want = plain.forward(xd, idd).clone()
+    cur = xd
+    for blk in blocks:      # the loop a caller without the stack writes
+        cur = S.w8a8_mlp_block(cur, *blk, idd, enabled=True)
+    assert torch.equal(cur.view(torch.int16), want.view(torch.int16))
+    stack = MLPStack(blocks, num_chunks=chunks)
+    assert stack.chunks_for(m) == chunks
+    for _ in range(3):      # repeated passes reuse the routing buffers and the scheduler counters
+        got = stack.forward(xd, idd)
+        torch.cuda.synchronize()
+        S.check_status()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    out = torch.empty_like(xd)
+    stack.forward(xd, idd, out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+
+
 @pytest.mark.parametrize("tp", [2, 4])
 def test_tensor_parallel_block_emulated_on_one_gpu(S, tp):
     # every rank's shard runs in turn on this GPU; the all-reduce is a sum of the fp32 partial buffers

@@ -249,3 +249,18 @@ def test_lora_parameter_grads_match_the_oracle_vjp_on_cpu():
     np.testing.assert_allclose(d_b.numpy(), want_db, rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(d_s.numpy(), want_ds, rtol=1e-5, atol=1e-5)
     assert not d_a[1].any() and not d_b[1].any() and d_s[1] == 0
+
+
+def test_row_chunk_stack_chooses_its_chunks_on_the_host():
+    from skyrl_tx_rocm_b200.stack import MLPStack
+
+    blk = (None, None, None, None, None)
+    stack = MLPStack([blk], num_chunks=2)
+    assert stack.chunks_for(16384) == 2          # 8192 rows per chunk
+    assert stack.chunks_for(2048) == 2           # exactly the 1024-row floor
+    assert stack.chunks_for(1500) == 1           # a 768-row chunk hides nothing: the plain loop
+    assert MLPStack([blk], num_chunks=4).chunks_for(3000) == 3   # 768 rows per chunk with four, 1024 (tile-rounded) with three
+    with pytest.raises(ValueError):
+        MLPStack([], num_chunks=2)
+    with pytest.raises(ValueError):
+        MLPStack([blk], num_chunks=0)
